@@ -1,0 +1,726 @@
+// C ABI of libhalo_b200.so (include/halo_b200.h): argument validation, choice
+// between the vector and scalar kernels, and launch by reference kernel name.
+// No function here allocates, synchronizes or keeps state (one tuning knob aside).
+#include <atomic>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/halo_b200.h"
+#include "kernels.h"
+
+using namespace halo_b200;
+
+namespace {
+
+std::atomic<int> g_norm_threads_per_row{0};
+
+int Fail(char* err, size_t errlen, const char* fmt, ...) {
+  if (err && errlen) {
+    va_list ap;
+    va_start(ap, fmt);
+    std::vsnprintf(err, errlen, fmt, ap);
+    va_end(ap);
+  }
+  return -1;
+}
+
+int Done(cudaError_t e, const char* what, char* err, size_t errlen) {
+  if (e == cudaSuccess) {
+    if (err && errlen) err[0] = '\0';
+    return 0;
+  }
+  return Fail(err, errlen, "%s: %s", what, cudaGetErrorString(e));
+}
+
+bool Aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+bool ValidDType(int t) { return t == kF32 || t == kF16 || t == kBF16; }
+cudaStream_t S(halo_b200_stream s) { return static_cast<cudaStream_t>(s); }
+
+#define REQUIRE(cond, ...) \
+  do {                     \
+    if (!(cond)) return Fail(err, errlen, __VA_ARGS__); \
+  } while (0)
+
+// pow(theta, -2 i / rot) in fp32 with the host libm: the expression of
+// src/model/cpu_ops.cpp:174-175, so device angles equal the CPU operator's bit for bit.
+bool FillInvFreq(InvFreq* f, uint32_t rot, float theta) {
+  if (rot / 2 > static_cast<uint32_t>(kMaxRotHalf)) return false;
+  for (uint32_t i = 0; i < rot / 2; ++i)
+    f->f[i] = std::pow(theta, -2.0F * static_cast<float>(i) / static_cast<float>(rot));
+  return true;
+}
+
+int RunNorm(NormArgs a, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+  REQUIRE(a.x != nullptr, "%s: x is null", what);
+  REQUIRE(a.d > 0, "%s: d is 0", what);
+  REQUIRE(ValidDType(a.x_dtype) && ValidDType(a.y_dtype), "%s: unknown dtype", what);
+  REQUIRE(a.y || a.y16 || a.q8_0 || a.xq || a.res || a.rscale, "%s: no output", what);
+  REQUIRE((a.delta == nullptr) == (a.res == nullptr), "%s: delta and res go together", what);
+  REQUIRE((a.xq == nullptr) == (a.xd == nullptr), "%s: xq and xd go together", what);
+  if (a.q8_0 || a.xq) REQUIRE(a.d % 32 == 0, "%s: Q8 output needs d %% 32 == 0 (d = %u)", what, a.d);
+  if (a.q8_0) REQUIRE(Aligned(a.q8_0, 2), "%s: Q8_0 output must be 2-byte aligned", what);
+  if (a.kb_tokens || a.y16_tokens) REQUIRE(a.d % 64 == 0, "%s: K-blocked layouts need d %% 64 == 0", what);
+  if (a.w_period == 0) a.w_period = 1;
+  if (a.kb_period == 0) a.kb_period = 1;
+  const size_t xs = DTypeSize(a.x_dtype), ys = DTypeSize(a.y_dtype);
+  REQUIRE(Aligned(a.x, xs) && Aligned(a.y, ys) && Aligned(a.delta, xs) && Aligned(a.res, xs) && Aligned(a.w, 4) &&
+              Aligned(a.y16, 2) && Aligned(a.xd, 4) && Aligned(a.rscale, 4),
+          "%s: pointer not aligned to its element type", what);
+  a.threads_per_row = g_norm_threads_per_row.load(std::memory_order_relaxed);
+  bool vec = a.d % 8 == 0 && a.d <= 256u * 8u * 8u && Aligned(a.x, 16) && Aligned(a.y, 16) && Aligned(a.delta, 16) &&
+             Aligned(a.res, 16) && Aligned(a.y16, 16) && Aligned(a.w, 16) && a.w_stride % 4 == 0 &&
+             Aligned(a.xq, 8) && a.entry_stride % 8 == 0;
+  if (vec && a.threads_per_row) {
+    const unsigned g = static_cast<unsigned>(a.threads_per_row);
+    const unsigned octs = a.d / 8, k = (octs + g - 1) / g;
+    if (k > 8 || ((a.q8_0 || a.xq) && g < 4)) a.threads_per_row = 0;
+  }
+  a.vec = vec;
+  return Done(LaunchNorm(a, S(stream)), what, err, errlen);
+}
+
+int RunGated(GatedArgs a, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+  REQUIRE(a.o && a.z && a.w && a.y, "%s: null pointer", what);
+  REQUIRE(a.d > 0, "%s: d is 0", what);
+  REQUIRE(ValidDType(a.o_dtype) && ValidDType(a.z_dtype) && ValidDType(a.y_dtype), "%s: unknown dtype", what);
+  REQUIRE(a.mode <= 1, "%s: mode must be 0 (SiLU) or 1 (sigmoid)", what);
+  REQUIRE(Aligned(a.o, DTypeSize(a.o_dtype)) && Aligned(a.z, DTypeSize(a.z_dtype)) &&
+              Aligned(a.y, DTypeSize(a.y_dtype)) && Aligned(a.w, 4),
+          "%s: pointer not aligned to its element type", what);
+  a.vec = a.d % 8 == 0 && a.d <= 256u * 8u * 4u && Aligned(a.o, 16) && Aligned(a.z, 16) && Aligned(a.y, 16) &&
+          Aligned(a.w, 16);
+  const cudaError_t e = LaunchGatedNorm(a, S(stream));
+  if (e == cudaErrorInvalidValue) return Fail(err, errlen, "%s: unsupported (o, z, y) dtype combination", what);
+  return Done(e, what, err, errlen);
+}
+
+int RunRope(RopeArgs a, float theta, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+  REQUIRE(a.x != nullptr, "%s: x is null", what);
+  REQUIRE(ValidDType(a.dtype), "%s: unknown dtype", what);
+  REQUIRE(a.rot % 2 == 0 && a.rot <= a.hd, "%s: rotary_dim %u must be even and <= head_dim %u", what, a.rot, a.hd);
+  REQUIRE(a.heads2 == 0 || a.x2 != nullptr, "%s: k is null", what);
+  InvFreq f;
+  REQUIRE(FillInvFreq(&f, a.rot, theta), "%s: rotary_dim %u exceeds %d", what, a.rot, 2 * kMaxRotHalf);
+  const size_t es = DTypeSize(a.dtype);
+  REQUIRE(Aligned(a.x, es) && Aligned(a.x2, es) && Aligned(a.pos.params, 4) && Aligned(a.pos_out, 4),
+          "%s: pointer not aligned to its element type", what);
+  a.vec = (a.rot / 2) % 8 == 0 && a.hd % 8 == 0 && a.token_stride % 8 == 0 && a.token_stride2 % 8 == 0 &&
+          Aligned(a.x, 16) && Aligned(a.x2, 16);
+  return Done(LaunchRope(a, f, S(stream)), what, err, errlen);
+}
+
+int RunElt(EltArgs a, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+  REQUIRE(a.a && a.b && a.y, "%s: null pointer", what);
+  REQUIRE(ValidDType(a.in_dtype) && ValidDType(a.y_dtype), "%s: unknown dtype", what);
+  REQUIRE(Aligned(a.a, DTypeSize(a.in_dtype)) && Aligned(a.b, DTypeSize(a.in_dtype)) &&
+              Aligned(a.y, DTypeSize(a.y_dtype)),
+          "%s: pointer not aligned to its element type", what);
+  a.vec = Aligned(a.a, 16) && Aligned(a.b, 16) && Aligned(a.y, 16);
+  const cudaError_t e = LaunchElementwise(a, S(stream));
+  if (e == cudaErrorInvalidValue) return Fail(err, errlen, "%s: unsupported (in, out) dtype combination", what);
+  return Done(e, what, err, errlen);
+}
+
+int RunEmbed(EmbedArgs a, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+  REQUIRE(a.table && a.out, "%s: null pointer", what);
+  REQUIRE(ValidDType(a.out_dtype), "%s: unknown dtype", what);
+  REQUIRE(a.cols % 32 == 0, "%s: Q8_0 rows need cols %% 32 == 0 (cols = %u)", what, a.cols);
+  REQUIRE(a.row_bytes >= static_cast<uint64_t>(a.cols / 32) * 34, "%s: row_bytes %llu smaller than %u Q8_0 blocks",
+          what, static_cast<unsigned long long>(a.row_bytes), a.cols / 32);
+  REQUIRE(Aligned(a.out, DTypeSize(a.out_dtype)) && Aligned(a.ids, 4), "%s: pointer not aligned to its element type",
+          what);
+  a.vec = a.row_bytes % 16 == 0 && Aligned(a.table, 16) && Aligned(a.out, 16);
+  return Done(LaunchEmbedQ8_0(a, S(stream)), what, err, errlen);
+}
+
+int RunQuant(QuantArgs a, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+  REQUIRE(a.x != nullptr, "%s: x is null", what);
+  REQUIRE(ValidDType(a.x_dtype), "%s: unknown dtype", what);
+  REQUIRE(a.q8_0 || a.xq, "%s: no output", what);
+  REQUIRE((a.xq == nullptr) == (a.xd == nullptr) && (a.xq2 == nullptr) == (a.xd2 == nullptr),
+          "%s: codes and scales go together", what);
+  REQUIRE(a.xq2 == nullptr || (a.xq != nullptr && a.kb_tokens == 0), "%s: second level needs row-major xq", what);
+  REQUIRE(a.cols % 32 == 0, "%s: cols %% 32 != 0 (cols = %u)", what, a.cols);
+  if (a.kb_tokens) REQUIRE(a.cols % 64 == 0, "%s: K-blocked layout needs cols %% 64 == 0", what);
+  REQUIRE(Aligned(a.x, DTypeSize(a.x_dtype)) && Aligned(a.xd, 4) && Aligned(a.xd2, 4) && Aligned(a.q8_0, 2),
+          "%s: pointer not aligned to its element type", what);
+  a.vec = Aligned(a.x, 16) && a.x_stride % 8 == 0 && Aligned(a.xq, 8) && Aligned(a.xq2, 8);
+  return Done(LaunchQuantize(a, S(stream)), what, err, errlen);
+}
+
+int RunNormRope(NormRopeArgs a, float theta, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+  REQUIRE(a.in && a.out, "%s: null pointer", what);
+  REQUIRE(ValidDType(a.in_dtype) && ValidDType(a.out_dtype), "%s: unknown dtype", what);
+  REQUIRE(a.d > 0 && a.d <= 256, "%s: d = %u outside 1..256", what, a.d);
+  REQUIRE(a.heads > 0, "%s: heads is 0", what);
+  REQUIRE(a.rot % 2 == 0 && a.rot <= a.d, "%s: rotary_dim %u must be even and <= d %u", what, a.rot, a.d);
+  REQUIRE(a.in_row_stride >= a.d, "%s: in_row_stride < d", what);
+  REQUIRE(a.gate == nullptr || a.in_row_stride >= 2ull * a.d, "%s: gate needs q|gate rows (in_row_stride >= 2 d)", what);
+  InvFreq f;
+  REQUIRE(FillInvFreq(&f, a.rot, theta), "%s: rotary_dim too large", what);
+  const bool vec = a.d % 8 == 0 && (a.rot / 2) % 8 == 0 && a.in_row_stride % 8 == 0 && Aligned(a.in, 16) &&
+                   Aligned(a.out, 16) && Aligned(a.gate, 16) && Aligned(a.cache, 16) && Aligned(a.w, 16);
+  if (vec) {
+    const cudaError_t e = LaunchNormRope(a, f, S(stream));
+    if (e == cudaErrorInvalidValue) return Fail(err, errlen, "%s: unsupported (in, out) dtype combination", what);
+    return Done(e, what, err, errlen);
+  }
+  // Odd shapes: the separate kernels in sequence (the reference's own unfused path,
+  // src/engine/qwen35_gpu.cpp:204-222): split, per-head norm, rope, cache copy.
+  REQUIRE(a.in_dtype == a.out_dtype, "%s: unaligned shapes need in_dtype == out_dtype", what);
+  REQUIRE(a.cache == nullptr, "%s: cache append needs 16-byte aligned rows with d %% 8 == 0 and rot %% 16 == 0", what);
+  const void* norm_in = a.in;
+  if (a.in_row_stride != a.d) {
+    REQUIRE(a.in_row_stride == 2ull * a.d && a.gate != nullptr, "%s: strided rows need the q|gate form with gate set",
+            what);
+    SplitArgs sp;
+    sp.qg = a.in;
+    sp.q = a.out;
+    sp.gate = a.gate;
+    sp.dtype = a.in_dtype;
+    sp.hd = a.d;
+    sp.rows = a.rows;
+    const cudaError_t e = LaunchSplitQgate(sp, S(stream));
+    if (e != cudaSuccess) return Done(e, what, err, errlen);
+    norm_in = a.out;
+  }
+  if (a.w) {
+    NormArgs n;
+    n.x = norm_in;
+    n.x_dtype = a.in_dtype;
+    n.y = a.out;
+    n.y_dtype = a.out_dtype;
+    n.w = a.w;
+    n.one_plus = a.one_plus;
+    n.d = a.d;
+    n.rows = a.rows;
+    n.eps = a.eps;
+    n.vec = false;
+    const cudaError_t e = LaunchNorm(n, S(stream));
+    if (e != cudaSuccess) return Done(e, what, err, errlen);
+  } else if (norm_in != a.out) {
+    return Fail(err, errlen, "%s: out must alias in when there is neither a norm nor a split", what);
+  }
+  RopeArgs r;
+  r.x = a.out;
+  r.dtype = a.out_dtype;
+  r.tokens = a.rows / a.heads;
+  r.heads = a.heads;
+  r.hd = a.d;
+  r.rot = a.rot;
+  r.token_stride = static_cast<uint64_t>(a.heads) * a.d;
+  r.pos = a.pos;
+  r.pos_out = a.pos_out;
+  r.vec = false;
+  REQUIRE(a.rows % a.heads == 0, "%s: rows %u not a multiple of heads %u", what, a.rows, a.heads);
+  return Done(LaunchRope(r, f, S(stream)), what, err, errlen);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* halo_b200_version(void) { return "halo_b200 0.1 sm_100a"; }
+
+int halo_b200_tune_norm_threads_per_row(int threads) {
+  if (threads < 0 || threads > 256 || (threads & (threads - 1)) != 0) return -1;
+  g_norm_threads_per_row.store(threads, std::memory_order_relaxed);
+  return 0;
+}
+
+// ---- group 1 -------------------------------------------------------------------------
+int halo_b200_add(halo_b200_stream stream, float* y, const float* x, uint32_t n, char* err, size_t errlen) {
+  EltArgs a;
+  a.op = kOpAdd;
+  a.a = y;
+  a.b = x;
+  a.y = y;
+  a.n = n;
+  return RunElt(a, "halo_add", stream, err, errlen);
+}
+
+int halo_b200_axpy(halo_b200_stream stream, float* y, const float* x, float alpha, uint32_t n, char* err,
+                   size_t errlen) {
+  EltArgs a;
+  a.op = kOpAxpy;
+  a.a = y;
+  a.b = x;
+  a.y = y;
+  a.alpha = alpha;
+  a.n = n;
+  return RunElt(a, "halo_axpy", stream, err, errlen);
+}
+
+int halo_b200_rmsnorm_ex(halo_b200_stream stream, const void* x, int x_dtype, const float* w, void* y, int y_dtype,
+                         uint32_t d, float eps, uint32_t w_stride, uint32_t w_period, int one_plus, uint32_t rows,
+                         char* err, size_t errlen) {
+  NormArgs a;
+  a.x = x;
+  a.x_dtype = x_dtype;
+  a.w = w;
+  a.w_stride = w_stride;
+  a.w_period = w_period;
+  a.one_plus = one_plus;
+  a.y = y;
+  a.y_dtype = y_dtype;
+  a.d = d;
+  a.eps = eps;
+  a.rows = rows;
+  REQUIRE(y != nullptr, "halo_rmsnorm: y is null");
+  return RunNorm(a, "halo_rmsnorm", stream, err, errlen);
+}
+
+int halo_b200_rmsnorm(halo_b200_stream stream, const float* x, const float* w_all, float* y, uint32_t d, float eps,
+                      uint32_t w_stride, uint32_t nvec, char* err, size_t errlen) {
+  REQUIRE(w_all != nullptr, "halo_rmsnorm: w_all is null");
+  // vector b uses gamma b * w_stride: a period of nvec rows
+  return halo_b200_rmsnorm_ex(stream, x, kF32, w_all, y, kF32, d, eps, w_stride, w_stride ? nvec : 1, 0, nvec, err,
+                              errlen);
+}
+
+int halo_b200_rmsnorm_rows(halo_b200_stream stream, const float* x, const float* w_all, float* y, uint32_t d,
+                           float eps, uint32_t w_stride, uint32_t w_period, uint32_t rows, char* err, size_t errlen) {
+  REQUIRE(w_all != nullptr, "halo_rmsnorm_rows: w_all is null");
+  REQUIRE(w_period > 0, "halo_rmsnorm_rows: w_period is 0");
+  return halo_b200_rmsnorm_ex(stream, x, kF32, w_all, y, kF32, d, eps, w_stride, w_period, 0, rows, err, errlen);
+}
+int halo_b200_rmsnorm_rows_r16(halo_b200_stream stream, const uint16_t* x, const float* w_all, float* y, uint32_t d,
+                               float eps, uint32_t w_stride, uint32_t w_period, uint32_t rows, char* err,
+                               size_t errlen) {
+  REQUIRE(w_all != nullptr, "halo_rmsnorm_rows_r16: w_all is null");
+  REQUIRE(w_period > 0, "halo_rmsnorm_rows_r16: w_period is 0");
+  return halo_b200_rmsnorm_ex(stream, x, kF16, w_all, y, kF32, d, eps, w_stride, w_period, 0, rows, err, errlen);
+}
+int halo_b200_rmsnorm_rows_rb(halo_b200_stream stream, const uint16_t* x, const float* w_all, float* y, uint32_t d,
+                              float eps, uint32_t w_stride, uint32_t w_period, uint32_t rows, char* err,
+                              size_t errlen) {
+  REQUIRE(w_all != nullptr, "halo_rmsnorm_rows_rb: w_all is null");
+  REQUIRE(w_period > 0, "halo_rmsnorm_rows_rb: w_period is 0");
+  return halo_b200_rmsnorm_ex(stream, x, kBF16, w_all, y, kF32, d, eps, w_stride, w_period, 0, rows, err, errlen);
+}
+
+int halo_b200_rmsnorm_rows_h(halo_b200_stream stream, const void* x, int x_dtype, const float* w_all, float* y,
+                             uint16_t* y16, uint32_t d, float eps, uint32_t w_stride, uint32_t w_period,
+                             const float* iw, float* ipart, uint32_t irows, uint32_t y16_tokens, uint32_t rows,
+                             char* err, size_t errlen) {
+  (void)ipart;
+  (void)irows;
+  REQUIRE(iw == nullptr, "halo_rmsnorm_rows_h: inject partial products (iw) are not implemented");
+  REQUIRE(w_all && y && y16, "halo_rmsnorm_rows_h: null pointer");
+  REQUIRE(w_period > 0, "halo_rmsnorm_rows_h: w_period is 0");
+  NormArgs a;
+  a.x = x;
+  a.x_dtype = x_dtype;
+  a.w = w_all;
+  a.w_stride = w_stride;
+  a.w_period = w_period;
+  a.y = y;
+  a.y_dtype = kF32;
+  a.y16 = y16;
+  a.y16_tokens = y16_tokens;
+  a.kb_period = w_period;
+  a.d = d;
+  a.eps = eps;
+  a.rows = rows;
+  return RunNorm(a, "halo_rmsnorm_rows_h", stream, err, errlen);
+}
+
+int halo_b200_rmsnorm_y(halo_b200_stream stream, float* x, const float* w_all, uint32_t d, float eps,
+                        uint32_t w_stride, uint32_t stride, uint32_t nvec, uint32_t batch, char* err, size_t errlen) {
+  REQUIRE(w_all != nullptr, "halo_rmsnorm_y: w_all is null");
+  NormArgs a;
+  a.x = x;
+  a.y = x;
+  a.w = w_all;
+  a.w_stride = w_stride;
+  a.w_period = w_stride ? nvec : 1;  // vector v of every entry uses gamma v * w_stride
+  a.d = d;
+  a.eps = eps;
+  a.rows = nvec * batch;
+  a.rows_per_entry = nvec;
+  a.entry_stride = stride;
+  return RunNorm(a, "halo_rmsnorm_y", stream, err, errlen);
+}
+
+int halo_b200_add_rmsnorm(halo_b200_stream stream, void* res, const void* delta, int res_dtype, const float* w,
+                          int one_plus, void* xn, int xn_dtype, uint8_t* xn_q8_0, int8_t* xq, float* xd, uint32_t d,
+                          float eps, uint32_t rows, char* err, size_t errlen) {
+  REQUIRE(res != nullptr, "halo_add_rmsnorm: res is null");
+  REQUIRE(xn || xn_q8_0 || xq, "halo_add_rmsnorm: no normalized output requested");
+  NormArgs a;
+  a.x = res;
+  a.x_dtype = res_dtype;
+  a.delta = delta;
+  a.res = delta ? res : nullptr;
+  a.w = w;
+  a.one_plus = one_plus;
+  a.y = xn;
+  a.y_dtype = xn_dtype;
+  a.q8_0 = xn_q8_0;
+  a.xq = xq;
+  a.xd = xd;
+  a.d = d;
+  a.eps = eps;
+  a.rows = rows;
+  return RunNorm(a, "halo_add_rmsnorm", stream, err, errlen);
+}
+
+int halo_b200_quantize_q8_rows(halo_b200_stream stream, const float* x, int8_t* xq, float* xd, uint32_t cols,
+                               uint32_t rows, char* err, size_t errlen) {
+  QuantArgs a;
+  a.x = x;
+  a.x_stride = cols;
+  a.cols = cols;
+  a.rows = rows;
+  a.xq = xq;
+  a.xd = xd;
+  REQUIRE(xq && xd, "halo_quantize_q8_rows: null output");
+  return RunQuant(a, "halo_quantize_q8_rows", stream, err, errlen);
+}
+
+int halo_b200_quantize_q8_kblocked(halo_b200_stream stream, const float* x, int8_t* xq, float* xd, uint32_t cols,
+                                   uint32_t tokens, char* err, size_t errlen) {
+  QuantArgs a;
+  a.x = x;
+  a.x_stride = cols;
+  a.cols = cols;
+  a.rows = tokens;
+  a.xq = xq;
+  a.xd = xd;
+  a.kb_tokens = tokens;
+  REQUIRE(xq && xd, "halo_quantize_q8_kblocked: null output");
+  if (tokens == 0) return Done(cudaSuccess, "", err, errlen);
+  return RunQuant(a, "halo_quantize_q8_kblocked", stream, err, errlen);
+}
+
+int halo_b200_q8x_cols(halo_b200_stream stream, const float* x, uint32_t xstride, uint32_t cols, int8_t* xq,
+                       float* xs, int8_t* xq2, float* xs2, uint32_t batch, char* err, size_t errlen) {
+  QuantArgs a;
+  a.x = x;
+  a.x_stride = xstride;
+  a.cols = cols;
+  a.rows = batch;
+  a.xq = xq;
+  a.xd = xs;
+  a.xq2 = xq2;
+  a.xd2 = xs2;
+  REQUIRE(xq && xs, "halo_q8x_cols: null output");
+  return RunQuant(a, "halo_q8x_cols", stream, err, errlen);
+}
+
+int halo_b200_encode_q8_0_rows(halo_b200_stream stream, const void* x, int x_dtype, uint8_t* out, uint32_t cols,
+                               uint32_t rows, char* err, size_t errlen) {
+  QuantArgs a;
+  a.x = x;
+  a.x_dtype = x_dtype;
+  a.x_stride = cols;
+  a.cols = cols;
+  a.rows = rows;
+  a.q8_0 = out;
+  REQUIRE(out != nullptr, "halo_encode_q8_0_rows: out is null");
+  return RunQuant(a, "halo_encode_q8_0_rows", stream, err, errlen);
+}
+
+// ---- group 2 -------------------------------------------------------------------------
+int halo_b200_l2norm_ex(halo_b200_stream stream, const void* x, int x_dtype, void* y, int y_dtype, uint32_t d,
+                        float eps, uint32_t rows, char* err, size_t errlen) {
+  NormArgs a;
+  a.x = x;
+  a.x_dtype = x_dtype;
+  a.y = y;
+  a.y_dtype = y_dtype;
+  a.d = d;
+  a.eps = eps;
+  a.rows = rows;
+  a.l2 = 1;
+  REQUIRE(y != nullptr, "halo_l2norm: y is null");
+  return RunNorm(a, "halo_l2norm", stream, err, errlen);
+}
+
+int halo_b200_l2norm(halo_b200_stream stream, float* x, uint32_t d, float eps, uint32_t nvec, char* err,
+                     size_t errlen) {
+  return halo_b200_l2norm_ex(stream, x, kF32, x, kF32, d, eps, nvec, err, errlen);
+}
+
+int halo_b200_gated_norm_ex(halo_b200_stream stream, const void* o, int o_dtype, const float* w, const void* z,
+                            int z_dtype, void* y, int y_dtype, uint32_t d, float eps, uint32_t mode, uint32_t rows,
+                            char* err, size_t errlen) {
+  GatedArgs a;
+  a.o = o;
+  a.o_dtype = o_dtype;
+  a.w = w;
+  a.z = z;
+  a.z_dtype = z_dtype;
+  a.y = y;
+  a.y_dtype = y_dtype;
+  a.d = d;
+  a.eps = eps;
+  a.mode = mode;
+  a.rows = rows;
+  return RunGated(a, "halo_gated_norm", stream, err, errlen);
+}
+
+int halo_b200_gated_norm(halo_b200_stream stream, float* o, const float* w, const float* z, uint32_t d, float eps,
+                         uint32_t mode, uint32_t rows, char* err, size_t errlen) {
+  return halo_b200_gated_norm_ex(stream, o, kF32, w, z, kF32, o, kF32, d, eps, mode, rows, err, errlen);
+}
+int halo_b200_gated_norm_h(halo_b200_stream stream, const float* o, const float* w, const float* z, uint16_t* y16,
+                           uint32_t d, float eps, uint32_t mode, uint32_t rows, char* err, size_t errlen) {
+  return halo_b200_gated_norm_ex(stream, o, kF32, w, z, kF32, y16, kF16, d, eps, mode, rows, err, errlen);
+}
+int halo_b200_gated_norm_hz(halo_b200_stream stream, const float* o, const float* w, const uint16_t* z,
+                            uint16_t* y16, uint32_t d, float eps, uint32_t mode, uint32_t rows, char* err,
+                            size_t errlen) {
+  return halo_b200_gated_norm_ex(stream, o, kF32, w, z, kF16, y16, kF16, d, eps, mode, rows, err, errlen);
+}
+int halo_b200_gated_norm_h128w(halo_b200_stream stream, const float* o, const float* w, const float* z,
+                               uint16_t* y16, uint32_t rows, float eps, uint32_t mode, char* err, size_t errlen) {
+  return halo_b200_gated_norm_ex(stream, o, kF32, w, z, kF32, y16, kF16, 128, eps, mode, rows, err, errlen);
+}
+int halo_b200_gated_norm_h128w_hh(halo_b200_stream stream, const uint16_t* o, const float* w, const uint16_t* z,
+                                  uint16_t* y16, uint32_t rows, float eps, uint32_t mode, char* err, size_t errlen) {
+  return halo_b200_gated_norm_ex(stream, o, kF16, w, z, kF16, y16, kF16, 128, eps, mode, rows, err, errlen);
+}
+
+// ---- group 3 -------------------------------------------------------------------------
+int halo_b200_rope_ex(halo_b200_stream stream, void* q, uint32_t q_heads, void* k, uint32_t k_heads, int dtype,
+                      uint32_t head_dim, uint32_t rotary_dim, float theta, uint32_t tokens, const uint32_t* params,
+                      uint32_t pstride, uint32_t slot, uint32_t pos0, uint32_t scale, uint32_t* pos_out, char* err,
+                      size_t errlen) {
+  RopeArgs a;
+  a.x = q;
+  a.dtype = dtype;
+  a.tokens = tokens;
+  a.heads = q_heads;
+  a.hd = head_dim;
+  a.rot = rotary_dim;
+  a.token_stride = static_cast<uint64_t>(q_heads) * head_dim;
+  a.x2 = k_heads ? k : nullptr;
+  a.heads2 = k ? k_heads : 0;
+  a.token_stride2 = static_cast<uint64_t>(k_heads) * head_dim;
+  a.pos.params = params;
+  a.pos.pstride = pstride;
+  a.pos.slot = slot;
+  a.pos.pos0 = pos0;
+  a.pos.scale = scale;
+  a.pos_out = pos_out;
+  return RunRope(a, theta, "halo_rope_neox", stream, err, errlen);
+}
+
+int halo_b200_rope_neox(halo_b200_stream stream, float* x, uint32_t head_dim, uint32_t rotary_dim, uint32_t pos,
+                        float theta, uint32_t heads, char* err, size_t errlen) {
+  return halo_b200_rope_ex(stream, x, heads, nullptr, 0, kF32, head_dim, rotary_dim, theta, 1, nullptr, 0, 0, pos, 1,
+                           nullptr, err, errlen);
+}
+
+int halo_b200_rope_neox_rows(halo_b200_stream stream, float* x, uint32_t head_dim, uint32_t rotary_dim,
+                             uint32_t pos0, uint32_t heads, float theta, uint32_t rows, char* err, size_t errlen) {
+  REQUIRE(heads > 0, "halo_rope_neox_rows: heads is 0");
+  // Row r is head r % heads of token r / heads. A trailing partial token (rows not a multiple
+  // of heads) is rotated too, as the reference's per-row grid would.
+  const uint32_t full = rows / heads, rest = rows % heads;
+  int rc = halo_b200_rope_ex(stream, x, heads, nullptr, 0, kF32, head_dim, rotary_dim, theta, full, nullptr, 0, 0,
+                             pos0, 1, nullptr, err, errlen);
+  if (rc == 0 && rest)
+    rc = halo_b200_rope_ex(stream, x + static_cast<size_t>(full) * heads * head_dim, rest, nullptr, 0, kF32, head_dim,
+                           rotary_dim, theta, 1, nullptr, 0, 0, pos0 + full, 1, nullptr, err, errlen);
+  return rc;
+}
+
+int halo_b200_rope_neox_p(halo_b200_stream stream, float* x, const uint32_t* params, uint32_t head_dim,
+                          uint32_t rotary_dim, uint32_t slot, uint32_t scale, float theta, uint32_t heads, char* err,
+                          size_t errlen) {
+  REQUIRE(params != nullptr, "halo_rope_neox_p: params is null");
+  return halo_b200_rope_ex(stream, x, heads, nullptr, 0, kF32, head_dim, rotary_dim, theta, 1, params, 0, slot, 0,
+                           scale, nullptr, err, errlen);
+}
+
+int halo_b200_rope_neox_blocks(halo_b200_stream stream, float* x, uint32_t head_dim, uint32_t rotary_dim,
+                               uint32_t b0, uint32_t ratio, float theta, uint32_t nblocks, char* err, size_t errlen) {
+  // one head-sized row per pooled block, block b at (b0 + b) * ratio
+  return halo_b200_rope_ex(stream, x, 1, nullptr, 0, kF32, head_dim, rotary_dim, theta, nblocks, nullptr, 0, 0, b0,
+                           ratio, nullptr, err, errlen);
+}
+
+int halo_b200_rope_neox_p_y(halo_b200_stream stream, float* x, const uint32_t* params, uint32_t head_dim,
+                            uint32_t rotary_dim, uint32_t slot, uint32_t scale, float theta, uint32_t stride,
+                            uint32_t pstride, uint32_t heads, uint32_t batch, char* err, size_t errlen) {
+  REQUIRE(params != nullptr, "halo_rope_neox_p_y: params is null");
+  RopeArgs a;
+  a.x = x;
+  a.tokens = batch;  // one "token" per session entry
+  a.heads = heads;
+  a.hd = head_dim;
+  a.rot = rotary_dim;
+  a.token_stride = stride;
+  a.pos.params = params;
+  a.pos.pstride = pstride;
+  a.pos.slot = slot;
+  a.pos.scale = scale;
+  return RunRope(a, theta, "halo_rope_neox_p_y", stream, err, errlen);
+}
+
+int halo_b200_split_qgate(halo_b200_stream stream, const float* qg, float* q, float* gate, uint32_t hd,
+                          uint32_t rows, char* err, size_t errlen) {
+  REQUIRE(qg && q && gate, "halo_split_qgate: null pointer");
+  SplitArgs a;
+  a.qg = qg;
+  a.q = q;
+  a.gate = gate;
+  a.hd = hd;
+  a.rows = rows;
+  return Done(LaunchSplitQgate(a, S(stream)), "halo_split_qgate", err, errlen);
+}
+
+int halo_b200_split_qgate_y(halo_b200_stream stream, const float* qg, float* q, float* gate, uint32_t hd,
+                            uint32_t qg_stride, uint32_t q_stride, uint32_t heads, uint32_t batch, char* err,
+                            size_t errlen) {
+  REQUIRE(qg && q && gate, "halo_split_qgate_y: null pointer");
+  SplitArgs a;
+  a.qg = qg;
+  a.q = q;
+  a.gate = gate;
+  a.hd = hd;
+  a.rows = heads * batch;
+  a.rows_per_entry = heads;
+  a.qg_entry_stride = qg_stride;
+  a.q_entry_stride = q_stride;
+  return Done(LaunchSplitQgate(a, S(stream)), "halo_split_qgate_y", err, errlen);
+}
+
+int halo_b200_norm_rope_ex(halo_b200_stream stream, const void* in, int in_dtype, uint64_t in_row_stride, void* out,
+                           int out_dtype, void* gate, void* cache, const float* w, int one_plus, float eps,
+                           uint32_t d, uint32_t rotary_dim, uint32_t heads, uint32_t rows, float theta,
+                           const uint32_t* params, uint32_t pstride, uint32_t slot, uint32_t pos0, uint32_t scale,
+                           uint32_t* pos_out, char* err, size_t errlen) {
+  NormRopeArgs a;
+  a.in = in;
+  a.in_dtype = in_dtype;
+  a.in_row_stride = in_row_stride;
+  a.out = out;
+  a.out_dtype = out_dtype;
+  a.gate = gate;
+  a.cache = cache;
+  a.w = w;
+  a.one_plus = one_plus;
+  a.eps = eps;
+  a.d = d;
+  a.rot = rotary_dim;
+  a.heads = heads;
+  a.rows = rows;
+  a.pos.params = params;
+  a.pos.pstride = pstride;
+  a.pos.slot = slot;
+  a.pos.pos0 = pos0;
+  a.pos.scale = scale;
+  a.pos_out = pos_out;
+  return RunNormRope(a, theta, "halo_norm_rope", stream, err, errlen);
+}
+
+int halo_b200_split_qgate_norm_rope(halo_b200_stream stream, const float* qg, float* q, float* gate, const float* w,
+                                    float eps, uint32_t rotary_dim, uint32_t pos0, uint32_t heads, float theta,
+                                    uint32_t hd, uint32_t rows, char* err, size_t errlen) {
+  REQUIRE(w != nullptr, "halo_split_qgate_norm_rope: w is null");
+  return halo_b200_norm_rope_ex(stream, qg, kF32, 2ull * hd, q, kF32, gate, nullptr, w, 0, eps, hd, rotary_dim, heads,
+                                rows, theta, nullptr, 0, 0, pos0, 1, nullptr, err, errlen);
+}
+
+int halo_b200_norm_rope_rows(halo_b200_stream stream, float* x, const float* w, float eps, uint32_t d,
+                             uint32_t rotary_dim, uint32_t pos0, uint32_t heads, float theta, float* cache,
+                             uint32_t rows, char* err, size_t errlen) {
+  REQUIRE(w != nullptr, "halo_norm_rope_rows: w is null");
+  return halo_b200_norm_rope_ex(stream, x, kF32, d, x, kF32, nullptr, cache, w, 0, eps, d, rotary_dim, heads, rows,
+                                theta, nullptr, 0, 0, pos0, 1, nullptr, err, errlen);
+}
+
+// ---- group 4 -------------------------------------------------------------------------
+int halo_b200_silu_mul_ex(halo_b200_stream stream, const void* g, const void* up, int in_dtype, void* y, int y_dtype,
+                          uint64_t n, char* err, size_t errlen) {
+  EltArgs a;
+  a.op = kOpSiluMul;
+  a.a = g;
+  a.b = up;
+  a.in_dtype = in_dtype;
+  a.y = y;
+  a.y_dtype = y_dtype;
+  a.n = n;
+  return RunElt(a, "halo_silu_mul", stream, err, errlen);
+}
+int halo_b200_silu_mul(halo_b200_stream stream, float* g, const float* up, uint32_t n, char* err, size_t errlen) {
+  return halo_b200_silu_mul_ex(stream, g, up, kF32, g, kF32, n, err, errlen);
+}
+int halo_b200_silu_mul_h(halo_b200_stream stream, const float* g, const float* up, uint16_t* y, uint32_t n, char* err,
+                         size_t errlen) {
+  return halo_b200_silu_mul_ex(stream, g, up, kF32, y, kF16, n, err, errlen);
+}
+int halo_b200_sigmoid_gate(halo_b200_stream stream, float* x, const float* gate, uint32_t n, char* err,
+                           size_t errlen) {
+  EltArgs a;
+  a.op = kOpSigmoidGate;
+  a.a = x;
+  a.b = gate;
+  a.y = x;
+  a.n = n;
+  return RunElt(a, "halo_sigmoid_gate", stream, err, errlen);
+}
+
+// ---- group 5 -------------------------------------------------------------------------
+int halo_b200_embed_q8_0_ex(halo_b200_stream stream, const uint8_t* w, uint64_t row_bytes, uint32_t vocab,
+                            const uint32_t* ids, uint32_t id_stride, uint32_t id_slot, uint32_t tokens, void* out,
+                            int out_dtype, uint32_t cols, char* err, size_t errlen) {
+  REQUIRE(ids != nullptr, "halo_embed_q8_0: ids is null");
+  EmbedArgs a;
+  a.table = w;
+  a.row_bytes = row_bytes;
+  a.cols = cols;
+  a.ids = ids;
+  a.id_stride = id_stride;
+  a.id_slot = id_slot;
+  a.tokens = tokens;
+  a.vocab = vocab;
+  a.out = out;
+  a.out_dtype = out_dtype;
+  return RunEmbed(a, "halo_embed_q8_0", stream, err, errlen);
+}
+
+int halo_b200_matvec_q8_0_embed(halo_b200_stream stream, const uint8_t* w, float* out, uint32_t token, uint32_t cols,
+                                uint64_t row_bytes, char* err, size_t errlen) {
+  EmbedArgs a;
+  a.table = w;
+  a.row_bytes = row_bytes;
+  a.cols = cols;
+  a.token = token;
+  a.out = out;
+  return RunEmbed(a, "halo_matvec_q8_0_embed", stream, err, errlen);
+}
+
+int halo_b200_matvec_q8_0_embed_p(halo_b200_stream stream, const uint8_t* w, float* out, const uint32_t* params,
+                                  uint32_t cols, uint64_t row_bytes, char* err, size_t errlen) {
+  REQUIRE(params != nullptr, "halo_matvec_q8_0_embed_p: params is null");
+  EmbedArgs a;
+  a.table = w;
+  a.row_bytes = row_bytes;
+  a.cols = cols;
+  a.ids = params;  // params[kHaloToken], slot 0 of the step parameters
+  a.id_stride = 0;
+  a.out = out;
+  return RunEmbed(a, "halo_matvec_q8_0_embed_p", stream, err, errlen);
+}
+
+int halo_b200_matvec_q8_0_embed_rows(halo_b200_stream stream, const uint8_t* w, float* out, const uint32_t* params,
+                                     uint32_t cols, uint64_t row_bytes, uint32_t tokens, char* err, size_t errlen) {
+  REQUIRE(params != nullptr, "halo_matvec_q8_0_embed_rows: params is null");
+  EmbedArgs a;
+  a.table = w;
+  a.row_bytes = row_bytes;
+  a.cols = cols;
+  a.ids = params;
+  a.id_stride = 16;  // parameter rows are 16 uint32 apart, token in slot 0
+  a.tokens = tokens;
+  a.out = out;
+  return RunEmbed(a, "halo_matvec_q8_0_embed_rows", stream, err, errlen);
+}
+
+}  // extern "C"

@@ -1,0 +1,176 @@
+// Internal launch interface between the C ABI (api.cu) and the kernel files.
+// Launchers validate nothing: api.cu has already checked pointers, sizes and
+// alignment and set `vec` (16-byte vector path) or cleared it (scalar path).
+// Each returns the cudaError_t of its launch.
+#ifndef HALO_B200_KERNELS_H_
+#define HALO_B200_KERNELS_H_
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace halo_b200 {
+
+enum DType : int { kF32 = 0, kF16 = 1, kBF16 = 2 };
+inline std::size_t DTypeSize(int t) { return t == kF32 ? 4 : 2; }
+
+// Where a token's position comes from (group 3). pos = base * scale, base =
+// params[t * pstride + slot] when params is set, else pos0 + t (uint32 wrap-around
+// arithmetic, as src/kernels/core.hip:289-311 computes it).
+struct PosSpec {
+  const uint32_t* params = nullptr;
+  uint32_t pstride = 0, slot = 0;
+  uint32_t pos0 = 0, scale = 1;
+};
+
+constexpr int kMaxRotHalf = 128;  // inverse-frequency table travels as a kernel argument
+struct InvFreq {
+  float f[kMaxRotHalf];
+};
+
+// ---- groups 1 and 2 (L2): row norms ------------------------------------------------
+// One kernel family covers RMSNorm, residual-add + RMSNorm, L2 norm and the Q8
+// epilogues. Row r lives at base + (r / rows_per_entry) * entry_stride +
+// (r % rows_per_entry) * d elements; dense tensors use rows_per_entry = rows.
+struct NormArgs {
+  const void* x = nullptr;      // [rows][d] x_dtype
+  int x_dtype = kF32;
+  const void* delta = nullptr;  // optional, x_dtype, dense [rows][d]: x + delta is normalized
+  void* res = nullptr;          // with delta: the sum is stored here in x_dtype (may alias x)
+  const float* w = nullptr;     // gamma rows (fp32) or null
+  uint32_t w_stride = 0, w_period = 1;
+  int one_plus = 0;             // multiply by (1 + w) instead of w
+  void* y = nullptr;            // normalized rows in y_dtype, or null (may alias x)
+  int y_dtype = kF32;
+  void* y16 = nullptr;          // optional extra fp16 copy (the reference's *_h kernels)
+  uint32_t y16_tokens = 0;      // > 0: y16 is K-blocked [cols / 64][tokens][64]
+  uint8_t* q8_0 = nullptr;      // optional Q8_0 rows, d / 32 blocks of 34 bytes
+  int8_t* xq = nullptr;         // optional int8 activation codes
+  float* xd = nullptr;          //   and their fp32 scales
+  uint32_t kb_tokens = 0;       // > 0: xq / xd K-blocked [cols / 64][tokens][64], [cols / 32][tokens]
+  uint32_t kb_period = 1;       // rows per token in the K-blocked layouts (column = (r % period) * d + i)
+  float* rscale = nullptr;      // optional per-row scale
+  uint32_t d = 0, rows = 0;
+  float eps = 0.0f;
+  int l2 = 0;                   // 1: scale = 1 / sqrt(ss + eps) (no mean, no gamma)
+  uint32_t rows_per_entry = 0;  // 0 = dense
+  uint64_t entry_stride = 0;
+  int threads_per_row = 0;      // 0 = pick automatically
+  bool vec = true;
+};
+cudaError_t LaunchNorm(const NormArgs& a, cudaStream_t s);
+
+// ---- group 2: gated RMSNorm --------------------------------------------------------
+struct GatedArgs {
+  const void* o = nullptr;
+  int o_dtype = kF32;
+  const void* z = nullptr;
+  int z_dtype = kF32;
+  const float* w = nullptr;  // [d], shared by every row
+  void* y = nullptr;         // may alias o
+  int y_dtype = kF32;
+  uint32_t d = 0, rows = 0;
+  float eps = 0.0f;
+  uint32_t mode = 0;  // 0 SiLU(z), 1 sigmoid(z)
+  int threads_per_row = 0;
+  bool vec = true;
+};
+cudaError_t LaunchGatedNorm(const GatedArgs& a, cudaStream_t s);
+
+// ---- group 3: rotary embedding --------------------------------------------------------
+struct RopeArgs {
+  void* x = nullptr;  // [tokens][heads][hd], in place
+  int dtype = kF32;
+  uint32_t tokens = 0, heads = 0, hd = 0, rot = 0;
+  uint64_t token_stride = 0;  // elements between tokens
+  void* x2 = nullptr;         // optional second tensor rotated with the same positions (K beside Q)
+  uint32_t heads2 = 0;
+  uint64_t token_stride2 = 0;
+  PosSpec pos;
+  uint32_t* pos_out = nullptr;  // optional [tokens]: the position each token used
+  bool vec = true;
+};
+cudaError_t LaunchRope(const RopeArgs& a, const InvFreq& f, cudaStream_t s);
+
+// RMSNorm (shared gamma) + RoPE on rows of d <= 2048 (one row = one head of one
+// token), optionally de-interleaving a [rows][2 * d] q|gate input and appending
+// the rotated row to a cache.
+struct NormRopeArgs {
+  const void* in = nullptr;
+  int in_dtype = kF32;
+  uint64_t in_row_stride = 0;  // elements between input rows (d, or 2 * d for q|gate)
+  void* out = nullptr;         // [rows][d] out_dtype, may alias in when in_row_stride == d
+  int out_dtype = kF32;
+  void* gate = nullptr;        // optional [rows][d] in_dtype copy of in[row][d .. 2d)
+  void* cache = nullptr;       // optional [rows][d] out_dtype second copy of the result
+  const float* w = nullptr;    // [d] or null (no norm: split + rope only)
+  int one_plus = 0;
+  float eps = 0.0f;
+  uint32_t d = 0, rot = 0, heads = 0, rows = 0;
+  PosSpec pos;
+  uint32_t* pos_out = nullptr;  // optional [rows / heads]
+};
+cudaError_t LaunchNormRope(const NormRopeArgs& a, const InvFreq& f, cudaStream_t s);
+
+struct SplitArgs {  // halo_split_qgate: [rows][2 * hd] -> q, gate
+  const void* qg = nullptr;
+  void* q = nullptr;
+  void* gate = nullptr;
+  int dtype = kF32;
+  uint32_t hd = 0, rows = 0;
+  uint32_t rows_per_entry = 0;  // 0 = dense
+  uint64_t qg_entry_stride = 0, q_entry_stride = 0;
+};
+cudaError_t LaunchSplitQgate(const SplitArgs& a, cudaStream_t s);
+
+// ---- group 4: elementwise ------------------------------------------------------------
+enum EltOp : int { kOpSiluMul = 0, kOpAdd = 1, kOpAxpy = 2, kOpSigmoidGate = 3 };
+struct EltArgs {
+  int op = kOpSiluMul;
+  const void* a = nullptr;  // g (SiLU argument) / y (accumulator) / x
+  const void* b = nullptr;  // up / x / gate
+  int in_dtype = kF32;
+  void* y = nullptr;  // may alias a
+  int y_dtype = kF32;
+  float alpha = 1.0f;  // axpy
+  uint64_t n = 0;
+  bool vec = true;
+};
+cudaError_t LaunchElementwise(const EltArgs& a, cudaStream_t s);
+
+// ---- group 5: Q8_0 embedding gather ---------------------------------------------------
+struct EmbedArgs {
+  const uint8_t* table = nullptr;  // [vocab][row_bytes]
+  uint64_t row_bytes = 0;
+  uint32_t cols = 0;
+  const uint32_t* ids = nullptr;  // token t at ids[t * id_stride + id_slot]; null: `token`
+  uint32_t id_stride = 1, id_slot = 0;
+  uint32_t token = 0;
+  uint32_t tokens = 1;
+  uint32_t vocab = 0;  // > 0: ids >= vocab produce a zero row instead of an out-of-range read
+  void* out = nullptr;  // [tokens][cols]
+  int out_dtype = kF32;
+  bool vec = true;
+};
+cudaError_t LaunchEmbedQ8_0(const EmbedArgs& a, cudaStream_t s);
+
+// ---- Q8 quantizers -------------------------------------------------------------------------
+struct QuantArgs {
+  const void* x = nullptr;  // row r at x + r * x_stride
+  int x_dtype = kF32;
+  uint64_t x_stride = 0;
+  uint32_t cols = 0, rows = 0;
+  uint8_t* q8_0 = nullptr;  // true Q8_0 rows
+  int8_t* xq = nullptr;     // int8 activation form
+  float* xd = nullptr;
+  uint32_t kb_tokens = 0;   // > 0: K-blocked
+  int8_t* xq2 = nullptr;    // optional second (residual) level, row-major only
+  float* xd2 = nullptr;
+  bool vec = true;
+};
+cudaError_t LaunchQuantize(const QuantArgs& a, cudaStream_t s);
+
+}  // namespace halo_b200
+
+#endif  // HALO_B200_KERNELS_H_

@@ -1,0 +1,330 @@
+// halo_b200_launch: the reference's launch-by-name call (rt::Device::Kernel + Launch,
+// src/rt/device.hpp:120-127) mapped onto this library's typed entry points. Each
+// handler unpacks the reference kernel's argument list in its declared order and
+// recovers the row / batch counts from the grid exactly as the kernel reads
+// blockIdx (src/kernels/core.hip, src/kernels/batch_decode.hip).
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/halo_b200.h"
+
+namespace {
+
+struct Reader {
+  const halo_b200_arg* args;
+  size_t n;
+  size_t i = 0;
+  bool bad = false;
+
+  const halo_b200_arg* next() {
+    if (i >= n) {
+      bad = true;
+      return nullptr;
+    }
+    return &args[i++];
+  }
+  template <typename T>
+  T* ptr() {
+    const halo_b200_arg* a = next();
+    if (!a) return nullptr;
+    if (a->is_buffer) return static_cast<T*>(a->v.ptr);
+    // a null optional pointer passed as a 64-bit zero scalar
+    uint64_t v = 0;
+    if (a->size != 8) bad = true;
+    std::memcpy(&v, a->v.bytes, 8);
+    if (v != 0) bad = true;
+    return nullptr;
+  }
+  template <typename T>
+  T val() {
+    const halo_b200_arg* a = next();
+    T v{};
+    if (!a) return v;
+    if (a->is_buffer || a->size != sizeof(T)) {
+      bad = true;
+      return v;
+    }
+    std::memcpy(&v, a->v.bytes, sizeof(T));
+    return v;
+  }
+  uint32_t u32() { return val<uint32_t>(); }
+  uint64_t u64() { return val<uint64_t>(); }
+  float f32() { return val<float>(); }
+};
+
+struct Ctx {
+  halo_b200_stream s;
+  const uint32_t* grid;
+  const uint32_t* block;
+  char* err;
+  size_t errlen;
+};
+
+using Handler = int (*)(Reader&, const Ctx&);
+
+int BadArgs(const Ctx& c, const char* name) {
+  if (c.err && c.errlen) std::snprintf(c.err, c.errlen, "%s: argument list does not match the kernel's parameters", name);
+  return -1;
+}
+
+#define HANDLER(fn) static int fn(Reader& r, const Ctx& c)
+#define CHECK_ARGS(name) \
+  if (r.bad || r.i != r.n) return BadArgs(c, name)
+
+HANDLER(H_add) {
+  auto* y = r.ptr<float>(); auto* x = r.ptr<const float>(); const uint32_t n = r.u32();
+  CHECK_ARGS("halo_add");
+  return halo_b200_add(c.s, y, x, n, c.err, c.errlen);
+}
+HANDLER(H_axpy) {
+  auto* y = r.ptr<float>(); auto* x = r.ptr<const float>(); const float a = r.f32(); const uint32_t n = r.u32();
+  CHECK_ARGS("halo_axpy");
+  return halo_b200_axpy(c.s, y, x, a, n, c.err, c.errlen);
+}
+HANDLER(H_rmsnorm) {
+  auto* x = r.ptr<const float>(); auto* w = r.ptr<const float>(); auto* y = r.ptr<float>();
+  const uint32_t d = r.u32(); const float eps = r.f32(); const uint32_t ws = r.u32();
+  CHECK_ARGS("halo_rmsnorm");
+  return halo_b200_rmsnorm(c.s, x, w, y, d, eps, ws, c.grid[0], c.err, c.errlen);
+}
+template <int DT>
+HANDLER(H_rmsnorm_rows) {
+  auto* x = r.ptr<const void>(); auto* w = r.ptr<const float>(); auto* y = r.ptr<float>();
+  const uint32_t d = r.u32(); const float eps = r.f32(); const uint32_t ws = r.u32(), wp = r.u32();
+  CHECK_ARGS("halo_rmsnorm_rows");
+  if (DT == HALO_B200_F32)
+    return halo_b200_rmsnorm_rows(c.s, static_cast<const float*>(x), w, y, d, eps, ws, wp, c.grid[0], c.err, c.errlen);
+  if (DT == HALO_B200_F16)
+    return halo_b200_rmsnorm_rows_r16(c.s, static_cast<const uint16_t*>(x), w, y, d, eps, ws, wp, c.grid[0], c.err,
+                                      c.errlen);
+  return halo_b200_rmsnorm_rows_rb(c.s, static_cast<const uint16_t*>(x), w, y, d, eps, ws, wp, c.grid[0], c.err,
+                                   c.errlen);
+}
+template <int DT>
+HANDLER(H_rmsnorm_rows_h) {
+  auto* x = r.ptr<const void>(); auto* w = r.ptr<const float>(); auto* y = r.ptr<float>();
+  auto* y16 = r.ptr<uint16_t>();
+  const uint32_t d = r.u32(); const float eps = r.f32(); const uint32_t ws = r.u32(), wp = r.u32();
+  auto* iw = r.ptr<const float>(); auto* ipart = r.ptr<float>();
+  const uint32_t irows = r.u32(), y16_tokens = r.u32();
+  CHECK_ARGS("halo_rmsnorm_rows_h");
+  return halo_b200_rmsnorm_rows_h(c.s, x, DT, w, y, y16, d, eps, ws, wp, iw, ipart, irows, y16_tokens, c.grid[0], c.err,
+                                  c.errlen);
+}
+HANDLER(H_rmsnorm_y) {
+  auto* x = r.ptr<float>(); auto* w = r.ptr<const float>();
+  const uint32_t d = r.u32(); const float eps = r.f32(); const uint32_t ws = r.u32(), stride = r.u32();
+  CHECK_ARGS("halo_rmsnorm_y");
+  return halo_b200_rmsnorm_y(c.s, x, w, d, eps, ws, stride, c.grid[0], c.grid[1], c.err, c.errlen);
+}
+HANDLER(H_l2norm) {
+  auto* x = r.ptr<float>(); const uint32_t d = r.u32(); const float eps = r.f32();
+  CHECK_ARGS("halo_l2norm");
+  return halo_b200_l2norm(c.s, x, d, eps, c.grid[0], c.err, c.errlen);
+}
+HANDLER(H_gated_norm) {
+  auto* o = r.ptr<float>(); auto* w = r.ptr<const float>(); auto* z = r.ptr<const float>();
+  const uint32_t d = r.u32(); const float eps = r.f32(); const uint32_t mode = r.u32();
+  CHECK_ARGS("halo_gated_norm");
+  return halo_b200_gated_norm(c.s, o, w, z, d, eps, mode, c.grid[0], c.err, c.errlen);
+}
+template <bool ZH>
+HANDLER(H_gated_norm_h) {
+  auto* o = r.ptr<const float>(); auto* w = r.ptr<const float>(); auto* z = r.ptr<const void>();
+  auto* y16 = r.ptr<uint16_t>();
+  const uint32_t d = r.u32(); const float eps = r.f32(); const uint32_t mode = r.u32();
+  CHECK_ARGS("halo_gated_norm_h");
+  if (ZH)
+    return halo_b200_gated_norm_hz(c.s, o, w, static_cast<const uint16_t*>(z), y16, d, eps, mode, c.grid[0], c.err,
+                                   c.errlen);
+  return halo_b200_gated_norm_h(c.s, o, w, static_cast<const float*>(z), y16, d, eps, mode, c.grid[0], c.err, c.errlen);
+}
+template <bool HH>
+HANDLER(H_gated_norm_h128w) {
+  auto* o = r.ptr<const void>(); auto* w = r.ptr<const float>(); auto* z = r.ptr<const void>();
+  auto* y16 = r.ptr<uint16_t>();
+  const uint32_t rows = r.u32(); const float eps = r.f32(); const uint32_t mode = r.u32();
+  CHECK_ARGS("halo_gated_norm_h128w");
+  if (HH)
+    return halo_b200_gated_norm_h128w_hh(c.s, static_cast<const uint16_t*>(o), w, static_cast<const uint16_t*>(z), y16,
+                                         rows, eps, mode, c.err, c.errlen);
+  return halo_b200_gated_norm_h128w(c.s, static_cast<const float*>(o), w, static_cast<const float*>(z), y16, rows, eps,
+                                    mode, c.err, c.errlen);
+}
+HANDLER(H_rope_neox) {
+  auto* x = r.ptr<float>(); const uint32_t hd = r.u32(), rot = r.u32(), pos = r.u32(); const float theta = r.f32();
+  CHECK_ARGS("halo_rope_neox");
+  return halo_b200_rope_neox(c.s, x, hd, rot, pos, theta, c.grid[0], c.err, c.errlen);
+}
+HANDLER(H_rope_neox_rows) {
+  auto* x = r.ptr<float>(); const uint32_t hd = r.u32(), rot = r.u32(), pos0 = r.u32(), heads = r.u32();
+  const float theta = r.f32();
+  CHECK_ARGS("halo_rope_neox_rows");
+  return halo_b200_rope_neox_rows(c.s, x, hd, rot, pos0, heads, theta, c.grid[0], c.err, c.errlen);
+}
+HANDLER(H_rope_neox_p) {
+  auto* x = r.ptr<float>(); auto* params = r.ptr<const uint32_t>();
+  const uint32_t hd = r.u32(), rot = r.u32(), slot = r.u32(), scale = r.u32(); const float theta = r.f32();
+  CHECK_ARGS("halo_rope_neox_p");
+  return halo_b200_rope_neox_p(c.s, x, params, hd, rot, slot, scale, theta, c.grid[0], c.err, c.errlen);
+}
+HANDLER(H_rope_neox_blocks) {
+  auto* x = r.ptr<float>(); const uint32_t hd = r.u32(), rot = r.u32(), b0 = r.u32(), ratio = r.u32();
+  const float theta = r.f32();
+  CHECK_ARGS("halo_rope_neox_blocks");
+  return halo_b200_rope_neox_blocks(c.s, x, hd, rot, b0, ratio, theta, c.grid[0], c.err, c.errlen);
+}
+HANDLER(H_rope_neox_p_y) {
+  auto* x = r.ptr<float>(); auto* params = r.ptr<const uint32_t>();
+  const uint32_t hd = r.u32(), rot = r.u32(), slot = r.u32(), scale = r.u32(); const float theta = r.f32();
+  const uint32_t stride = r.u32(), pstride = r.u32();
+  CHECK_ARGS("halo_rope_neox_p_y");
+  return halo_b200_rope_neox_p_y(c.s, x, params, hd, rot, slot, scale, theta, stride, pstride, c.grid[0], c.grid[1],
+                                 c.err, c.errlen);
+}
+HANDLER(H_split_qgate) {
+  auto* qg = r.ptr<const float>(); auto* q = r.ptr<float>(); auto* gate = r.ptr<float>(); const uint32_t hd = r.u32();
+  CHECK_ARGS("halo_split_qgate");
+  return halo_b200_split_qgate(c.s, qg, q, gate, hd, c.grid[0], c.err, c.errlen);
+}
+HANDLER(H_split_qgate_y) {
+  auto* qg = r.ptr<const float>(); auto* q = r.ptr<float>(); auto* gate = r.ptr<float>();
+  const uint32_t hd = r.u32(), qs = r.u32(), os = r.u32();
+  CHECK_ARGS("halo_split_qgate_y");
+  return halo_b200_split_qgate_y(c.s, qg, q, gate, hd, qs, os, c.grid[0], c.grid[1], c.err, c.errlen);
+}
+HANDLER(H_split_qgate_norm_rope) {
+  auto* qg = r.ptr<const float>(); auto* q = r.ptr<float>(); auto* gate = r.ptr<float>(); auto* w = r.ptr<const float>();
+  const float eps = r.f32(); const uint32_t rot = r.u32(), pos0 = r.u32(), heads = r.u32(); const float theta = r.f32();
+  CHECK_ARGS("halo_split_qgate_norm_rope");
+  return halo_b200_split_qgate_norm_rope(c.s, qg, q, gate, w, eps, rot, pos0, heads, theta, c.block[0], c.grid[0], c.err,
+                                         c.errlen);
+}
+HANDLER(H_norm_rope_rows) {
+  auto* x = r.ptr<float>(); auto* w = r.ptr<const float>(); const float eps = r.f32();
+  const uint32_t d = r.u32(), rot = r.u32(), pos0 = r.u32(), heads = r.u32(); const float theta = r.f32();
+  auto* cache = r.ptr<float>();
+  CHECK_ARGS("halo_norm_rope_rows");
+  return halo_b200_norm_rope_rows(c.s, x, w, eps, d, rot, pos0, heads, theta, cache, c.grid[0], c.err, c.errlen);
+}
+HANDLER(H_silu_mul) {
+  auto* g = r.ptr<float>(); auto* up = r.ptr<const float>(); const uint32_t n = r.u32();
+  CHECK_ARGS("halo_silu_mul");
+  return halo_b200_silu_mul(c.s, g, up, n, c.err, c.errlen);
+}
+HANDLER(H_silu_mul_h) {
+  auto* g = r.ptr<const float>(); auto* up = r.ptr<const float>(); auto* y = r.ptr<uint16_t>(); const uint32_t n = r.u32();
+  CHECK_ARGS("halo_silu_mul_h");
+  return halo_b200_silu_mul_h(c.s, g, up, y, n, c.err, c.errlen);
+}
+HANDLER(H_sigmoid_gate) {
+  auto* x = r.ptr<float>(); auto* gate = r.ptr<const float>(); const uint32_t n = r.u32();
+  CHECK_ARGS("halo_sigmoid_gate");
+  return halo_b200_sigmoid_gate(c.s, x, gate, n, c.err, c.errlen);
+}
+HANDLER(H_quantize_q8_rows) {
+  auto* x = r.ptr<const float>(); auto* xq = r.ptr<int8_t>(); auto* xd = r.ptr<float>(); const uint32_t cols = r.u32();
+  CHECK_ARGS("halo_quantize_q8_rows");
+  return halo_b200_quantize_q8_rows(c.s, x, xq, xd, cols, c.grid[0], c.err, c.errlen);
+}
+HANDLER(H_quantize_q8_kblocked) {
+  auto* x = r.ptr<const float>(); auto* xq = r.ptr<int8_t>(); auto* xd = r.ptr<float>();
+  const uint32_t cols = r.u32(), tokens = r.u32();
+  CHECK_ARGS("halo_quantize_q8_kblocked");
+  if (tokens != c.grid[0]) return BadArgs(c, "halo_quantize_q8_kblocked (tokens != grid.x)");
+  return halo_b200_quantize_q8_kblocked(c.s, x, xq, xd, cols, tokens, c.err, c.errlen);
+}
+HANDLER(H_q8x_cols) {
+  auto* x = r.ptr<const float>(); const uint32_t xstride = r.u32(), cols = r.u32();
+  auto* xq = r.ptr<int8_t>(); auto* xs = r.ptr<float>(); auto* xq2 = r.ptr<int8_t>(); auto* xs2 = r.ptr<float>();
+  CHECK_ARGS("halo_q8x_cols");
+  return halo_b200_q8x_cols(c.s, x, xstride, cols, xq, xs, xq2, xs2, c.grid[1], c.err, c.errlen);
+}
+HANDLER(H_embed) {
+  auto* w = r.ptr<const uint8_t>(); auto* out = r.ptr<float>(); const uint32_t token = r.u32(), cols = r.u32();
+  const uint64_t rb = r.u64();
+  CHECK_ARGS("halo_matvec_q8_0_embed");
+  return halo_b200_matvec_q8_0_embed(c.s, w, out, token, cols, rb, c.err, c.errlen);
+}
+HANDLER(H_embed_p) {
+  auto* w = r.ptr<const uint8_t>(); auto* out = r.ptr<float>(); auto* params = r.ptr<const uint32_t>();
+  const uint32_t cols = r.u32(); const uint64_t rb = r.u64();
+  CHECK_ARGS("halo_matvec_q8_0_embed_p");
+  return halo_b200_matvec_q8_0_embed_p(c.s, w, out, params, cols, rb, c.err, c.errlen);
+}
+HANDLER(H_embed_rows) {
+  auto* w = r.ptr<const uint8_t>(); auto* out = r.ptr<float>(); auto* params = r.ptr<const uint32_t>();
+  const uint32_t cols = r.u32(); const uint64_t rb = r.u64();
+  CHECK_ARGS("halo_matvec_q8_0_embed_rows");
+  return halo_b200_matvec_q8_0_embed_rows(c.s, w, out, params, cols, rb, c.grid[1], c.err, c.errlen);
+}
+
+struct Entry {
+  const char* name;
+  Handler fn;
+};
+
+const Entry kTable[] = {
+    {"halo_add", H_add},
+    {"halo_axpy", H_axpy},
+    {"halo_rmsnorm", H_rmsnorm},
+    {"halo_rmsnorm_rows", H_rmsnorm_rows<HALO_B200_F32>},
+    {"halo_rmsnorm_rows_r16", H_rmsnorm_rows<HALO_B200_F16>},
+    {"halo_rmsnorm_rows_rb", H_rmsnorm_rows<HALO_B200_BF16>},
+    {"halo_rmsnorm_rows_h", H_rmsnorm_rows_h<HALO_B200_F32>},
+    {"halo_rmsnorm_rows_h_r16", H_rmsnorm_rows_h<HALO_B200_F16>},
+    {"halo_rmsnorm_rows_h_rb", H_rmsnorm_rows_h<HALO_B200_BF16>},
+    {"halo_rmsnorm_y", H_rmsnorm_y},
+    {"halo_l2norm", H_l2norm},
+    {"halo_gated_norm", H_gated_norm},
+    {"halo_gated_norm_h", H_gated_norm_h<false>},
+    {"halo_gated_norm_hz", H_gated_norm_h<true>},
+    {"halo_gated_norm_h128w", H_gated_norm_h128w<false>},
+    {"halo_gated_norm_h128w_hh", H_gated_norm_h128w<true>},
+    {"halo_rope_neox", H_rope_neox},
+    {"halo_rope_neox_rows", H_rope_neox_rows},
+    {"halo_rope_neox_p", H_rope_neox_p},
+    {"halo_rope_neox_blocks", H_rope_neox_blocks},
+    {"halo_rope_neox_p_y", H_rope_neox_p_y},
+    {"halo_split_qgate", H_split_qgate},
+    {"halo_split_qgate_y", H_split_qgate_y},
+    {"halo_split_qgate_norm_rope", H_split_qgate_norm_rope},
+    {"halo_norm_rope_rows", H_norm_rope_rows},
+    {"halo_silu_mul", H_silu_mul},
+    {"halo_silu_mul_h", H_silu_mul_h},
+    {"halo_sigmoid_gate", H_sigmoid_gate},
+    {"halo_quantize_q8_rows", H_quantize_q8_rows},
+    {"halo_quantize_q8_kblocked", H_quantize_q8_kblocked},
+    {"halo_q8x_cols", H_q8x_cols},
+    {"halo_matvec_q8_0_embed", H_embed},
+    {"halo_matvec_q8_0_embed_p", H_embed_p},
+    {"halo_matvec_q8_0_embed_rows", H_embed_rows},
+};
+constexpr size_t kCount = sizeof(kTable) / sizeof(kTable[0]);
+
+}  // namespace
+
+extern "C" {
+
+size_t halo_b200_kernel_count(void) { return kCount; }
+const char* halo_b200_kernel_name(size_t index) { return index < kCount ? kTable[index].name : nullptr; }
+
+int halo_b200_launch(halo_b200_stream stream, const char* name, const halo_b200_arg* args, size_t nargs,
+                     const uint32_t grid[3], const uint32_t block[3], char* err, size_t errlen) {
+  if (!name || !grid || !block || (nargs && !args)) {
+    if (err && errlen) std::snprintf(err, errlen, "halo_b200_launch: null argument");
+    return -1;
+  }
+  for (size_t i = 0; i < kCount; ++i) {
+    if (std::strcmp(kTable[i].name, name) == 0) {
+      Reader r{args, nargs};
+      const Ctx c{stream, grid, block, err, errlen};
+      return kTable[i].fn(r, c);
+    }
+  }
+  if (err && errlen) std::snprintf(err, errlen, "halo_b200_launch: unknown kernel %s", name);
+  return -1;
+}
+
+}  // extern "C"

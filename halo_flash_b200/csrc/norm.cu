@@ -1,0 +1,412 @@
+// Row norms for sm_100a: RMSNorm, residual-add + RMSNorm, L2 norm, gated RMSNorm,
+// with the Q8 re-quantise epilogues. Replaces halo-flash's halo_rmsnorm*,
+// halo_l2norm, halo_gated_norm*, halo_quantize_q8_* epilogue and the add+norm
+// fusion of halo_hc_combine_norm_rows (src/kernels/core.hip:247-273, 495-510,
+// 4045-4077, 4105-4210, 4502-4632); arithmetic follows src/model/cpu_ops.cpp:134-156.
+//
+// Layout: a row of d elements is split into octets (8 consecutive elements, one
+// 16-byte load for 16-bit types, two for fp32). A group of g threads (g a power
+// of two, 1..256) owns one row; thread `lir` of the group holds octets
+// lir, lir + g, ... (K of them, compile-time), so every warp-wide load
+// instruction covers one contiguous 512-byte (16-bit) or 1 KiB (fp32) span.
+// The whole row stays in registers between the sum of squares and the scaled
+// store: each activation byte crosses HBM exactly once per direction. g <= 32
+// reduces with shuffles only; g > 32 adds one shared-memory stage.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace halo_b200 {
+namespace {
+
+template <typename T>
+__device__ __forceinline__ T* at(void* p, size_t off) { return static_cast<T*>(p) + off; }
+template <typename T>
+__device__ __forceinline__ const T* at(const void* p, size_t off) { return static_cast<const T*>(p) + off; }
+
+// Epilogues on one normalized octet `v` (columns [c0, c0 + 8) of row `row`); all 32
+// lanes of the warp call (quad shuffles), `ok` marks lanes that hold real data.
+__device__ __forceinline__ void q8_epilogues(const NormArgs& a, const float (&v)[8], uint32_t row, uint32_t c0, bool ok) {
+  const float amax = quad_amax(v);
+  if (a.q8_0) {
+    uint16_t dbits;
+    const uint2 codes = q8_0_codes(v, amax, &dbits);
+    if (ok) {
+      uint8_t* blk = a.q8_0 + static_cast<size_t>(row) * (a.d / 32) * 34 + static_cast<size_t>(c0 / 32) * 34;
+      if ((c0 & 31u) == 0) *reinterpret_cast<uint16_t*>(blk) = dbits;
+      store_codes_u16(blk + 2 + (c0 & 31u), codes);
+    }
+  }
+  if (a.xq) {
+    const float scale = amax / 127.0f;
+    const uint2 codes = i8_codes(v, scale);
+    if (ok) {
+      if (a.kb_tokens) {
+        const uint32_t t = row / a.kb_period, c = (row % a.kb_period) * a.d + c0;
+        *reinterpret_cast<uint2*>(a.xq + (static_cast<size_t>(c / 64) * a.kb_tokens + t) * 64 + c % 64) = codes;
+        if ((c0 & 31u) == 0) a.xd[static_cast<size_t>(c / 32) * a.kb_tokens + t] = scale;
+      } else {
+        *reinterpret_cast<uint2*>(a.xq + static_cast<size_t>(row) * a.d + c0) = codes;
+        if ((c0 & 31u) == 0) a.xd[static_cast<size_t>(row) * (a.d / 32) + c0 / 32] = scale;
+      }
+    }
+  }
+}
+
+template <typename XT, typename YT, int K, bool ADD>
+__global__ void __launch_bounds__(kBlock) norm_rows_kernel(const NormArgs a, const unsigned g) {
+  __shared__ float scratch[kBlock / 32];
+  const unsigned lir = threadIdx.x & (g - 1);
+  const uint32_t row = blockIdx.x * (kBlock / g) + threadIdx.x / g;
+  const bool row_ok = row < a.rows;
+  const unsigned octs = a.d >> 3;
+  const size_t dense = static_cast<size_t>(row) * a.d;
+  const size_t xoff = a.rows_per_entry
+                          ? static_cast<size_t>(row / a.rows_per_entry) * a.entry_stride +
+                                static_cast<size_t>(row % a.rows_per_entry) * a.d
+                          : dense;
+
+  float v[K][8];
+  // Every load of the thread is issued before any is consumed.
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const unsigned j = k * g + lir;
+    if (row_ok && j < octs) {
+      load8(at<XT>(a.x, xoff + j * 8), v[k]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[k][i] = 0.0f;
+    }
+  }
+  if constexpr (ADD) {
+    float dl[K][8];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const unsigned j = k * g + lir;
+      if (row_ok && j < octs) {
+        load8(at<XT>(a.delta, dense + j * 8), dl[k]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dl[k][i] = 0.0f;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const unsigned j = k * g + lir;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[k][i] = v[k][i] + dl[k][i];
+      if (row_ok && j < octs) store8(at<XT>(a.res, xoff + j * 8), v[k]);
+      round_through8<XT>(v[k]);  // the norm reads the residual as stored
+    }
+  }
+
+  float ss = 0.0f;
+#pragma unroll
+  for (int k = 0; k < K; ++k)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += v[k][i] * v[k][i];
+  ss = group_sum(ss, g, scratch);
+  const float scale = a.l2 ? 1.0f / sqrtf(ss + a.eps) : 1.0f / sqrtf(ss / static_cast<float>(a.d) + a.eps);
+  if (a.rscale && row_ok && lir == 0) a.rscale[row] = scale;
+
+  const float* wrow = a.w ? a.w + static_cast<size_t>(row % a.w_period) * a.w_stride : nullptr;
+  const bool epi = a.q8_0 != nullptr || a.xq != nullptr;
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const unsigned j = k * g + lir;
+    const bool ok = row_ok && j < octs;
+    if (wrow) {
+      float gm[8];
+      if (ok) {
+        load8_cached(wrow + j * 8, gm);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) gm[i] = 0.0f;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[k][i] = v[k][i] * scale * (a.one_plus ? 1.0f + gm[i] : gm[i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[k][i] = v[k][i] * scale;
+    }
+    if (ok) {
+      if (a.y) store8(at<YT>(a.y, xoff + j * 8), v[k]);
+      if (a.y16) {
+        size_t o16 = dense + j * 8;
+        if (a.y16_tokens) {
+          const uint32_t t = row / a.kb_period, c = (row % a.kb_period) * a.d + j * 8;
+          o16 = (static_cast<size_t>(c / 64) * a.y16_tokens + t) * 64 + c % 64;
+        }
+        store8(at<f16>(a.y16, o16), v[k]);
+      }
+    }
+    if (epi) q8_epilogues(a, v[k], row, j * 8, ok);
+  }
+}
+
+// Any d, any alignment: one CTA per row, scalar accesses, the row is re-read
+// after the reduction. Correctness path for shapes the vector kernel refuses.
+template <typename XT, typename YT, bool ADD>
+__global__ void __launch_bounds__(kBlock) norm_rows_scalar_kernel(const NormArgs a) {
+  __shared__ float scratch[kBlock / 32];
+  __shared__ float total;
+  const uint32_t row = blockIdx.x;
+  const size_t dense = static_cast<size_t>(row) * a.d;
+  const size_t xoff = a.rows_per_entry
+                          ? static_cast<size_t>(row / a.rows_per_entry) * a.entry_stride +
+                                static_cast<size_t>(row % a.rows_per_entry) * a.d
+                          : dense;
+  const XT* x = at<XT>(a.x, xoff);
+  float ss = 0.0f;
+  for (uint32_t i = threadIdx.x; i < a.d; i += kBlock) {
+    float xv = to_f32(x[i]);
+    if constexpr (ADD) {
+      xv = xv + to_f32(at<XT>(a.delta, dense)[i]);
+      at<XT>(a.res, xoff)[i] = from_f32<XT>(xv);
+      xv = round_through<XT>(xv);
+    }
+    ss += xv * xv;
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31u) == 0) scratch[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.0f;
+    for (int i = 0; i < kBlock / 32; ++i) t += scratch[i];
+    total = t;
+  }
+  __syncthreads();
+  ss = total;
+  const float scale = a.l2 ? 1.0f / sqrtf(ss + a.eps) : 1.0f / sqrtf(ss / static_cast<float>(a.d) + a.eps);
+  if (a.rscale && threadIdx.x == 0) a.rscale[row] = scale;
+  const float* wrow = a.w ? a.w + static_cast<size_t>(row % a.w_period) * a.w_stride : nullptr;
+  const XT* src = ADD ? at<XT>(static_cast<const void*>(a.res), xoff) : x;
+  const bool epi = a.q8_0 != nullptr || a.xq != nullptr;  // api.cu guarantees d % 32 == 0 then
+  const uint32_t lane = threadIdx.x & 31u;
+  for (uint32_t base = threadIdx.x - lane; base < a.d; base += kBlock) {
+    const uint32_t i = base + lane;
+    const bool ok = i < a.d;
+    float v = ok ? to_f32(src[i]) : 0.0f;
+    if (wrow) {
+      const float gm = ok ? wrow[i] : 0.0f;
+      v = v * scale * (a.one_plus ? 1.0f + gm : gm);
+    } else {
+      v = v * scale;
+    }
+    if (ok) {
+      if (a.y) at<YT>(a.y, xoff)[i] = from_f32<YT>(v);
+      if (a.y16) {
+        size_t o16 = dense + i;
+        if (a.y16_tokens) {
+          const uint32_t t = row / a.kb_period, c = (row % a.kb_period) * a.d + i;
+          o16 = (static_cast<size_t>(c / 64) * a.y16_tokens + t) * 64 + c % 64;
+        }
+        at<f16>(a.y16, o16)[0] = __float2half_rn(v);
+      }
+    }
+    if (epi) {
+      const float amax = warp_max(fabsf(v));
+      if (a.q8_0) {
+        const f16 dh = __float2half_rn(amax / 127.0f);
+        const float d = __half2float(dh);
+        float q = 0.0f;
+        if (d > 0.0f) q = fminf(fmaxf(rintf(v / d), -127.0f), 127.0f);
+        uint8_t* blk = a.q8_0 + static_cast<size_t>(row) * (a.d / 32) * 34 + static_cast<size_t>(i / 32) * 34;
+        if (ok) {
+          if (lane == 0) *reinterpret_cast<uint16_t*>(blk) = __half_as_ushort(dh);
+          blk[2 + lane] = static_cast<uint8_t>(static_cast<int8_t>(static_cast<int>(q)));
+        }
+      }
+      if (a.xq) {
+        const float qs = amax / 127.0f;
+        const int8_t code = static_cast<int8_t>(qs > 0.0f ? static_cast<int>(rintf(v / qs)) : 0);
+        if (ok) {
+          if (a.kb_tokens) {
+            const uint32_t t = row / a.kb_period, c = (row % a.kb_period) * a.d + i;
+            a.xq[(static_cast<size_t>(c / 64) * a.kb_tokens + t) * 64 + c % 64] = code;
+            if (lane == 0) a.xd[static_cast<size_t>(c / 32) * a.kb_tokens + t] = qs;
+          } else {
+            a.xq[static_cast<size_t>(row) * a.d + i] = code;
+            if (lane == 0) a.xd[static_cast<size_t>(row) * (a.d / 32) + i / 32] = qs;
+          }
+        }
+      }
+    }
+  }
+}
+
+// ---- gated RMSNorm: y = ((o * scale) * w) * gate(z) ----------------------------------------
+template <typename OT, typename ZT, typename YT, int K>
+__global__ void __launch_bounds__(kBlock) gated_norm_kernel(const GatedArgs a, const unsigned g) {
+  __shared__ float scratch[kBlock / 32];
+  const unsigned lir = threadIdx.x & (g - 1);
+  const uint32_t row = blockIdx.x * (kBlock / g) + threadIdx.x / g;
+  const bool row_ok = row < a.rows;
+  const unsigned octs = a.d >> 3;
+  const size_t off = static_cast<size_t>(row) * a.d;
+  float v[K][8], zz[K][8];
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const unsigned j = k * g + lir;
+    if (row_ok && j < octs) {
+      load8(at<OT>(a.o, off + j * 8), v[k]);
+      load8(at<ZT>(a.z, off + j * 8), zz[k]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[k][i] = 0.0f, zz[k][i] = 0.0f;
+    }
+  }
+  float ss = 0.0f;
+#pragma unroll
+  for (int k = 0; k < K; ++k)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += v[k][i] * v[k][i];
+  ss = group_sum(ss, g, scratch);
+  const float scale = 1.0f / sqrtf(ss / static_cast<float>(a.d) + a.eps);
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const unsigned j = k * g + lir;
+    if (row_ok && j < octs) {
+      float gm[8];
+      load8_cached(a.w + j * 8, gm);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float gate = a.mode == 0 ? silu_f(zz[k][i]) : sigmoid_f(zz[k][i]);
+        v[k][i] = v[k][i] * scale * gm[i] * gate;
+      }
+      store8(at<YT>(a.y, off + j * 8), v[k]);
+    }
+  }
+}
+
+template <typename OT, typename ZT, typename YT>
+__global__ void __launch_bounds__(kBlock) gated_norm_scalar_kernel(const GatedArgs a) {
+  __shared__ float scratch[kBlock / 32];
+  __shared__ float total;
+  const size_t off = static_cast<size_t>(blockIdx.x) * a.d;
+  const OT* o = at<OT>(a.o, off);
+  const ZT* z = at<ZT>(a.z, off);
+  float ss = 0.0f;
+  for (uint32_t i = threadIdx.x; i < a.d; i += kBlock) {
+    const float xv = to_f32(o[i]);
+    ss += xv * xv;
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31u) == 0) scratch[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.0f;
+    for (int i = 0; i < kBlock / 32; ++i) t += scratch[i];
+    total = t;
+  }
+  __syncthreads();
+  const float scale = 1.0f / sqrtf(total / static_cast<float>(a.d) + a.eps);
+  for (uint32_t i = threadIdx.x; i < a.d; i += kBlock) {
+    const float zf = to_f32(z[i]);
+    const float gate = a.mode == 0 ? silu_f(zf) : sigmoid_f(zf);
+    at<YT>(a.y, off)[i] = from_f32<YT>(to_f32(o[i]) * scale * a.w[i] * gate);
+  }
+}
+
+// Threads per row and octets per thread for a row of `octs` octets.
+struct Shape {
+  unsigned g;
+  int k;
+};
+Shape PickShape(unsigned octs, int want_g) {
+  unsigned g;
+  if (want_g > 0) {
+    g = static_cast<unsigned>(want_g);
+  } else if (octs <= 32) {
+    g = 1;
+    while (g < octs) g <<= 1;
+  } else if (octs <= 256) {
+    g = 32;  // one warp per row: no barrier
+  } else {
+    g = 256;
+  }
+  unsigned k = (octs + g - 1) / g, kp = 1;
+  while (kp < k) kp <<= 1;
+  return {g, static_cast<int>(kp)};
+}
+
+template <typename XT, typename YT, bool ADD>
+cudaError_t LaunchNormT(const NormArgs& a, cudaStream_t s) {
+  if (!a.vec) {
+    norm_rows_scalar_kernel<XT, YT, ADD><<<a.rows, kBlock, 0, s>>>(a);
+    return cudaGetLastError();
+  }
+  const Shape sh = PickShape(a.d / 8, a.threads_per_row);
+  const unsigned rows_per_cta = kBlock / sh.g;
+  const unsigned grid = (a.rows + rows_per_cta - 1) / rows_per_cta;
+  switch (sh.k) {
+    case 1: norm_rows_kernel<XT, YT, 1, ADD><<<grid, kBlock, 0, s>>>(a, sh.g); break;
+    case 2: norm_rows_kernel<XT, YT, 2, ADD><<<grid, kBlock, 0, s>>>(a, sh.g); break;
+    case 4: norm_rows_kernel<XT, YT, 4, ADD><<<grid, kBlock, 0, s>>>(a, sh.g); break;
+    case 8: norm_rows_kernel<XT, YT, 8, ADD><<<grid, kBlock, 0, s>>>(a, sh.g); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+template <typename XT, typename YT>
+cudaError_t LaunchNormA(const NormArgs& a, cudaStream_t s) {
+  return a.delta ? LaunchNormT<XT, YT, true>(a, s) : LaunchNormT<XT, YT, false>(a, s);
+}
+
+template <typename XT>
+cudaError_t LaunchNormY(const NormArgs& a, cudaStream_t s) {
+  switch (a.y_dtype) {
+    case kF32: return LaunchNormA<XT, float>(a, s);
+    case kF16: return LaunchNormA<XT, f16>(a, s);
+    case kBF16: return LaunchNormA<XT, bf16>(a, s);
+  }
+  return cudaErrorInvalidValue;
+}
+
+template <typename OT, typename ZT, typename YT>
+cudaError_t LaunchGatedT(const GatedArgs& a, cudaStream_t s) {
+  if (!a.vec) {
+    gated_norm_scalar_kernel<OT, ZT, YT><<<a.rows, kBlock, 0, s>>>(a);
+    return cudaGetLastError();
+  }
+  const Shape sh = PickShape(a.d / 8, a.threads_per_row);
+  const unsigned rows_per_cta = kBlock / sh.g;
+  const unsigned grid = (a.rows + rows_per_cta - 1) / rows_per_cta;
+  switch (sh.k) {
+    case 1: gated_norm_kernel<OT, ZT, YT, 1><<<grid, kBlock, 0, s>>>(a, sh.g); break;
+    case 2: gated_norm_kernel<OT, ZT, YT, 2><<<grid, kBlock, 0, s>>>(a, sh.g); break;
+    case 4: gated_norm_kernel<OT, ZT, YT, 4><<<grid, kBlock, 0, s>>>(a, sh.g); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+// Largest d the vector path accepts: 256 threads x 8 octets x 8 elements.
+cudaError_t LaunchNorm(const NormArgs& a, cudaStream_t s) {
+  if (a.rows == 0) return cudaSuccess;
+  switch (a.x_dtype) {
+    case kF32: return LaunchNormY<float>(a, s);
+    case kF16: return LaunchNormY<f16>(a, s);
+    case kBF16: return LaunchNormY<bf16>(a, s);
+  }
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t LaunchGatedNorm(const GatedArgs& a, cudaStream_t s) {
+  if (a.rows == 0) return cudaSuccess;
+  const int key = a.o_dtype * 9 + a.z_dtype * 3 + a.y_dtype;
+  switch (key) {
+    case kF32 * 9 + kF32 * 3 + kF32: return LaunchGatedT<float, float, float>(a, s);
+    case kF32 * 9 + kF32 * 3 + kF16: return LaunchGatedT<float, float, f16>(a, s);
+    case kF32 * 9 + kF32 * 3 + kBF16: return LaunchGatedT<float, float, bf16>(a, s);
+    case kF32 * 9 + kF16 * 3 + kF16: return LaunchGatedT<float, f16, f16>(a, s);
+    case kF16 * 9 + kF16 * 3 + kF16: return LaunchGatedT<f16, f16, f16>(a, s);
+    case kBF16 * 9 + kBF16 * 3 + kBF16: return LaunchGatedT<bf16, bf16, bf16>(a, s);
+    case kBF16 * 9 + kBF16 * 3 + kF32: return LaunchGatedT<bf16, bf16, float>(a, s);
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace halo_b200

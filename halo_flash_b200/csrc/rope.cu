@@ -1,0 +1,233 @@
+// Partial NEOX rotary embedding for sm_100a, standalone and fused behind the
+// per-head RMSNorm. Replaces halo_rope_neox, _rows, _p, _blocks, _p_y,
+// halo_split_qgate(_y), halo_split_qgate_norm_rope and halo_norm_rope_rows
+// (src/kernels/core.hip:275-311, 356-443; src/kernels/batch_decode.hip:1679-1697);
+// arithmetic follows src/model/cpu_ops.cpp:168-185.
+//
+// The angle must be bit-identical to the CPU operator's: a one-ulp difference in
+// the inverse frequency becomes 1e-2 rad at position 262143. So the host computes
+// pow(theta, -2 i / rot) with the CPU's libm and passes the table as a kernel
+// argument; the device does the single fp32 multiply float(pos) * freq and a
+// full-range sincosf.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace halo_b200 {
+namespace {
+
+__device__ __forceinline__ uint32_t token_pos(const PosSpec& p, uint32_t t) {
+  const uint32_t base = p.params ? p.params[static_cast<size_t>(t) * p.pstride + p.slot] : p.pos0 + t;
+  return base * p.scale;
+}
+
+// Standalone, in place. A CTA owns `tpc` consecutive tokens: it first fills a
+// shared (cos, sin) table of tpc x rot/2 entries - one sincosf per token and
+// frequency instead of one per head - then rotates every head of both tensors.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(kBlock) rope_kernel(const RopeArgs a, const __grid_constant__ InvFreq f,
+                                                     const unsigned tpc) {
+  extern __shared__ float2 cs[];  // [tpc][half]
+  const uint32_t half = a.rot / 2;
+  const uint32_t t0 = blockIdx.x * tpc;
+  for (uint32_t idx = threadIdx.x; idx < tpc * half; idx += kBlock) {
+    const uint32_t t = t0 + idx / half, i = idx % half;
+    if (t < a.tokens) {
+      const uint32_t pos = token_pos(a.pos, t);
+      const float angle = __fmul_rn(static_cast<float>(pos), f.f[i]);
+      float sn, c;
+      sincosf(angle, &sn, &c);
+      cs[idx] = make_float2(c, sn);
+      if (i == 0 && a.pos_out) a.pos_out[t] = pos;
+    }
+  }
+  __syncthreads();
+  const uint32_t heads_all = a.heads + a.heads2;
+  const uint32_t per_head = VEC ? half / 8 : half;
+  const uint32_t per_token = heads_all * per_head;
+  for (uint32_t item = threadIdx.x; item < tpc * per_token; item += kBlock) {
+    const uint32_t tl = item / per_token, r = item % per_token;
+    const uint32_t t = t0 + tl;
+    if (t >= a.tokens) break;
+    const uint32_t h = r / per_head, p = r % per_head;
+    T* v = h < a.heads ? static_cast<T*>(a.x) + static_cast<size_t>(t) * a.token_stride + static_cast<size_t>(h) * a.hd
+                       : static_cast<T*>(a.x2) + static_cast<size_t>(t) * a.token_stride2 +
+                             static_cast<size_t>(h - a.heads) * a.hd;
+    const float2* tab = cs + tl * half;
+    if constexpr (VEC) {
+      float lo[8], hi[8];
+      load8(v + p * 8, lo);
+      load8(v + half + p * 8, hi);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float2 t2 = tab[p * 8 + i];
+        const float x0 = lo[i], x1 = hi[i];
+        lo[i] = x0 * t2.x - x1 * t2.y;
+        hi[i] = x0 * t2.y + x1 * t2.x;
+      }
+      store8(v + p * 8, lo);
+      store8(v + half + p * 8, hi);
+    } else {
+      const float2 t2 = tab[p];
+      const float x0 = to_f32(v[p]), x1 = to_f32(v[p + half]);
+      v[p] = from_f32<T>(x0 * t2.x - x1 * t2.y);
+      v[p + half] = from_f32<T>(x0 * t2.y + x1 * t2.x);
+    }
+  }
+}
+
+// RMSNorm (shared gamma) + RoPE on rows of d <= 256: g = d / 8 rounded up to a
+// power of two (<= 32) lanes per row, one octet per lane, shuffles only. Lane
+// `lir` < half/8 holds the first halves of 8 pairs, lane lir + half/8 their
+// partners; the two exchange their normalized values with one shuffle per element.
+template <typename IT, typename OT>
+__global__ void __launch_bounds__(kBlock) norm_rope_kernel(const NormRopeArgs a, const __grid_constant__ InvFreq f,
+                                                          const unsigned g) {
+  const unsigned lane = threadIdx.x & 31u;
+  const unsigned lir = threadIdx.x & (g - 1);
+  const uint32_t row = blockIdx.x * (kBlock / g) + threadIdx.x / g;
+  const unsigned octs = a.d >> 3;
+  const bool ok = row < a.rows && lir < octs;
+  float v[8];
+  if (ok) {
+    const IT* src = static_cast<const IT*>(a.in) + static_cast<size_t>(row) * a.in_row_stride;
+    load8(src + lir * 8, v);
+    if (a.gate) {
+      float gt[8];
+      load8(src + a.d + lir * 8, gt);
+      store8(static_cast<IT*>(a.gate) + static_cast<size_t>(row) * a.d + lir * 8, gt);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+  }
+  if (a.w) {
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+    ss = group_sum(ss, g, nullptr);  // g <= 32: shuffles only
+    const float scale = 1.0f / sqrtf(ss / static_cast<float>(a.d) + a.eps);
+    float gm[8];
+    if (ok) {
+      load8_cached(a.w + lir * 8, gm);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) gm[i] = 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = v[i] * scale * (a.one_plus ? 1.0f + gm[i] : gm[i]);
+  }
+  const unsigned hp = a.rot / 16;  // lanes per half of the rotated span
+  const bool rotates = lir < 2 * hp;
+  const bool low = lir < hp;
+  const unsigned partner = rotates ? (low ? lir + hp : lir - hp) : lir;
+  const unsigned src_lane = lane - lir + partner;
+  const uint32_t token = row / a.heads;
+  uint32_t pos = 0;
+  if (row < a.rows) {
+    pos = token_pos(a.pos, token);
+    if (a.pos_out && lir == 0 && row % a.heads == 0) a.pos_out[token] = pos;
+  }
+  const unsigned fi = (low ? lir : lir - hp) * 8;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float other = __shfl_sync(kFullMask, v[i], src_lane);
+    if (rotates) {
+      const float angle = __fmul_rn(static_cast<float>(pos), f.f[fi + i]);
+      float sn, c;
+      sincosf(angle, &sn, &c);
+      v[i] = low ? v[i] * c - other * sn : other * sn + v[i] * c;
+    }
+  }
+  if (ok) {
+    store8(static_cast<OT*>(a.out) + static_cast<size_t>(row) * a.d + lir * 8, v);
+    if (a.cache) store8(static_cast<OT*>(a.cache) + static_cast<size_t>(row) * a.d + lir * 8, v);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kBlock) split_qgate_kernel(const SplitArgs a) {
+  const size_t total = static_cast<size_t>(a.rows) * a.hd;
+  const T* qg = static_cast<const T*>(a.qg);
+  T* q = static_cast<T*>(a.q);
+  T* gate = static_cast<T*>(a.gate);
+  for (size_t idx = static_cast<size_t>(blockIdx.x) * kBlock + threadIdx.x; idx < total;
+       idx += static_cast<size_t>(gridDim.x) * kBlock) {
+    const uint32_t row = static_cast<uint32_t>(idx / a.hd), i = static_cast<uint32_t>(idx % a.hd);
+    size_t in_off = static_cast<size_t>(row) * 2 * a.hd, out_off = static_cast<size_t>(row) * a.hd;
+    if (a.rows_per_entry) {
+      const uint32_t e = row / a.rows_per_entry, r = row % a.rows_per_entry;
+      in_off = static_cast<size_t>(e) * a.qg_entry_stride + static_cast<size_t>(r) * 2 * a.hd;
+      out_off = static_cast<size_t>(e) * a.q_entry_stride + static_cast<size_t>(r) * a.hd;
+    }
+    q[out_off + i] = qg[in_off + i];
+    gate[out_off + i] = qg[in_off + a.hd + i];
+  }
+}
+
+template <typename T>
+cudaError_t LaunchRopeT(const RopeArgs& a, const InvFreq& f, cudaStream_t s) {
+  const uint32_t half = a.rot / 2;
+  const uint32_t per_token = (a.heads + a.heads2) * (a.vec ? half / 8 : half);
+  // Enough tokens per CTA for about two items per thread, bounded by the table size.
+  unsigned tpc = per_token ? (2 * kBlock + per_token - 1) / per_token : 1;
+  if (tpc < 1) tpc = 1;
+  if (tpc > 64) tpc = 64;
+  if (tpc > a.tokens) tpc = a.tokens;
+  const unsigned grid = (a.tokens + tpc - 1) / tpc;
+  const size_t smem = static_cast<size_t>(tpc) * half * sizeof(float2);
+  if (a.vec) rope_kernel<T, true><<<grid, kBlock, smem, s>>>(a, f, tpc);
+  else rope_kernel<T, false><<<grid, kBlock, smem, s>>>(a, f, tpc);
+  return cudaGetLastError();
+}
+
+template <typename IT, typename OT>
+cudaError_t LaunchNormRopeT(const NormRopeArgs& a, const InvFreq& f, cudaStream_t s) {
+  unsigned g = 1;
+  while (g < a.d / 8) g <<= 1;
+  const unsigned rows_per_cta = kBlock / g;
+  const unsigned grid = (a.rows + rows_per_cta - 1) / rows_per_cta;
+  norm_rope_kernel<IT, OT><<<grid, kBlock, 0, s>>>(a, f, g);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t LaunchRope(const RopeArgs& a, const InvFreq& f, cudaStream_t s) {
+  if (a.tokens == 0 || a.heads + a.heads2 == 0 || a.rot < 2) return cudaSuccess;
+  switch (a.dtype) {
+    case kF32: return LaunchRopeT<float>(a, f, s);
+    case kF16: return LaunchRopeT<f16>(a, f, s);
+    case kBF16: return LaunchRopeT<bf16>(a, f, s);
+  }
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t LaunchNormRope(const NormRopeArgs& a, const InvFreq& f, cudaStream_t s) {
+  if (a.rows == 0) return cudaSuccess;
+  const int key = a.in_dtype * 3 + a.out_dtype;
+  switch (key) {
+    case kF32 * 3 + kF32: return LaunchNormRopeT<float, float>(a, f, s);
+    case kF32 * 3 + kBF16: return LaunchNormRopeT<float, bf16>(a, f, s);
+    case kF32 * 3 + kF16: return LaunchNormRopeT<float, f16>(a, f, s);
+    case kBF16 * 3 + kBF16: return LaunchNormRopeT<bf16, bf16>(a, f, s);
+    case kBF16 * 3 + kF32: return LaunchNormRopeT<bf16, float>(a, f, s);
+    case kF16 * 3 + kF16: return LaunchNormRopeT<f16, f16>(a, f, s);
+  }
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t LaunchSplitQgate(const SplitArgs& a, cudaStream_t s) {
+  const size_t total = static_cast<size_t>(a.rows) * a.hd;
+  if (total == 0) return cudaSuccess;
+  size_t grid = (total + kBlock - 1) / kBlock;
+  if (grid > 148u * 16u) grid = 148u * 16u;
+  switch (a.dtype) {
+    case kF32: split_qgate_kernel<float><<<static_cast<unsigned>(grid), kBlock, 0, s>>>(a); break;
+    case kF16: split_qgate_kernel<f16><<<static_cast<unsigned>(grid), kBlock, 0, s>>>(a); break;
+    case kBF16: split_qgate_kernel<bf16><<<static_cast<unsigned>(grid), kBlock, 0, s>>>(a); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace halo_b200

@@ -1,0 +1,153 @@
+"""Tensor-level front end of the C ABI: the five op groups on torch CUDA tensors.
+
+torch is plumbing here (device memory and the current stream); every function
+forwards to one `halo_b200_*` entry point of libhalo_b200.so and nothing else.
+CPU tensors are rejected: the CUDA library is the only implementation.
+
+Conventions follow the reference kernels (src/kernels/core.hip): rows are the
+leading dimensions flattened, the last dimension is `d`; in-place is the
+default where the reference kernel is in-place.
+"""
+from __future__ import annotations
+
+import torch
+
+from ._lib import BF16, F16, F32, lib
+
+_DT = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _chk(t: torch.Tensor | None, name: str, dtypes=None):
+    if t is None:
+        return None
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise TypeError(f"{name}: expected a CUDA tensor (halo_flash_b200 has no CPU path)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name}: tensor must be contiguous")
+    if dtypes is not None and t.dtype not in dtypes:
+        raise TypeError(f"{name}: dtype {t.dtype} not in {dtypes}")
+    return t
+
+
+def _p(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}") from None
+
+
+_ACT = (torch.float32, torch.float16, torch.bfloat16)
+
+
+# ---- group 1 ---------------------------------------------------------------
+def rmsnorm(x, w, eps, *, y=None, one_plus=False, w_stride=0, w_period=1):
+    """y = x * rsqrt(mean(x^2) + eps) * g per row, g = w or 1 + w. y defaults to x (in place)."""
+    _chk(x, "x", _ACT), _chk(w, "w", (torch.float32,))
+    y = x if y is None else _chk(y, "y", _ACT)
+    d = x.shape[-1]
+    rows = x.numel() // d if d else 0
+    lib().call("rmsnorm_ex", _stream(), _p(x), _code(x), _p(w), _p(y), _code(y), d, eps, w_stride, w_period,
+               int(one_plus), rows)
+    return y
+
+
+def add_rmsnorm(res, delta, w, eps, *, one_plus=True, xn=None, q8_0=None, xq=None, xd=None):
+    """res += delta (stored in res' dtype); then RMSNorm of the stored rows into any of
+    xn (fp32/fp16/bf16), q8_0 (uint8 [rows, d/32*34]), xq/xd (int8 codes + fp32 scales)."""
+    _chk(res, "res", _ACT), _chk(delta, "delta", (res.dtype,)), _chk(w, "w", (torch.float32,))
+    _chk(xn, "xn", _ACT), _chk(q8_0, "q8_0", (torch.uint8,)), _chk(xq, "xq", (torch.int8,))
+    _chk(xd, "xd", (torch.float32,))
+    d = res.shape[-1]
+    rows = res.numel() // d if d else 0
+    lib().call("add_rmsnorm", _stream(), _p(res), _p(delta), _code(res), _p(w), int(one_plus), _p(xn),
+               _code(xn) if xn is not None else F32, _p(q8_0), _p(xq), _p(xd), d, eps, rows)
+    return xn
+
+
+def encode_q8_0(x, out):
+    """Q8_0 rows (34-byte blocks) of x [rows, cols] into out uint8 [rows, cols/32*34]."""
+    _chk(x, "x", _ACT), _chk(out, "out", (torch.uint8,))
+    cols = x.shape[-1]
+    lib().call("encode_q8_0_rows", _stream(), _p(x), _code(x), _p(out), cols, x.numel() // cols if cols else 0)
+    return out
+
+
+def quantize_q8_rows(x, xq, xd):
+    _chk(x, "x", (torch.float32,)), _chk(xq, "xq", (torch.int8,)), _chk(xd, "xd", (torch.float32,))
+    cols = x.shape[-1]
+    lib().call("quantize_q8_rows", _stream(), _p(x), _p(xq), _p(xd), cols, x.numel() // cols if cols else 0)
+    return xq, xd
+
+
+# ---- group 2 ---------------------------------------------------------------
+def l2norm(x, eps, *, y=None):
+    """y = x * rsqrt(sum(x^2) + eps) per row (eps inside the root, on the sum)."""
+    _chk(x, "x", _ACT)
+    y = x if y is None else _chk(y, "y", _ACT)
+    d = x.shape[-1]
+    lib().call("l2norm_ex", _stream(), _p(x), _code(x), _p(y), _code(y), d, eps, x.numel() // d if d else 0)
+    return y
+
+
+def gated_norm(o, w, z, eps, *, mode=0, y=None):
+    """y = RMSNorm(o; plain weight w[d]) * SiLU(z) (mode 0) or * sigmoid(z) (mode 1), per head row."""
+    _chk(o, "o", _ACT), _chk(z, "z", _ACT), _chk(w, "w", (torch.float32,))
+    y = o if y is None else _chk(y, "y", _ACT)
+    d = o.shape[-1]
+    lib().call("gated_norm_ex", _stream(), _p(o), _code(o), _p(w), _p(z), _code(z), _p(y), _code(y), d, eps, mode,
+               o.numel() // d if d else 0)
+    return y
+
+
+# ---- group 3 ---------------------------------------------------------------
+def rope(q, k, rot, theta, *, pos0=0, params=None, pstride=0, slot=0, scale=1, pos_out=None):
+    """In-place partial NEOX RoPE on q [T, Hq, hd] and optionally k [T, Hk, hd].
+    Token t rotates at (params[t*pstride+slot] if params is given else pos0 + t) * scale."""
+    _chk(q, "q", _ACT), _chk(k, "k", (q.dtype,)), _chk(params, "params", (torch.int32, torch.uint32))
+    _chk(pos_out, "pos_out", (torch.int32, torch.uint32))
+    tokens, hq, hd = q.shape
+    hk = 0 if k is None else k.shape[1]
+    lib().call("rope_ex", _stream(), _p(q), hq, _p(k), hk, _code(q), hd, rot, theta, tokens, _p(params), pstride, slot,
+               pos0, scale, _p(pos_out))
+    return q, k
+
+
+def norm_rope(x, w, eps, rot, theta, heads, *, out=None, gate=None, cache=None, one_plus=True, in_row_stride=None,
+              pos0=0, params=None, pstride=0, slot=0, scale=1, pos_out=None):
+    """Per-head RMSNorm (gamma w or 1 + w) fused with RoPE on rows [T * heads, d]."""
+    _chk(x, "x", _ACT), _chk(w, "w", (torch.float32,))
+    out = x if out is None else _chk(out, "out", _ACT)
+    _chk(gate, "gate", (x.dtype,)), _chk(cache, "cache", (out.dtype,))
+    d = out.shape[-1]
+    rows = out.numel() // d if d else 0
+    stride = d if in_row_stride is None else in_row_stride
+    lib().call("norm_rope_ex", _stream(), _p(x), _code(x), stride, _p(out), _code(out), _p(gate), _p(cache), _p(w),
+               int(one_plus), eps, d, rot, heads, rows, theta, _p(params), pstride, slot, pos0, scale, _p(pos_out))
+    return out
+
+
+# ---- group 4 ---------------------------------------------------------------
+def silu_mul(g, up, *, y=None):
+    """y = SiLU(g) * up elementwise; y defaults to g (in place)."""
+    _chk(g, "g", _ACT), _chk(up, "up", (g.dtype,))
+    y = g if y is None else _chk(y, "y", _ACT)
+    lib().call("silu_mul_ex", _stream(), _p(g), _p(up), _code(g), _p(y), _code(y), g.numel())
+    return y
+
+
+# ---- group 5 ---------------------------------------------------------------
+def embed_q8_0(table, ids, cols, out, *, id_stride=1, id_slot=0, vocab=0):
+    """out[t] = dequant(table[ids[t*id_stride + id_slot]]); table uint8 [vocab, cols/32*34]."""
+    _chk(table, "table", (torch.uint8,)), _chk(ids, "ids", (torch.int32, torch.uint32)), _chk(out, "out", _ACT)
+    tokens = out.numel() // cols if cols else 0
+    lib().call("embed_q8_0_ex", _stream(), _p(table), table.shape[-1], vocab, _p(ids), id_stride, id_slot, tokens,
+               _p(out), _code(out), cols)
+    return out

@@ -1,0 +1,267 @@
+/* halo_b200: B200 (sm_100a) replacements for halo-flash's fused per-layer
+ * elementwise kernels, behind a C ABI.
+ *
+ * halo-flash's engine never links kernels: it looks a kernel up by name
+ * (rt::Device::Kernel, src/rt/device.hpp:120) and launches it with a grid, a block
+ * and an ordered argument list (rt::Device::Launch, src/rt/device.hpp:127; pointer
+ * parameters are buffers, everything else a by-value scalar, device.hpp:8-11).
+ * Each function below replaces one such kernel entry point of src/kernels/core.hip
+ * or src/kernels/batch_decode.hip. It keeps the kernel's name and its parameter
+ * list in the kernel's own order, and adds
+ *   - the stream first (the engine's single stream, src/rt/hip_device.cpp:49-50),
+ *   - the row / batch counts the reference passes through its grid dimensions,
+ *   - the error out-parameters of the repository's C ABIs
+ *     (include/halo_variant.h:12-13).
+ * Launch geometry is this library's own; a caller's block size is irrelevant.
+ * halo_b200_launch() takes the reference's (name, grid, block, args) call as is.
+ *
+ * Contract
+ *   - Returns 0 on success, -1 on failure with a NUL-terminated message in err
+ *     (truncated to errlen; err may be NULL).
+ *   - All pointers are device pointers owned by the caller. Nothing is allocated,
+ *     no state is kept, nothing synchronizes: every call only enqueues kernels on
+ *     `stream` and may be recorded by CUDA stream capture.
+ *   - In-place use is allowed wherever the reference kernel works in place.
+ *   - Buffers that are 16-byte aligned with row lengths that are multiples of 8
+ *     elements take the vector kernels; anything else takes a slower scalar
+ *     kernel with identical results. Q8 outputs need cols % 32 == 0.
+ *   - No CPU fallback exists: without a CUDA device every call fails.
+ *   - Thread-compatible: concurrent calls on different streams are fine.
+ *
+ * Numerics: fp32 arithmetic in the evaluation order of the CPU operators
+ * (src/model/cpu_ops.cpp), IEEE division/sqrt, no fused multiply-add; 16-bit
+ * outputs are rounded once from the fp32 result, to nearest even.
+ */
+#ifndef HALO_B200_H_
+#define HALO_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* halo_b200_stream; /* a cudaStream_t; NULL is the default stream */
+
+enum halo_b200_dtype { HALO_B200_F32 = 0, HALO_B200_F16 = 1, HALO_B200_BF16 = 2 };
+
+/* Version string of the library, e.g. "halo_b200 0.1 sm_100a". */
+const char* halo_b200_version(void);
+
+/* ---- group 1: residual add, RMSNorm, Q8 re-quantise ------------------------------ */
+
+/* halo_add, src/kernels/core.hip:313-315: y[i] += x[i]. */
+int halo_b200_add(halo_b200_stream stream, float* y, const float* x, uint32_t n, char* err, size_t errlen);
+/* halo_axpy, src/kernels/core.hip:317-319: y[i] += a * x[i]. */
+int halo_b200_axpy(halo_b200_stream stream, float* y, const float* x, float a, uint32_t n, char* err, size_t errlen);
+
+/* halo_rmsnorm, src/kernels/core.hip:247-262: nvec vectors of length d (grid.x in the
+ * reference); vector b uses gamma w_all + b * w_stride (0 = shared). x == y allowed. */
+int halo_b200_rmsnorm(halo_b200_stream stream, const float* x, const float* w_all, float* y, uint32_t d, float eps,
+                      uint32_t w_stride, uint32_t nvec, char* err, size_t errlen);
+/* halo_rmsnorm_rows, src/kernels/core.hip:4045-4056: row r uses gamma (r % w_period) * w_stride.
+ * _r16 / _rb (core.hip:4070-4077) read fp16 / bf16 rows and write fp32. rows = grid.x. */
+int halo_b200_rmsnorm_rows(halo_b200_stream stream, const float* x, const float* w_all, float* y, uint32_t d,
+                           float eps, uint32_t w_stride, uint32_t w_period, uint32_t rows, char* err, size_t errlen);
+int halo_b200_rmsnorm_rows_r16(halo_b200_stream stream, const uint16_t* x, const float* w_all, float* y, uint32_t d,
+                               float eps, uint32_t w_stride, uint32_t w_period, uint32_t rows, char* err,
+                               size_t errlen);
+int halo_b200_rmsnorm_rows_rb(halo_b200_stream stream, const uint16_t* x, const float* w_all, float* y, uint32_t d,
+                              float eps, uint32_t w_stride, uint32_t w_period, uint32_t rows, char* err,
+                              size_t errlen);
+/* halo_rmsnorm_rows_h (+ _r16, _rb), src/kernels/core.hip:4502-4552: also writes an fp16
+ * copy y16, row-major or (y16_tokens > 0) K-blocked [cols / 64][y16_tokens][64]. The fused
+ * inject partial products (iw / ipart / irows) belong to Flash-Next's hyper-connection
+ * mixer and are not implemented: iw must be NULL. x_dtype selects the variant. */
+int halo_b200_rmsnorm_rows_h(halo_b200_stream stream, const void* x, int x_dtype, const float* w_all, float* y,
+                             uint16_t* y16, uint32_t d, float eps, uint32_t w_stride, uint32_t w_period,
+                             const float* iw, float* ipart, uint32_t irows, uint32_t y16_tokens, uint32_t rows,
+                             char* err, size_t errlen);
+/* halo_rmsnorm_y, src/kernels/batch_decode.hip:1685-1691: in place, entry e (grid.y) at
+ * x + e * stride, nvec vectors (grid.x) per entry. */
+int halo_b200_rmsnorm_y(halo_b200_stream stream, float* x, const float* w_all, uint32_t d, float eps,
+                        uint32_t w_stride, uint32_t stride, uint32_t nvec, uint32_t batch, char* err, size_t errlen);
+
+/* Typed RMSNorm: x_dtype rows in, y_dtype rows out, gamma = w or (one_plus) 1 + w, the
+ * zero-centred form the GGUF converter folds into the stored weight
+ * (src/model/qwen35.cpp:55-58). w may be NULL (raw scale). */
+int halo_b200_rmsnorm_ex(halo_b200_stream stream, const void* x, int x_dtype, const float* w, void* y, int y_dtype,
+                         uint32_t d, float eps, uint32_t w_stride, uint32_t w_period, int one_plus, uint32_t rows,
+                         char* err, size_t errlen);
+
+/* Fused residual add + RMSNorm with optional Q8 epilogues: one pass over
+ *   res[r] += delta[r]            (stored back in res_dtype; the norm reads the stored value,
+ *                                  as src/kernels/core.hip:4132-4135 does for 16-bit residuals)
+ *   xn[r]   = res[r] * scale * g  (g = w or 1 + w; src/model/qwen35.cpp:319-329)
+ * Outputs, each optional (NULL to skip) but at least one present: xn in xn_dtype; xn_q8_0 =
+ * Q8_0 rows of the fp32 xn (d / 32 blocks of 34 bytes, src/core/lowbit.cpp:285-298); xq / xd =
+ * int8 codes + fp32 scales per 32 values (src/kernels/core.hip:4160-4170), row-major.
+ * This is the add + norm fusion of halo_hc_combine_norm_rows(_q8) (core.hip:4105-4238)
+ * for a plain residual stream. delta NULL skips the add (res is then read only). */
+int halo_b200_add_rmsnorm(halo_b200_stream stream, void* res, const void* delta, int res_dtype, const float* w,
+                          int one_plus, void* xn, int xn_dtype, uint8_t* xn_q8_0, int8_t* xq, float* xd, uint32_t d,
+                          float eps, uint32_t rows, char* err, size_t errlen);
+
+/* halo_quantize_q8_rows, src/kernels/core.hip:3086-3101 (rows = grid.x). */
+int halo_b200_quantize_q8_rows(halo_b200_stream stream, const float* x, int8_t* xq, float* xd, uint32_t cols,
+                               uint32_t rows, char* err, size_t errlen);
+/* halo_quantize_q8_kblocked, src/kernels/core.hip:3313-3331 (grid.x = tokens). */
+int halo_b200_quantize_q8_kblocked(halo_b200_stream stream, const float* x, int8_t* xq, float* xd, uint32_t cols,
+                                   uint32_t tokens, char* err, size_t errlen);
+/* halo_q8x_cols, src/kernels/batch_decode.hip:197-222 (batch = grid.y); xq2 / xs2 may be NULL. */
+int halo_b200_q8x_cols(halo_b200_stream stream, const float* x, uint32_t xstride, uint32_t cols, int8_t* xq,
+                       float* xs, int8_t* xq2, float* xs2, uint32_t batch, char* err, size_t errlen);
+/* EncodeQ8_0, src/core/lowbit.cpp:285-298, as a device op over rows of x_dtype values. */
+int halo_b200_encode_q8_0_rows(halo_b200_stream stream, const void* x, int x_dtype, uint8_t* out, uint32_t cols,
+                               uint32_t rows, char* err, size_t errlen);
+
+/* ---- group 2: L2 norm and gated RMSNorm -------------------------------------------- */
+
+/* halo_l2norm, src/kernels/core.hip:264-273: in place, nvec vectors (grid.x). */
+int halo_b200_l2norm(halo_b200_stream stream, float* x, uint32_t d, float eps, uint32_t nvec, char* err,
+                     size_t errlen);
+int halo_b200_l2norm_ex(halo_b200_stream stream, const void* x, int x_dtype, void* y, int y_dtype, uint32_t d,
+                        float eps, uint32_t rows, char* err, size_t errlen);
+
+/* halo_gated_norm, src/kernels/core.hip:495-510: in place on o, rows = grid.x heads. mode 0 =
+ * SiLU(z) (src/model/qwen35.cpp:232-234), 1 = sigmoid(z) (src/model/reference.cpp:359-363). */
+int halo_b200_gated_norm(halo_b200_stream stream, float* o, const float* w, const float* z, uint32_t d, float eps,
+                         uint32_t mode, uint32_t rows, char* err, size_t errlen);
+/* halo_gated_norm_h / _hz, src/kernels/core.hip:4554-4585: fp16 output only; _hz reads fp16 z. */
+int halo_b200_gated_norm_h(halo_b200_stream stream, const float* o, const float* w, const float* z, uint16_t* y16,
+                           uint32_t d, float eps, uint32_t mode, uint32_t rows, char* err, size_t errlen);
+int halo_b200_gated_norm_hz(halo_b200_stream stream, const float* o, const float* w, const uint16_t* z,
+                            uint16_t* y16, uint32_t d, float eps, uint32_t mode, uint32_t rows, char* err,
+                            size_t errlen);
+/* halo_gated_norm_h128w / _h128w_hh, src/kernels/core.hip:4587-4632: d = 128, rows is a parameter. */
+int halo_b200_gated_norm_h128w(halo_b200_stream stream, const float* o, const float* w, const float* z,
+                               uint16_t* y16, uint32_t rows, float eps, uint32_t mode, char* err, size_t errlen);
+int halo_b200_gated_norm_h128w_hh(halo_b200_stream stream, const uint16_t* o, const float* w, const uint16_t* z,
+                                  uint16_t* y16, uint32_t rows, float eps, uint32_t mode, char* err, size_t errlen);
+/* Typed form. Supported (o, z, y) dtypes: (f32,f32,f32|f16|bf16), (f32,f16,f16), (f16,f16,f16),
+ * (bf16,bf16,bf16|f32). y may alias o when the dtypes match. */
+int halo_b200_gated_norm_ex(halo_b200_stream stream, const void* o, int o_dtype, const float* w, const void* z,
+                            int z_dtype, void* y, int y_dtype, uint32_t d, float eps, uint32_t mode, uint32_t rows,
+                            char* err, size_t errlen);
+
+/* ---- group 3: partial rotary embedding (NEOX pairs i, i + rot/2) ------------------- */
+
+/* halo_rope_neox, src/kernels/core.hip:289-292: heads = grid.x, all at position pos. */
+int halo_b200_rope_neox(halo_b200_stream stream, float* x, uint32_t head_dim, uint32_t rotary_dim, uint32_t pos,
+                        float theta, uint32_t heads, char* err, size_t errlen);
+/* halo_rope_neox_rows, src/kernels/core.hip:293-298: rows = grid.x = T * heads, token t at pos0 + t. */
+int halo_b200_rope_neox_rows(halo_b200_stream stream, float* x, uint32_t head_dim, uint32_t rotary_dim,
+                             uint32_t pos0, uint32_t heads, float theta, uint32_t rows, char* err, size_t errlen);
+/* halo_rope_neox_p, src/kernels/core.hip:299-304: position params[slot] * scale read on the device. */
+int halo_b200_rope_neox_p(halo_b200_stream stream, float* x, const uint32_t* params, uint32_t head_dim,
+                          uint32_t rotary_dim, uint32_t slot, uint32_t scale, float theta, uint32_t heads, char* err,
+                          size_t errlen);
+/* halo_rope_neox_blocks, src/kernels/core.hip:306-311: block b (grid.x) at (b0 + b) * ratio. */
+int halo_b200_rope_neox_blocks(halo_b200_stream stream, float* x, uint32_t head_dim, uint32_t rotary_dim,
+                               uint32_t b0, uint32_t ratio, float theta, uint32_t nblocks, char* err, size_t errlen);
+/* halo_rope_neox_p_y, src/kernels/batch_decode.hip:1693-1697: entry e (grid.y) at x + e * stride
+ * with params + e * pstride. */
+int halo_b200_rope_neox_p_y(halo_b200_stream stream, float* x, const uint32_t* params, uint32_t head_dim,
+                            uint32_t rotary_dim, uint32_t slot, uint32_t scale, float theta, uint32_t stride,
+                            uint32_t pstride, uint32_t heads, uint32_t batch, char* err, size_t errlen);
+/* Typed form rotating Q [tokens][q_heads][hd] and (optionally, k may be NULL) K
+ * [tokens][k_heads][hd] in one launch. Token t rotates at
+ * (params ? params[t * pstride + slot] : pos0 + t) * scale. pos_out (optional, [tokens])
+ * receives the position each token used. rotary_dim <= 256. */
+int halo_b200_rope_ex(halo_b200_stream stream, void* q, uint32_t q_heads, void* k, uint32_t k_heads, int dtype,
+                      uint32_t head_dim, uint32_t rotary_dim, float theta, uint32_t tokens, const uint32_t* params,
+                      uint32_t pstride, uint32_t slot, uint32_t pos0, uint32_t scale, uint32_t* pos_out, char* err,
+                      size_t errlen);
+
+/* halo_split_qgate, src/kernels/core.hip:356-366 (rows = grid.x), and halo_split_qgate_y,
+ * src/kernels/batch_decode.hip:1680-1684 (heads = grid.x, batch = grid.y). */
+int halo_b200_split_qgate(halo_b200_stream stream, const float* qg, float* q, float* gate, uint32_t hd,
+                          uint32_t rows, char* err, size_t errlen);
+int halo_b200_split_qgate_y(halo_b200_stream stream, const float* qg, float* q, float* gate, uint32_t hd,
+                            uint32_t qg_stride, uint32_t q_stride, uint32_t heads, uint32_t batch, char* err,
+                            size_t errlen);
+/* halo_split_qgate_norm_rope, src/kernels/core.hip:368-405: hd is the reference's block size,
+ * rows = grid.x = T * heads; gate may be NULL. */
+int halo_b200_split_qgate_norm_rope(halo_b200_stream stream, const float* qg, float* q, float* gate, const float* w,
+                                    float eps, uint32_t rotary_dim, uint32_t pos0, uint32_t heads, float theta,
+                                    uint32_t hd, uint32_t rows, char* err, size_t errlen);
+/* halo_norm_rope_rows, src/kernels/core.hip:407-443: in place, d <= 256, cache may be NULL. */
+int halo_b200_norm_rope_rows(halo_b200_stream stream, float* x, const float* w, float eps, uint32_t d,
+                             uint32_t rotary_dim, uint32_t pos0, uint32_t heads, float theta, float* cache,
+                             uint32_t rows, char* err, size_t errlen);
+/* Typed fused per-head RMSNorm + RoPE. in rows are in_row_stride elements apart (d, or 2 * d
+ * for interleaved q|gate rows, whose second half is copied to `gate` when given); out may alias
+ * in when in_row_stride == d. w NULL skips the norm. d <= 256 and a multiple of 8. */
+int halo_b200_norm_rope_ex(halo_b200_stream stream, const void* in, int in_dtype, uint64_t in_row_stride, void* out,
+                           int out_dtype, void* gate, void* cache, const float* w, int one_plus, float eps,
+                           uint32_t d, uint32_t rotary_dim, uint32_t heads, uint32_t rows, float theta,
+                           const uint32_t* params, uint32_t pstride, uint32_t slot, uint32_t pos0, uint32_t scale,
+                           uint32_t* pos_out, char* err, size_t errlen);
+
+/* ---- group 4: SwiGLU ----------------------------------------------------------------- */
+
+/* halo_silu_mul, src/kernels/core.hip:321-325: g = SiLU(g) * up. */
+int halo_b200_silu_mul(halo_b200_stream stream, float* g, const float* up, uint32_t n, char* err, size_t errlen);
+/* halo_silu_mul_h, src/kernels/core.hip:326-333: fp16 output only. */
+int halo_b200_silu_mul_h(halo_b200_stream stream, const float* g, const float* up, uint16_t* y, uint32_t n, char* err,
+                         size_t errlen);
+/* Typed form over n elements (rows x ff flattened; routed-expert rows are (token, slot) pairs,
+ * pair = t * k + slot, src/kernels/core.hip:4718-4722). (in, y) dtypes: (f32, f32|f16|bf16),
+ * (f16,f16), (bf16, bf16|f32). y may alias g when the dtypes match. */
+int halo_b200_silu_mul_ex(halo_b200_stream stream, const void* g, const void* up, int in_dtype, void* y, int y_dtype,
+                          uint64_t n, char* err, size_t errlen);
+/* halo_sigmoid_gate, src/kernels/core.hip:335-339: x *= sigmoid(gate). */
+int halo_b200_sigmoid_gate(halo_b200_stream stream, float* x, const float* gate, uint32_t n, char* err,
+                           size_t errlen);
+
+/* ---- group 5: token-embedding gather with Q8_0 dequant -------------------------------- */
+
+/* halo_matvec_q8_0_embed, _embed_p, _embed_rows, src/kernels/core.hip:200-232. _embed_p reads the
+ * token from params[kHaloToken] (slot 0, src/kernels/step_params.h:7-8); _embed_rows reads token t
+ * from params[t * 16 + kHaloToken] and writes row t (tokens = grid.y). fp32 output. */
+int halo_b200_matvec_q8_0_embed(halo_b200_stream stream, const uint8_t* w, float* out, uint32_t token, uint32_t cols,
+                                uint64_t row_bytes, char* err, size_t errlen);
+int halo_b200_matvec_q8_0_embed_p(halo_b200_stream stream, const uint8_t* w, float* out, const uint32_t* params,
+                                  uint32_t cols, uint64_t row_bytes, char* err, size_t errlen);
+int halo_b200_matvec_q8_0_embed_rows(halo_b200_stream stream, const uint8_t* w, float* out, const uint32_t* params,
+                                     uint32_t cols, uint64_t row_bytes, uint32_t tokens, char* err, size_t errlen);
+/* Typed form: token t from ids[t * id_stride + id_slot], out in out_dtype. vocab > 0 guards the
+ * gather: an id >= vocab yields a zero row instead of an out-of-range read. */
+int halo_b200_embed_q8_0_ex(halo_b200_stream stream, const uint8_t* w, uint64_t row_bytes, uint32_t vocab,
+                            const uint32_t* ids, uint32_t id_stride, uint32_t id_slot, uint32_t tokens, void* out,
+                            int out_dtype, uint32_t cols, char* err, size_t errlen);
+
+/* ---- launch by kernel name -------------------------------------------------------------- */
+
+/* One launch argument, as rt::Arg (src/rt/device.hpp:35-59): a device pointer (buffer base +
+ * byte offset already added) or a by-value scalar of <= 8 bytes. A NULL optional pointer may be
+ * passed either way (the engine passes Arg::Val<uint64_t>(0), src/engine/prefill_chunk.cpp:384). */
+typedef struct halo_b200_arg {
+  uint32_t is_buffer; /* 1: `ptr` is a device pointer; 0: scalar in `bytes` */
+  uint32_t size;      /* scalar size in bytes (1..8); ignored for buffers */
+  union {
+    void* ptr;
+    uint8_t bytes[8];
+  } v;
+} halo_b200_arg;
+
+/* Runs the replacement of reference kernel `name` ("halo_rmsnorm_rows", ...) given the
+ * reference's own launch: its argument list, grid and block. Row and batch counts are decoded
+ * from `grid` exactly as the reference kernel reads blockIdx; `block` is only used where the
+ * reference derives a size from it (halo_split_qgate_norm_rope: hd = block[0]). */
+int halo_b200_launch(halo_b200_stream stream, const char* name, const halo_b200_arg* args, size_t nargs,
+                     const uint32_t grid[3], const uint32_t block[3], char* err, size_t errlen);
+/* Names halo_b200_launch accepts. */
+size_t halo_b200_kernel_count(void);
+const char* halo_b200_kernel_name(size_t index);
+
+/* Tuning hook for experiments (process-wide, not for production dispatch): threads per row
+ * of the norm kernels; 0 restores the built-in choice. Must be a power of two <= 256. */
+int halo_b200_tune_norm_threads_per_row(int threads);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* HALO_B200_H_ */
