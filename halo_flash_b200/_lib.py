@@ -64,7 +64,7 @@ SIGNATURES: dict[str, list] = {
 
 # Entry points with other calling shapes.
 OTHER_EXPORTS = ["halo_b200_version", "halo_b200_launch", "halo_b200_kernel_count", "halo_b200_kernel_name",
-                 "halo_b200_tune_norm_threads_per_row"]
+                 "halo_b200_tune"]
 
 
 class HaloArgValue(C.Union):
@@ -100,8 +100,8 @@ class Library:
         self.cdll.halo_b200_kernel_count.argtypes = []
         self.cdll.halo_b200_kernel_name.restype = C.c_char_p
         self.cdll.halo_b200_kernel_name.argtypes = [_sz]
-        self.cdll.halo_b200_tune_norm_threads_per_row.restype = C.c_int
-        self.cdll.halo_b200_tune_norm_threads_per_row.argtypes = [C.c_int]
+        self.cdll.halo_b200_tune.restype = C.c_int
+        self.cdll.halo_b200_tune.argtypes = [C.c_char_p, C.c_int]
         self.cdll.halo_b200_launch.restype = C.c_int
         self.cdll.halo_b200_launch.argtypes = [_p, C.c_char_p, C.POINTER(HaloArg), _sz, C.POINTER(C.c_uint32 * 3),
                                                C.POINTER(C.c_uint32 * 3), C.c_char_p, _sz]
@@ -109,6 +109,10 @@ class Library:
 
     def version(self) -> str:
         return self.cdll.halo_b200_version().decode()
+
+    def tune(self, key: str, value: int) -> None:
+        if self.cdll.halo_b200_tune(key.encode(), value) != 0:
+            raise HaloError(f"halo_b200_tune: bad key or value ({key}={value})")
 
     def kernel_names(self) -> list[str]:
         return [self.cdll.halo_b200_kernel_name(i).decode() for i in range(self.cdll.halo_b200_kernel_count())]

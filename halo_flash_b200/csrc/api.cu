@@ -15,6 +15,7 @@ using namespace halo_b200;
 namespace {
 
 std::atomic<int> g_norm_threads_per_row{0};
+std::atomic<int> g_norm_short_rows_k1{0};
 
 int Fail(char* err, size_t errlen, const char* fmt, ...) {
   if (err && errlen) {
@@ -53,6 +54,7 @@ bool FillInvFreq(InvFreq* f, uint32_t rot, float theta) {
 }
 
 int RunNorm(NormArgs a, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+  if (a.rows == 0) return Done(cudaSuccess, what, err, errlen);  // an empty chunk is a no-op
   REQUIRE(a.x != nullptr, "%s: x is null", what);
   REQUIRE(a.d > 0, "%s: d is 0", what);
   REQUIRE(ValidDType(a.x_dtype) && ValidDType(a.y_dtype), "%s: unknown dtype", what);
@@ -69,6 +71,7 @@ int RunNorm(NormArgs a, const char* what, halo_b200_stream stream, char* err, si
               Aligned(a.y16, 2) && Aligned(a.xd, 4) && Aligned(a.rscale, 4),
           "%s: pointer not aligned to its element type", what);
   a.threads_per_row = g_norm_threads_per_row.load(std::memory_order_relaxed);
+  if (g_norm_short_rows_k1.load(std::memory_order_relaxed)) a.short_rows_k1 = 1;
   bool vec = a.d % 8 == 0 && a.d <= 256u * 8u * 8u && Aligned(a.x, 16) && Aligned(a.y, 16) && Aligned(a.delta, 16) &&
              Aligned(a.res, 16) && Aligned(a.y16, 16) && Aligned(a.w, 16) && a.w_stride % 4 == 0 &&
              Aligned(a.xq, 8) && a.entry_stride % 8 == 0;
@@ -82,6 +85,7 @@ int RunNorm(NormArgs a, const char* what, halo_b200_stream stream, char* err, si
 }
 
 int RunGated(GatedArgs a, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+  if (a.rows == 0) return Done(cudaSuccess, what, err, errlen);  // an empty chunk is a no-op
   REQUIRE(a.o && a.z && a.w && a.y, "%s: null pointer", what);
   REQUIRE(a.d > 0, "%s: d is 0", what);
   REQUIRE(ValidDType(a.o_dtype) && ValidDType(a.z_dtype) && ValidDType(a.y_dtype), "%s: unknown dtype", what);
@@ -91,12 +95,16 @@ int RunGated(GatedArgs a, const char* what, halo_b200_stream stream, char* err, 
           "%s: pointer not aligned to its element type", what);
   a.vec = a.d % 8 == 0 && a.d <= 256u * 8u * 4u && Aligned(a.o, 16) && Aligned(a.z, 16) && Aligned(a.y, 16) &&
           Aligned(a.w, 16);
+  a.threads_per_row = g_norm_threads_per_row.load(std::memory_order_relaxed);
+  a.short_rows_k1 = g_norm_short_rows_k1.load(std::memory_order_relaxed);
+  if (a.threads_per_row && (a.d / 8 + a.threads_per_row - 1) / a.threads_per_row > 4) a.threads_per_row = 0;
   const cudaError_t e = LaunchGatedNorm(a, S(stream));
   if (e == cudaErrorInvalidValue) return Fail(err, errlen, "%s: unsupported (o, z, y) dtype combination", what);
   return Done(e, what, err, errlen);
 }
 
 int RunRope(RopeArgs a, float theta, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+  if (a.tokens == 0 || a.heads + a.heads2 == 0) return Done(cudaSuccess, what, err, errlen);  // an empty chunk is a no-op
   REQUIRE(a.x != nullptr, "%s: x is null", what);
   REQUIRE(ValidDType(a.dtype), "%s: unknown dtype", what);
   REQUIRE(a.rot % 2 == 0 && a.rot <= a.hd, "%s: rotary_dim %u must be even and <= head_dim %u", what, a.rot, a.hd);
@@ -112,6 +120,7 @@ int RunRope(RopeArgs a, float theta, const char* what, halo_b200_stream stream, 
 }
 
 int RunElt(EltArgs a, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+  if (a.n == 0) return Done(cudaSuccess, what, err, errlen);  // an empty chunk is a no-op
   REQUIRE(a.a && a.b && a.y, "%s: null pointer", what);
   REQUIRE(ValidDType(a.in_dtype) && ValidDType(a.y_dtype), "%s: unknown dtype", what);
   REQUIRE(Aligned(a.a, DTypeSize(a.in_dtype)) && Aligned(a.b, DTypeSize(a.in_dtype)) &&
@@ -124,6 +133,7 @@ int RunElt(EltArgs a, const char* what, halo_b200_stream stream, char* err, size
 }
 
 int RunEmbed(EmbedArgs a, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+  if (a.tokens == 0) return Done(cudaSuccess, what, err, errlen);  // an empty chunk is a no-op
   REQUIRE(a.table && a.out, "%s: null pointer", what);
   REQUIRE(ValidDType(a.out_dtype), "%s: unknown dtype", what);
   REQUIRE(a.cols % 32 == 0, "%s: Q8_0 rows need cols %% 32 == 0 (cols = %u)", what, a.cols);
@@ -136,6 +146,7 @@ int RunEmbed(EmbedArgs a, const char* what, halo_b200_stream stream, char* err, 
 }
 
 int RunQuant(QuantArgs a, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+  if (a.rows == 0) return Done(cudaSuccess, what, err, errlen);  // an empty chunk is a no-op
   REQUIRE(a.x != nullptr, "%s: x is null", what);
   REQUIRE(ValidDType(a.x_dtype), "%s: unknown dtype", what);
   REQUIRE(a.q8_0 || a.xq, "%s: no output", what);
@@ -151,6 +162,7 @@ int RunQuant(QuantArgs a, const char* what, halo_b200_stream stream, char* err, 
 }
 
 int RunNormRope(NormRopeArgs a, float theta, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+  if (a.rows == 0) return Done(cudaSuccess, what, err, errlen);  // an empty chunk is a no-op
   REQUIRE(a.in && a.out, "%s: null pointer", what);
   REQUIRE(ValidDType(a.in_dtype) && ValidDType(a.out_dtype), "%s: unknown dtype", what);
   REQUIRE(a.d > 0 && a.d <= 256, "%s: d = %u outside 1..256", what, a.d);
@@ -224,10 +236,19 @@ extern "C" {
 
 const char* halo_b200_version(void) { return "halo_b200 0.1 sm_100a"; }
 
-int halo_b200_tune_norm_threads_per_row(int threads) {
-  if (threads < 0 || threads > 256 || (threads & (threads - 1)) != 0) return -1;
-  g_norm_threads_per_row.store(threads, std::memory_order_relaxed);
-  return 0;
+int halo_b200_tune(const char* key, int value) {
+  if (!key) return -1;
+  if (std::strcmp(key, "norm_threads_per_row") == 0) {
+    if (value < 0 || value > 256 || (value & (value - 1)) != 0) return -1;
+    g_norm_threads_per_row.store(value, std::memory_order_relaxed);
+    return 0;
+  }
+  if (std::strcmp(key, "norm_short_rows_k1") == 0) {
+    if (value != 0 && value != 1) return -1;
+    g_norm_short_rows_k1.store(value, std::memory_order_relaxed);
+    return 0;
+  }
+  return -1;
 }
 
 // ---- group 1 -------------------------------------------------------------------------
@@ -253,9 +274,12 @@ int halo_b200_axpy(halo_b200_stream stream, float* y, const float* x, float alph
   return RunElt(a, "halo_axpy", stream, err, errlen);
 }
 
-int halo_b200_rmsnorm_ex(halo_b200_stream stream, const void* x, int x_dtype, const float* w, void* y, int y_dtype,
-                         uint32_t d, float eps, uint32_t w_stride, uint32_t w_period, int one_plus, uint32_t rows,
-                         char* err, size_t errlen) {
+// short_rows_k1: rows of <= 256 elements keep one octet per thread, the layout of the fused
+// norm + RoPE kernel, so that the reference-named fp32 kernels agree with it bit for bit
+// (the reference's fused-equals-separate property, tests/gpu/quant_gpu_test.cpp:2635-2749).
+static int RmsnormTyped(halo_b200_stream stream, const void* x, int x_dtype, const float* w, void* y, int y_dtype,
+                        uint32_t d, float eps, uint32_t w_stride, uint32_t w_period, int one_plus, uint32_t rows,
+                        int short_rows_k1, char* err, size_t errlen) {
   NormArgs a;
   a.x = x;
   a.x_dtype = x_dtype;
@@ -268,37 +292,43 @@ int halo_b200_rmsnorm_ex(halo_b200_stream stream, const void* x, int x_dtype, co
   a.d = d;
   a.eps = eps;
   a.rows = rows;
-  REQUIRE(y != nullptr, "halo_rmsnorm: y is null");
+  a.short_rows_k1 = short_rows_k1;
+  REQUIRE(rows == 0 || y != nullptr, "halo_rmsnorm: y is null");
   return RunNorm(a, "halo_rmsnorm", stream, err, errlen);
+}
+
+int halo_b200_rmsnorm_ex(halo_b200_stream stream, const void* x, int x_dtype, const float* w, void* y, int y_dtype,
+                         uint32_t d, float eps, uint32_t w_stride, uint32_t w_period, int one_plus, uint32_t rows,
+                         char* err, size_t errlen) {
+  return RmsnormTyped(stream, x, x_dtype, w, y, y_dtype, d, eps, w_stride, w_period, one_plus, rows, 0, err, errlen);
 }
 
 int halo_b200_rmsnorm(halo_b200_stream stream, const float* x, const float* w_all, float* y, uint32_t d, float eps,
                       uint32_t w_stride, uint32_t nvec, char* err, size_t errlen) {
   REQUIRE(w_all != nullptr, "halo_rmsnorm: w_all is null");
   // vector b uses gamma b * w_stride: a period of nvec rows
-  return halo_b200_rmsnorm_ex(stream, x, kF32, w_all, y, kF32, d, eps, w_stride, w_stride ? nvec : 1, 0, nvec, err,
-                              errlen);
+  return RmsnormTyped(stream, x, kF32, w_all, y, kF32, d, eps, w_stride, w_stride ? nvec : 1, 0, nvec, 1, err, errlen);
 }
 
 int halo_b200_rmsnorm_rows(halo_b200_stream stream, const float* x, const float* w_all, float* y, uint32_t d,
                            float eps, uint32_t w_stride, uint32_t w_period, uint32_t rows, char* err, size_t errlen) {
   REQUIRE(w_all != nullptr, "halo_rmsnorm_rows: w_all is null");
   REQUIRE(w_period > 0, "halo_rmsnorm_rows: w_period is 0");
-  return halo_b200_rmsnorm_ex(stream, x, kF32, w_all, y, kF32, d, eps, w_stride, w_period, 0, rows, err, errlen);
+  return RmsnormTyped(stream, x, kF32, w_all, y, kF32, d, eps, w_stride, w_period, 0, rows, 1, err, errlen);
 }
 int halo_b200_rmsnorm_rows_r16(halo_b200_stream stream, const uint16_t* x, const float* w_all, float* y, uint32_t d,
                                float eps, uint32_t w_stride, uint32_t w_period, uint32_t rows, char* err,
                                size_t errlen) {
   REQUIRE(w_all != nullptr, "halo_rmsnorm_rows_r16: w_all is null");
   REQUIRE(w_period > 0, "halo_rmsnorm_rows_r16: w_period is 0");
-  return halo_b200_rmsnorm_ex(stream, x, kF16, w_all, y, kF32, d, eps, w_stride, w_period, 0, rows, err, errlen);
+  return RmsnormTyped(stream, x, kF16, w_all, y, kF32, d, eps, w_stride, w_period, 0, rows, 1, err, errlen);
 }
 int halo_b200_rmsnorm_rows_rb(halo_b200_stream stream, const uint16_t* x, const float* w_all, float* y, uint32_t d,
                               float eps, uint32_t w_stride, uint32_t w_period, uint32_t rows, char* err,
                               size_t errlen) {
   REQUIRE(w_all != nullptr, "halo_rmsnorm_rows_rb: w_all is null");
   REQUIRE(w_period > 0, "halo_rmsnorm_rows_rb: w_period is 0");
-  return halo_b200_rmsnorm_ex(stream, x, kBF16, w_all, y, kF32, d, eps, w_stride, w_period, 0, rows, err, errlen);
+  return RmsnormTyped(stream, x, kBF16, w_all, y, kF32, d, eps, w_stride, w_period, 0, rows, 1, err, errlen);
 }
 
 int halo_b200_rmsnorm_rows_h(halo_b200_stream stream, const void* x, int x_dtype, const float* w_all, float* y,
@@ -308,7 +338,7 @@ int halo_b200_rmsnorm_rows_h(halo_b200_stream stream, const void* x, int x_dtype
   (void)ipart;
   (void)irows;
   REQUIRE(iw == nullptr, "halo_rmsnorm_rows_h: inject partial products (iw) are not implemented");
-  REQUIRE(w_all && y && y16, "halo_rmsnorm_rows_h: null pointer");
+  REQUIRE(rows == 0 || (w_all && y && y16), "halo_rmsnorm_rows_h: null pointer");
   REQUIRE(w_period > 0, "halo_rmsnorm_rows_h: w_period is 0");
   NormArgs a;
   a.x = x;
@@ -347,6 +377,7 @@ int halo_b200_rmsnorm_y(halo_b200_stream stream, float* x, const float* w_all, u
 int halo_b200_add_rmsnorm(halo_b200_stream stream, void* res, const void* delta, int res_dtype, const float* w,
                           int one_plus, void* xn, int xn_dtype, uint8_t* xn_q8_0, int8_t* xq, float* xd, uint32_t d,
                           float eps, uint32_t rows, char* err, size_t errlen) {
+  if (rows == 0) return Done(cudaSuccess, "halo_add_rmsnorm", err, errlen);
   REQUIRE(res != nullptr, "halo_add_rmsnorm: res is null");
   REQUIRE(xn || xn_q8_0 || xq, "halo_add_rmsnorm: no normalized output requested");
   NormArgs a;
@@ -376,7 +407,7 @@ int halo_b200_quantize_q8_rows(halo_b200_stream stream, const float* x, int8_t* 
   a.rows = rows;
   a.xq = xq;
   a.xd = xd;
-  REQUIRE(xq && xd, "halo_quantize_q8_rows: null output");
+  REQUIRE(rows == 0 || (xq && xd), "halo_quantize_q8_rows: null output");
   return RunQuant(a, "halo_quantize_q8_rows", stream, err, errlen);
 }
 
@@ -390,8 +421,8 @@ int halo_b200_quantize_q8_kblocked(halo_b200_stream stream, const float* x, int8
   a.xq = xq;
   a.xd = xd;
   a.kb_tokens = tokens;
-  REQUIRE(xq && xd, "halo_quantize_q8_kblocked: null output");
   if (tokens == 0) return Done(cudaSuccess, "", err, errlen);
+  REQUIRE(xq && xd, "halo_quantize_q8_kblocked: null output");
   return RunQuant(a, "halo_quantize_q8_kblocked", stream, err, errlen);
 }
 
@@ -406,7 +437,7 @@ int halo_b200_q8x_cols(halo_b200_stream stream, const float* x, uint32_t xstride
   a.xd = xs;
   a.xq2 = xq2;
   a.xd2 = xs2;
-  REQUIRE(xq && xs, "halo_q8x_cols: null output");
+  REQUIRE(batch == 0 || (xq && xs), "halo_q8x_cols: null output");
   return RunQuant(a, "halo_q8x_cols", stream, err, errlen);
 }
 
@@ -419,7 +450,7 @@ int halo_b200_encode_q8_0_rows(halo_b200_stream stream, const void* x, int x_dty
   a.cols = cols;
   a.rows = rows;
   a.q8_0 = out;
-  REQUIRE(out != nullptr, "halo_encode_q8_0_rows: out is null");
+  REQUIRE(rows == 0 || out != nullptr, "halo_encode_q8_0_rows: out is null");
   return RunQuant(a, "halo_encode_q8_0_rows", stream, err, errlen);
 }
 
@@ -435,7 +466,7 @@ int halo_b200_l2norm_ex(halo_b200_stream stream, const void* x, int x_dtype, voi
   a.eps = eps;
   a.rows = rows;
   a.l2 = 1;
-  REQUIRE(y != nullptr, "halo_l2norm: y is null");
+  REQUIRE(rows == 0 || y != nullptr, "halo_l2norm: y is null");
   return RunNorm(a, "halo_l2norm", stream, err, errlen);
 }
 
@@ -564,7 +595,7 @@ int halo_b200_rope_neox_p_y(halo_b200_stream stream, float* x, const uint32_t* p
 
 int halo_b200_split_qgate(halo_b200_stream stream, const float* qg, float* q, float* gate, uint32_t hd,
                           uint32_t rows, char* err, size_t errlen) {
-  REQUIRE(qg && q && gate, "halo_split_qgate: null pointer");
+  REQUIRE(rows == 0 || (qg && q && gate), "halo_split_qgate: null pointer");
   SplitArgs a;
   a.qg = qg;
   a.q = q;
@@ -577,7 +608,7 @@ int halo_b200_split_qgate(halo_b200_stream stream, const float* qg, float* q, fl
 int halo_b200_split_qgate_y(halo_b200_stream stream, const float* qg, float* q, float* gate, uint32_t hd,
                             uint32_t qg_stride, uint32_t q_stride, uint32_t heads, uint32_t batch, char* err,
                             size_t errlen) {
-  REQUIRE(qg && q && gate, "halo_split_qgate_y: null pointer");
+  REQUIRE(heads * batch == 0 || (qg && q && gate), "halo_split_qgate_y: null pointer");
   SplitArgs a;
   a.qg = qg;
   a.q = q;
@@ -670,7 +701,7 @@ int halo_b200_sigmoid_gate(halo_b200_stream stream, float* x, const float* gate,
 int halo_b200_embed_q8_0_ex(halo_b200_stream stream, const uint8_t* w, uint64_t row_bytes, uint32_t vocab,
                             const uint32_t* ids, uint32_t id_stride, uint32_t id_slot, uint32_t tokens, void* out,
                             int out_dtype, uint32_t cols, char* err, size_t errlen) {
-  REQUIRE(ids != nullptr, "halo_embed_q8_0: ids is null");
+  REQUIRE(tokens == 0 || ids != nullptr, "halo_embed_q8_0: ids is null");
   EmbedArgs a;
   a.table = w;
   a.row_bytes = row_bytes;

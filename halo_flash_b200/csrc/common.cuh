@@ -3,8 +3,11 @@
 //
 // Arithmetic rules for every kernel in this library (they make the results
 // comparable with halo-flash's scalar CPU operators, src/model/cpu_ops.cpp):
-//   * fp32 arithmetic, IEEE division / sqrt / expf / sincosf (no fast-math),
-//     compiled with -fmad=false so multiplies and adds round separately;
+//   * fp32 arithmetic compiled with -fmad=false, so multiplies and adds round
+//     separately as on the CPU; the only deliberate departures are the sum of
+//     squares (fused multiply-add), the norm scale (hardware rsqrt, 2 ulp) and the
+//     gate functions (hardware exp2 / reciprocal), all far inside the 1e-5 the
+//     path allows. Q8 encoders use IEEE division: their codes must be bit-exact;
 //   * 16-bit outputs are rounded once, to nearest even, from the fp32 value
 //     (bf16 as src/kernels/core.hip:70-73, fp16 as a _Float16 cast).
 #ifndef HALO_B200_COMMON_CUH_
@@ -108,6 +111,159 @@ __device__ __forceinline__ void round_through8(float (&v)[8]) {
 template <>
 __device__ __forceinline__ void round_through8<float>(float (&)[8]) {}
 
+// ---- octets as four float2 pairs (packed fp32x2 arithmetic on sm_100) --------------
+// The row kernels are bound by instruction issue as much as by HBM, so their inner
+// math runs on FADD2 / FMUL2 / FFMA2: one instruction per two elements, each lane
+// rounded exactly as the scalar instruction would.
+struct Oct {
+  float2 p[4];
+};
+__device__ __forceinline__ Oct oct_zero() {
+  Oct o;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o.p[i] = make_float2(0.0f, 0.0f);
+  return o;
+}
+__device__ __forceinline__ Oct oct_unpack_bf16(uint4 u) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+  Oct o;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o.p[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u));
+  return o;
+}
+__device__ __forceinline__ uint4 oct_pack_bf16(const Oct& o) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(o.p[i].x, o.p[i].y);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+__device__ __forceinline__ Oct oct_unpack_f16(uint4 u) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+  Oct o;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o.p[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+  return o;
+}
+__device__ __forceinline__ uint4 oct_pack_f16(const Oct& o) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 h = __floats2half2_rn(o.p[i].x, o.p[i].y);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+__device__ __forceinline__ Oct oct_load(const float* p) {
+  const float4 a = __ldcs(reinterpret_cast<const float4*>(p));
+  const float4 b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
+  Oct o;
+  o.p[0] = make_float2(a.x, a.y); o.p[1] = make_float2(a.z, a.w);
+  o.p[2] = make_float2(b.x, b.y); o.p[3] = make_float2(b.z, b.w);
+  return o;
+}
+__device__ __forceinline__ Oct oct_load(const bf16* p) { return oct_unpack_bf16(__ldcs(reinterpret_cast<const uint4*>(p))); }
+__device__ __forceinline__ Oct oct_load(const f16* p) { return oct_unpack_f16(__ldcs(reinterpret_cast<const uint4*>(p))); }
+__device__ __forceinline__ Oct oct_load_cached(const float* p) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p));
+  const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  Oct o;
+  o.p[0] = make_float2(a.x, a.y); o.p[1] = make_float2(a.z, a.w);
+  o.p[2] = make_float2(b.x, b.y); o.p[3] = make_float2(b.z, b.w);
+  return o;
+}
+__device__ __forceinline__ void oct_store(float* p, const Oct& o) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(o.p[0].x, o.p[0].y, o.p[1].x, o.p[1].y);
+  reinterpret_cast<float4*>(p)[1] = make_float4(o.p[2].x, o.p[2].y, o.p[3].x, o.p[3].y);
+}
+__device__ __forceinline__ void oct_store(bf16* p, const Oct& o) { *reinterpret_cast<uint4*>(p) = oct_pack_bf16(o); }
+__device__ __forceinline__ void oct_store(f16* p, const Oct& o) { *reinterpret_cast<uint4*>(p) = oct_pack_f16(o); }
+// Store, and leave in `o` the values a later reader of the buffer sees.
+__device__ __forceinline__ void oct_store_round(float* p, Oct& o) { oct_store(p, o); }
+__device__ __forceinline__ void oct_store_round(bf16* p, Oct& o) {
+  const uint4 u = oct_pack_bf16(o);
+  *reinterpret_cast<uint4*>(p) = u;
+  o = oct_unpack_bf16(u);
+}
+__device__ __forceinline__ void oct_store_round(f16* p, Oct& o) {
+  const uint4 u = oct_pack_f16(o);
+  *reinterpret_cast<uint4*>(p) = u;
+  o = oct_unpack_f16(u);
+}
+__device__ __forceinline__ Oct oct_add(const Oct& a, const Oct& b) {
+  Oct o;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o.p[i] = __fadd2_rn(a.p[i], b.p[i]);
+  return o;
+}
+__device__ __forceinline__ Oct oct_mul(const Oct& a, const Oct& b) {
+  Oct o;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o.p[i] = __fmul2_rn(a.p[i], b.p[i]);
+  return o;
+}
+__device__ __forceinline__ Oct oct_scale(const Oct& a, float s) {
+  const float2 s2 = make_float2(s, s);
+  Oct o;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o.p[i] = __fmul2_rn(a.p[i], s2);
+  return o;
+}
+// acc += a * a per lane (fused: the sum of squares is the one place an FMA is used)
+__device__ __forceinline__ float2 oct_sumsq(const Oct& a, float2 acc) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) acc = __ffma2_rn(a.p[i], a.p[i], acc);
+  return acc;
+}
+__device__ __forceinline__ void oct_to_array(const Oct& o, float (&v)[8]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[2 * i] = o.p[i].x, v[2 * i + 1] = o.p[i].y;
+}
+
+// Raw octets: the loaded bits, converted only where they are consumed, so a thread that
+// issues many loads up front holds 4 registers per 16-bit octet instead of 8.
+template <typename T>
+struct Raw;
+template <>
+struct Raw<float> {
+  float4 a, b;
+};
+template <>
+struct Raw<bf16> {
+  uint4 u;
+};
+template <>
+struct Raw<f16> {
+  uint4 u;
+};
+__device__ __forceinline__ Raw<float> raw_load(const float* p) {
+  Raw<float> r;
+  r.a = __ldcs(reinterpret_cast<const float4*>(p));
+  r.b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
+  return r;
+}
+__device__ __forceinline__ Raw<bf16> raw_load(const bf16* p) {
+  Raw<bf16> r;
+  r.u = __ldcs(reinterpret_cast<const uint4*>(p));
+  return r;
+}
+__device__ __forceinline__ Raw<f16> raw_load(const f16* p) {
+  Raw<f16> r;
+  r.u = __ldcs(reinterpret_cast<const uint4*>(p));
+  return r;
+}
+__device__ __forceinline__ Oct raw_unpack(const Raw<float>& r) {
+  Oct o;
+  o.p[0] = make_float2(r.a.x, r.a.y); o.p[1] = make_float2(r.a.z, r.a.w);
+  o.p[2] = make_float2(r.b.x, r.b.y); o.p[3] = make_float2(r.b.z, r.b.w);
+  return o;
+}
+__device__ __forceinline__ Oct raw_unpack(const Raw<bf16>& r) { return oct_unpack_bf16(r.u); }
+__device__ __forceinline__ Oct raw_unpack(const Raw<f16>& r) { return oct_unpack_f16(r.u); }
+
 // ---- reductions ---------------------------------------------------------------
 // Sum over the `g` threads of a row group (g a power of two, g <= kBlock, groups
 // aligned to g within the CTA). g <= 32: shuffles only. g > 32: one shared-memory
@@ -139,7 +295,14 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 // ---- activations: src/model/cpu_ops.cpp:158-163 -------------------------------
-__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+// sigmoid(x) = 1 / (1 + exp(-x)) with the hardware exp2 and reciprocal units
+// (ex2.approx of -x * log2(e), rcp.approx): about 6 instructions instead of ~30
+// for the IEEE expf + division, which made the gate math, not HBM, the bound of
+// SwiGLU and the gated norm. Relative error <= ~1e-6 for |x| <= 30 and
+// <= ~6e-8 * |x| beyond (the product -x * log2e rounds once), against the 1e-5
+// the path allows; x -> -inf gives exp = +inf and a gate of exactly 0, as the
+// CPU operator does.
+__device__ __forceinline__ float sigmoid_f(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 __device__ __forceinline__ float silu_f(float x) { return x * sigmoid_f(x); }
 
 // ---- Q8 block epilogues (32 values = the 4 lanes of a quad, 8 values each) ----

@@ -23,28 +23,55 @@ __device__ __forceinline__ float apply(int op, float a, float b, float alpha) {
   }
 }
 
+template <int OP>
+__device__ __forceinline__ Oct apply8(const Oct& a, const Oct& b, float alpha) {
+  Oct o;
+  if constexpr (OP == kOpAdd) {
+    o = oct_add(a, b);
+  } else if constexpr (OP == kOpAxpy) {
+    o = oct_add(a, oct_scale(b, alpha));
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if constexpr (OP == kOpSiluMul) {
+        const float2 s = make_float2(silu_f(a.p[i].x), silu_f(a.p[i].y));
+        o.p[i] = __fmul2_rn(s, b.p[i]);
+      } else {
+        const float2 s = make_float2(sigmoid_f(b.p[i].x), sigmoid_f(b.p[i].y));
+        o.p[i] = __fmul2_rn(a.p[i], s);
+      }
+    }
+  }
+  return o;
+}
+
+// The raw loads of all kUnroll octets are issued first (kUnroll * 2 * 16 bytes in flight per
+// thread); each octet is then converted, computed and stored in turn, which keeps the
+// register count low enough for 5 resident CTAs per SM.
 template <typename IT, typename OT, int OP>
-__global__ void __launch_bounds__(kBlock) elementwise_vec_kernel(const EltArgs a, const uint64_t octs) {
+__global__ void __launch_bounds__(kBlock, sizeof(IT) == 4 ? 3 : 5) elementwise_vec_kernel(const EltArgs a, const uint64_t octs) {
   const IT* pa = static_cast<const IT*>(a.a);
   const IT* pb = static_cast<const IT*>(a.b);
   OT* py = static_cast<OT*>(a.y);
   const uint64_t base = static_cast<uint64_t>(blockIdx.x) * (kBlock * kUnroll) + threadIdx.x;
-  float va[kUnroll][8], vb[kUnroll][8];
+  if (base + static_cast<uint64_t>(kUnroll - 1) * kBlock < octs) {  // the whole CTA tile is inside: no predicates
+    Raw<IT> ra[kUnroll], rb[kUnroll];
 #pragma unroll
-  for (int u = 0; u < kUnroll; ++u) {
-    const uint64_t j = base + static_cast<uint64_t>(u) * kBlock;
-    if (j < octs) {
-      load8(pa + j * 8, va[u]);
-      load8(pb + j * 8, vb[u]);
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint64_t j = base + static_cast<uint64_t>(u) * kBlock;
+      ra[u] = raw_load(pa + j * 8);
+      rb[u] = raw_load(pb + j * 8);
     }
-  }
 #pragma unroll
-  for (int u = 0; u < kUnroll; ++u) {
-    const uint64_t j = base + static_cast<uint64_t>(u) * kBlock;
-    if (j < octs) {
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint64_t j = base + static_cast<uint64_t>(u) * kBlock;
+      oct_store(py + j * 8, apply8<OP>(raw_unpack(ra[u]), raw_unpack(rb[u]), a.alpha));
+    }
+  } else {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) va[u][i] = apply(OP, va[u][i], vb[u][i], a.alpha);
-      store8(py + j * 8, va[u]);
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint64_t j = base + static_cast<uint64_t>(u) * kBlock;
+      if (j < octs) oct_store(py + j * 8, apply8<OP>(oct_load(pa + j * 8), oct_load(pb + j * 8), a.alpha));
     }
   }
 }

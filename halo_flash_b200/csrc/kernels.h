@@ -57,6 +57,7 @@ struct NormArgs {
   uint32_t rows_per_entry = 0;  // 0 = dense
   uint64_t entry_stride = 0;
   int threads_per_row = 0;      // 0 = pick automatically
+  int short_rows_k1 = 0;        // 1: rows of <= 32 octets keep one octet per thread (default two)
   bool vec = true;
 };
 cudaError_t LaunchNorm(const NormArgs& a, cudaStream_t s);
@@ -74,6 +75,7 @@ struct GatedArgs {
   float eps = 0.0f;
   uint32_t mode = 0;  // 0 SiLU(z), 1 sigmoid(z)
   int threads_per_row = 0;
+  int short_rows_k1 = 0;
   bool vec = true;
 };
 cudaError_t LaunchGatedNorm(const GatedArgs& a, cudaStream_t s);

@@ -52,95 +52,144 @@ __device__ __forceinline__ void q8_epilogues(const NormArgs& a, const float (&v)
   }
 }
 
-template <typename XT, typename YT, int K, bool ADD>
-__global__ void __launch_bounds__(kBlock) norm_rows_kernel(const NormArgs a, const unsigned g) {
-  __shared__ float scratch[kBlock / 32];
+// R rows per thread group (R > 1 only for short rows, K == 1): row u of group `slot` is
+// row0 + u * (groups per CTA), so neighbouring groups still read neighbouring rows.
+// FULL: every row of the grid exists and every thread's octets lie inside the row, so no
+// load or store is predicated (the launcher checks d == 8 K g and rows % (rows per CTA) == 0).
+// These kernels are bound by instruction issue as much as by HBM: the arithmetic is packed
+// fp32x2, offsets are shifts, and rare features hide behind warp-uniform branches.
+template <typename XT, typename YT, int K, int R, bool ADD, bool FULL>
+__device__ __forceinline__ void norm_rows_body(const NormArgs& a, const unsigned lg, const float inv_d,
+                                               float* scratch) {
+  const unsigned g = 1u << lg;
   const unsigned lir = threadIdx.x & (g - 1);
-  const uint32_t row = blockIdx.x * (kBlock / g) + threadIdx.x / g;
-  const bool row_ok = row < a.rows;
+  const unsigned rpc = kBlock >> lg;
+  const uint32_t row0 = blockIdx.x * (rpc * R) + (threadIdx.x >> lg);
   const unsigned octs = a.d >> 3;
-  const size_t dense = static_cast<size_t>(row) * a.d;
-  const size_t xoff = a.rows_per_entry
-                          ? static_cast<size_t>(row / a.rows_per_entry) * a.entry_stride +
-                                static_cast<size_t>(row % a.rows_per_entry) * a.d
-                          : dense;
 
-  float v[K][8];
+  Oct v[R][K];
+  size_t dense[R], xoff[R];
+  bool row_ok[R];
   // Every load of the thread is issued before any is consumed.
 #pragma unroll
-  for (int k = 0; k < K; ++k) {
-    const unsigned j = k * g + lir;
-    if (row_ok && j < octs) {
-      load8(at<XT>(a.x, xoff + j * 8), v[k]);
-    } else {
+  for (int u = 0; u < R; ++u) {
+    const uint32_t row = row0 + u * rpc;
+    row_ok[u] = FULL || row < a.rows;
+    dense[u] = static_cast<size_t>(row) * a.d;
+    xoff[u] = dense[u];
+    if (a.rows_per_entry)
+      xoff[u] = static_cast<size_t>(row / a.rows_per_entry) * a.entry_stride +
+                static_cast<size_t>(row % a.rows_per_entry) * a.d;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[k][i] = 0.0f;
+    for (int k = 0; k < K; ++k) {
+      const unsigned j = (k << lg) + lir;
+      if (FULL || (row_ok[u] && j < octs)) v[u][k] = oct_load(at<XT>(a.x, xoff[u] + j * 8));
+      else v[u][k] = oct_zero();
     }
   }
   if constexpr (ADD) {
-    float dl[K][8];
+    Oct dl[R][K];
 #pragma unroll
-    for (int k = 0; k < K; ++k) {
-      const unsigned j = k * g + lir;
-      if (row_ok && j < octs) {
-        load8(at<XT>(a.delta, dense + j * 8), dl[k]);
-      } else {
+    for (int u = 0; u < R; ++u)
 #pragma unroll
-        for (int i = 0; i < 8; ++i) dl[k][i] = 0.0f;
+      for (int k = 0; k < K; ++k) {
+        const unsigned j = (k << lg) + lir;
+        if (FULL || (row_ok[u] && j < octs)) dl[u][k] = oct_load(at<XT>(a.delta, dense[u] + j * 8));
+        else dl[u][k] = oct_zero();
       }
-    }
 #pragma unroll
-    for (int k = 0; k < K; ++k) {
-      const unsigned j = k * g + lir;
+    for (int u = 0; u < R; ++u)
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[k][i] = v[k][i] + dl[k][i];
-      if (row_ok && j < octs) store8(at<XT>(a.res, xoff + j * 8), v[k]);
-      round_through8<XT>(v[k]);  // the norm reads the residual as stored
+      for (int k = 0; k < K; ++k) {
+        const unsigned j = (k << lg) + lir;
+        v[u][k] = oct_add(v[u][k], dl[u][k]);
+        // stored in the residual's type; the norm then reads the residual as stored
+        if (FULL || (row_ok[u] && j < octs)) oct_store_round(at<XT>(a.res, xoff[u] + j * 8), v[u][k]);
+      }
+  }
+
+  // Gammas do not depend on the reduction: for long rows (one row per group, at most two
+  // octets per thread) they are fetched before it, so the L2 round trip overlaps the
+  // shuffle / barrier instead of following it. Short rows re-read a gamma that sits in L1.
+  constexpr bool kEarlyGamma = K <= 2 && R == 1;
+  Oct gm[kEarlyGamma ? K : 1];
+  if constexpr (kEarlyGamma) {
+    if (a.w) {
+      const float* wrow = a.w + (a.w_period > 1 ? static_cast<size_t>(row0 % a.w_period) * a.w_stride : 0);
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const unsigned j = (k << lg) + lir;
+        if (FULL || (row_ok[0] && j < octs)) gm[k] = oct_load_cached(wrow + j * 8);
+        else gm[k] = oct_zero();
+        if (a.one_plus) {
+          const float2 one = make_float2(1.0f, 1.0f);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) gm[k].p[i] = __fadd2_rn(one, gm[k].p[i]);
+        }
+      }
     }
   }
 
-  float ss = 0.0f;
-#pragma unroll
-  for (int k = 0; k < K; ++k)
-#pragma unroll
-    for (int i = 0; i < 8; ++i) ss += v[k][i] * v[k][i];
-  ss = group_sum(ss, g, scratch);
-  const float scale = a.l2 ? 1.0f / sqrtf(ss + a.eps) : 1.0f / sqrtf(ss / static_cast<float>(a.d) + a.eps);
-  if (a.rscale && row_ok && lir == 0) a.rscale[row] = scale;
-
-  const float* wrow = a.w ? a.w + static_cast<size_t>(row % a.w_period) * a.w_stride : nullptr;
   const bool epi = a.q8_0 != nullptr || a.xq != nullptr;
 #pragma unroll
-  for (int k = 0; k < K; ++k) {
-    const unsigned j = k * g + lir;
-    const bool ok = row_ok && j < octs;
-    if (wrow) {
-      float gm[8];
-      if (ok) {
-        load8_cached(wrow + j * 8, gm);
-      } else {
+  for (int u = 0; u < R; ++u) {
+    const uint32_t row = row0 + u * rpc;
+    float2 acc = make_float2(0.0f, 0.0f);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) gm[i] = 0.0f;
-      }
+    for (int k = 0; k < K; ++k) acc = oct_sumsq(v[u][k], acc);
+    const float ss = group_sum(acc.x + acc.y, g, scratch);
+    const float scale = a.l2 ? rsqrtf(ss + a.eps) : rsqrtf(__fmaf_rn(ss, inv_d, a.eps));
+    if (a.rscale && row_ok[u] && lir == 0) a.rscale[row] = scale;
+    const float* wrow = nullptr;
+    if (!kEarlyGamma && a.w)
+      wrow = a.w + (a.w_period > 1 ? static_cast<size_t>(row % a.w_period) * a.w_stride : 0);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[k][i] = v[k][i] * scale * (a.one_plus ? 1.0f + gm[i] : gm[i]);
-    } else {
+    for (int k = 0; k < K; ++k) {
+      const unsigned j = (k << lg) + lir;
+      const bool ok = FULL || (row_ok[u] && j < octs);
+      v[u][k] = oct_scale(v[u][k], scale);
+      if constexpr (kEarlyGamma) {
+        if (a.w) v[u][k] = oct_mul(v[u][k], gm[k]);
+      } else if (wrow) {
+        Oct gl = ok ? oct_load_cached(wrow + j * 8) : oct_zero();
+        if (a.one_plus) {
+          const float2 one = make_float2(1.0f, 1.0f);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[k][i] = v[k][i] * scale;
-    }
-    if (ok) {
-      if (a.y) store8(at<YT>(a.y, xoff + j * 8), v[k]);
-      if (a.y16) {
-        size_t o16 = dense + j * 8;
-        if (a.y16_tokens) {
-          const uint32_t t = row / a.kb_period, c = (row % a.kb_period) * a.d + j * 8;
-          o16 = (static_cast<size_t>(c / 64) * a.y16_tokens + t) * 64 + c % 64;
+          for (int i = 0; i < 4; ++i) gl.p[i] = __fadd2_rn(one, gl.p[i]);
         }
-        store8(at<f16>(a.y16, o16), v[k]);
+        v[u][k] = oct_mul(v[u][k], gl);
+      }
+      if (ok) {
+        if (a.y) oct_store(at<YT>(a.y, xoff[u] + j * 8), v[u][k]);
+        if (a.y16) {
+          size_t o16 = dense[u] + j * 8;
+          if (a.y16_tokens) {
+            const uint32_t t = row / a.kb_period, c = (row % a.kb_period) * a.d + j * 8;
+            o16 = (static_cast<size_t>(c / 64) * a.y16_tokens + t) * 64 + c % 64;
+          }
+          oct_store(at<f16>(a.y16, o16), v[u][k]);
+        }
+      }
+      if (epi) {
+        float arr[8];
+        oct_to_array(v[u][k], arr);
+        q8_epilogues(a, arr, row, j * 8, ok);
       }
     }
-    if (epi) q8_epilogues(a, v[k], row, j * 8, ok);
   }
+}
+
+// Resident CTAs per SM the register allocation is held to: the kernels wait on HBM most of
+// the time, so for short per-thread rows more warps in flight beat a few saved instructions.
+// `live` = octets a thread holds in fp32 across the reduction (8 registers each).
+constexpr int MinCtas(int live) { return live <= 1 ? 6 : (live <= 2 ? 5 : (live <= 4 ? 3 : 1)); }
+
+template <typename XT, typename YT, int K, int R, bool ADD>
+__global__ void __launch_bounds__(kBlock, MinCtas(K * R)) norm_rows_kernel(const NormArgs a, const unsigned lg, const float inv_d,
+                                                          const unsigned full) {
+  __shared__ float scratch[kBlock / 32];
+  if (full) norm_rows_body<XT, YT, K, R, ADD, true>(a, lg, inv_d, scratch);
+  else norm_rows_body<XT, YT, K, R, ADD, false>(a, lg, inv_d, scratch);
 }
 
 // Any d, any alignment: one CTA per row, scalar accesses, the row is re-read
@@ -235,47 +284,75 @@ __global__ void __launch_bounds__(kBlock) norm_rows_scalar_kernel(const NormArgs
 }
 
 // ---- gated RMSNorm: y = ((o * scale) * w) * gate(z) ----------------------------------------
-template <typename OT, typename ZT, typename YT, int K>
-__global__ void __launch_bounds__(kBlock) gated_norm_kernel(const GatedArgs a, const unsigned g) {
-  __shared__ float scratch[kBlock / 32];
+template <typename OT, typename ZT, typename YT, int K, int R, bool FULL>
+__device__ __forceinline__ void gated_norm_body(const GatedArgs& a, const unsigned lg, const float inv_d,
+                                                float* scratch) {
+  const unsigned g = 1u << lg;
   const unsigned lir = threadIdx.x & (g - 1);
-  const uint32_t row = blockIdx.x * (kBlock / g) + threadIdx.x / g;
-  const bool row_ok = row < a.rows;
+  const unsigned rpc = kBlock >> lg;
+  const uint32_t row0 = blockIdx.x * (rpc * R) + (threadIdx.x >> lg);
   const unsigned octs = a.d >> 3;
-  const size_t off = static_cast<size_t>(row) * a.d;
-  float v[K][8], zz[K][8];
+  Oct v[R][K], zz[R][K];
 #pragma unroll
-  for (int k = 0; k < K; ++k) {
-    const unsigned j = k * g + lir;
-    if (row_ok && j < octs) {
-      load8(at<OT>(a.o, off + j * 8), v[k]);
-      load8(at<ZT>(a.z, off + j * 8), zz[k]);
-    } else {
+  for (int u = 0; u < R; ++u) {
+    const uint32_t row = row0 + u * rpc;
+    const size_t off = static_cast<size_t>(row) * a.d;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[k][i] = 0.0f, zz[k][i] = 0.0f;
-    }
-  }
-  float ss = 0.0f;
-#pragma unroll
-  for (int k = 0; k < K; ++k)
-#pragma unroll
-    for (int i = 0; i < 8; ++i) ss += v[k][i] * v[k][i];
-  ss = group_sum(ss, g, scratch);
-  const float scale = 1.0f / sqrtf(ss / static_cast<float>(a.d) + a.eps);
-#pragma unroll
-  for (int k = 0; k < K; ++k) {
-    const unsigned j = k * g + lir;
-    if (row_ok && j < octs) {
-      float gm[8];
-      load8_cached(a.w + j * 8, gm);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float gate = a.mode == 0 ? silu_f(zz[k][i]) : sigmoid_f(zz[k][i]);
-        v[k][i] = v[k][i] * scale * gm[i] * gate;
+    for (int k = 0; k < K; ++k) {
+      const unsigned j = (k << lg) + lir;
+      if (FULL || (row < a.rows && j < octs)) {
+        v[u][k] = oct_load(at<OT>(a.o, off + j * 8));
+        zz[u][k] = oct_load(at<ZT>(a.z, off + j * 8));
+      } else {
+        v[u][k] = oct_zero();
+        zz[u][k] = oct_zero();
       }
-      store8(at<YT>(a.y, off + j * 8), v[k]);
     }
   }
+  // Neither the gamma (shared by every row) nor the gate depends on the reduction: both are
+  // ready before it, so the gamma fetch and the exp2 / reciprocal work overlap the shuffles.
+  // The product itself keeps the CPU operator's order, ((o * scale) * w) * gate.
+  Oct gm[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const unsigned j = (k << lg) + lir;
+    gm[k] = (FULL || j < octs) ? oct_load_cached(a.w + j * 8) : oct_zero();
+  }
+#pragma unroll
+  for (int u = 0; u < R; ++u)
+#pragma unroll
+    for (int k = 0; k < K; ++k)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2& z2 = zz[u][k].p[i];
+        z2.x = a.mode == 0 ? silu_f(z2.x) : sigmoid_f(z2.x);
+        z2.y = a.mode == 0 ? silu_f(z2.y) : sigmoid_f(z2.y);
+      }
+#pragma unroll
+  for (int u = 0; u < R; ++u) {
+    const uint32_t row = row0 + u * rpc;
+    float2 acc = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int k = 0; k < K; ++k) acc = oct_sumsq(v[u][k], acc);
+    const float ss = group_sum(acc.x + acc.y, g, scratch);
+    const float scale = rsqrtf(__fmaf_rn(ss, inv_d, a.eps));
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const unsigned j = (k << lg) + lir;
+      if (FULL || (row < a.rows && j < octs)) {
+        const Oct r = oct_mul(oct_mul(oct_scale(v[u][k], scale), gm[k]), zz[u][k]);
+        oct_store(at<YT>(a.y, static_cast<size_t>(row) * a.d + j * 8), r);
+      }
+    }
+  }
+}
+
+template <typename OT, typename ZT, typename YT, int K, int R>
+__global__ void __launch_bounds__(kBlock, MinCtas(2 * K * R)) gated_norm_kernel(const GatedArgs a, const unsigned lg, const float inv_d,
+                                                           const unsigned full) {
+  __shared__ float scratch[kBlock / 32];
+  if (full) gated_norm_body<OT, ZT, YT, K, R, true>(a, lg, inv_d, scratch);
+  else gated_norm_body<OT, ZT, YT, K, R, false>(a, lg, inv_d, scratch);
 }
 
 template <typename OT, typename ZT, typename YT>
@@ -307,26 +384,41 @@ __global__ void __launch_bounds__(kBlock) gated_norm_scalar_kernel(const GatedAr
   }
 }
 
-// Threads per row and octets per thread for a row of `octs` octets.
+// Threads per row (g = 1 << lg), octets per thread (k) and rows per thread group (r).
 struct Shape {
-  unsigned g;
-  int k;
+  unsigned lg;
+  int k, r;
+  unsigned rows_per_cta;
+  bool full;
 };
-Shape PickShape(unsigned octs, int want_g) {
+Shape PickShape(unsigned octs, unsigned rows, int want_g, unsigned min_g, int want_k1) {
   unsigned g;
   if (want_g > 0) {
     g = static_cast<unsigned>(want_g);
   } else if (octs <= 32) {
+    // Short rows (one head), shuffles only. Two octets per thread measured faster than one
+    // (13.8 vs 14.8 us for the 16 x 128 q/k L2 norm at 4096 tokens) and faster than several
+    // rows per group; want_k1 keeps one octet per thread, the layout of the fused norm + RoPE
+    // kernel, for callers that need the two to agree bit for bit.
     g = 1;
-    while (g < octs) g <<= 1;
-  } else if (octs <= 256) {
-    g = 32;  // one warp per row: no barrier
+    while ((want_k1 ? g : 2 * g) < octs) g <<= 1;
   } else {
-    g = 256;
+    // Two octets per thread keep registers low (many resident CTAs, many loads in flight)
+    // and the gammas prefetchable; measured best at d = 2048 (g = 128) on B200.
+    g = 64;
+    while (g < 256 && octs > 2 * g) g <<= 1;
   }
+  if (g < min_g) g = min_g;
   unsigned k = (octs + g - 1) / g, kp = 1;
   while (kp < k) kp <<= 1;
-  return {g, static_cast<int>(kp)};
+  Shape sh;
+  sh.lg = 0;
+  while ((1u << sh.lg) < g) ++sh.lg;
+  sh.k = static_cast<int>(kp);
+  sh.r = 1;
+  sh.rows_per_cta = kBlock / g;
+  sh.full = octs == kp * g && rows % sh.rows_per_cta == 0;
+  return sh;
 }
 
 template <typename XT, typename YT, bool ADD>
@@ -335,14 +427,14 @@ cudaError_t LaunchNormT(const NormArgs& a, cudaStream_t s) {
     norm_rows_scalar_kernel<XT, YT, ADD><<<a.rows, kBlock, 0, s>>>(a);
     return cudaGetLastError();
   }
-  const Shape sh = PickShape(a.d / 8, a.threads_per_row);
-  const unsigned rows_per_cta = kBlock / sh.g;
-  const unsigned grid = (a.rows + rows_per_cta - 1) / rows_per_cta;
+  const Shape sh = PickShape(a.d / 8, a.rows, a.threads_per_row, (a.q8_0 || a.xq) ? 4u : 1u, a.short_rows_k1);
+  const unsigned grid = (a.rows + sh.rows_per_cta - 1) / sh.rows_per_cta;
+  const float inv_d = 1.0f / static_cast<float>(a.d);
   switch (sh.k) {
-    case 1: norm_rows_kernel<XT, YT, 1, ADD><<<grid, kBlock, 0, s>>>(a, sh.g); break;
-    case 2: norm_rows_kernel<XT, YT, 2, ADD><<<grid, kBlock, 0, s>>>(a, sh.g); break;
-    case 4: norm_rows_kernel<XT, YT, 4, ADD><<<grid, kBlock, 0, s>>>(a, sh.g); break;
-    case 8: norm_rows_kernel<XT, YT, 8, ADD><<<grid, kBlock, 0, s>>>(a, sh.g); break;
+    case 1: norm_rows_kernel<XT, YT, 1, 1, ADD><<<grid, kBlock, 0, s>>>(a, sh.lg, inv_d, sh.full); break;
+    case 2: norm_rows_kernel<XT, YT, 2, 1, ADD><<<grid, kBlock, 0, s>>>(a, sh.lg, inv_d, sh.full); break;
+    case 4: norm_rows_kernel<XT, YT, 4, 1, ADD><<<grid, kBlock, 0, s>>>(a, sh.lg, inv_d, sh.full); break;
+    case 8: norm_rows_kernel<XT, YT, 8, 1, ADD><<<grid, kBlock, 0, s>>>(a, sh.lg, inv_d, sh.full); break;
     default: return cudaErrorInvalidValue;
   }
   return cudaGetLastError();
@@ -369,13 +461,13 @@ cudaError_t LaunchGatedT(const GatedArgs& a, cudaStream_t s) {
     gated_norm_scalar_kernel<OT, ZT, YT><<<a.rows, kBlock, 0, s>>>(a);
     return cudaGetLastError();
   }
-  const Shape sh = PickShape(a.d / 8, a.threads_per_row);
-  const unsigned rows_per_cta = kBlock / sh.g;
-  const unsigned grid = (a.rows + rows_per_cta - 1) / rows_per_cta;
+  const Shape sh = PickShape(a.d / 8, a.rows, a.threads_per_row, 1u, a.short_rows_k1);
+  const unsigned grid = (a.rows + sh.rows_per_cta - 1) / sh.rows_per_cta;
+  const float inv_d = 1.0f / static_cast<float>(a.d);
   switch (sh.k) {
-    case 1: gated_norm_kernel<OT, ZT, YT, 1><<<grid, kBlock, 0, s>>>(a, sh.g); break;
-    case 2: gated_norm_kernel<OT, ZT, YT, 2><<<grid, kBlock, 0, s>>>(a, sh.g); break;
-    case 4: gated_norm_kernel<OT, ZT, YT, 4><<<grid, kBlock, 0, s>>>(a, sh.g); break;
+    case 1: gated_norm_kernel<OT, ZT, YT, 1, 1><<<grid, kBlock, 0, s>>>(a, sh.lg, inv_d, sh.full); break;
+    case 2: gated_norm_kernel<OT, ZT, YT, 2, 1><<<grid, kBlock, 0, s>>>(a, sh.lg, inv_d, sh.full); break;
+    case 4: gated_norm_kernel<OT, ZT, YT, 4, 1><<<grid, kBlock, 0, s>>>(a, sh.lg, inv_d, sh.full); break;
     default: return cudaErrorInvalidValue;
   }
   return cudaGetLastError();

@@ -75,72 +75,106 @@ __global__ void __launch_bounds__(kBlock) rope_kernel(const RopeArgs a, const __
   }
 }
 
-// RMSNorm (shared gamma) + RoPE on rows of d <= 256: g = d / 8 rounded up to a
-// power of two (<= 32) lanes per row, one octet per lane, shuffles only. Lane
-// `lir` < half/8 holds the first halves of 8 pairs, lane lir + half/8 their
-// partners; the two exchange their normalized values with one shuffle per element.
+// RMSNorm (shared gamma) + RoPE on rows of d <= 256 (one row = one head of one token).
+// A CTA owns `tpc` whole tokens: it first fills the shared (cos, sin) table for those
+// tokens - one sincosf per token and frequency instead of one per head and lane - then
+// its thread groups walk the tokens' head rows, kRows rows per group per pass with all
+// loads issued up front. g = d / 8 rounded up to a power of two (<= 32) lanes per row,
+// one octet per lane, shuffles only: the sum of squares is formed exactly as the
+// standalone norm kernel forms it for such rows, so the fused result equals
+// norm-then-rope bit for bit. Lane `lir` < half/8 holds the first halves of 8 pairs,
+// lane lir + half/8 their partners; the two exchange their normalized values with one
+// shuffle per element.
+constexpr int kRows = 4;
+
 template <typename IT, typename OT>
 __global__ void __launch_bounds__(kBlock) norm_rope_kernel(const NormRopeArgs a, const __grid_constant__ InvFreq f,
-                                                          const unsigned g) {
+                                                          const unsigned g, const unsigned tpc, const float inv_d) {
+  extern __shared__ float2 cs[];  // [tpc][half]
+  const uint32_t half = a.rot / 2;
+  const uint32_t tokens = (a.rows + a.heads - 1) / a.heads;
+  const uint32_t t0 = blockIdx.x * tpc;
+  for (uint32_t idx = threadIdx.x; idx < tpc * half; idx += kBlock) {
+    const uint32_t t = t0 + idx / half, i = idx % half;
+    if (t < tokens) {
+      const uint32_t pos = token_pos(a.pos, t);
+      const float angle = __fmul_rn(static_cast<float>(pos), f.f[i]);
+      float sn, c;
+      sincosf(angle, &sn, &c);
+      cs[idx] = make_float2(c, sn);
+      if (i == 0 && a.pos_out) a.pos_out[t] = pos;
+    }
+  }
+  __syncthreads();
+
   const unsigned lane = threadIdx.x & 31u;
   const unsigned lir = threadIdx.x & (g - 1);
-  const uint32_t row = blockIdx.x * (kBlock / g) + threadIdx.x / g;
+  const unsigned slots = kBlock / g, slot = threadIdx.x / g;
   const unsigned octs = a.d >> 3;
-  const bool ok = row < a.rows && lir < octs;
-  float v[8];
-  if (ok) {
-    const IT* src = static_cast<const IT*>(a.in) + static_cast<size_t>(row) * a.in_row_stride;
-    load8(src + lir * 8, v);
-    if (a.gate) {
-      float gt[8];
-      load8(src + a.d + lir * 8, gt);
-      store8(static_cast<IT*>(a.gate) + static_cast<size_t>(row) * a.d + lir * 8, gt);
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = 0.0f;
-  }
-  if (a.w) {
-    float ss = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
-    ss = group_sum(ss, g, nullptr);  // g <= 32: shuffles only
-    const float scale = 1.0f / sqrtf(ss / static_cast<float>(a.d) + a.eps);
-    float gm[8];
-    if (ok) {
-      load8_cached(a.w + lir * 8, gm);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) gm[i] = 0.0f;
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = v[i] * scale * (a.one_plus ? 1.0f + gm[i] : gm[i]);
-  }
   const unsigned hp = a.rot / 16;  // lanes per half of the rotated span
   const bool rotates = lir < 2 * hp;
   const bool low = lir < hp;
   const unsigned partner = rotates ? (low ? lir + hp : lir - hp) : lir;
   const unsigned src_lane = lane - lir + partner;
-  const uint32_t token = row / a.heads;
-  uint32_t pos = 0;
-  if (row < a.rows) {
-    pos = token_pos(a.pos, token);
-    if (a.pos_out && lir == 0 && row % a.heads == 0) a.pos_out[token] = pos;
-  }
   const unsigned fi = (low ? lir : lir - hp) * 8;
+  const uint32_t row_begin = t0 * a.heads;
+  uint32_t row_end = (t0 + tpc) * a.heads;
+  if (row_end > a.rows) row_end = a.rows;
+
+  for (uint32_t base = row_begin; base < row_end; base += slots * kRows) {
+    Oct x[kRows];
+    bool ok[kRows];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const float other = __shfl_sync(kFullMask, v[i], src_lane);
-    if (rotates) {
-      const float angle = __fmul_rn(static_cast<float>(pos), f.f[fi + i]);
-      float sn, c;
-      sincosf(angle, &sn, &c);
-      v[i] = low ? v[i] * c - other * sn : other * sn + v[i] * c;
+    for (int u = 0; u < kRows; ++u) {
+      const uint32_t row = base + u * slots + slot;
+      ok[u] = row < row_end && lir < octs;
+      if (ok[u]) x[u] = oct_load(static_cast<const IT*>(a.in) + static_cast<size_t>(row) * a.in_row_stride + lir * 8);
+      else x[u] = oct_zero();
     }
-  }
-  if (ok) {
-    store8(static_cast<OT*>(a.out) + static_cast<size_t>(row) * a.d + lir * 8, v);
-    if (a.cache) store8(static_cast<OT*>(a.cache) + static_cast<size_t>(row) * a.d + lir * 8, v);
+    if (a.gate) {
+#pragma unroll
+      for (int u = 0; u < kRows; ++u) {
+        const uint32_t row = base + u * slots + slot;
+        if (ok[u]) {
+          const Oct gt = oct_load(static_cast<const IT*>(a.in) + static_cast<size_t>(row) * a.in_row_stride + a.d + lir * 8);
+          oct_store(static_cast<IT*>(a.gate) + static_cast<size_t>(row) * a.d + lir * 8, gt);
+        }
+      }
+    }
+    Oct gm = oct_zero();
+    if (a.w && lir < octs) {
+      gm = oct_load_cached(a.w + lir * 8);
+      if (a.one_plus) {
+        const float2 one = make_float2(1.0f, 1.0f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) gm.p[i] = __fadd2_rn(one, gm.p[i]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kRows; ++u) {
+      const uint32_t row = base + u * slots + slot;
+      if (a.w) {  // the norm kernel's arithmetic for a one-octet-per-thread row, step for step
+        const float2 acc = oct_sumsq(x[u], make_float2(0.0f, 0.0f));
+        const float ss = group_sum(acc.x + acc.y, g, nullptr);  // g <= 32: shuffles only
+        const float scale = rsqrtf(__fmaf_rn(ss, inv_d, a.eps));
+        x[u] = oct_mul(oct_scale(x[u], scale), gm);
+      }
+      float v[8];
+      oct_to_array(x[u], v);
+      const float2* tab = cs + static_cast<size_t>(row < row_end ? row / a.heads - t0 : 0) * half + fi;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float other = __shfl_sync(kFullMask, v[i], src_lane);
+        if (rotates) {
+          const float2 t2 = tab[i];
+          v[i] = low ? v[i] * t2.x - other * t2.y : other * t2.y + v[i] * t2.x;
+        }
+      }
+      if (ok[u]) {
+        store8(static_cast<OT*>(a.out) + static_cast<size_t>(row) * a.d + lir * 8, v);
+        if (a.cache) store8(static_cast<OT*>(a.cache) + static_cast<size_t>(row) * a.d + lir * 8, v);
+      }
+    }
   }
 }
 
@@ -184,9 +218,15 @@ template <typename IT, typename OT>
 cudaError_t LaunchNormRopeT(const NormRopeArgs& a, const InvFreq& f, cudaStream_t s) {
   unsigned g = 1;
   while (g < a.d / 8) g <<= 1;
-  const unsigned rows_per_cta = kBlock / g;
-  const unsigned grid = (a.rows + rows_per_cta - 1) / rows_per_cta;
-  norm_rope_kernel<IT, OT><<<grid, kBlock, 0, s>>>(a, f, g);
+  // whole tokens per CTA: about one pass of rows (kBlock / g groups x kRows rows)
+  const unsigned rows_per_pass = kBlock / g * kRows;
+  unsigned tpc = rows_per_pass / a.heads;
+  if (tpc < 1) tpc = 1;
+  if (tpc > 32) tpc = 32;
+  const unsigned tokens = (a.rows + a.heads - 1) / a.heads;
+  const unsigned grid = (tokens + tpc - 1) / tpc;
+  const size_t smem = static_cast<size_t>(tpc) * (a.rot / 2) * sizeof(float2);
+  norm_rope_kernel<IT, OT><<<grid, kBlock, smem, s>>>(a, f, g, tpc, 1.0f / static_cast<float>(a.d));
   return cudaGetLastError();
 }
 

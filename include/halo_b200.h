@@ -256,9 +256,11 @@ int halo_b200_launch(halo_b200_stream stream, const char* name, const halo_b200_
 size_t halo_b200_kernel_count(void);
 const char* halo_b200_kernel_name(size_t index);
 
-/* Tuning hook for experiments (process-wide, not for production dispatch): threads per row
- * of the norm kernels; 0 restores the built-in choice. Must be a power of two <= 256. */
-int halo_b200_tune_norm_threads_per_row(int threads);
+/* Tuning hook for experiments (process-wide, not for production dispatch). Keys:
+ * "norm_threads_per_row" (power of two <= 256; 0 = built-in choice),
+ * "norm_short_rows_k1" (1 = rows of <= 256 elements use one 8-element chunk per thread; 0 = built-in choice).
+ * Returns 0, or -1 for an unknown key or value. */
+int halo_b200_tune(const char* key, int value);
 
 #ifdef __cplusplus
 }
