@@ -16,6 +16,7 @@ namespace {
 
 std::atomic<int> g_norm_threads_per_row{0};
 std::atomic<int> g_norm_short_rows_k1{0};
+std::atomic<int> g_norm_force_general{0};
 
 int Fail(char* err, size_t errlen, const char* fmt, ...) {
   if (err && errlen) {
@@ -72,6 +73,7 @@ int RunNorm(NormArgs a, const char* what, halo_b200_stream stream, char* err, si
           "%s: pointer not aligned to its element type", what);
   a.threads_per_row = g_norm_threads_per_row.load(std::memory_order_relaxed);
   if (g_norm_short_rows_k1.load(std::memory_order_relaxed)) a.short_rows_k1 = 1;
+  a.force_general = g_norm_force_general.load(std::memory_order_relaxed);
   bool vec = a.d % 8 == 0 && a.d <= 256u * 8u * 8u && Aligned(a.x, 16) && Aligned(a.y, 16) && Aligned(a.delta, 16) &&
              Aligned(a.res, 16) && Aligned(a.y16, 16) && Aligned(a.w, 16) && a.w_stride % 4 == 0 &&
              Aligned(a.xq, 8) && a.entry_stride % 8 == 0;
@@ -243,6 +245,11 @@ int halo_b200_tune(const char* key, int value) {
     g_norm_threads_per_row.store(value, std::memory_order_relaxed);
     return 0;
   }
+  if (std::strcmp(key, "norm_force_general") == 0) {
+    if (value != 0 && value != 1) return -1;
+    g_norm_force_general.store(value, std::memory_order_relaxed);
+    return 0;
+  }
   if (std::strcmp(key, "norm_short_rows_k1") == 0) {
     if (value != 0 && value != 1) return -1;
     g_norm_short_rows_k1.store(value, std::memory_order_relaxed);
@@ -274,9 +281,10 @@ int halo_b200_axpy(halo_b200_stream stream, float* y, const float* x, float alph
   return RunElt(a, "halo_axpy", stream, err, errlen);
 }
 
-// short_rows_k1: rows of <= 256 elements keep one octet per thread, the layout of the fused
-// norm + RoPE kernel, so that the reference-named fp32 kernels agree with it bit for bit
-// (the reference's fused-equals-separate property, tests/gpu/quant_gpu_test.cpp:2635-2749).
+// short_rows_k1 forces one octet per thread on rows of <= 256 elements. The default layout is
+// shared with the fused norm + RoPE kernel, so the separate kernels agree with the fused one
+// bit for bit whenever rot <= d / 2 (the reference's fused-equals-separate property,
+// tests/gpu/quant_gpu_test.cpp:2635-2749).
 static int RmsnormTyped(halo_b200_stream stream, const void* x, int x_dtype, const float* w, void* y, int y_dtype,
                         uint32_t d, float eps, uint32_t w_stride, uint32_t w_period, int one_plus, uint32_t rows,
                         int short_rows_k1, char* err, size_t errlen) {
@@ -307,28 +315,28 @@ int halo_b200_rmsnorm(halo_b200_stream stream, const float* x, const float* w_al
                       uint32_t w_stride, uint32_t nvec, char* err, size_t errlen) {
   REQUIRE(w_all != nullptr, "halo_rmsnorm: w_all is null");
   // vector b uses gamma b * w_stride: a period of nvec rows
-  return RmsnormTyped(stream, x, kF32, w_all, y, kF32, d, eps, w_stride, w_stride ? nvec : 1, 0, nvec, 1, err, errlen);
+  return RmsnormTyped(stream, x, kF32, w_all, y, kF32, d, eps, w_stride, w_stride ? nvec : 1, 0, nvec, 0, err, errlen);
 }
 
 int halo_b200_rmsnorm_rows(halo_b200_stream stream, const float* x, const float* w_all, float* y, uint32_t d,
                            float eps, uint32_t w_stride, uint32_t w_period, uint32_t rows, char* err, size_t errlen) {
   REQUIRE(w_all != nullptr, "halo_rmsnorm_rows: w_all is null");
   REQUIRE(w_period > 0, "halo_rmsnorm_rows: w_period is 0");
-  return RmsnormTyped(stream, x, kF32, w_all, y, kF32, d, eps, w_stride, w_period, 0, rows, 1, err, errlen);
+  return RmsnormTyped(stream, x, kF32, w_all, y, kF32, d, eps, w_stride, w_period, 0, rows, 0, err, errlen);
 }
 int halo_b200_rmsnorm_rows_r16(halo_b200_stream stream, const uint16_t* x, const float* w_all, float* y, uint32_t d,
                                float eps, uint32_t w_stride, uint32_t w_period, uint32_t rows, char* err,
                                size_t errlen) {
   REQUIRE(w_all != nullptr, "halo_rmsnorm_rows_r16: w_all is null");
   REQUIRE(w_period > 0, "halo_rmsnorm_rows_r16: w_period is 0");
-  return RmsnormTyped(stream, x, kF16, w_all, y, kF32, d, eps, w_stride, w_period, 0, rows, 1, err, errlen);
+  return RmsnormTyped(stream, x, kF16, w_all, y, kF32, d, eps, w_stride, w_period, 0, rows, 0, err, errlen);
 }
 int halo_b200_rmsnorm_rows_rb(halo_b200_stream stream, const uint16_t* x, const float* w_all, float* y, uint32_t d,
                               float eps, uint32_t w_stride, uint32_t w_period, uint32_t rows, char* err,
                               size_t errlen) {
   REQUIRE(w_all != nullptr, "halo_rmsnorm_rows_rb: w_all is null");
   REQUIRE(w_period > 0, "halo_rmsnorm_rows_rb: w_period is 0");
-  return RmsnormTyped(stream, x, kBF16, w_all, y, kF32, d, eps, w_stride, w_period, 0, rows, 1, err, errlen);
+  return RmsnormTyped(stream, x, kBF16, w_all, y, kF32, d, eps, w_stride, w_period, 0, rows, 0, err, errlen);
 }
 
 int halo_b200_rmsnorm_rows_h(halo_b200_stream stream, const void* x, int x_dtype, const float* w_all, float* y,

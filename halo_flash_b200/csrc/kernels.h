@@ -58,6 +58,7 @@ struct NormArgs {
   uint64_t entry_stride = 0;
   int threads_per_row = 0;      // 0 = pick automatically
   int short_rows_k1 = 0;        // 1: rows of <= 32 octets keep one octet per thread (default two)
+  int force_general = 0;        // 1: never take the lean kernel (tests compare the two)
   bool vec = true;
 };
 cudaError_t LaunchNorm(const NormArgs& a, cudaStream_t s);

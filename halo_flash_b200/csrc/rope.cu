@@ -76,21 +76,23 @@ __global__ void __launch_bounds__(kBlock) rope_kernel(const RopeArgs a, const __
 }
 
 // RMSNorm (shared gamma) + RoPE on rows of d <= 256 (one row = one head of one token).
-// A CTA owns `tpc` whole tokens: it first fills the shared (cos, sin) table for those
-// tokens - one sincosf per token and frequency instead of one per head and lane - then
-// its thread groups walk the tokens' head rows, kRows rows per group per pass with all
-// loads issued up front. g = d / 8 rounded up to a power of two (<= 32) lanes per row,
-// one octet per lane, shuffles only: the sum of squares is formed exactly as the
-// standalone norm kernel forms it for such rows, so the fused result equals
-// norm-then-rope bit for bit. Lane `lir` < half/8 holds the first halves of 8 pairs,
-// lane lir + half/8 their partners; the two exchange their normalized values with one
-// shuffle per element.
-constexpr int kRows = 4;
+// A CTA owns `tpc` whole tokens: it first fills shared (cos, -sin) / (cos, +sin) tables for
+// those tokens - one sincosf per token and frequency instead of one per head and lane - then
+// its thread groups walk the tokens' head rows, kRows rows per group per pass with all loads
+// issued up front. A group of g lanes (g <= 32, shuffles only) owns a row; lane `lir` holds
+// octets lir and (K == 2) lir + g. The sum of squares is formed exactly as the standalone
+// norm kernel forms it for the same row length, so fused equals norm-then-rope bit for bit.
+// Rotation: lane lir < half/8 holds the first halves of 8 pairs, lane lir + half/8 their
+// partners, both in the k = 0 octet (the launcher picks K == 2 only when rot <= d / 2); the
+// two exchange their normalized values with one shuffle per element and each computes
+// own * cos + other * (-/+ sin): the CPU operator's a*c - b*s and a*s + b*c, term for term.
+constexpr int kRows = 2;
 
-template <typename IT, typename OT>
-__global__ void __launch_bounds__(kBlock) norm_rope_kernel(const NormRopeArgs a, const __grid_constant__ InvFreq f,
-                                                          const unsigned g, const unsigned tpc, const float inv_d) {
-  extern __shared__ float2 cs[];  // [tpc][half]
+template <typename IT, typename OT, int K>
+__global__ void __launch_bounds__(kBlock, K == 2 ? 3 : 4) norm_rope_kernel(const NormRopeArgs a, const __grid_constant__ InvFreq f,
+                                                             const unsigned lg, const unsigned tpc,
+                                                             const float inv_d, const uint32_t heads_magic) {
+  extern __shared__ float2 cs[];  // [2][tpc][half]: (cos, -sin) then (cos, +sin)
   const uint32_t half = a.rot / 2;
   const uint32_t tokens = (a.rows + a.heads - 1) / a.heads;
   const uint32_t t0 = blockIdx.x * tpc;
@@ -101,78 +103,114 @@ __global__ void __launch_bounds__(kBlock) norm_rope_kernel(const NormRopeArgs a,
       const float angle = __fmul_rn(static_cast<float>(pos), f.f[i]);
       float sn, c;
       sincosf(angle, &sn, &c);
-      cs[idx] = make_float2(c, sn);
+      cs[idx] = make_float2(c, -sn);
+      cs[tpc * half + idx] = make_float2(c, sn);
       if (i == 0 && a.pos_out) a.pos_out[t] = pos;
     }
   }
   __syncthreads();
 
+  const unsigned g = 1u << lg;
   const unsigned lane = threadIdx.x & 31u;
   const unsigned lir = threadIdx.x & (g - 1);
-  const unsigned slots = kBlock / g, slot = threadIdx.x / g;
+  const unsigned slots = kBlock >> lg, slot = threadIdx.x >> lg;
   const unsigned octs = a.d >> 3;
   const unsigned hp = a.rot / 16;  // lanes per half of the rotated span
   const bool rotates = lir < 2 * hp;
   const bool low = lir < hp;
-  const unsigned partner = rotates ? (low ? lir + hp : lir - hp) : lir;
-  const unsigned src_lane = lane - lir + partner;
-  const unsigned fi = (low ? lir : lir - hp) * 8;
+  const unsigned src_lane = lane - lir + (rotates ? (low ? lir + hp : lir - hp) : lir);
+  const float2* lane_tab = cs + (low ? 0u : tpc * half) + (low ? lir : lir - hp) * 8;
   const uint32_t row_begin = t0 * a.heads;
   uint32_t row_end = (t0 + tpc) * a.heads;
   if (row_end > a.rows) row_end = a.rows;
 
+  Oct gm[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const unsigned j = (k << lg) + lir;
+    gm[k] = oct_zero();
+    if (a.w && j < octs) {
+      gm[k] = oct_load_cached(a.w + j * 8);
+      if (a.one_plus) {
+        const float2 one = make_float2(1.0f, 1.0f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) gm[k].p[i] = __fadd2_rn(one, gm[k].p[i]);
+      }
+    }
+  }
+
   for (uint32_t base = row_begin; base < row_end; base += slots * kRows) {
-    Oct x[kRows];
-    bool ok[kRows];
+    Raw<IT> raw[kRows][K];
+    bool ok[kRows][K];
 #pragma unroll
     for (int u = 0; u < kRows; ++u) {
       const uint32_t row = base + u * slots + slot;
-      ok[u] = row < row_end && lir < octs;
-      if (ok[u]) x[u] = oct_load(static_cast<const IT*>(a.in) + static_cast<size_t>(row) * a.in_row_stride + lir * 8);
-      else x[u] = oct_zero();
+      const IT* src = static_cast<const IT*>(a.in) + static_cast<size_t>(row) * a.in_row_stride;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const unsigned j = (k << lg) + lir;
+        ok[u][k] = row < row_end && j < octs;
+        if (ok[u][k]) raw[u][k] = raw_load(src + j * 8);
+        else raw[u][k] = Raw<IT>{};
+      }
     }
     if (a.gate) {
 #pragma unroll
       for (int u = 0; u < kRows; ++u) {
         const uint32_t row = base + u * slots + slot;
-        if (ok[u]) {
-          const Oct gt = oct_load(static_cast<const IT*>(a.in) + static_cast<size_t>(row) * a.in_row_stride + a.d + lir * 8);
-          oct_store(static_cast<IT*>(a.gate) + static_cast<size_t>(row) * a.d + lir * 8, gt);
-        }
-      }
-    }
-    Oct gm = oct_zero();
-    if (a.w && lir < octs) {
-      gm = oct_load_cached(a.w + lir * 8);
-      if (a.one_plus) {
-        const float2 one = make_float2(1.0f, 1.0f);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) gm.p[i] = __fadd2_rn(one, gm.p[i]);
+        for (int k = 0; k < K; ++k) {
+          const unsigned j = (k << lg) + lir;
+          if (ok[u][k]) {
+            const Oct gt = oct_load(static_cast<const IT*>(a.in) + static_cast<size_t>(row) * a.in_row_stride + a.d + j * 8);
+            oct_store(static_cast<IT*>(a.gate) + static_cast<size_t>(row) * a.d + j * 8, gt);
+          }
+        }
       }
     }
 #pragma unroll
     for (int u = 0; u < kRows; ++u) {
       const uint32_t row = base + u * slots + slot;
-      if (a.w) {  // the norm kernel's arithmetic for a one-octet-per-thread row, step for step
-        const float2 acc = oct_sumsq(x[u], make_float2(0.0f, 0.0f));
+      Oct x[K];
+#pragma unroll
+      for (int k = 0; k < K; ++k) x[k] = raw_unpack(raw[u][k]);
+      if (a.w) {  // the norm kernel's arithmetic for a row of this length, step for step
+        float2 acc = make_float2(0.0f, 0.0f);
+#pragma unroll
+        for (int k = 0; k < K; ++k) acc = oct_sumsq(x[k], acc);
         const float ss = group_sum(acc.x + acc.y, g, nullptr);  // g <= 32: shuffles only
         const float scale = rsqrtf(__fmaf_rn(ss, inv_d, a.eps));
-        x[u] = oct_mul(oct_scale(x[u], scale), gm);
+#pragma unroll
+        for (int k = 0; k < K; ++k) x[k] = oct_mul(oct_scale(x[k], scale), gm[k]);
       }
       float v[8];
-      oct_to_array(x[u], v);
-      const float2* tab = cs + static_cast<size_t>(row < row_end ? row / a.heads - t0 : 0) * half + fi;
+      oct_to_array(x[0], v);
+      const uint32_t rl = row < row_end ? row - row_begin : 0;
+      const uint32_t tl = heads_magic ? __umulhi(rl, heads_magic) : rl / a.heads;
+      const float2* tab = lane_tab + tl * half;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float other = __shfl_sync(kFullMask, v[i], src_lane);
+      for (int i = 0; i < 8; i += 2) {
+        const float o0 = __shfl_sync(kFullMask, v[i], src_lane);
+        const float o1 = __shfl_sync(kFullMask, v[i + 1], src_lane);
         if (rotates) {
-          const float2 t2 = tab[i];
-          v[i] = low ? v[i] * t2.x - other * t2.y : other * t2.y + v[i] * t2.x;
+          const float4 t4 = *reinterpret_cast<const float4*>(tab + i);  // (cos, sin) of two frequencies
+          v[i] = v[i] * t4.x + o0 * t4.y;
+          v[i + 1] = v[i + 1] * t4.z + o1 * t4.w;
         }
       }
-      if (ok[u]) {
-        store8(static_cast<OT*>(a.out) + static_cast<size_t>(row) * a.d + lir * 8, v);
-        if (a.cache) store8(static_cast<OT*>(a.cache) + static_cast<size_t>(row) * a.d + lir * 8, v);
+      OT* dst = static_cast<OT*>(a.out) + static_cast<size_t>(row) * a.d;
+      OT* cdst = a.cache ? static_cast<OT*>(a.cache) + static_cast<size_t>(row) * a.d : nullptr;
+      if (ok[u][0]) {
+        store8(dst + lir * 8, v);
+        if (cdst) store8(cdst + lir * 8, v);
+      }
+#pragma unroll
+      for (int k = 1; k < K; ++k) {
+        const unsigned j = (k << lg) + lir;
+        if (ok[u][k]) {
+          oct_store(dst + j * 8, x[k]);
+          if (cdst) oct_store(cdst + j * 8, x[k]);
+        }
       }
     }
   }
@@ -214,19 +252,40 @@ cudaError_t LaunchRopeT(const RopeArgs& a, const InvFreq& f, cudaStream_t s) {
   return cudaGetLastError();
 }
 
+unsigned Gcd(unsigned a, unsigned b) {
+  while (b) {
+    const unsigned t = a % b;
+    a = b;
+    b = t;
+  }
+  return a;
+}
+
 template <typename IT, typename OT>
 cudaError_t LaunchNormRopeT(const NormRopeArgs& a, const InvFreq& f, cudaStream_t s) {
-  unsigned g = 1;
-  while (g < a.d / 8) g <<= 1;
-  // whole tokens per CTA: about one pass of rows (kBlock / g groups x kRows rows)
+  const unsigned octs = a.d / 8;
+  // Two octets per lane halve the instructions per row; the rotated span must then sit in
+  // the first octet of the lanes (rot <= d / 2), which holds for 64-of-256 and 16-of-64.
+  const int k = (octs >= 2 && a.rot * 2 <= a.d) ? 2 : 1;
+  unsigned g = 1, lg = 0;
+  while (g * k < octs) g <<= 1, ++lg;
+  // whole tokens per CTA such that the CTA's rows fill its passes (groups x kRows rows each)
   const unsigned rows_per_pass = kBlock / g * kRows;
-  unsigned tpc = rows_per_pass / a.heads;
-  if (tpc < 1) tpc = 1;
+  unsigned tpc = rows_per_pass / Gcd(rows_per_pass, a.heads);
   if (tpc > 32) tpc = 32;
   const unsigned tokens = (a.rows + a.heads - 1) / a.heads;
+  if (tpc > tokens) tpc = tokens;
+  // ... but never so many that the grid falls under about three CTAs per SM
+  while (tpc > 1 && (tokens + tpc - 1) / tpc < 148u * 3u) tpc = (tpc + 1) / 2;
   const unsigned grid = (tokens + tpc - 1) / tpc;
-  const size_t smem = static_cast<size_t>(tpc) * (a.rot / 2) * sizeof(float2);
-  norm_rope_kernel<IT, OT><<<grid, kBlock, smem, s>>>(a, f, g, tpc, 1.0f / static_cast<float>(a.d));
+  const size_t smem = 2 * static_cast<size_t>(tpc) * (a.rot / 2) * sizeof(float2);
+  const float inv_d = 1.0f / static_cast<float>(a.d);
+  // floor(n / heads) == umulhi(n, ceil(2^32 / heads)) for the n < 2^16 a CTA can see
+  const uint32_t magic = (a.heads > 1 && a.heads < 2048)
+                             ? static_cast<uint32_t>(((1ull << 32) + a.heads - 1) / a.heads)
+                             : 0u;
+  if (k == 2) norm_rope_kernel<IT, OT, 2><<<grid, kBlock, smem, s>>>(a, f, lg, tpc, inv_d, magic);
+  else norm_rope_kernel<IT, OT, 1><<<grid, kBlock, smem, s>>>(a, f, lg, tpc, inv_d, magic);
   return cudaGetLastError();
 }
 

@@ -651,3 +651,26 @@ def test_full_size_prefill_properties(orc):
     assert torch.equal(emb[0], emb[1])
     wante = orc.embed_q8_0_rows(table.cpu().numpy(), ids[pick].cpu().numpy().view(np.uint32), s.hidden)
     assert np.array_equal(bits16(emb[pick]), oracle.bf16_bits(wante))
+
+
+def test_lean_and_general_norm_kernels_agree_bit_for_bit():
+    """The lean kernel (dense, full grid) and the general kernel compute the same bits."""
+    s = synth.FULL
+    rows = 64
+    res, delta = to_dev(synth.act("t.lg.res", rows, s.hidden), "bf16"), to_dev(synth.act("t.lg.delta", rows, s.hidden), "bf16")
+    w = to_dev(synth.norm_w("t.lg.w", s.hidden))
+    outs = []
+    for force in (0, 1):
+        lib().tune("norm_force_general", force)
+        try:
+            r = res.clone()
+            xn = torch.empty_like(r)
+            q8 = torch.empty(rows, s.q8_row_bytes, dtype=torch.uint8, device=DEV)
+            ops.add_rmsnorm(r, delta, w, s.eps, xn=xn, q8_0=q8)
+            qk = to_dev(synth.act("t.lg.qk", rows * 32, s.lin_dim), "bf16")
+            ops.l2norm(qk, s.eps)
+            outs.append((r, xn, q8, qk))
+        finally:
+            lib().tune("norm_force_general", 0)
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
