@@ -366,7 +366,8 @@ def run_ours(args) -> None:
     value = T * n_gpus / (ms_step * 1e-3)
 
     # end to end through host buffers (every rank, max over ranks)
-    e2e = run_e2e(torch, ch, max(2, min(args.steps, args.e2e_steps)))
+    e2e = {"ms_per_step": float("nan"), "h2d": 0, "d2h": 0} if args.no_e2e else \
+        run_e2e(torch, ch, max(2, min(args.steps, args.e2e_steps)))
     e2e_ms = e2e["ms_per_step"]
     if dist is not None:
         t = torch.tensor([e2e_ms], device="cuda")
@@ -380,8 +381,15 @@ def run_ours(args) -> None:
 
     del ch
     torch.cuda.empty_cache()
-    table = kernel_table(torch, synth.FULL, T, peaks)
     top = "add_rmsnorm"
+    if args.no_kernel_table:
+        print(json.dumps({"metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": n_gpus,
+                          "ms_per_step": round(ms_step, 4), "note": "profiler run: legs skipped"}), flush=True)
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+    table = kernel_table(torch, synth.FULL, T, peaks)
     launches = {"add_rmsnorm": 96, "l2norm": 36, "gated_norm": 36, "norm_rope_q": 12, "norm_rope_k": 12,
                 "swiglu_shared": 48, "swiglu_routed": 48, "embed": 1}
     est = {k: v["us"] * launches[k] for k, v in table.items()}
@@ -420,9 +428,11 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--tokens", type=int, default=4096, help="tokens per GPU per step")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--cpu-tokens", type=int, default=512, help="token sample of the CPU path")
+    ap.add_argument("--cpu-tokens", type=int, default=1024, help="token sample of the CPU path")
     ap.add_argument("--e2e-steps", type=int, default=3)
-    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
+    ap.add_argument("--no-kernel-table", action="store_true", help="skip the per-kernel timing leg (profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
