@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T] [--impl ours|reference]
 
-One step = the 48-layer op chain (36 Gated-DeltaNet + 12 GQA layers, 289 kernel launches,
+One step = the 48-layer op chain (36 Gated-DeltaNet + 12 GQA layers, 229 kernel launches,
 halo_flash_b200/chain.py) over a T-token shard per GPU, bf16 activations, full-size dims
 (hidden 2048, 16 Q / 2 KV heads x 256 with 64 rotated dims, 32 value heads x 128, 16 key heads
 x 128, shared ff 512 + 10 routed x 512, Q8_0 vocabulary 151936). With N GPUs every rank runs its
@@ -226,22 +226,19 @@ def kernel_table(torch, shapes, T: int, peaks: dict) -> dict:
         "gated_norm": (lambda: (r(T * s.v_heads, s.lin_dim), r(T * s.v_heads, s.lin_dim),
                                 torch.empty(T * s.v_heads, s.lin_dim, device=dev, dtype=bf)),
                        lambda b: ops.gated_norm(b[0], w_g, b[1], s.eps, y=b[2])),
-        "norm_rope_q": (lambda: (r(T * s.q_heads, s.head_dim),),
-                        lambda b: ops.norm_rope(b[0], w_hd, s.eps, s.rot, s.theta, s.q_heads)),
-        "norm_rope_k": (lambda: (r(T * s.kv_heads, s.head_dim),),
-                        lambda b: ops.norm_rope(b[0], w_hd, s.eps, s.rot, s.theta, s.kv_heads)),
-        "swiglu_shared": (lambda: (r(T, s.ff), r(T, s.ff), torch.empty(T, s.ff, device=dev, dtype=bf)),
-                          lambda b: ops.silu_mul(b[0], b[1], y=b[2])),
-        "swiglu_routed": (lambda: (r(T * k, s.ff), r(T * k, s.ff), torch.empty(T * k, s.ff, device=dev, dtype=bf)),
-                          lambda b: ops.silu_mul(b[0], b[1], y=b[2])),
+        "norm_rope_qk": (lambda: (r(T, s.q_heads, s.head_dim), r(T, s.kv_heads, s.head_dim)),
+                         lambda b: ops.norm_rope_qk(b[0], b[1], w_hd, w_hd, s.eps, s.rot, s.theta)),
+        "swiglu_moe": (lambda: (r(T, s.ff), r(T, s.ff), torch.empty(T, s.ff, device=dev, dtype=bf),
+                                r(T * k, s.ff), r(T * k, s.ff), torch.empty(T * k, s.ff, device=dev, dtype=bf)),
+                       lambda b: ops.silu_mul_multi([(b[0], b[1]), (b[3], b[4])], [b[2], b[5]])),
         "embed": (lambda: (torch.randint(0, 8192, (T,), device=dev, dtype=torch.int32),
                            torch.empty(T, s.hidden, device=dev, dtype=bf)),
                   lambda b: ops.embed_q8_0(table, b[0], s.hidden, b[1])),
     }
     out = {}
     for name, (make, run) in specs.items():
-        nbytes = bpt[name] * T if name in bpt else \
-            2 * 2 * s.head_dim * (s.q_heads if name.endswith("_q") else s.kv_heads) * T
+        nbytes = {"norm_rope_qk": bpt["norm_rope"], "swiglu_moe": bpt["swiglu_shared"] + bpt["swiglu_routed"]}.get(
+            name, bpt.get(name, 0)) * T
         sets = ring(nbytes, make)
         run(sets[0])
         torch.cuda.synchronize()
@@ -390,8 +387,7 @@ def run_ours(args) -> None:
             dist.destroy_process_group()
         return
     table = kernel_table(torch, synth.FULL, T, peaks)
-    launches = {"add_rmsnorm": 96, "l2norm": 36, "gated_norm": 36, "norm_rope_q": 12, "norm_rope_k": 12,
-                "swiglu_shared": 48, "swiglu_routed": 48, "embed": 1}
+    launches = {"add_rmsnorm": 96, "l2norm": 36, "gated_norm": 36, "norm_rope_qk": 12, "swiglu_moe": 48, "embed": 1}
     est = {k: v["us"] * launches[k] for k, v in table.items()}
     step_bytes = chain_mod.chain_bytes_per_token(synth.FULL, 2) * T
     roofline = {"bound": "hbm", "kernel": "norm_rows_lean_kernel<bf16,bf16,K=2,ADD> (residual add + RMSNorm(1+w), H=2048)",

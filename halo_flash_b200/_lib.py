@@ -52,9 +52,12 @@ SIGNATURES: dict[str, list] = {
     "halo_b200_norm_rope_rows": [_p, _p, _f, _u32, _u32, _u32, _u32, _f, _p, _u32],
     "halo_b200_norm_rope_ex": [_p, _i, _u64, _p, _i, _p, _p, _p, _i, _f, _u32, _u32, _u32, _u32, _f, _p, _u32, _u32,
                                _u32, _u32, _p],
+    "halo_b200_norm_rope_qk_ex": [_p, _u64, _p, _p, _p, _u32, _p, _p, _p, _p, _u32, _i, _i, _i, _f, _u32, _u32, _u32, _f,
+                                  _p, _u32, _u32, _u32, _u32, _p],
     "halo_b200_silu_mul": [_p, _p, _u32],
     "halo_b200_silu_mul_h": [_p, _p, _p, _u32],
     "halo_b200_silu_mul_ex": [_p, _p, _i, _p, _i, _u64],
+    "halo_b200_silu_mul_multi_ex": [_u32, _p, _p, _p, _p, _i, _i],
     "halo_b200_sigmoid_gate": [_p, _p, _u32],
     "halo_b200_matvec_q8_0_embed": [_p, _p, _u32, _u32, _u64],
     "halo_b200_matvec_q8_0_embed_p": [_p, _p, _p, _u32, _u64],

@@ -7,9 +7,9 @@ engine order src/engine/qwen35_gpu.cpp:439-589):
 
     add + RMSNorm(1+w)                      res += previous block's output; xn = norm(res)
     DeltaNet layer : q/k L2 norm, gated RMSNorm of the recurrence output     (qwen35.cpp:196-197, 232-234)
-    GQA layer      : per-head RMSNorm(1+w) + partial RoPE on Q and on K, fused (qwen35.cpp:251-255)
+    GQA layer      : per-head RMSNorm(1+w) + partial RoPE on Q and K, one fused launch (qwen35.cpp:251-255)
     add + RMSNorm(1+w)                      res += mixer output; xn = norm(res)
-    SwiGLU on the shared-expert and on the routed-expert gate/up rows       (qwen35.cpp:327)
+    SwiGLU on the shared-expert and on the routed-expert gate/up rows, one launch (qwen35.cpp:327)
 
 The projections, the recurrence and attention between these ops are not part of the path;
 their outputs are synthetic device tensors (the "block outputs" below). Only the residual
@@ -71,8 +71,8 @@ class BlockOutputs:
     o: torch.Tensor         # [T*v_heads, lin_dim]      recurrence output
     z: torch.Tensor         # [T*v_heads, lin_dim]      output gate
     y: torch.Tensor         # [T*v_heads, lin_dim]      gated-norm result
-    q: torch.Tensor         # [T*q_heads, head_dim]
-    k: torch.Tensor         # [T*kv_heads, head_dim]
+    q: torch.Tensor         # [T, q_heads, head_dim]
+    k: torch.Tensor         # [T, kv_heads, head_dim]
     gate_s: torch.Tensor    # [T, ff]
     up_s: torch.Tensor
     gate_r: torch.Tensor    # [T*top_k, ff]
@@ -104,7 +104,7 @@ class LayerChain:
             qk=act(T, 2 * s.k_heads, s.lin_dim),
             o=act(T * s.v_heads, s.lin_dim), z=act(T * s.v_heads, s.lin_dim),
             y=torch.empty(T * s.v_heads, s.lin_dim, device=dev, dtype=dtype),
-            q=act(T * s.q_heads, s.head_dim), k=act(T * s.kv_heads, s.head_dim),
+            q=act(T, s.q_heads, s.head_dim), k=act(T, s.kv_heads, s.head_dim),
             gate_s=act(T, s.ff), up_s=act(T, s.ff), gate_r=act(T * k, s.ff), up_r=act(T * k, s.ff),
         ) for _ in range(sets)]
         self.res = torch.empty(T, s.hidden, device=dev, dtype=dtype)
@@ -132,7 +132,7 @@ class LayerChain:
         self.table = table.view(self.vocab, nb * 34)
         del codes, half, table
         self.ids = torch.randint(0, self.vocab, (T,), device=dev, generator=g, dtype=torch.int32)
-        self.launches_per_step = 1 + 6 * synth.LAYERS
+        self.launches_per_step = 1 + 4 * synth.LAYERS + sum(not synth.layer_is_gqa(l) for l in range(synth.LAYERS))
         self._graph: torch.cuda.CUDAGraph | None = None
 
     # ---- one step, eager ------------------------------------------------------------------
@@ -140,17 +140,17 @@ class LayerChain:
         s = self.s
         ops.add_rmsnorm(self.res, bo.delta_a, self.w_attn[l], s.eps, one_plus=True, xn=self.xn)
         if synth.layer_is_gqa(l):
-            ops.norm_rope(bo.q, self.w_q, s.eps, s.rot, s.theta, s.q_heads, one_plus=True, pos0=self.pos0)
-            ops.norm_rope(bo.k, self.w_k, s.eps, s.rot, s.theta, s.kv_heads, one_plus=True, pos0=self.pos0)
+            ops.norm_rope_qk(bo.q, bo.k, self.w_q, self.w_k, s.eps, s.rot, s.theta, one_plus=True, pos0=self.pos0)
         else:
             ops.l2norm(bo.qk, s.eps)
             ops.gated_norm(bo.o, self.w_gated, bo.z, s.eps, mode=0, y=bo.y)
         ops.add_rmsnorm(self.res, bo.delta_b, self.w_post[l], s.eps, one_plus=True, xn=self.xn)
-        ops.silu_mul(bo.gate_s, bo.up_s, y=self.h_s)
-        ops.silu_mul(bo.gate_r, bo.up_r, y=self.h_r)
+        ops.silu_mul_multi([(bo.gate_s, bo.up_s), (bo.gate_r, bo.up_r)], [self.h_s, self.h_r])
 
     def step(self) -> None:
-        """Enqueue one full step on the current stream (1 + 6 * 48 kernel launches)."""
+        """Enqueue one full step on the current stream: the embedding gather, then per DeltaNet layer
+        5 launches (add+norm, L2, gated norm, add+norm, SwiGLU shared+routed) and per GQA layer 4
+        (add+norm, Q/K norm+RoPE, add+norm, SwiGLU): 1 + 36*5 + 12*4 = 229."""
         ops.embed_q8_0(self.table, self.ids, self.s.hidden, self.res, vocab=self.vocab)
         for l in range(synth.LAYERS):
             self.layer(l, self.sets[l % len(self.sets)])

@@ -122,13 +122,23 @@ int RunRope(RopeArgs a, float theta, const char* what, halo_b200_stream stream, 
 }
 
 int RunElt(EltArgs a, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
-  if (a.n == 0) return Done(cudaSuccess, what, err, errlen);  // an empty chunk is a no-op
-  REQUIRE(a.a && a.b && a.y, "%s: null pointer", what);
+  REQUIRE(a.nseg >= 1 && a.nseg <= kMaxSegments, "%s: 1..%d segments", what, kMaxSegments);
   REQUIRE(ValidDType(a.in_dtype) && ValidDType(a.y_dtype), "%s: unknown dtype", what);
-  REQUIRE(Aligned(a.a, DTypeSize(a.in_dtype)) && Aligned(a.b, DTypeSize(a.in_dtype)) &&
-              Aligned(a.y, DTypeSize(a.y_dtype)),
-          "%s: pointer not aligned to its element type", what);
-  a.vec = Aligned(a.a, 16) && Aligned(a.b, 16) && Aligned(a.y, 16);
+  // drop empty segments (an empty chunk is a no-op)
+  int n = 0;
+  for (int i = 0; i < a.nseg; ++i)
+    if (a.seg[i].n) a.seg[n++] = a.seg[i];
+  a.nseg = n;
+  if (n == 0) return Done(cudaSuccess, what, err, errlen);
+  a.vec = true;
+  for (int i = 0; i < n; ++i) {
+    const EltSegment& g = a.seg[i];
+    REQUIRE(g.a && g.b && g.y, "%s: null pointer", what);
+    REQUIRE(Aligned(g.a, DTypeSize(a.in_dtype)) && Aligned(g.b, DTypeSize(a.in_dtype)) &&
+                Aligned(g.y, DTypeSize(a.y_dtype)),
+            "%s: pointer not aligned to its element type", what);
+    a.vec = a.vec && Aligned(g.a, 16) && Aligned(g.b, 16) && Aligned(g.y, 16);
+  }
   const cudaError_t e = LaunchElementwise(a, S(stream));
   if (e == cudaErrorInvalidValue) return Fail(err, errlen, "%s: unsupported (in, out) dtype combination", what);
   return Done(e, what, err, errlen);
@@ -175,7 +185,16 @@ int RunNormRope(NormRopeArgs a, float theta, const char* what, halo_b200_stream 
   InvFreq f;
   REQUIRE(FillInvFreq(&f, a.rot, theta), "%s: rotary_dim too large", what);
   const bool vec = a.d % 8 == 0 && (a.rot / 2) % 8 == 0 && a.in_row_stride % 8 == 0 && Aligned(a.in, 16) &&
-                   Aligned(a.out, 16) && Aligned(a.gate, 16) && Aligned(a.cache, 16) && Aligned(a.w, 16);
+                   Aligned(a.out, 16) && Aligned(a.gate, 16) && Aligned(a.cache, 16) && Aligned(a.w, 16) &&
+                   a.in_row_stride2 % 8 == 0 && Aligned(a.in2, 16) && Aligned(a.out2, 16) && Aligned(a.cache2, 16) &&
+                   Aligned(a.w2, 16);
+  if (a.heads2) {
+    REQUIRE(a.in2 && a.out2, "%s: second tensor is null", what);
+    REQUIRE((a.w == nullptr) == (a.w2 == nullptr), "%s: both tensors need a gamma, or neither", what);
+    REQUIRE(a.rows % a.heads == 0, "%s: rows %u not a multiple of heads %u", what, a.rows, a.heads);
+    REQUIRE(a.in_row_stride2 >= a.d, "%s: in_row_stride2 < d", what);
+    REQUIRE(vec, "%s: two tensors in one launch need 16-byte aligned rows, d %% 8 == 0 and rot %% 16 == 0", what);
+  }
   if (vec) {
     const cudaError_t e = LaunchNormRope(a, f, S(stream));
     if (e == cudaErrorInvalidValue) return Fail(err, errlen, "%s: unsupported (in, out) dtype combination", what);
@@ -262,10 +281,7 @@ int halo_b200_tune(const char* key, int value) {
 int halo_b200_add(halo_b200_stream stream, float* y, const float* x, uint32_t n, char* err, size_t errlen) {
   EltArgs a;
   a.op = kOpAdd;
-  a.a = y;
-  a.b = x;
-  a.y = y;
-  a.n = n;
+  a.seg[0] = {y, x, y, n};
   return RunElt(a, "halo_add", stream, err, errlen);
 }
 
@@ -273,11 +289,8 @@ int halo_b200_axpy(halo_b200_stream stream, float* y, const float* x, float alph
                    size_t errlen) {
   EltArgs a;
   a.op = kOpAxpy;
-  a.a = y;
-  a.b = x;
-  a.y = y;
+  a.seg[0] = {y, x, y, n};
   a.alpha = alpha;
-  a.n = n;
   return RunElt(a, "halo_axpy", stream, err, errlen);
 }
 
@@ -658,6 +671,41 @@ int halo_b200_norm_rope_ex(halo_b200_stream stream, const void* in, int in_dtype
   return RunNormRope(a, theta, "halo_norm_rope", stream, err, errlen);
 }
 
+int halo_b200_norm_rope_qk_ex(halo_b200_stream stream, const void* q_in, uint64_t q_row_stride, void* q_out,
+                              void* q_gate, const float* w_q, uint32_t q_heads, const void* k_in, void* k_out,
+                              void* k_cache, const float* w_k, uint32_t k_heads, int in_dtype, int out_dtype,
+                              int one_plus, float eps, uint32_t d, uint32_t rotary_dim, uint32_t tokens, float theta,
+                              const uint32_t* params, uint32_t pstride, uint32_t slot, uint32_t pos0, uint32_t scale,
+                              uint32_t* pos_out, char* err, size_t errlen) {
+  NormRopeArgs a;
+  a.in = q_in;
+  a.in_dtype = in_dtype;
+  a.in_row_stride = q_row_stride;
+  a.out = q_out;
+  a.out_dtype = out_dtype;
+  a.gate = q_gate;
+  a.w = w_q;
+  a.heads = q_heads;
+  a.rows = tokens * q_heads;
+  a.in2 = k_in;
+  a.in_row_stride2 = d;
+  a.out2 = k_out;
+  a.cache2 = k_cache;
+  a.w2 = w_k;
+  a.heads2 = k_heads;
+  a.one_plus = one_plus;
+  a.eps = eps;
+  a.d = d;
+  a.rot = rotary_dim;
+  a.pos.params = params;
+  a.pos.pstride = pstride;
+  a.pos.slot = slot;
+  a.pos.pos0 = pos0;
+  a.pos.scale = scale;
+  a.pos_out = pos_out;
+  return RunNormRope(a, theta, "halo_norm_rope_qk", stream, err, errlen);
+}
+
 int halo_b200_split_qgate_norm_rope(halo_b200_stream stream, const float* qg, float* q, float* gate, const float* w,
                                     float eps, uint32_t rotary_dim, uint32_t pos0, uint32_t heads, float theta,
                                     uint32_t hd, uint32_t rows, char* err, size_t errlen) {
@@ -679,13 +727,24 @@ int halo_b200_silu_mul_ex(halo_b200_stream stream, const void* g, const void* up
                           uint64_t n, char* err, size_t errlen) {
   EltArgs a;
   a.op = kOpSiluMul;
-  a.a = g;
-  a.b = up;
+  a.seg[0] = {g, up, y, n};
   a.in_dtype = in_dtype;
-  a.y = y;
   a.y_dtype = y_dtype;
-  a.n = n;
   return RunElt(a, "halo_silu_mul", stream, err, errlen);
+}
+
+int halo_b200_silu_mul_multi_ex(halo_b200_stream stream, uint32_t nseg, const void* const* g, const void* const* up,
+                                void* const* y, const uint64_t* n, int in_dtype, int y_dtype, char* err,
+                                size_t errlen) {
+  REQUIRE(nseg >= 1 && nseg <= static_cast<uint32_t>(kMaxSegments), "halo_silu_mul_multi: 1..%d segments", kMaxSegments);
+  REQUIRE(g && up && y && n, "halo_silu_mul_multi: null argument array");
+  EltArgs a;
+  a.op = kOpSiluMul;
+  a.nseg = static_cast<int>(nseg);
+  for (uint32_t i = 0; i < nseg; ++i) a.seg[i] = {g[i], up[i], y[i], n[i]};
+  a.in_dtype = in_dtype;
+  a.y_dtype = y_dtype;
+  return RunElt(a, "halo_silu_mul_multi", stream, err, errlen);
 }
 int halo_b200_silu_mul(halo_b200_stream stream, float* g, const float* up, uint32_t n, char* err, size_t errlen) {
   return halo_b200_silu_mul_ex(stream, g, up, kF32, g, kF32, n, err, errlen);
@@ -698,10 +757,7 @@ int halo_b200_sigmoid_gate(halo_b200_stream stream, float* x, const float* gate,
                            size_t errlen) {
   EltArgs a;
   a.op = kOpSigmoidGate;
-  a.a = x;
-  a.b = gate;
-  a.y = x;
-  a.n = n;
+  a.seg[0] = {x, gate, x, n};
   return RunElt(a, "halo_sigmoid_gate", stream, err, errlen);
 }
 

@@ -45,16 +45,31 @@ __device__ __forceinline__ Oct apply8(const Oct& a, const Oct& b, float alpha) {
   return o;
 }
 
+// Kernel-side view of the segments: CTA b belongs to the segment s with
+// first_cta[s] <= b < first_cta[s + 1]; a CTA never straddles two tensors.
+struct VecSegments {
+  const void* a[kMaxSegments];
+  const void* b[kMaxSegments];
+  void* y[kMaxSegments];
+  uint64_t octs[kMaxSegments];
+  uint32_t first_cta[kMaxSegments + 1];
+  float alpha;
+};
+
 // The raw loads of all kUnroll octets are issued first (kUnroll * 2 * 16 bytes in flight per
 // thread); each octet is then converted, computed and stored in turn, which keeps the
 // register count low enough for 5 resident CTAs per SM.
 template <typename IT, typename OT, int OP>
-__global__ void __launch_bounds__(kBlock, sizeof(IT) == 4 ? 3 : 5) elementwise_vec_kernel(const EltArgs a, const uint64_t octs) {
-  const IT* pa = static_cast<const IT*>(a.a);
-  const IT* pb = static_cast<const IT*>(a.b);
-  OT* py = static_cast<OT*>(a.y);
-  const uint64_t base = static_cast<uint64_t>(blockIdx.x) * (kBlock * kUnroll) + threadIdx.x;
-  if (base + static_cast<uint64_t>(kUnroll - 1) * kBlock < octs) {  // the whole CTA tile is inside: no predicates
+__global__ void __launch_bounds__(kBlock, sizeof(IT) == 4 ? 3 : 5) elementwise_vec_kernel(const VecSegments v) {
+  int sidx = 0;
+#pragma unroll
+  for (int i = 1; i < kMaxSegments; ++i) sidx += blockIdx.x >= v.first_cta[i] ? 1 : 0;
+  const IT* pa = static_cast<const IT*>(v.a[sidx]);
+  const IT* pb = static_cast<const IT*>(v.b[sidx]);
+  OT* py = static_cast<OT*>(v.y[sidx]);
+  const uint64_t octs = v.octs[sidx];
+  const uint64_t base = static_cast<uint64_t>(blockIdx.x - v.first_cta[sidx]) * (kBlock * kUnroll) + threadIdx.x;
+  if (base + static_cast<uint64_t>(kUnroll - 1) * kBlock < octs) {  // the whole tile is inside: no predicates
     Raw<IT> ra[kUnroll], rb[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
@@ -65,48 +80,65 @@ __global__ void __launch_bounds__(kBlock, sizeof(IT) == 4 ? 3 : 5) elementwise_v
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const uint64_t j = base + static_cast<uint64_t>(u) * kBlock;
-      oct_store(py + j * 8, apply8<OP>(raw_unpack(ra[u]), raw_unpack(rb[u]), a.alpha));
+      oct_store(py + j * 8, apply8<OP>(raw_unpack(ra[u]), raw_unpack(rb[u]), v.alpha));
     }
   } else {
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const uint64_t j = base + static_cast<uint64_t>(u) * kBlock;
-      if (j < octs) oct_store(py + j * 8, apply8<OP>(oct_load(pa + j * 8), oct_load(pb + j * 8), a.alpha));
+      if (j < octs) oct_store(py + j * 8, apply8<OP>(oct_load(pa + j * 8), oct_load(pb + j * 8), v.alpha));
     }
   }
 }
 
 // Scalar path: unaligned buffers and the < 8 element tail of the vector path.
 template <typename IT, typename OT, int OP>
-__global__ void __launch_bounds__(kBlock) elementwise_scalar_kernel(const EltArgs a, const uint64_t begin) {
-  const IT* pa = static_cast<const IT*>(a.a);
-  const IT* pb = static_cast<const IT*>(a.b);
-  OT* py = static_cast<OT*>(a.y);
-  for (uint64_t i = begin + static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x; i < a.n;
+__global__ void __launch_bounds__(kBlock) elementwise_scalar_kernel(const IT* pa, const IT* pb, OT* py,
+                                                                   const uint64_t begin, const uint64_t n,
+                                                                   const float alpha) {
+  for (uint64_t i = begin + static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x; i < n;
        i += static_cast<uint64_t>(gridDim.x) * kBlock)
-    py[i] = from_f32<OT>(apply(OP, to_f32(pa[i]), to_f32(pb[i]), a.alpha));
+    py[i] = from_f32<OT>(apply(OP, to_f32(pa[i]), to_f32(pb[i]), alpha));
 }
 
 template <typename IT, typename OT, int OP>
 cudaError_t LaunchOp(const EltArgs& a, cudaStream_t s) {
-  uint64_t done = 0;
+  uint64_t done[kMaxSegments] = {};
   if (a.vec) {
-    const uint64_t octs = a.n / 8;
-    if (octs) {
-      const uint64_t per_cta = static_cast<uint64_t>(kBlock) * kUnroll;
-      const uint64_t grid = (octs + per_cta - 1) / per_cta;
-      if (grid > 0x7FFFFFFFull) return cudaErrorInvalidValue;
-      elementwise_vec_kernel<IT, OT, OP><<<static_cast<unsigned>(grid), kBlock, 0, s>>>(a, octs);
+    VecSegments v = {};
+    v.alpha = a.alpha;
+    const uint64_t per_cta = static_cast<uint64_t>(kBlock) * kUnroll;
+    uint64_t ctas = 0;
+    for (int i = 0; i < kMaxSegments; ++i) {
+      v.first_cta[i] = static_cast<uint32_t>(ctas);
+      if (i < a.nseg) {
+        v.a[i] = a.seg[i].a;
+        v.b[i] = a.seg[i].b;
+        v.y[i] = a.seg[i].y;
+        v.octs[i] = a.seg[i].n / 8;
+        done[i] = v.octs[i] * 8;
+        ctas += (v.octs[i] + per_cta - 1) / per_cta;
+        if (ctas > 0x7FFFFFFFull) return cudaErrorInvalidValue;
+      }
+    }
+    v.first_cta[kMaxSegments] = static_cast<uint32_t>(ctas);
+    for (int i = a.nseg; i < kMaxSegments; ++i) v.first_cta[i] = 0xFFFFFFFFu;  // never selected
+    if (ctas) {
+      elementwise_vec_kernel<IT, OT, OP><<<static_cast<unsigned>(ctas), kBlock, 0, s>>>(v);
       const cudaError_t e = cudaGetLastError();
       if (e != cudaSuccess) return e;
     }
-    done = octs * 8;
   }
-  if (done < a.n) {
-    uint64_t grid = (a.n - done + kBlock - 1) / kBlock;
-    if (grid > 148u * 32u) grid = 148u * 32u;
-    elementwise_scalar_kernel<IT, OT, OP><<<static_cast<unsigned>(grid), kBlock, 0, s>>>(a, done);
-    return cudaGetLastError();
+  for (int i = 0; i < a.nseg; ++i) {
+    if (done[i] < a.seg[i].n) {
+      uint64_t grid = (a.seg[i].n - done[i] + kBlock - 1) / kBlock;
+      if (grid > 148u * 32u) grid = 148u * 32u;
+      elementwise_scalar_kernel<IT, OT, OP><<<static_cast<unsigned>(grid), kBlock, 0, s>>>(
+          static_cast<const IT*>(a.seg[i].a), static_cast<const IT*>(a.seg[i].b), static_cast<OT*>(a.seg[i].y), done[i],
+          a.seg[i].n, a.alpha);
+      const cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return e;
+    }
   }
   return cudaSuccess;
 }
@@ -125,7 +157,7 @@ cudaError_t LaunchIO(const EltArgs& a, cudaStream_t s) {
 }  // namespace
 
 cudaError_t LaunchElementwise(const EltArgs& a, cudaStream_t s) {
-  if (a.n == 0) return cudaSuccess;
+  if (a.nseg < 1 || a.nseg > kMaxSegments) return cudaErrorInvalidValue;
   const int key = a.in_dtype * 3 + a.y_dtype;
   switch (key) {
     case kF32 * 3 + kF32: return LaunchIO<float, float>(a, s);

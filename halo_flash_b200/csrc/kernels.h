@@ -111,6 +111,14 @@ struct NormRopeArgs {
   int one_plus = 0;
   float eps = 0.0f;
   uint32_t d = 0, rot = 0, heads = 0, rows = 0;
+  // Optional second tensor with its own gamma, normalized and rotated in the same launch with
+  // the same positions (K beside Q): token t owns rows [t * heads2, (t + 1) * heads2) of it.
+  const void* in2 = nullptr;
+  uint64_t in_row_stride2 = 0;
+  void* out2 = nullptr;
+  void* cache2 = nullptr;
+  const float* w2 = nullptr;
+  uint32_t heads2 = 0;
   PosSpec pos;
   uint32_t* pos_out = nullptr;  // optional [rows / heads]
 };
@@ -129,16 +137,23 @@ cudaError_t LaunchSplitQgate(const SplitArgs& a, cudaStream_t s);
 
 // ---- group 4: elementwise ------------------------------------------------------------
 enum EltOp : int { kOpSiluMul = 0, kOpAdd = 1, kOpAxpy = 2, kOpSigmoidGate = 3 };
-struct EltArgs {
-  int op = kOpSiluMul;
+constexpr int kMaxSegments = 4;
+// One launch covers up to kMaxSegments independent tensors (e.g. the shared-expert and the
+// routed-expert gate/up rows of a MoE layer): small tensors stop paying a launch of their own.
+struct EltSegment {
   const void* a = nullptr;  // g (SiLU argument) / y (accumulator) / x
   const void* b = nullptr;  // up / x / gate
+  void* y = nullptr;        // may alias a
+  uint64_t n = 0;           // elements
+};
+struct EltArgs {
+  int op = kOpSiluMul;
+  int nseg = 1;
+  EltSegment seg[kMaxSegments];
   int in_dtype = kF32;
-  void* y = nullptr;  // may alias a
   int y_dtype = kF32;
   float alpha = 1.0f;  // axpy
-  uint64_t n = 0;
-  bool vec = true;
+  bool vec = true;     // every segment 16-byte aligned
 };
 cudaError_t LaunchElementwise(const EltArgs& a, cudaStream_t s);
 

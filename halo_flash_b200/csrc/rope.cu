@@ -75,142 +75,146 @@ __global__ void __launch_bounds__(kBlock) rope_kernel(const RopeArgs a, const __
   }
 }
 
-// RMSNorm (shared gamma) + RoPE on rows of d <= 256 (one row = one head of one token).
-// A CTA owns `tpc` whole tokens: it first fills shared (cos, -sin) / (cos, +sin) tables for
-// those tokens - one sincosf per token and frequency instead of one per head and lane - then
-// its thread groups walk the tokens' head rows, kRows rows per group per pass with all loads
-// issued up front. A group of g lanes (g <= 32, shuffles only) owns a row; lane `lir` holds
-// octets lir and (K == 2) lir + g. The sum of squares is formed exactly as the standalone
-// norm kernel forms it for the same row length, so fused equals norm-then-rope bit for bit.
-// Rotation: lane lir < half/8 holds the first halves of 8 pairs, lane lir + half/8 their
-// partners, both in the k = 0 octet (the launcher picks K == 2 only when rot <= d / 2); the
-// two exchange their normalized values with one shuffle per element and each computes
+// RMSNorm (shared gamma) + RoPE on rows of d <= 256 (one row = one head of one token), for one
+// tensor or for Q and K together. Rows are numbered token by token (token t: tensor 1's heads,
+// then tensor 2's); a CTA owns one pass of consecutive rows - kBlock / g thread groups x kRows
+// rows, 32 rows at d = 256 - so the grid has thousands of short-lived CTAs and no tail. It first
+// fills shared (cos, -sin) / (cos, +sin) tables for the two or three tokens those rows belong
+// to - one sincosf per token and frequency instead of one per head and lane - then every group
+// loads its kRows rows up front. A group of g lanes (g <= 32, shuffles only) owns a row; lane
+// `lir` holds octets lir and (K == 2) lir + g. The sum of squares is formed exactly as the
+// standalone norm kernel forms it for the same row length, so fused equals norm-then-rope bit
+// for bit. Rotation: lane lir < half/8 holds the first halves of 8 pairs, lane lir + half/8
+// their partners, both in the k = 0 octet (the launcher picks K == 2 only when rot <= d / 2);
+// the two exchange their normalized values with one shuffle per element and each computes
 // own * cos + other * (-/+ sin): the CPU operator's a*c - b*s and a*s + b*c, term for term.
 constexpr int kRows = 2;
 
+__device__ __forceinline__ uint32_t div_magic(uint32_t n, uint32_t d, uint32_t magic) {
+  return magic ? __umulhi(n, magic) : n / d;
+}
+
 template <typename IT, typename OT, int K>
 __global__ void __launch_bounds__(kBlock, K == 2 ? 3 : 4) norm_rope_kernel(const NormRopeArgs a, const __grid_constant__ InvFreq f,
-                                                             const unsigned lg, const unsigned tpc,
+                                                             const unsigned lg, const uint32_t rows_total,
                                                              const float inv_d, const uint32_t heads_magic) {
-  extern __shared__ float2 cs[];  // [2][tpc][half]: (cos, -sin) then (cos, +sin)
+  extern __shared__ float2 cs[];  // [2][ntok][half]: (cos, -sin) then (cos, +sin)
   const uint32_t half = a.rot / 2;
-  const uint32_t tokens = (a.rows + a.heads - 1) / a.heads;
-  const uint32_t t0 = blockIdx.x * tpc;
-  for (uint32_t idx = threadIdx.x; idx < tpc * half; idx += kBlock) {
-    const uint32_t t = t0 + idx / half, i = idx % half;
-    if (t < tokens) {
-      const uint32_t pos = token_pos(a.pos, t);
-      const float angle = __fmul_rn(static_cast<float>(pos), f.f[i]);
-      float sn, c;
-      sincosf(angle, &sn, &c);
-      cs[idx] = make_float2(c, -sn);
-      cs[tpc * half + idx] = make_float2(c, sn);
-      if (i == 0 && a.pos_out) a.pos_out[t] = pos;
-    }
+  const uint32_t hall = a.heads + a.heads2;
+  const unsigned slots = kBlock >> lg;
+  const uint32_t vr0 = blockIdx.x * (slots * kRows);
+  uint32_t vr1 = vr0 + slots * kRows;
+  if (vr1 > rows_total) vr1 = rows_total;
+  const uint32_t tok0 = div_magic(vr0, hall, heads_magic);
+  const uint32_t ntok = div_magic(vr1 - 1, hall, heads_magic) - tok0 + 1;
+  for (uint32_t idx = threadIdx.x; idx < ntok * half; idx += kBlock) {
+    const uint32_t t = tok0 + idx / half, i = idx % half;
+    const uint32_t pos = token_pos(a.pos, t);
+    const float angle = __fmul_rn(static_cast<float>(pos), f.f[i]);
+    float sn, c;
+    sincosf(angle, &sn, &c);
+    cs[idx] = make_float2(c, -sn);
+    cs[ntok * half + idx] = make_float2(c, sn);
+    // the first row of a token writes its position (exactly one CTA holds that row)
+    if (i == 0 && a.pos_out && t * hall >= vr0) a.pos_out[t] = pos;
   }
   __syncthreads();
 
   const unsigned g = 1u << lg;
   const unsigned lane = threadIdx.x & 31u;
   const unsigned lir = threadIdx.x & (g - 1);
-  const unsigned slots = kBlock >> lg, slot = threadIdx.x >> lg;
+  const unsigned slot = threadIdx.x >> lg;
   const unsigned octs = a.d >> 3;
   const unsigned hp = a.rot / 16;  // lanes per half of the rotated span
   const bool rotates = lir < 2 * hp;
   const bool low = lir < hp;
   const unsigned src_lane = lane - lir + (rotates ? (low ? lir + hp : lir - hp) : lir);
-  const float2* lane_tab = cs + (low ? 0u : tpc * half) + (low ? lir : lir - hp) * 8;
-  const uint32_t row_begin = t0 * a.heads;
-  uint32_t row_end = (t0 + tpc) * a.heads;
-  if (row_end > a.rows) row_end = a.rows;
+  const float2* lane_tab = cs + (low ? 0u : ntok * half) + (low ? lir : lir - hp) * 8;
 
-  Oct gm[K];
+  Raw<IT> raw[kRows][K];
+  bool ok[kRows][K];
+  size_t out_off[kRows];
+  uint32_t tl[kRows];
+  bool second[kRows];
 #pragma unroll
-  for (int k = 0; k < K; ++k) {
-    const unsigned j = (k << lg) + lir;
-    gm[k] = oct_zero();
-    if (a.w && j < octs) {
-      gm[k] = oct_load_cached(a.w + j * 8);
-      if (a.one_plus) {
-        const float2 one = make_float2(1.0f, 1.0f);
+  for (int u = 0; u < kRows; ++u) {
+    const uint32_t vr = vr0 + u * slots + slot;
+    const bool in_cta = vr < vr1;
+    const uint32_t token = in_cta ? div_magic(vr, hall, heads_magic) : tok0;
+    tl[u] = token - tok0;
+    const uint32_t h = in_cta ? vr - token * hall : 0;
+    second[u] = h >= a.heads;
+    const size_t row = second[u] ? static_cast<size_t>(token) * a.heads2 + (h - a.heads)
+                                 : static_cast<size_t>(token) * a.heads + h;
+    const bool row_ok = in_cta && (second[u] || row < a.rows);
+    const IT* src = second[u] ? static_cast<const IT*>(a.in2) + row * a.in_row_stride2
+                              : static_cast<const IT*>(a.in) + row * a.in_row_stride;
+    out_off[u] = row * a.d;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) gm[k].p[i] = __fadd2_rn(one, gm[k].p[i]);
-      }
+    for (int k = 0; k < K; ++k) {
+      const unsigned j = (k << lg) + lir;
+      ok[u][k] = row_ok && j < octs;
+      raw[u][k] = Raw<IT>{};
+      if (ok[u][k]) raw[u][k] = raw_load(src + j * 8);
     }
-  }
-
-  for (uint32_t base = row_begin; base < row_end; base += slots * kRows) {
-    Raw<IT> raw[kRows][K];
-    bool ok[kRows][K];
-#pragma unroll
-    for (int u = 0; u < kRows; ++u) {
-      const uint32_t row = base + u * slots + slot;
-      const IT* src = static_cast<const IT*>(a.in) + static_cast<size_t>(row) * a.in_row_stride;
+    if (a.gate && !second[u]) {
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         const unsigned j = (k << lg) + lir;
-        ok[u][k] = row < row_end && j < octs;
-        if (ok[u][k]) raw[u][k] = raw_load(src + j * 8);
-        else raw[u][k] = Raw<IT>{};
+        if (ok[u][k]) oct_store(static_cast<IT*>(a.gate) + out_off[u] + j * 8, oct_load(src + a.d + j * 8));
       }
     }
-    if (a.gate) {
+  }
 #pragma unroll
-      for (int u = 0; u < kRows; ++u) {
-        const uint32_t row = base + u * slots + slot;
+  for (int u = 0; u < kRows; ++u) {
+    Oct x[K];
 #pragma unroll
-        for (int k = 0; k < K; ++k) {
-          const unsigned j = (k << lg) + lir;
-          if (ok[u][k]) {
-            const Oct gt = oct_load(static_cast<const IT*>(a.in) + static_cast<size_t>(row) * a.in_row_stride + a.d + j * 8);
-            oct_store(static_cast<IT*>(a.gate) + static_cast<size_t>(row) * a.d + j * 8, gt);
-          }
-        }
-      }
-    }
+    for (int k = 0; k < K; ++k) x[k] = raw_unpack(raw[u][k]);
+    if (a.w) {  // the norm kernel's arithmetic for a row of this length, step for step
+      float2 acc = make_float2(0.0f, 0.0f);
 #pragma unroll
-    for (int u = 0; u < kRows; ++u) {
-      const uint32_t row = base + u * slots + slot;
-      Oct x[K];
+      for (int k = 0; k < K; ++k) acc = oct_sumsq(x[k], acc);
+      const float ss = group_sum(acc.x + acc.y, g, nullptr);  // g <= 32: shuffles only
+      const float scale = rsqrtf(__fmaf_rn(ss, inv_d, a.eps));
+      const float* w = second[u] ? a.w2 : a.w;  // 1 KiB, resident in L1 after the first rows
 #pragma unroll
-      for (int k = 0; k < K; ++k) x[k] = raw_unpack(raw[u][k]);
-      if (a.w) {  // the norm kernel's arithmetic for a row of this length, step for step
-        float2 acc = make_float2(0.0f, 0.0f);
-#pragma unroll
-        for (int k = 0; k < K; ++k) acc = oct_sumsq(x[k], acc);
-        const float ss = group_sum(acc.x + acc.y, g, nullptr);  // g <= 32: shuffles only
-        const float scale = rsqrtf(__fmaf_rn(ss, inv_d, a.eps));
-#pragma unroll
-        for (int k = 0; k < K; ++k) x[k] = oct_mul(oct_scale(x[k], scale), gm[k]);
-      }
-      float v[8];
-      oct_to_array(x[0], v);
-      const uint32_t rl = row < row_end ? row - row_begin : 0;
-      const uint32_t tl = heads_magic ? __umulhi(rl, heads_magic) : rl / a.heads;
-      const float2* tab = lane_tab + tl * half;
-#pragma unroll
-      for (int i = 0; i < 8; i += 2) {
-        const float o0 = __shfl_sync(kFullMask, v[i], src_lane);
-        const float o1 = __shfl_sync(kFullMask, v[i + 1], src_lane);
-        if (rotates) {
-          const float4 t4 = *reinterpret_cast<const float4*>(tab + i);  // (cos, sin) of two frequencies
-          v[i] = v[i] * t4.x + o0 * t4.y;
-          v[i + 1] = v[i + 1] * t4.z + o1 * t4.w;
-        }
-      }
-      OT* dst = static_cast<OT*>(a.out) + static_cast<size_t>(row) * a.d;
-      OT* cdst = a.cache ? static_cast<OT*>(a.cache) + static_cast<size_t>(row) * a.d : nullptr;
-      if (ok[u][0]) {
-        store8(dst + lir * 8, v);
-        if (cdst) store8(cdst + lir * 8, v);
-      }
-#pragma unroll
-      for (int k = 1; k < K; ++k) {
+      for (int k = 0; k < K; ++k) {
         const unsigned j = (k << lg) + lir;
-        if (ok[u][k]) {
-          oct_store(dst + j * 8, x[k]);
-          if (cdst) oct_store(cdst + j * 8, x[k]);
+        Oct gm = j < octs ? oct_load_cached(w + j * 8) : oct_zero();
+        if (a.one_plus) {
+          const float2 one = make_float2(1.0f, 1.0f);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) gm.p[i] = __fadd2_rn(one, gm.p[i]);
         }
+        x[k] = oct_mul(oct_scale(x[k], scale), gm);
+      }
+    }
+    float v[8];
+    oct_to_array(x[0], v);
+    const float2* tab = lane_tab + tl[u] * half;
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+      const float o0 = __shfl_sync(kFullMask, v[i], src_lane);
+      const float o1 = __shfl_sync(kFullMask, v[i + 1], src_lane);
+      if (rotates) {
+        const float4 t4 = *reinterpret_cast<const float4*>(tab + i);  // (cos, sin) of two frequencies
+        v[i] = v[i] * t4.x + o0 * t4.y;
+        v[i + 1] = v[i + 1] * t4.z + o1 * t4.w;
+      }
+    }
+    OT* dst = static_cast<OT*>(second[u] ? a.out2 : a.out) + out_off[u];
+    void* cache = second[u] ? a.cache2 : a.cache;
+    OT* cdst = cache ? static_cast<OT*>(cache) + out_off[u] : nullptr;
+    if (ok[u][0]) {
+      store8(dst + lir * 8, v);
+      if (cdst) store8(cdst + lir * 8, v);
+    }
+#pragma unroll
+    for (int k = 1; k < K; ++k) {
+      const unsigned j = (k << lg) + lir;
+      if (ok[u][k]) {
+        oct_store(dst + j * 8, x[k]);
+        if (cdst) oct_store(cdst + j * 8, x[k]);
       }
     }
   }
@@ -252,15 +256,6 @@ cudaError_t LaunchRopeT(const RopeArgs& a, const InvFreq& f, cudaStream_t s) {
   return cudaGetLastError();
 }
 
-unsigned Gcd(unsigned a, unsigned b) {
-  while (b) {
-    const unsigned t = a % b;
-    a = b;
-    b = t;
-  }
-  return a;
-}
-
 template <typename IT, typename OT>
 cudaError_t LaunchNormRopeT(const NormRopeArgs& a, const InvFreq& f, cudaStream_t s) {
   const unsigned octs = a.d / 8;
@@ -269,23 +264,23 @@ cudaError_t LaunchNormRopeT(const NormRopeArgs& a, const InvFreq& f, cudaStream_
   const int k = (octs >= 2 && a.rot * 2 <= a.d) ? 2 : 1;
   unsigned g = 1, lg = 0;
   while (g * k < octs) g <<= 1, ++lg;
-  // whole tokens per CTA such that the CTA's rows fill its passes (groups x kRows rows each)
-  const unsigned rows_per_pass = kBlock / g * kRows;
-  unsigned tpc = rows_per_pass / Gcd(rows_per_pass, a.heads);
-  if (tpc > 32) tpc = 32;
+  const unsigned rows_per_cta = kBlock / g * kRows;
+  const unsigned hall = a.heads + a.heads2;
   const unsigned tokens = (a.rows + a.heads - 1) / a.heads;
-  if (tpc > tokens) tpc = tokens;
-  // ... but never so many that the grid falls under about three CTAs per SM
-  while (tpc > 1 && (tokens + tpc - 1) / tpc < 148u * 3u) tpc = (tpc + 1) / 2;
-  const unsigned grid = (tokens + tpc - 1) / tpc;
-  const size_t smem = 2 * static_cast<size_t>(tpc) * (a.rot / 2) * sizeof(float2);
+  const uint64_t rows_total = static_cast<uint64_t>(tokens) * hall;
+  if (rows_total > 0xFFFFFFFFull) return cudaErrorInvalidValue;
+  const unsigned grid = static_cast<unsigned>((rows_total + rows_per_cta - 1) / rows_per_cta);
+  const unsigned max_tok = rows_per_cta / hall + 2;  // tokens a CTA's rows can touch
+  const size_t smem = 2 * static_cast<size_t>(max_tok) * (a.rot / 2) * sizeof(float2);
+  if (smem > 48u * 1024u) return cudaErrorInvalidValue;
   const float inv_d = 1.0f / static_cast<float>(a.d);
-  // floor(n / heads) == umulhi(n, ceil(2^32 / heads)) for the n < 2^16 a CTA can see
-  const uint32_t magic = (a.heads > 1 && a.heads < 2048)
-                             ? static_cast<uint32_t>(((1ull << 32) + a.heads - 1) / a.heads)
+  // floor(n / hall) == umulhi(n, ceil(2^32 / hall)) whenever n * hall < 2^32
+  const uint32_t magic = (hall > 1 && rows_total * hall < (1ull << 32))
+                             ? static_cast<uint32_t>(((1ull << 32) + hall - 1) / hall)
                              : 0u;
-  if (k == 2) norm_rope_kernel<IT, OT, 2><<<grid, kBlock, smem, s>>>(a, f, lg, tpc, inv_d, magic);
-  else norm_rope_kernel<IT, OT, 1><<<grid, kBlock, smem, s>>>(a, f, lg, tpc, inv_d, magic);
+  const uint32_t rt = static_cast<uint32_t>(rows_total);
+  if (k == 2) norm_rope_kernel<IT, OT, 2><<<grid, kBlock, smem, s>>>(a, f, lg, rt, inv_d, magic);
+  else norm_rope_kernel<IT, OT, 1><<<grid, kBlock, smem, s>>>(a, f, lg, rt, inv_d, magic);
   return cudaGetLastError();
 }
 

@@ -134,6 +134,21 @@ def norm_rope(x, w, eps, rot, theta, heads, *, out=None, gate=None, cache=None, 
     return out
 
 
+def norm_rope_qk(q, k, w_q, w_k, eps, rot, theta, *, q_out=None, q_gate=None, k_cache=None, one_plus=True,
+                 q_row_stride=None, pos0=0, params=None, pstride=0, slot=0, scale=1, pos_out=None):
+    """Per-head RMSNorm + RoPE of Q [T, Hq, d] and K [T, Hk, d] in one launch (in place unless q_out is given)."""
+    _chk(q, "q", _ACT), _chk(k, "k", (q.dtype,)), _chk(w_q, "w_q", (torch.float32,)), _chk(w_k, "w_k", (torch.float32,))
+    q_out = q if q_out is None else _chk(q_out, "q_out", _ACT)
+    _chk(q_gate, "q_gate", (q.dtype,)), _chk(k_cache, "k_cache", (q_out.dtype,))
+    tokens, hq, d = q_out.shape
+    hk = k.shape[1]
+    stride = d if q_row_stride is None else q_row_stride
+    lib().call("norm_rope_qk_ex", _stream(), _p(q), stride, _p(q_out), _p(q_gate), _p(w_q), hq, _p(k), _p(k), _p(k_cache),
+               _p(w_k), hk, _code(q), _code(q_out), int(one_plus), eps, d, rot, tokens, theta, _p(params), pstride, slot,
+               pos0, scale, _p(pos_out))
+    return q_out, k
+
+
 # ---- group 4 ---------------------------------------------------------------
 def silu_mul(g, up, *, y=None):
     """y = SiLU(g) * up elementwise; y defaults to g (in place)."""
@@ -141,6 +156,21 @@ def silu_mul(g, up, *, y=None):
     y = g if y is None else _chk(y, "y", _ACT)
     lib().call("silu_mul_ex", _stream(), _p(g), _p(up), _code(g), _p(y), _code(y), g.numel())
     return y
+
+
+def silu_mul_multi(pairs, outs):
+    """SiLU(g) * up for several (g, up) -> y tensors in one launch (at most 4; same dtypes)."""
+    import ctypes as C
+    n = len(pairs)
+    assert n == len(outs) and 1 <= n <= 4
+    for (g, up), y in zip(pairs, outs):
+        _chk(g, "g", _ACT), _chk(up, "up", (pairs[0][0].dtype,)), _chk(y, "y", (outs[0].dtype,))
+        assert g.dtype == pairs[0][0].dtype and g.numel() == up.numel() == y.numel()
+    arr = lambda vals: (C.c_void_p * n)(*vals)
+    gs, us, ys = arr([g.data_ptr() for g, _ in pairs]), arr([u.data_ptr() for _, u in pairs]), arr([y.data_ptr() for y in outs])
+    ns = (C.c_uint64 * n)(*[g.numel() for g, _ in pairs])
+    lib().call("silu_mul_multi_ex", _stream(), n, gs, us, ys, ns, _code(pairs[0][0]), _code(outs[0]))
+    return outs
 
 
 # ---- group 5 ---------------------------------------------------------------

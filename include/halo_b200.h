@@ -199,6 +199,19 @@ int halo_b200_norm_rope_ex(halo_b200_stream stream, const void* in, int in_dtype
                            const uint32_t* params, uint32_t pstride, uint32_t slot, uint32_t pos0, uint32_t scale,
                            uint32_t* pos_out, char* err, size_t errlen);
 
+/* Q and K of one attention layer in ONE launch: per-head RMSNorm (gammas w_q / w_k, or 1 + w) and
+ * RoPE at the same positions, the sequence of src/model/qwen35.cpp:251-255. Q rows
+ * [tokens * q_heads] are q_row_stride elements apart in q_in (d, or 2 * d with the gate halves
+ * copied to q_gate); K rows [tokens * k_heads][d] may also be appended to k_cache. Outputs may
+ * alias inputs (q_row_stride == d). The small K tensor stops paying a launch of its own and
+ * the (cos, sin) tables are computed once for both. */
+int halo_b200_norm_rope_qk_ex(halo_b200_stream stream, const void* q_in, uint64_t q_row_stride, void* q_out,
+                              void* q_gate, const float* w_q, uint32_t q_heads, const void* k_in, void* k_out,
+                              void* k_cache, const float* w_k, uint32_t k_heads, int in_dtype, int out_dtype,
+                              int one_plus, float eps, uint32_t d, uint32_t rotary_dim, uint32_t tokens, float theta,
+                              const uint32_t* params, uint32_t pstride, uint32_t slot, uint32_t pos0, uint32_t scale,
+                              uint32_t* pos_out, char* err, size_t errlen);
+
 /* ---- group 4: SwiGLU ----------------------------------------------------------------- */
 
 /* halo_silu_mul, src/kernels/core.hip:321-325: g = SiLU(g) * up. */
@@ -211,6 +224,13 @@ int halo_b200_silu_mul_h(halo_b200_stream stream, const float* g, const float* u
  * (f16,f16), (bf16, bf16|f32). y may alias g when the dtypes match. */
 int halo_b200_silu_mul_ex(halo_b200_stream stream, const void* g, const void* up, int in_dtype, void* y, int y_dtype,
                           uint64_t n, char* err, size_t errlen);
+/* The same op over up to 4 independent tensors in ONE launch (e.g. the shared-expert rows [T x ff]
+ * and the routed-expert rows [T*k x ff] of a MoE layer, which the reference computes in two GEMM
+ * epilogues, src/kernels/core.hip:2937, 5257). g, up, y, n are HOST arrays of nseg entries, read
+ * at call time; small tensors stop paying a launch of their own. */
+int halo_b200_silu_mul_multi_ex(halo_b200_stream stream, uint32_t nseg, const void* const* g, const void* const* up,
+                                void* const* y, const uint64_t* n, int in_dtype, int y_dtype, char* err,
+                                size_t errlen);
 /* halo_sigmoid_gate, src/kernels/core.hip:335-339: x *= sigmoid(gate). */
 int halo_b200_sigmoid_gate(halo_b200_stream stream, float* x, const float* gate, uint32_t n, char* err,
                            size_t errlen);

@@ -674,3 +674,62 @@ def test_lean_and_general_norm_kernels_agree_bit_for_bit():
             lib().tune("norm_force_general", 0)
     for a, b in zip(*outs):
         assert torch.equal(a, b)
+
+
+def test_q_and_k_norm_rope_in_one_launch(orc):
+    """halo_b200_norm_rope_qk_ex == the two single-tensor launches bit for bit, and matches the oracle;
+    also the q|gate split with K appended to a cache."""
+    s, T, pos0 = synth.FULL, 21, 4000
+    hd = s.head_dim
+    q = rounded(synth.act("t.qk.q", T, s.q_heads, hd), "bf16")
+    k = rounded(synth.act("t.qk.k", T, s.kv_heads, hd), "bf16")
+    wq, wk = synth.norm_w("t.qk.wq", hd), synth.norm_w("t.qk.wk", hd)
+    dwq, dwk = to_dev(wq), to_dev(wk)
+    q1, k1 = to_dev(q, "bf16"), to_dev(k, "bf16")
+    ops.norm_rope(q1.view(-1, hd), dwq, s.eps, s.rot, s.theta, s.q_heads, pos0=pos0)
+    ops.norm_rope(k1.view(-1, hd), dwk, s.eps, s.rot, s.theta, s.kv_heads, pos0=pos0)
+    q2, k2 = to_dev(q, "bf16"), to_dev(k, "bf16")
+    used = Guarded((T,), torch.int32)
+    ops.norm_rope_qk(q2, k2, dwq, dwk, s.eps, s.rot, s.theta, pos0=pos0, pos_out=used.t)
+    assert torch.equal(q1, q2) and torch.equal(k1, k2)
+    assert np.array_equal(used.t.cpu().numpy(), np.arange(pos0, pos0 + T))
+    used.check()
+    pos = np.arange(pos0, pos0 + T, dtype=np.uint32)
+    wantq = orc.rope_rows(orc.rmsnorm_rows(q.reshape(-1, hd).copy(), ONE + wq, s.eps).reshape(q.shape), pos, s.rot, s.theta)
+    wantk = orc.rope_rows(orc.rmsnorm_rows(k.reshape(-1, hd).copy(), ONE + wk, s.eps).reshape(k.shape), pos, s.rot, s.theta)
+    assert_bf16_within_1ulp(bits16(q2), wantq, "q")
+    assert_bf16_within_1ulp(bits16(k2), wantk, "k")
+    # fp32, interleaved q|gate rows, K cache append, tiny shapes (4 Q / 2 KV heads x 64, rot 16)
+    c, T2 = synth.C1, 9
+    qg = synth.act("t.qk.qg", T2 * c.q_heads, 2 * c.head_dim)
+    kk = synth.act("t.qk.kk", T2, c.kv_heads, c.head_dim)
+    w1, w2 = synth.norm_w("t.qk.w1", c.head_dim), synth.norm_w("t.qk.w2", c.head_dim)
+    qo, gate = Guarded((T2, c.q_heads, c.head_dim), torch.float32), Guarded((T2 * c.q_heads, c.head_dim), torch.float32)
+    cache = Guarded((T2, c.kv_heads, c.head_dim), torch.float32)
+    dk = to_dev(kk)
+    ops.norm_rope_qk(to_dev(qg), dk, to_dev(w1), to_dev(w2), c.eps, c.rot, c.theta, q_out=qo.t, q_gate=gate.t,
+                     k_cache=cache.t, q_row_stride=2 * c.head_dim, pos0=77)
+    p2 = np.arange(77, 77 + T2, dtype=np.uint32)
+    wq2 = orc.rope_rows(orc.rmsnorm_rows(np.ascontiguousarray(qg[:, :c.head_dim]), ONE + w1, c.eps).reshape(T2, c.q_heads, -1), p2, c.rot, c.theta)
+    wk2 = orc.rope_rows(orc.rmsnorm_rows(kk.reshape(-1, c.head_dim).copy(), ONE + w2, c.eps).reshape(kk.shape), p2, c.rot, c.theta)
+    assert_rows_close(to_f32(qo.t).reshape(-1, c.head_dim), wq2.reshape(-1, c.head_dim), what="q of q|gate")
+    assert_rows_close(to_f32(dk).reshape(-1, c.head_dim), wk2.reshape(-1, c.head_dim), what="k")
+    assert to_f32(gate.t).tobytes() == np.ascontiguousarray(qg[:, c.head_dim:]).tobytes()
+    assert torch.equal(cache.t, dk)
+    for gd in (qo, gate, cache):
+        gd.check()
+
+
+def test_swiglu_several_tensors_in_one_launch(orc):
+    shapes = [(4096 * 3, ), (7, 512), (1, 8), (33, 5)]  # the last two exercise the tile tail and the scalar tail
+    gs = [rounded(synth.act(f"t.mm.g{i}", *sh) * 3, "bf16") for i, sh in enumerate(shapes)]
+    us = [rounded(synth.act(f"t.mm.u{i}", *sh), "bf16") for i, sh in enumerate(shapes)]
+    outs = [Guarded(sh, torch.bfloat16) for sh in shapes]
+    ops.silu_mul_multi([(to_dev(g, "bf16"), to_dev(u, "bf16")) for g, u in zip(gs, us)], [o.t for o in outs])
+    for g, u, o in zip(gs, us, outs):
+        want = orc.silu_mul(g.copy().reshape(-1), u.reshape(-1))
+        assert_bf16_within_1ulp(bits16(o.t).reshape(-1), want, "multi swiglu")
+        o.check()
+    single = Guarded(shapes[0], torch.bfloat16)
+    ops.silu_mul(to_dev(gs[0], "bf16"), to_dev(us[0], "bf16"), y=single.t)
+    assert torch.equal(single.t, outs[0].t)
