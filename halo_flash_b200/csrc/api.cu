@@ -17,6 +17,7 @@ namespace {
 std::atomic<int> g_norm_threads_per_row{0};
 std::atomic<int> g_norm_short_rows_k1{0};
 std::atomic<int> g_norm_force_general{0};
+std::atomic<int> g_rope_rows_per_group{0};
 
 int Fail(char* err, size_t errlen, const char* fmt, ...) {
   if (err && errlen) {
@@ -184,6 +185,7 @@ int RunNormRope(NormRopeArgs a, float theta, const char* what, halo_b200_stream 
   REQUIRE(a.gate == nullptr || a.in_row_stride >= 2ull * a.d, "%s: gate needs q|gate rows (in_row_stride >= 2 d)", what);
   InvFreq f;
   REQUIRE(FillInvFreq(&f, a.rot, theta), "%s: rotary_dim too large", what);
+  a.rows_per_group = g_rope_rows_per_group.load(std::memory_order_relaxed);
   const bool vec = a.d % 8 == 0 && (a.rot / 2) % 8 == 0 && a.in_row_stride % 8 == 0 && Aligned(a.in, 16) &&
                    Aligned(a.out, 16) && Aligned(a.gate, 16) && Aligned(a.cache, 16) && Aligned(a.w, 16) &&
                    a.in_row_stride2 % 8 == 0 && Aligned(a.in2, 16) && Aligned(a.out2, 16) && Aligned(a.cache2, 16) &&
@@ -262,6 +264,11 @@ int halo_b200_tune(const char* key, int value) {
   if (std::strcmp(key, "norm_threads_per_row") == 0) {
     if (value < 0 || value > 256 || (value & (value - 1)) != 0) return -1;
     g_norm_threads_per_row.store(value, std::memory_order_relaxed);
+    return 0;
+  }
+  if (std::strcmp(key, "rope_rows_per_group") == 0) {
+    if (value != 0 && value != 2 && value != 4) return -1;
+    g_rope_rows_per_group.store(value, std::memory_order_relaxed);
     return 0;
   }
   if (std::strcmp(key, "norm_force_general") == 0) {

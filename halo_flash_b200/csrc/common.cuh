@@ -269,8 +269,12 @@ __device__ __forceinline__ Oct raw_unpack(const Raw<f16>& r) { return oct_unpack
 // aligned to g within the CTA). g <= 32: shuffles only. g > 32: one shared-memory
 // stage; `scratch` holds kBlock / 32 floats and every thread of the CTA must call.
 __device__ __forceinline__ float group_sum(float v, unsigned g, float* scratch) {
-  const unsigned gl = g < 32u ? g : 32u;
-  for (unsigned o = gl >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(kFullMask, v, o);
+  // Butterfly over min(g, 32) lanes, widest stride first. Fully unrolled with warp-uniform
+  // guards: the same additions in the same order as a loop from g/2 down to 1, without its
+  // loop-carried compare and branch.
+#pragma unroll
+  for (unsigned o = 16; o > 0; o >>= 1)
+    if (o < g) v += __shfl_xor_sync(kFullMask, v, o);
   if (g > 32u) {
     const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     if (lane == 0) scratch[warp] = v;

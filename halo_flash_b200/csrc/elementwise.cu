@@ -29,7 +29,9 @@ __device__ __forceinline__ Oct apply8(const Oct& a, const Oct& b, float alpha) {
   if constexpr (OP == kOpAdd) {
     o = oct_add(a, b);
   } else if constexpr (OP == kOpAxpy) {
-    o = oct_add(a, oct_scale(b, alpha));
+    // scalar on purpose: a packed multiply feeding a packed add was seen to contract into an FMA
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o.p[i] = make_float2(a.p[i].x + alpha * b.p[i].x, a.p[i].y + alpha * b.p[i].y);
   } else {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {

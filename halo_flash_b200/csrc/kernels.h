@@ -121,6 +121,7 @@ struct NormRopeArgs {
   uint32_t heads2 = 0;
   PosSpec pos;
   uint32_t* pos_out = nullptr;  // optional [rows / heads]
+  int rows_per_group = 0;       // rows a thread group keeps in flight: 2 (default) or 4
 };
 cudaError_t LaunchNormRope(const NormRopeArgs& a, const InvFreq& f, cudaStream_t s);
 

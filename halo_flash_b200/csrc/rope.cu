@@ -76,52 +76,46 @@ __global__ void __launch_bounds__(kBlock) rope_kernel(const RopeArgs a, const __
 }
 
 // RMSNorm (shared gamma) + RoPE on rows of d <= 256 (one row = one head of one token), for one
-// tensor or for Q and K together. Rows are numbered token by token (token t: tensor 1's heads,
-// then tensor 2's); a CTA owns one pass of consecutive rows - kBlock / g thread groups x kRows
-// rows, 32 rows at d = 256 - so the grid has thousands of short-lived CTAs and no tail. It first
-// fills shared (cos, -sin) / (cos, +sin) tables for the two or three tokens those rows belong
-// to - one sincosf per token and frequency instead of one per head and lane - then every group
-// loads its kRows rows up front. A group of g lanes (g <= 32, shuffles only) owns a row; lane
-// `lir` holds octets lir and (K == 2) lir + g. The sum of squares is formed exactly as the
-// standalone norm kernel forms it for the same row length, so fused equals norm-then-rope bit
-// for bit. Rotation: lane lir < half/8 holds the first halves of 8 pairs, lane lir + half/8
-// their partners, both in the k = 0 octet (the launcher picks K == 2 only when rot <= d / 2);
-// the two exchange their normalized values with one shuffle per element and each computes
-// own * cos + other * (-/+ sin): the CPU operator's a*c - b*s and a*s + b*c, term for term.
-constexpr int kRows = 2;
-
+// tensor or for Q and K in one launch (the first CTAs take Q's rows, the rest K's: which tensor
+// a CTA works on is uniform, so nothing is selected per row). A CTA owns one pass of consecutive
+// rows - kBlock / g thread groups x ROWS rows, 32 or 64 rows at d = 256 - so the grid has
+// thousands of short-lived CTAs and no tail. It first fills shared cos and signed-sin tables
+// for the few tokens those rows belong to - one sincosf per token and frequency instead of one
+// per head and lane - then every group loads its rows up front. A group of g lanes (g <= 32,
+// shuffles only) owns a row; lane `lir` holds octets lir and (K == 2) lir + g. The sum of squares
+// is formed exactly as the standalone norm kernel forms it for the same row length, so fused
+// equals norm-then-rope bit for bit. Rotation: lane lir < half/8 holds the first halves of 8
+// pairs, lane lir + half/8 their partners, both in the k = 0 octet (the launcher picks K == 2 only
+// when rot <= d / 2); the two exchange their normalized values with one shuffle per element and
+// each computes own * cos + other * (-/+ sin): the CPU operator's a*c - b*s and a*s + b*c, term
+// for term. FULL: every row of the CTA exists and d == 8 K g, so nothing is predicated.
 __device__ __forceinline__ uint32_t div_magic(uint32_t n, uint32_t d, uint32_t magic) {
   return magic ? __umulhi(n, magic) : n / d;
 }
 
-template <typename IT, typename OT, int K>
-__global__ void __launch_bounds__(kBlock, K == 2 ? 3 : 4) norm_rope_kernel(const NormRopeArgs a, const __grid_constant__ InvFreq f,
-                                                             const unsigned lg, const uint32_t rows_total,
-                                                             const float inv_d, const uint32_t heads_magic) {
-  extern __shared__ float2 cs[];  // [2][ntok][half]: (cos, -sin) then (cos, +sin)
-  const uint32_t half = a.rot / 2;
-  const uint32_t hall = a.heads + a.heads2;
-  const unsigned slots = kBlock >> lg;
-  const uint32_t vr0 = blockIdx.x * (slots * kRows);
-  uint32_t vr1 = vr0 + slots * kRows;
-  if (vr1 > rows_total) vr1 = rows_total;
-  const uint32_t tok0 = div_magic(vr0, hall, heads_magic);
-  const uint32_t ntok = div_magic(vr1 - 1, hall, heads_magic) - tok0 + 1;
-  for (uint32_t idx = threadIdx.x; idx < ntok * half; idx += kBlock) {
-    const uint32_t t = tok0 + idx / half, i = idx % half;
-    const uint32_t pos = token_pos(a.pos, t);
-    const float angle = __fmul_rn(static_cast<float>(pos), f.f[i]);
-    float sn, c;
-    sincosf(angle, &sn, &c);
-    cs[idx] = make_float2(c, -sn);
-    cs[ntok * half + idx] = make_float2(c, sn);
-    // the first row of a token writes its position (exactly one CTA holds that row)
-    if (i == 0 && a.pos_out && t * hall >= vr0) a.pos_out[t] = pos;
-  }
-  __syncthreads();
+struct RopeCta {
+  const void* in;
+  uint64_t in_row_stride;
+  void* out;
+  void* gate;
+  void* cache;
+  const float* w;
+  uint32_t heads, rows, magic;
+};
 
+template <typename IT, typename OT, int K, int ROWS, bool FULL>
+__device__ __forceinline__ void norm_rope_body(const RopeCta t, const NormRopeArgs& a, const InvFreq& f,
+                                               const unsigned lg, const uint32_t cta, const float inv_d,
+                                               float* smem) {
+  const uint32_t half = a.rot / 2;
+  const unsigned slots = kBlock >> lg;
+  const uint32_t r0 = cta * (slots * ROWS);  // first row of this CTA within its tensor
+  uint32_t r1 = r0 + slots * ROWS;
+  if (!FULL && r1 > t.rows) r1 = t.rows;
+  const uint32_t tok0 = div_magic(r0, t.heads, t.magic);
+  const uint32_t ntok = div_magic(r1 - 1, t.heads, t.magic) - tok0 + 1;
+  const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const unsigned g = 1u << lg;
-  const unsigned lane = threadIdx.x & 31u;
   const unsigned lir = threadIdx.x & (g - 1);
   const unsigned slot = threadIdx.x >> lg;
   const unsigned octs = a.d >> 3;
@@ -129,95 +123,135 @@ __global__ void __launch_bounds__(kBlock, K == 2 ? 3 : 4) norm_rope_kernel(const
   const bool rotates = lir < 2 * hp;
   const bool low = lir < hp;
   const unsigned src_lane = lane - lir + (rotates ? (low ? lir + hp : lir - hp) : lir);
-  const float2* lane_tab = cs + (low ? 0u : ntok * half) + (low ? lir : lir - hp) * 8;
+  const unsigned fbase = (low ? lir : lir - hp) * 8;
 
-  Raw<IT> raw[kRows][K];
-  bool ok[kRows][K];
-  size_t out_off[kRows];
-  uint32_t tl[kRows];
-  bool second[kRows];
+  Raw<IT> raw[ROWS][K];
+  const IT* src0 = static_cast<const IT*>(t.in) + static_cast<size_t>(r0 + slot) * t.in_row_stride;
+  const size_t src_step = static_cast<size_t>(slots) * t.in_row_stride;
 #pragma unroll
-  for (int u = 0; u < kRows; ++u) {
-    const uint32_t vr = vr0 + u * slots + slot;
-    const bool in_cta = vr < vr1;
-    const uint32_t token = in_cta ? div_magic(vr, hall, heads_magic) : tok0;
-    tl[u] = token - tok0;
-    const uint32_t h = in_cta ? vr - token * hall : 0;
-    second[u] = h >= a.heads;
-    const size_t row = second[u] ? static_cast<size_t>(token) * a.heads2 + (h - a.heads)
-                                 : static_cast<size_t>(token) * a.heads + h;
-    const bool row_ok = in_cta && (second[u] || row < a.rows);
-    const IT* src = second[u] ? static_cast<const IT*>(a.in2) + row * a.in_row_stride2
-                              : static_cast<const IT*>(a.in) + row * a.in_row_stride;
-    out_off[u] = row * a.d;
+  for (int u = 0; u < ROWS; ++u) {
+    const IT* src = src0 + u * src_step;
+    const bool row_ok = FULL || r0 + u * slots + slot < r1;
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const unsigned j = (k << lg) + lir;
-      ok[u][k] = row_ok && j < octs;
-      raw[u][k] = Raw<IT>{};
-      if (ok[u][k]) raw[u][k] = raw_load(src + j * 8);
+      if (FULL || (row_ok && j < octs)) raw[u][k] = raw_load(src + j * 8);
+      else raw[u][k] = Raw<IT>{};
     }
-    if (a.gate && !second[u]) {
+  }
+  if (t.gate) {  // the gate halves of q|gate rows: copied through, after the main loads are out
+#pragma unroll
+    for (int u = 0; u < ROWS; ++u) {
+      const IT* src = src0 + u * src_step + a.d;
+      IT* gdst = static_cast<IT*>(t.gate) + static_cast<size_t>(r0 + u * slots + slot) * a.d;
+      const bool row_ok = FULL || r0 + u * slots + slot < r1;
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         const unsigned j = (k << lg) + lir;
-        if (ok[u][k]) oct_store(static_cast<IT*>(a.gate) + out_off[u] + j * 8, oct_load(src + a.d + j * 8));
+        if (FULL || (row_ok && j < octs)) oct_store(gdst + j * 8, oct_load(src + j * 8));
       }
     }
   }
+  Oct gm[K];
+  if (t.w) {  // 1 KiB of gamma, fetched while the rows are in flight
 #pragma unroll
-  for (int u = 0; u < kRows; ++u) {
+    for (int k = 0; k < K; ++k) {
+      const unsigned j = (k << lg) + lir;
+      gm[k] = (FULL || j < octs) ? oct_load_cached(t.w + j * 8) : oct_zero();
+      if (a.one_plus) {
+        const float2 one = make_float2(1.0f, 1.0f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) gm[k].p[i] = __fadd2_rn(one, gm[k].p[i]);
+      }
+    }
+  }
+  // The tables are filled while the row loads issued above are in flight.
+  float* cosv = smem;                  // [ntok][half]
+  float* sinl = smem + ntok * half;    // -sin: first halves of the pairs
+  float* sinh = sinl + ntok * half;    // +sin: second halves
+  for (uint32_t tl = warp; tl < ntok; tl += kBlock / 32) {
+    const uint32_t tok = tok0 + tl;
+    const uint32_t pos = token_pos(a.pos, tok);
+    for (uint32_t i = lane; i < half; i += 32) {
+      const float angle = __fmul_rn(static_cast<float>(pos), f.f[i]);
+      float sn, c;
+      sincosf(angle, &sn, &c);
+      cosv[tl * half + i] = c;
+      sinl[tl * half + i] = -sn;
+      sinh[tl * half + i] = sn;
+    }
+    // the CTA holding a token's first row of the first tensor reports its position
+    if (lane == 0 && a.pos_out && t.in == a.in && tok * t.heads >= r0) a.pos_out[tok] = pos;
+  }
+  __syncthreads();
+
+  const float* lane_cos = cosv + fbase;
+  const float* lane_sin = (low ? sinl : sinh) + fbase;
+
+#pragma unroll
+  for (int u = 0; u < ROWS; ++u) {
+    const uint32_t row = r0 + u * slots + slot;
+    const bool row_ok = FULL || row < r1;
     Oct x[K];
 #pragma unroll
     for (int k = 0; k < K; ++k) x[k] = raw_unpack(raw[u][k]);
-    if (a.w) {  // the norm kernel's arithmetic for a row of this length, step for step
+    if (t.w) {  // the norm kernel's arithmetic for a row of this length, step for step
       float2 acc = make_float2(0.0f, 0.0f);
 #pragma unroll
       for (int k = 0; k < K; ++k) acc = oct_sumsq(x[k], acc);
       const float ss = group_sum(acc.x + acc.y, g, nullptr);  // g <= 32: shuffles only
       const float scale = rsqrtf(__fmaf_rn(ss, inv_d, a.eps));
-      const float* w = second[u] ? a.w2 : a.w;  // 1 KiB, resident in L1 after the first rows
 #pragma unroll
-      for (int k = 0; k < K; ++k) {
-        const unsigned j = (k << lg) + lir;
-        Oct gm = j < octs ? oct_load_cached(w + j * 8) : oct_zero();
-        if (a.one_plus) {
-          const float2 one = make_float2(1.0f, 1.0f);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) gm.p[i] = __fadd2_rn(one, gm.p[i]);
-        }
-        x[k] = oct_mul(oct_scale(x[k], scale), gm);
-      }
+      for (int k = 0; k < K; ++k) x[k] = oct_mul(oct_scale(x[k], scale), gm[k]);
     }
-    float v[8];
+    const uint32_t tl = row_ok ? div_magic(row, t.heads, t.magic) - tok0 : 0;
+    const float* tc = lane_cos + tl * half;
+    const float* ts = lane_sin + tl * half;
+    // Scalar multiplies and adds on purpose: each rounds separately (-fmad=false), exactly as the
+    // standalone rope kernel and the CPU operator do; a packed mul/add pair was seen to contract.
+    float v[8], o[8];
     oct_to_array(x[0], v);
-    const float2* tab = lane_tab + tl[u] * half;
 #pragma unroll
-    for (int i = 0; i < 8; i += 2) {
-      const float o0 = __shfl_sync(kFullMask, v[i], src_lane);
-      const float o1 = __shfl_sync(kFullMask, v[i + 1], src_lane);
-      if (rotates) {
-        const float4 t4 = *reinterpret_cast<const float4*>(tab + i);  // (cos, sin) of two frequencies
-        v[i] = v[i] * t4.x + o0 * t4.y;
-        v[i + 1] = v[i + 1] * t4.z + o1 * t4.w;
-      }
-    }
-    OT* dst = static_cast<OT*>(second[u] ? a.out2 : a.out) + out_off[u];
-    void* cache = second[u] ? a.cache2 : a.cache;
-    OT* cdst = cache ? static_cast<OT*>(cache) + out_off[u] : nullptr;
-    if (ok[u][0]) {
-      store8(dst + lir * 8, v);
-      if (cdst) store8(cdst + lir * 8, v);
-    }
+    for (int i = 0; i < 8; ++i) o[i] = __shfl_sync(kFullMask, v[i], src_lane);
+    if (rotates) {
+      const float4 c0 = *reinterpret_cast<const float4*>(tc), c1 = *reinterpret_cast<const float4*>(tc + 4);
+      const float4 s0 = *reinterpret_cast<const float4*>(ts), s1 = *reinterpret_cast<const float4*>(ts + 4);
+      const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      const float sg[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
-    for (int k = 1; k < K; ++k) {
+      for (int i = 0; i < 8; ++i) v[i] = v[i] * c[i] + o[i] * sg[i];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) x[0].p[i] = make_float2(v[2 * i], v[2 * i + 1]);
+    }
+    OT* dst = static_cast<OT*>(t.out) + static_cast<size_t>(row) * a.d;
+    OT* cdst = t.cache ? static_cast<OT*>(t.cache) + static_cast<size_t>(row) * a.d : nullptr;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
       const unsigned j = (k << lg) + lir;
-      if (ok[u][k]) {
+      if (FULL || (row_ok && j < octs)) {
         oct_store(dst + j * 8, x[k]);
         if (cdst) oct_store(cdst + j * 8, x[k]);
       }
     }
   }
+}
+
+template <typename IT, typename OT, int K, int ROWS>
+__global__ void __launch_bounds__(kBlock, K * ROWS >= 8 ? 2 : 3) norm_rope_kernel(const NormRopeArgs a, const __grid_constant__ InvFreq f,
+                                                             const unsigned lg, const uint32_t ctas1,
+                                                             const float inv_d, const uint32_t magic1,
+                                                             const uint32_t magic2) {
+  extern __shared__ float rope_smem[];
+  const unsigned slots = kBlock >> lg;
+  const bool second = blockIdx.x >= ctas1;
+  RopeCta t;
+  if (!second) t = RopeCta{a.in, a.in_row_stride, a.out, a.gate, a.cache, a.w, a.heads, a.rows, magic1};
+  else t = RopeCta{a.in2, a.in_row_stride2, a.out2, nullptr, a.cache2, a.w2, a.heads2,
+                   ((a.rows + a.heads - 1) / a.heads) * a.heads2, magic2};
+  const uint32_t cta = second ? blockIdx.x - ctas1 : blockIdx.x;
+  const bool full = (a.d >> 3) == (static_cast<unsigned>(K) << lg) && (cta + 1) * (slots * ROWS) <= t.rows;
+  if (full) norm_rope_body<IT, OT, K, ROWS, true>(t, a, f, lg, cta, inv_d, rope_smem);
+  else norm_rope_body<IT, OT, K, ROWS, false>(t, a, f, lg, cta, inv_d, rope_smem);
 }
 
 template <typename T>
@@ -256,6 +290,12 @@ cudaError_t LaunchRopeT(const RopeArgs& a, const InvFreq& f, cudaStream_t s) {
   return cudaGetLastError();
 }
 
+uint32_t Magic(uint32_t divisor, uint64_t max_n) {
+  // floor(n / d) == umulhi(n, ceil(2^32 / d)) whenever n * d < 2^32; 0 = use a real division
+  return (divisor > 1 && max_n * divisor < (1ull << 32)) ? static_cast<uint32_t>(((1ull << 32) + divisor - 1) / divisor)
+                                                          : 0u;
+}
+
 template <typename IT, typename OT>
 cudaError_t LaunchNormRopeT(const NormRopeArgs& a, const InvFreq& f, cudaStream_t s) {
   const unsigned octs = a.d / 8;
@@ -264,23 +304,24 @@ cudaError_t LaunchNormRopeT(const NormRopeArgs& a, const InvFreq& f, cudaStream_
   const int k = (octs >= 2 && a.rot * 2 <= a.d) ? 2 : 1;
   unsigned g = 1, lg = 0;
   while (g * k < octs) g <<= 1, ++lg;
-  const unsigned rows_per_cta = kBlock / g * kRows;
-  const unsigned hall = a.heads + a.heads2;
+  const unsigned rows_in_flight = a.rows_per_group ? static_cast<unsigned>(a.rows_per_group) : 2u;
+  const unsigned rows_per_cta = kBlock / g * rows_in_flight;
   const unsigned tokens = (a.rows + a.heads - 1) / a.heads;
-  const uint64_t rows_total = static_cast<uint64_t>(tokens) * hall;
-  if (rows_total > 0xFFFFFFFFull) return cudaErrorInvalidValue;
-  const unsigned grid = static_cast<unsigned>((rows_total + rows_per_cta - 1) / rows_per_cta);
-  const unsigned max_tok = rows_per_cta / hall + 2;  // tokens a CTA's rows can touch
-  const size_t smem = 2 * static_cast<size_t>(max_tok) * (a.rot / 2) * sizeof(float2);
+  const uint64_t rows2 = static_cast<uint64_t>(tokens) * a.heads2;
+  if (rows2 > 0xFFFFFFFFull) return cudaErrorInvalidValue;
+  const unsigned ctas1 = (a.rows + rows_per_cta - 1) / rows_per_cta;
+  const unsigned ctas2 = static_cast<unsigned>((rows2 + rows_per_cta - 1) / rows_per_cta);
+  const unsigned min_heads = a.heads2 && a.heads2 < a.heads ? a.heads2 : a.heads;
+  const unsigned max_tok = rows_per_cta / min_heads + 2;  // tokens a CTA's rows can touch
+  const size_t smem = 3 * static_cast<size_t>(max_tok) * (a.rot / 2) * sizeof(float);
   if (smem > 48u * 1024u) return cudaErrorInvalidValue;
   const float inv_d = 1.0f / static_cast<float>(a.d);
-  // floor(n / hall) == umulhi(n, ceil(2^32 / hall)) whenever n * hall < 2^32
-  const uint32_t magic = (hall > 1 && rows_total * hall < (1ull << 32))
-                             ? static_cast<uint32_t>(((1ull << 32) + hall - 1) / hall)
-                             : 0u;
-  const uint32_t rt = static_cast<uint32_t>(rows_total);
-  if (k == 2) norm_rope_kernel<IT, OT, 2><<<grid, kBlock, smem, s>>>(a, f, lg, rt, inv_d, magic);
-  else norm_rope_kernel<IT, OT, 1><<<grid, kBlock, smem, s>>>(a, f, lg, rt, inv_d, magic);
+  const uint32_t m1 = Magic(a.heads, a.rows), m2 = a.heads2 ? Magic(a.heads2, rows2) : 0u;
+  const unsigned grid = ctas1 + ctas2;
+  if (k == 2 && rows_in_flight == 4) norm_rope_kernel<IT, OT, 2, 4><<<grid, kBlock, smem, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
+  else if (k == 2) norm_rope_kernel<IT, OT, 2, 2><<<grid, kBlock, smem, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
+  else if (rows_in_flight == 4) norm_rope_kernel<IT, OT, 1, 4><<<grid, kBlock, smem, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
+  else norm_rope_kernel<IT, OT, 1, 2><<<grid, kBlock, smem, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
   return cudaGetLastError();
 }
 
