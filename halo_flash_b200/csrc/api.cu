@@ -18,6 +18,7 @@ std::atomic<int> g_norm_threads_per_row{0};
 std::atomic<int> g_norm_short_rows_k1{0};
 std::atomic<int> g_norm_force_general{0};
 std::atomic<int> g_rope_rows_per_group{0};
+std::atomic<int> g_gated_rows_per_group{0};
 
 int Fail(char* err, size_t errlen, const char* fmt, ...) {
   if (err && errlen) {
@@ -100,6 +101,8 @@ int RunGated(GatedArgs a, const char* what, halo_b200_stream stream, char* err, 
           Aligned(a.w, 16);
   a.threads_per_row = g_norm_threads_per_row.load(std::memory_order_relaxed);
   a.short_rows_k1 = g_norm_short_rows_k1.load(std::memory_order_relaxed);
+  a.rows_per_group = g_gated_rows_per_group.load(std::memory_order_relaxed);
+  a.force_general = g_norm_force_general.load(std::memory_order_relaxed);
   if (a.threads_per_row && (a.d / 8 + a.threads_per_row - 1) / a.threads_per_row > 4) a.threads_per_row = 0;
   const cudaError_t e = LaunchGatedNorm(a, S(stream));
   if (e == cudaErrorInvalidValue) return Fail(err, errlen, "%s: unsupported (o, z, y) dtype combination", what);
@@ -264,6 +267,11 @@ int halo_b200_tune(const char* key, int value) {
   if (std::strcmp(key, "norm_threads_per_row") == 0) {
     if (value < 0 || value > 256 || (value & (value - 1)) != 0) return -1;
     g_norm_threads_per_row.store(value, std::memory_order_relaxed);
+    return 0;
+  }
+  if (std::strcmp(key, "gated_rows_per_group") == 0) {
+    if (value != 0 && value != 1 && value != 2) return -1;
+    g_gated_rows_per_group.store(value, std::memory_order_relaxed);
     return 0;
   }
   if (std::strcmp(key, "rope_rows_per_group") == 0) {

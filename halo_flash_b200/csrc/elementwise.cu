@@ -35,13 +35,8 @@ __device__ __forceinline__ Oct apply8(const Oct& a, const Oct& b, float alpha) {
   } else {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      if constexpr (OP == kOpSiluMul) {
-        const float2 s = make_float2(silu_f(a.p[i].x), silu_f(a.p[i].y));
-        o.p[i] = __fmul2_rn(s, b.p[i]);
-      } else {
-        const float2 s = make_float2(sigmoid_f(b.p[i].x), sigmoid_f(b.p[i].y));
-        o.p[i] = __fmul2_rn(a.p[i], s);
-      }
+      if constexpr (OP == kOpSiluMul) o.p[i] = __fmul2_rn(silu2_f(a.p[i]), b.p[i]);
+      else o.p[i] = __fmul2_rn(a.p[i], sigmoid2_f(b.p[i]));
     }
   }
   return o;

@@ -77,6 +77,8 @@ struct GatedArgs {
   uint32_t mode = 0;  // 0 SiLU(z), 1 sigmoid(z)
   int threads_per_row = 0;
   int short_rows_k1 = 0;
+  int rows_per_group = 0;  // 2: short rows keep two rows per thread group in flight
+  int force_general = 0;   // 1: never take the lean kernel (tests compare the two)
   bool vec = true;
 };
 cudaError_t LaunchGatedNorm(const GatedArgs& a, cudaStream_t s);

@@ -669,7 +669,10 @@ def test_lean_and_general_norm_kernels_agree_bit_for_bit():
             ops.add_rmsnorm(r, delta, w, s.eps, xn=xn, q8_0=q8)
             qk = to_dev(synth.act("t.lg.qk", rows * 32, s.lin_dim), "bf16")
             ops.l2norm(qk, s.eps)
-            outs.append((r, xn, q8, qk))
+            o = to_dev(synth.act("t.lg.o", rows * 32, s.lin_dim), "bf16")
+            z = to_dev(synth.act("t.lg.z", rows * 32, s.lin_dim), "bf16")
+            ops.gated_norm(o, to_dev(synth.gated_w("t.lg.gw", s.lin_dim)), z, s.eps)
+            outs.append((r, xn, q8, qk, o))
         finally:
             lib().tune("norm_force_general", 0)
     for a, b in zip(*outs):
