@@ -287,6 +287,16 @@ __device__ __forceinline__ float group_sum(float v, unsigned g, float* scratch) 
   return v;
 }
 
+// The same for g <= 32 with no shared-memory stage in the code at all. Kernels that can only see
+// short rows use this form: the mere presence of the (never executed) barrier path of
+// group_sum cost the one-octet-per-thread kernels about 9 % (18.1 vs 16.6 us on the gated norm).
+__device__ __forceinline__ float group_sum_narrow(float v, unsigned g) {
+#pragma unroll
+  for (unsigned o = 16; o > 0; o >>= 1)
+    if (o < g) v += __shfl_xor_sync(kFullMask, v, o);
+  return v;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(kFullMask, v, o);

@@ -212,9 +212,10 @@ struct LeanArgs {
   int one_plus, l2;
 };
 
-template <typename XT, typename YT, int K, bool ADD, bool EPI>
+// WIDE: more than one warp per row (g > 32), the reduction crosses shared memory and a barrier.
+template <typename XT, typename YT, int K, bool ADD, bool EPI, bool WIDE>
 __global__ void __launch_bounds__(kBlock) norm_rows_lean_kernel(const LeanArgs a) {
-  __shared__ float scratch[kBlock / 32];
+  __shared__ float scratch[WIDE ? kBlock / 32 : 1];
   const unsigned lg = a.lg, g = 1u << lg;
   const unsigned lir = threadIdx.x & (g - 1);
   const uint32_t row = blockIdx.x * (kBlock >> lg) + (threadIdx.x >> lg);
@@ -254,7 +255,7 @@ __global__ void __launch_bounds__(kBlock) norm_rows_lean_kernel(const LeanArgs a
   float2 acc = make_float2(0.0f, 0.0f);
 #pragma unroll
   for (int k = 0; k < K; ++k) acc = oct_sumsq(v[k], acc);
-  const float ss = group_sum(acc.x + acc.y, g, scratch);
+  const float ss = WIDE ? group_sum(acc.x + acc.y, g, scratch) : group_sum_narrow(acc.x + acc.y, g);
   const float scale = a.l2 ? rsqrtf(ss + a.eps) : rsqrtf(__fmaf_rn(ss, a.inv_d, a.eps));
 #pragma unroll
   for (int k = 0; k < K; ++k) {
@@ -485,7 +486,7 @@ __global__ void __launch_bounds__(kBlock) gated_norm_lean_kernel(const GatedLean
 #pragma unroll
     for (int i = 0; i < 4; ++i) zz.p[i] = sigmoid2_f(zz.p[i]);
   }
-  const float ss = group_sum(acc.x + acc.y, g, nullptr);  // g <= 32: shuffles only
+  const float ss = group_sum_narrow(acc.x + acc.y, g);
   const float scale = rsqrtf(__fmaf_rn(ss, a.inv_d, a.eps));
   oct_store(static_cast<YT*>(a.y) + off, oct_mul(oct_mul(oct_scale(v, scale), gm), zz));
 }
@@ -573,8 +574,14 @@ cudaError_t LaunchLean(const NormArgs& a, const Shape& sh, unsigned grid, cudaSt
   l.lg = sh.lg;
   l.one_plus = a.one_plus;
   l.l2 = a.l2;
-  if (a.q8_0 || a.xq) norm_rows_lean_kernel<XT, YT, K, ADD, true><<<grid, kBlock, 0, s>>>(l);
-  else norm_rows_lean_kernel<XT, YT, K, ADD, false><<<grid, kBlock, 0, s>>>(l);
+  const bool epi = a.q8_0 || a.xq;
+  if (sh.lg > 5) {
+    if (epi) norm_rows_lean_kernel<XT, YT, K, ADD, true, true><<<grid, kBlock, 0, s>>>(l);
+    else norm_rows_lean_kernel<XT, YT, K, ADD, false, true><<<grid, kBlock, 0, s>>>(l);
+  } else {
+    if (epi) norm_rows_lean_kernel<XT, YT, K, ADD, true, false><<<grid, kBlock, 0, s>>>(l);
+    else norm_rows_lean_kernel<XT, YT, K, ADD, false, false><<<grid, kBlock, 0, s>>>(l);
+  }
   return cudaGetLastError();
 }
 

@@ -199,7 +199,7 @@ __device__ __forceinline__ void norm_rope_body(const RopeCta t, const NormRopeAr
       float2 acc = make_float2(0.0f, 0.0f);
 #pragma unroll
       for (int k = 0; k < K; ++k) acc = oct_sumsq(x[k], acc);
-      const float ss = group_sum(acc.x + acc.y, g, nullptr);  // g <= 32: shuffles only
+      const float ss = group_sum_narrow(acc.x + acc.y, g);
       const float scale = rsqrtf(__fmaf_rn(ss, inv_d, a.eps));
 #pragma unroll
       for (int k = 0; k < K; ++k) x[k] = oct_mul(oct_scale(x[k], scale), gm[k]);
