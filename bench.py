@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T] [--impl ours|reference]
 
-One step = the 48-layer op chain (36 Gated-DeltaNet + 12 GQA layers, 229 kernel launches,
+One step = the 48-layer op chain (36 Gated-DeltaNet + 12 GQA layers, 230 kernel launches,
 halo_flash_b200/chain.py) over a T-token shard per GPU, bf16 activations, full-size dims
 (hidden 2048, 16 Q / 2 KV heads x 256 with 64 rotated dims, 32 value heads x 128, 16 key heads
 x 128, shared ff 512 + 10 routed x 512, Q8_0 vocabulary 151936). With N GPUs every rank runs its
@@ -219,6 +219,7 @@ def kernel_table(torch, shapes, T: int, peaks: dict) -> dict:
     w_g = 1 + torch.randn(s.lin_dim, device=dev) * 0.1
     table = torch.randint(0, 255, (8192, s.q8_row_bytes), device=dev, dtype=torch.uint8)
     table.view(8192, -1, 34)[:, :, 1] = 0x3C  # finite fp16 scales
+    rope_tab = ops.rope_table(torch.empty(T, 2, s.rot // 2, device=dev), s.rot, s.theta)
     specs = {
         "add_rmsnorm": (lambda: (r(T, s.hidden), r(T, s.hidden), torch.empty(T, s.hidden, device=dev, dtype=bf)),
                         lambda b: ops.add_rmsnorm(b[0], b[1], w_h, s.eps, xn=b[2])),
@@ -227,7 +228,7 @@ def kernel_table(torch, shapes, T: int, peaks: dict) -> dict:
                                 torch.empty(T * s.v_heads, s.lin_dim, device=dev, dtype=bf)),
                        lambda b: ops.gated_norm(b[0], w_g, b[1], s.eps, y=b[2])),
         "norm_rope_qk": (lambda: (r(T, s.q_heads, s.head_dim), r(T, s.kv_heads, s.head_dim)),
-                         lambda b: ops.norm_rope_qk(b[0], b[1], w_hd, w_hd, s.eps, s.rot, s.theta)),
+                         lambda b: ops.norm_rope_qk_table(b[0], b[1], w_hd, w_hd, s.eps, s.rot, rope_tab)),
         "swiglu_moe": (lambda: (r(T, s.ff), r(T, s.ff), torch.empty(T, s.ff, device=dev, dtype=bf),
                                 r(T * k, s.ff), r(T * k, s.ff), torch.empty(T * k, s.ff, device=dev, dtype=bf)),
                        lambda b: ops.silu_mul_multi([(b[0], b[1]), (b[3], b[4])], [b[2], b[5]])),

@@ -111,6 +111,7 @@ class LayerChain:
         self.xn = torch.empty(T, s.hidden, device=dev, dtype=dtype)
         self.h_s = torch.empty(T, s.ff, device=dev, dtype=dtype)
         self.h_r = torch.empty(T * k, s.ff, device=dev, dtype=dtype)
+        self.rope_tab = torch.empty(T, 2, s.rot // 2, device=dev, dtype=torch.float32)
         # weights: zero-centred norm gammas (applied as 1 + w), plain gated-norm gamma
         wg = torch.Generator(device="cpu").manual_seed(seed)
         def nw(d, mean=0.0):
@@ -132,7 +133,7 @@ class LayerChain:
         self.table = table.view(self.vocab, nb * 34)
         del codes, half, table
         self.ids = torch.randint(0, self.vocab, (T,), device=dev, generator=g, dtype=torch.int32)
-        self.launches_per_step = 1 + 4 * synth.LAYERS + sum(not synth.layer_is_gqa(l) for l in range(synth.LAYERS))
+        self.launches_per_step = 2 + 4 * synth.LAYERS + sum(not synth.layer_is_gqa(l) for l in range(synth.LAYERS))
         self._graph: torch.cuda.CUDAGraph | None = None
 
     # ---- one step, eager ------------------------------------------------------------------
@@ -140,7 +141,7 @@ class LayerChain:
         s = self.s
         ops.add_rmsnorm(self.res, bo.delta_a, self.w_attn[l], s.eps, one_plus=True, xn=self.xn)
         if synth.layer_is_gqa(l):
-            ops.norm_rope_qk(bo.q, bo.k, self.w_q, self.w_k, s.eps, s.rot, s.theta, one_plus=True, pos0=self.pos0)
+            ops.norm_rope_qk_table(bo.q, bo.k, self.w_q, self.w_k, s.eps, s.rot, self.rope_tab, one_plus=True)
         else:
             ops.l2norm(bo.qk, s.eps)
             ops.gated_norm(bo.o, self.w_gated, bo.z, s.eps, mode=0, y=bo.y)
@@ -148,10 +149,12 @@ class LayerChain:
         ops.silu_mul_multi([(bo.gate_s, bo.up_s), (bo.gate_r, bo.up_r)], [self.h_s, self.h_r])
 
     def step(self) -> None:
-        """Enqueue one full step on the current stream: the embedding gather, then per DeltaNet layer
-        5 launches (add+norm, L2, gated norm, add+norm, SwiGLU shared+routed) and per GQA layer 4
-        (add+norm, Q/K norm+RoPE, add+norm, SwiGLU): 1 + 36*5 + 12*4 = 229."""
+        """Enqueue one full step on the current stream: the embedding gather and the rotation table,
+        then per DeltaNet layer 5 launches (add+norm, L2, gated norm, add+norm, SwiGLU shared+routed)
+        and per GQA layer 4 (add+norm, Q/K norm+RoPE, add+norm, SwiGLU): 2 + 36*5 + 12*4 = 230."""
         ops.embed_q8_0(self.table, self.ids, self.s.hidden, self.res, vocab=self.vocab)
+        # every GQA layer rotates at the same positions: one cos / sin table per step
+        ops.rope_table(self.rope_tab, self.s.rot, self.s.theta, pos0=self.pos0)
         for l in range(synth.LAYERS):
             self.layer(l, self.sets[l % len(self.sets)])
 

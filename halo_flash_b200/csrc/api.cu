@@ -186,9 +186,14 @@ int RunNormRope(NormRopeArgs a, float theta, const char* what, halo_b200_stream 
   REQUIRE(a.rot % 2 == 0 && a.rot <= a.d, "%s: rotary_dim %u must be even and <= d %u", what, a.rot, a.d);
   REQUIRE(a.in_row_stride >= a.d, "%s: in_row_stride < d", what);
   REQUIRE(a.gate == nullptr || a.in_row_stride >= 2ull * a.d, "%s: gate needs q|gate rows (in_row_stride >= 2 d)", what);
-  InvFreq f;
-  REQUIRE(FillInvFreq(&f, a.rot, theta), "%s: rotary_dim too large", what);
+  InvFreq f = {};
+  if (a.table) {
+    REQUIRE(Aligned(a.table, 16), "%s: rotation table must be 16-byte aligned", what);
+  } else {
+    REQUIRE(FillInvFreq(&f, a.rot, theta), "%s: rotary_dim too large", what);
+  }
   a.rows_per_group = g_rope_rows_per_group.load(std::memory_order_relaxed);
+  a.force_general = g_norm_force_general.load(std::memory_order_relaxed);
   const bool vec = a.d % 8 == 0 && (a.rot / 2) % 8 == 0 && a.in_row_stride % 8 == 0 && Aligned(a.in, 16) &&
                    Aligned(a.out, 16) && Aligned(a.gate, 16) && Aligned(a.cache, 16) && Aligned(a.w, 16) &&
                    a.in_row_stride2 % 8 == 0 && Aligned(a.in2, 16) && Aligned(a.out2, 16) && Aligned(a.cache2, 16) &&
@@ -205,6 +210,7 @@ int RunNormRope(NormRopeArgs a, float theta, const char* what, halo_b200_stream 
     if (e == cudaErrorInvalidValue) return Fail(err, errlen, "%s: unsupported (in, out) dtype combination", what);
     return Done(e, what, err, errlen);
   }
+  REQUIRE(a.table == nullptr, "%s: a rotation table needs 16-byte aligned rows, d %% 8 == 0 and rot %% 16 == 0", what);
   // Odd shapes: the separate kernels in sequence (the reference's own unfused path,
   // src/engine/qwen35_gpu.cpp:204-222): split, per-head norm, rope, cache copy.
   REQUIRE(a.in_dtype == a.out_dtype, "%s: unaligned shapes need in_dtype == out_dtype", what);
@@ -719,6 +725,58 @@ int halo_b200_norm_rope_qk_ex(halo_b200_stream stream, const void* q_in, uint64_
   a.pos.scale = scale;
   a.pos_out = pos_out;
   return RunNormRope(a, theta, "halo_norm_rope_qk", stream, err, errlen);
+}
+
+int halo_b200_rope_table_ex(halo_b200_stream stream, float* table, uint32_t tokens, uint32_t rotary_dim, float theta,
+                            const uint32_t* params, uint32_t pstride, uint32_t slot, uint32_t pos0, uint32_t scale,
+                            uint32_t* pos_out, char* err, size_t errlen) {
+  if (tokens == 0) return Done(cudaSuccess, "halo_rope_table", err, errlen);
+  REQUIRE(table != nullptr, "halo_rope_table: table is null");
+  REQUIRE(rotary_dim >= 2 && rotary_dim % 2 == 0, "halo_rope_table: rotary_dim %u must be even", rotary_dim);
+  REQUIRE(Aligned(table, 4) && Aligned(params, 4) && Aligned(pos_out, 4), "halo_rope_table: pointer not aligned");
+  InvFreq f;
+  REQUIRE(FillInvFreq(&f, rotary_dim, theta), "halo_rope_table: rotary_dim %u exceeds %d", rotary_dim, 2 * kMaxRotHalf);
+  RopeTableArgs a;
+  a.table = table;
+  a.tokens = tokens;
+  a.rot = rotary_dim;
+  a.pos.params = params;
+  a.pos.pstride = pstride;
+  a.pos.slot = slot;
+  a.pos.pos0 = pos0;
+  a.pos.scale = scale;
+  a.pos_out = pos_out;
+  return Done(LaunchRopeTable(a, f, S(stream)), "halo_rope_table", err, errlen);
+}
+
+int halo_b200_norm_rope_qk_table_ex(halo_b200_stream stream, const void* q_in, uint64_t q_row_stride, void* q_out,
+                                    void* q_gate, const float* w_q, uint32_t q_heads, const void* k_in, void* k_out,
+                                    void* k_cache, const float* w_k, uint32_t k_heads, int in_dtype, int out_dtype,
+                                    int one_plus, float eps, uint32_t d, uint32_t rotary_dim, uint32_t tokens,
+                                    const float* table, char* err, size_t errlen) {
+  REQUIRE(tokens == 0 || table != nullptr, "halo_norm_rope_qk_table: table is null");
+  NormRopeArgs a;
+  a.in = q_in;
+  a.in_dtype = in_dtype;
+  a.in_row_stride = q_row_stride;
+  a.out = q_out;
+  a.out_dtype = out_dtype;
+  a.gate = q_gate;
+  a.w = w_q;
+  a.heads = q_heads;
+  a.rows = tokens * q_heads;
+  a.in2 = k_heads ? k_in : nullptr;
+  a.in_row_stride2 = d;
+  a.out2 = k_heads ? k_out : nullptr;
+  a.cache2 = k_heads ? k_cache : nullptr;
+  a.w2 = k_heads ? w_k : nullptr;
+  a.heads2 = k_heads;
+  a.one_plus = one_plus;
+  a.eps = eps;
+  a.d = d;
+  a.rot = rotary_dim;
+  a.table = table;
+  return RunNormRope(a, 0.0f, "halo_norm_rope_qk_table", stream, err, errlen);
 }
 
 int halo_b200_split_qgate_norm_rope(halo_b200_stream stream, const float* qg, float* q, float* gate, const float* w,

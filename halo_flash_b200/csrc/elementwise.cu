@@ -58,14 +58,23 @@ struct VecSegments {
 // register count low enough for 5 resident CTAs per SM.
 template <typename IT, typename OT, int OP>
 __global__ void __launch_bounds__(kBlock, sizeof(IT) == 4 ? 3 : 5) elementwise_vec_kernel(const VecSegments v) {
-  int sidx = 0;
+  // Segment lookup by compare-and-select over constant indices: indexing the parameter arrays
+  // with a run-time value would make the compiler copy them to local memory.
+  const void* sa = v.a[0];
+  const void* sb = v.b[0];
+  void* sy = v.y[0];
+  uint64_t octs = v.octs[0];
+  uint32_t first = 0;
 #pragma unroll
-  for (int i = 1; i < kMaxSegments; ++i) sidx += blockIdx.x >= v.first_cta[i] ? 1 : 0;
-  const IT* pa = static_cast<const IT*>(v.a[sidx]);
-  const IT* pb = static_cast<const IT*>(v.b[sidx]);
-  OT* py = static_cast<OT*>(v.y[sidx]);
-  const uint64_t octs = v.octs[sidx];
-  const uint64_t base = static_cast<uint64_t>(blockIdx.x - v.first_cta[sidx]) * (kBlock * kUnroll) + threadIdx.x;
+  for (int i = 1; i < kMaxSegments; ++i) {
+    if (blockIdx.x >= v.first_cta[i]) {
+      sa = v.a[i], sb = v.b[i], sy = v.y[i], octs = v.octs[i], first = v.first_cta[i];
+    }
+  }
+  const IT* pa = static_cast<const IT*>(sa);
+  const IT* pb = static_cast<const IT*>(sb);
+  OT* py = static_cast<OT*>(sy);
+  const uint64_t base = static_cast<uint64_t>(blockIdx.x - first) * (kBlock * kUnroll) + threadIdx.x;
   if (base + static_cast<uint64_t>(kUnroll - 1) * kBlock < octs) {  // the whole tile is inside: no predicates
     Raw<IT> ra[kUnroll], rb[kUnroll];
 #pragma unroll

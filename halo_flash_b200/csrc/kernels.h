@@ -123,9 +123,23 @@ struct NormRopeArgs {
   uint32_t heads2 = 0;
   PosSpec pos;
   uint32_t* pos_out = nullptr;  // optional [rows / heads]
+  // Optional precomputed rotation table [tokens][2][rot / 2] fp32 (cos row, then sin row, per token;
+  // LaunchRopeTable fills it). With it the kernel computes no sincosf, uses no shared memory and
+  // has no barrier; pos / pos_out / the inverse frequencies are then unused.
+  const float* table = nullptr;
   int rows_per_group = 0;       // rows a thread group keeps in flight: 2 (default) or 4
+  int force_general = 0;        // 1: never take the lean kernel (tests compare the two)
 };
 cudaError_t LaunchNormRope(const NormRopeArgs& a, const InvFreq& f, cudaStream_t s);
+
+// cos / sin of float(pos) * inv_freq[i] for every token: table[t][0][i] = cos, table[t][1][i] = sin.
+struct RopeTableArgs {
+  float* table = nullptr;
+  uint32_t tokens = 0, rot = 0;
+  PosSpec pos;
+  uint32_t* pos_out = nullptr;
+};
+cudaError_t LaunchRopeTable(const RopeTableArgs& a, const InvFreq& f, cudaStream_t s);
 
 struct SplitArgs {  // halo_split_qgate: [rows][2 * hd] -> q, gate
   const void* qg = nullptr;

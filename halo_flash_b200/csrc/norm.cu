@@ -12,6 +12,8 @@
 // The whole row stays in registers between the sum of squares and the scaled
 // store: each activation byte crosses HBM exactly once per direction. g <= 32
 // reduces with shuffles only; g > 32 adds one shared-memory stage.
+#include <type_traits>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -213,7 +215,10 @@ struct LeanArgs {
 };
 
 // WIDE: more than one warp per row (g > 32), the reduction crosses shared memory and a barrier.
-template <typename XT, typename YT, int K, bool ADD, bool EPI, bool WIDE>
+// MODE: 0 = w, y, one_plus and l2 are tested at run time; 1 = RMSNorm with gamma w into y;
+// 2 = the same with gamma 1 + w. The two fixed modes exist because even warp-uniform tests
+// cost these microsecond CTAs 3-4 % (12.6 vs 12.1 us on the add + norm of 4096 x 2048).
+template <typename XT, typename YT, int K, bool ADD, bool EPI, bool WIDE, int MODE>
 __global__ void __launch_bounds__(kBlock) norm_rows_lean_kernel(const LeanArgs a) {
   __shared__ float scratch[WIDE ? kBlock / 32 : 1];
   const unsigned lg = a.lg, g = 1u << lg;
@@ -241,11 +246,11 @@ __global__ void __launch_bounds__(kBlock) norm_rows_lean_kernel(const LeanArgs a
     for (int k = 0; k < K; ++k) v[k] = raw_unpack(rx[k]);
   }
   Oct gm[K];
-  if (a.w) {  // fetched before the reduction: the L2 round trip overlaps the shuffles / barrier
+  if (MODE != 0 || a.w) {  // fetched before the reduction: the L2 round trip overlaps the shuffles / barrier
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       gm[k] = oct_load_cached(a.w + (((k << lg) + lir) << 3));
-      if (a.one_plus) {
+      if (MODE == 2 || (MODE == 0 && a.one_plus)) {
         const float2 one = make_float2(1.0f, 1.0f);
 #pragma unroll
         for (int i = 0; i < 4; ++i) gm[k].p[i] = __fadd2_rn(one, gm[k].p[i]);
@@ -256,13 +261,13 @@ __global__ void __launch_bounds__(kBlock) norm_rows_lean_kernel(const LeanArgs a
 #pragma unroll
   for (int k = 0; k < K; ++k) acc = oct_sumsq(v[k], acc);
   const float ss = WIDE ? group_sum(acc.x + acc.y, g, scratch) : group_sum_narrow(acc.x + acc.y, g);
-  const float scale = a.l2 ? rsqrtf(ss + a.eps) : rsqrtf(__fmaf_rn(ss, a.inv_d, a.eps));
+  const float scale = (MODE == 0 && a.l2) ? rsqrtf(ss + a.eps) : rsqrtf(__fmaf_rn(ss, a.inv_d, a.eps));
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const unsigned j = (k << lg) + lir;
     v[k] = oct_scale(v[k], scale);
-    if (a.w) v[k] = oct_mul(v[k], gm[k]);
-    if (a.y) oct_store(static_cast<YT*>(a.y) + off + (j << 3), v[k]);
+    if (MODE != 0 || a.w) v[k] = oct_mul(v[k], gm[k]);
+    if (MODE != 0 || a.y) oct_store(static_cast<YT*>(a.y) + off + (j << 3), v[k]);
     if constexpr (EPI) {
       float arr[8];
       oct_to_array(v[k], arr);
@@ -575,12 +580,17 @@ cudaError_t LaunchLean(const NormArgs& a, const Shape& sh, unsigned grid, cudaSt
   l.one_plus = a.one_plus;
   l.l2 = a.l2;
   const bool epi = a.q8_0 || a.xq;
+  const int mode = (!epi && a.w && a.y && !a.l2) ? (a.one_plus ? 2 : 1) : 0;
   if (sh.lg > 5) {
-    if (epi) norm_rows_lean_kernel<XT, YT, K, ADD, true, true><<<grid, kBlock, 0, s>>>(l);
-    else norm_rows_lean_kernel<XT, YT, K, ADD, false, true><<<grid, kBlock, 0, s>>>(l);
+    if (epi) norm_rows_lean_kernel<XT, YT, K, ADD, true, true, 0><<<grid, kBlock, 0, s>>>(l);
+    else if (mode == 2) norm_rows_lean_kernel<XT, YT, K, ADD, false, true, 2><<<grid, kBlock, 0, s>>>(l);
+    else if (mode == 1) norm_rows_lean_kernel<XT, YT, K, ADD, false, true, 1><<<grid, kBlock, 0, s>>>(l);
+    else norm_rows_lean_kernel<XT, YT, K, ADD, false, true, 0><<<grid, kBlock, 0, s>>>(l);
   } else {
-    if (epi) norm_rows_lean_kernel<XT, YT, K, ADD, true, false><<<grid, kBlock, 0, s>>>(l);
-    else norm_rows_lean_kernel<XT, YT, K, ADD, false, false><<<grid, kBlock, 0, s>>>(l);
+    if (epi) norm_rows_lean_kernel<XT, YT, K, ADD, true, false, 0><<<grid, kBlock, 0, s>>>(l);
+    else if (mode == 2) norm_rows_lean_kernel<XT, YT, K, ADD, false, false, 2><<<grid, kBlock, 0, s>>>(l);
+    else if (mode == 1) norm_rows_lean_kernel<XT, YT, K, ADD, false, false, 1><<<grid, kBlock, 0, s>>>(l);
+    else norm_rows_lean_kernel<XT, YT, K, ADD, false, false, 0><<<grid, kBlock, 0, s>>>(l);
   }
   return cudaGetLastError();
 }
@@ -593,9 +603,15 @@ cudaError_t LaunchNormT(const NormArgs& a, cudaStream_t s) {
   }
   const Shape sh = PickShape(a.d / 8, a.rows, a.threads_per_row, (a.q8_0 || a.xq) ? 4u : 1u, a.short_rows_k1);
   const unsigned grid = (a.rows + sh.rows_per_cta - 1) / sh.rows_per_cta;
+  // (in, out) pairs the lean kernels are built for; the rest go through the general kernel
+  constexpr bool kLeanTypes = (std::is_same_v<XT, float> && !std::is_same_v<YT, f16>) ||
+                              (std::is_same_v<XT, bf16> && !std::is_same_v<YT, f16>) ||
+                              (std::is_same_v<XT, f16> && std::is_same_v<YT, f16>);
   const bool lean = sh.full && sh.k <= 2 && a.rows_per_entry == 0 && a.w_period <= 1 && a.y16 == nullptr &&
                     a.rscale == nullptr && a.kb_tokens == 0 && !a.force_general;
-  if (lean) return sh.k == 1 ? LaunchLean<XT, YT, 1, ADD>(a, sh, grid, s) : LaunchLean<XT, YT, 2, ADD>(a, sh, grid, s);
+  if constexpr (kLeanTypes) {
+    if (lean) return sh.k == 1 ? LaunchLean<XT, YT, 1, ADD>(a, sh, grid, s) : LaunchLean<XT, YT, 2, ADD>(a, sh, grid, s);
+  }
   const float inv_d = 1.0f / static_cast<float>(a.d);
   switch (sh.k) {
     case 1: norm_rows_kernel<XT, YT, 1, 1, ADD><<<grid, kBlock, 0, s>>>(a, sh.lg, inv_d); break;

@@ -93,6 +93,33 @@ __device__ __forceinline__ uint32_t div_magic(uint32_t n, uint32_t d, uint32_t m
   return magic ? __umulhi(n, magic) : n / d;
 }
 
+// Rotate the 8 values of `x` (first or second halves of 8 pairs) given their partners `o`, the
+// 8 cosines (c0, c1) and the 8 signed sines (s0, s1): x = x * cos + o * sin. Scalar multiplies
+// and adds, each rounded separately (-fmad=false), exactly as the standalone rope kernel and the
+// CPU operator compute a*c - b*s and a*s + b*c; a packed mul/add pair was seen to contract into
+// an FMA. Everything stays in named registers: arrays indexed here ended up in local memory.
+__device__ __forceinline__ void rotate8(Oct& x, const Oct& o, const float4 c0, const float4 c1, const float4 s0,
+                                        const float4 s1) {
+  x.p[0].x = x.p[0].x * c0.x + o.p[0].x * s0.x;
+  x.p[0].y = x.p[0].y * c0.y + o.p[0].y * s0.y;
+  x.p[1].x = x.p[1].x * c0.z + o.p[1].x * s0.z;
+  x.p[1].y = x.p[1].y * c0.w + o.p[1].y * s0.w;
+  x.p[2].x = x.p[2].x * c1.x + o.p[2].x * s1.x;
+  x.p[2].y = x.p[2].y * c1.y + o.p[2].y * s1.y;
+  x.p[3].x = x.p[3].x * c1.z + o.p[3].x * s1.z;
+  x.p[3].y = x.p[3].y * c1.w + o.p[3].y * s1.w;
+}
+__device__ __forceinline__ float4 scale4(float4 v, float s) { return make_float4(v.x * s, v.y * s, v.z * s, v.w * s); }
+__device__ __forceinline__ Oct shuffle_oct(const Oct& x, unsigned src_lane) {
+  Oct o;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    o.p[i].x = __shfl_sync(kFullMask, x.p[i].x, src_lane);
+    o.p[i].y = __shfl_sync(kFullMask, x.p[i].y, src_lane);
+  }
+  return o;
+}
+
 struct RopeCta {
   const void* in;
   uint64_t in_row_stride;
@@ -103,7 +130,7 @@ struct RopeCta {
   uint32_t heads, rows, magic;
 };
 
-template <typename IT, typename OT, int K, int ROWS, bool FULL>
+template <typename IT, typename OT, int K, int ROWS, bool FULL, bool GT>
 __device__ __forceinline__ void norm_rope_body(const RopeCta t, const NormRopeArgs& a, const InvFreq& f,
                                                const unsigned lg, const uint32_t cta, const float inv_d,
                                                float* smem) {
@@ -112,8 +139,8 @@ __device__ __forceinline__ void norm_rope_body(const RopeCta t, const NormRopeAr
   const uint32_t r0 = cta * (slots * ROWS);  // first row of this CTA within its tensor
   uint32_t r1 = r0 + slots * ROWS;
   if (!FULL && r1 > t.rows) r1 = t.rows;
-  const uint32_t tok0 = div_magic(r0, t.heads, t.magic);
-  const uint32_t ntok = div_magic(r1 - 1, t.heads, t.magic) - tok0 + 1;
+  const uint32_t tok0 = GT ? 0u : div_magic(r0, t.heads, t.magic);
+  const uint32_t ntok = GT ? 0u : div_magic(r1 - 1, t.heads, t.magic) - tok0 + 1;
   const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const unsigned g = 1u << lg;
   const unsigned lir = threadIdx.x & (g - 1);
@@ -165,28 +192,37 @@ __device__ __forceinline__ void norm_rope_body(const RopeCta t, const NormRopeAr
       }
     }
   }
-  // The tables are filled while the row loads issued above are in flight.
-  float* cosv = smem;                  // [ntok][half]
-  float* sinl = smem + ntok * half;    // -sin: first halves of the pairs
-  float* sinh = sinl + ntok * half;    // +sin: second halves
-  for (uint32_t tl = warp; tl < ntok; tl += kBlock / 32) {
-    const uint32_t tok = tok0 + tl;
-    const uint32_t pos = token_pos(a.pos, tok);
-    for (uint32_t i = lane; i < half; i += 32) {
-      const float angle = __fmul_rn(static_cast<float>(pos), f.f[i]);
-      float sn, c;
-      sincosf(angle, &sn, &c);
-      cosv[tl * half + i] = c;
-      sinl[tl * half + i] = -sn;
-      sinh[tl * half + i] = sn;
+  const float* lane_cos;
+  const float* lane_sin;
+  uint32_t tok_step;  // floats between two tokens' table rows
+  if constexpr (GT) {
+    // precomputed table in global memory (L2-resident, read through the read-only path)
+    lane_cos = a.table + fbase;
+    lane_sin = a.table + half + fbase;
+    tok_step = a.rot;
+  } else {
+    // The tables are filled while the row loads issued above are in flight.
+    float* cosv = smem;                // [ntok][half]
+    float* sinv = smem + ntok * half;  // [ntok][half]
+    for (uint32_t tl = warp; tl < ntok; tl += kBlock / 32) {
+      const uint32_t tok = tok0 + tl;
+      const uint32_t pos = token_pos(a.pos, tok);
+      for (uint32_t i = lane; i < half; i += 32) {
+        const float angle = __fmul_rn(static_cast<float>(pos), f.f[i]);
+        float sn, c;
+        sincosf(angle, &sn, &c);
+        cosv[tl * half + i] = c;
+        sinv[tl * half + i] = sn;
+      }
+      // the CTA holding a token's first row of the first tensor reports its position
+      if (lane == 0 && a.pos_out && t.in == a.in && tok * t.heads >= r0) a.pos_out[tok] = pos;
     }
-    // the CTA holding a token's first row of the first tensor reports its position
-    if (lane == 0 && a.pos_out && t.in == a.in && tok * t.heads >= r0) a.pos_out[tok] = pos;
+    __syncthreads();
+    lane_cos = cosv + fbase;
+    lane_sin = sinv + fbase;
+    tok_step = half;
   }
-  __syncthreads();
-
-  const float* lane_cos = cosv + fbase;
-  const float* lane_sin = (low ? sinl : sinh) + fbase;
+  const float sign = low ? -1.0f : 1.0f;  // first halves take -sin, second halves +sin
 
 #pragma unroll
   for (int u = 0; u < ROWS; ++u) {
@@ -205,23 +241,19 @@ __device__ __forceinline__ void norm_rope_body(const RopeCta t, const NormRopeAr
       for (int k = 0; k < K; ++k) x[k] = oct_mul(oct_scale(x[k], scale), gm[k]);
     }
     const uint32_t tl = row_ok ? div_magic(row, t.heads, t.magic) - tok0 : 0;
-    const float* tc = lane_cos + tl * half;
-    const float* ts = lane_sin + tl * half;
-    // Scalar multiplies and adds on purpose: each rounds separately (-fmad=false), exactly as the
-    // standalone rope kernel and the CPU operator do; a packed mul/add pair was seen to contract.
-    float v[8], o[8];
-    oct_to_array(x[0], v);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) o[i] = __shfl_sync(kFullMask, v[i], src_lane);
+    const float* tc = lane_cos + static_cast<size_t>(tl) * tok_step;
+    const float* ts = lane_sin + static_cast<size_t>(tl) * tok_step;
+    const Oct o = shuffle_oct(x[0], src_lane);
     if (rotates) {
-      const float4 c0 = *reinterpret_cast<const float4*>(tc), c1 = *reinterpret_cast<const float4*>(tc + 4);
-      const float4 s0 = *reinterpret_cast<const float4*>(ts), s1 = *reinterpret_cast<const float4*>(ts + 4);
-      const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-      const float sg[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = v[i] * c[i] + o[i] * sg[i];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) x[0].p[i] = make_float2(v[2 * i], v[2 * i + 1]);
+      float4 c0, c1, s0, s1;
+      if constexpr (GT) {
+        c0 = __ldg(reinterpret_cast<const float4*>(tc)), c1 = __ldg(reinterpret_cast<const float4*>(tc + 4));
+        s0 = __ldg(reinterpret_cast<const float4*>(ts)), s1 = __ldg(reinterpret_cast<const float4*>(ts + 4));
+      } else {
+        c0 = *reinterpret_cast<const float4*>(tc), c1 = *reinterpret_cast<const float4*>(tc + 4);
+        s0 = *reinterpret_cast<const float4*>(ts), s1 = *reinterpret_cast<const float4*>(ts + 4);
+      }
+      rotate8(x[0], o, c0, c1, scale4(s0, sign), scale4(s1, sign));  // +-sin is exact
     }
     OT* dst = static_cast<OT*>(t.out) + static_cast<size_t>(row) * a.d;
     OT* cdst = t.cache ? static_cast<OT*>(t.cache) + static_cast<size_t>(row) * a.d : nullptr;
@@ -236,7 +268,7 @@ __device__ __forceinline__ void norm_rope_body(const RopeCta t, const NormRopeAr
   }
 }
 
-template <typename IT, typename OT, int K, int ROWS>
+template <typename IT, typename OT, int K, int ROWS, bool GT>
 __global__ void __launch_bounds__(kBlock, K * ROWS >= 8 ? 2 : 3) norm_rope_kernel(const NormRopeArgs a, const __grid_constant__ InvFreq f,
                                                              const unsigned lg, const uint32_t ctas1,
                                                              const float inv_d, const uint32_t magic1,
@@ -250,8 +282,96 @@ __global__ void __launch_bounds__(kBlock, K * ROWS >= 8 ? 2 : 3) norm_rope_kerne
                    ((a.rows + a.heads - 1) / a.heads) * a.heads2, magic2};
   const uint32_t cta = second ? blockIdx.x - ctas1 : blockIdx.x;
   const bool full = (a.d >> 3) == (static_cast<unsigned>(K) << lg) && (cta + 1) * (slots * ROWS) <= t.rows;
-  if (full) norm_rope_body<IT, OT, K, ROWS, true>(t, a, f, lg, cta, inv_d, rope_smem);
-  else norm_rope_body<IT, OT, K, ROWS, false>(t, a, f, lg, cta, inv_d, rope_smem);
+  if (full) norm_rope_body<IT, OT, K, ROWS, true, GT>(t, a, f, lg, cta, inv_d, rope_smem);
+  else norm_rope_body<IT, OT, K, ROWS, false, GT>(t, a, f, lg, cta, inv_d, rope_smem);
+}
+
+// The lean fused kernel for the common case: Q (and K) rows that fill the grid exactly, gammas
+// present, rotation table given, no q|gate split and no cache copy. One row per thread group, one or
+// two octets per lane, operands as plain arguments, no shared memory, no barrier, nothing
+// predicated; which tensor a CTA works on is uniform. Same arithmetic, bit for bit, as the general
+// kernel above.
+struct RopeLeanArgs {  // scalar fields on purpose: indexing a parameter array by tensor copies it to local memory
+  const void *in0, *in1;
+  void *out0, *out1;
+  const float *w0, *w1;
+  uint32_t heads0, heads1, magic0, magic1;
+  uint32_t ctas0;  // CTAs that belong to tensor 0
+  uint32_t d, rot, lg;
+  float eps, inv_d;
+  const float* table;
+};
+
+template <typename IT, typename OT, int K, bool ONEPLUS>
+__global__ void __launch_bounds__(kBlock) norm_rope_lean_kernel(const RopeLeanArgs a) {
+  const bool sel = blockIdx.x >= a.ctas0;
+  const uint32_t cta = blockIdx.x - (sel ? a.ctas0 : 0u);
+  const unsigned lg = a.lg, g = 1u << lg;
+  const unsigned lane = threadIdx.x & 31u;
+  const unsigned lir = threadIdx.x & (g - 1);
+  const uint32_t row = cta * (kBlock >> lg) + (threadIdx.x >> lg);
+  const size_t off = static_cast<size_t>(row) * a.d;
+  const IT* src = static_cast<const IT*>(sel ? a.in1 : a.in0) + off;
+  Raw<IT> rx[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) rx[k] = raw_load(src + (((k << lg) + lir) << 3));
+  const float* w = sel ? a.w1 : a.w0;
+  Oct gm[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    gm[k] = oct_load_cached(w + (((k << lg) + lir) << 3));
+    if (ONEPLUS) {
+      const float2 one = make_float2(1.0f, 1.0f);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) gm[k].p[i] = __fadd2_rn(one, gm[k].p[i]);
+    }
+  }
+  const unsigned hp = a.rot >> 4;  // lanes per half of the rotated span
+  const bool rotates = lir < 2 * hp;
+  const bool low = lir < hp;
+  const unsigned src_lane = lane - lir + (rotates ? (low ? lir + hp : lir - hp) : lir);
+  float4 c0 = make_float4(1.0f, 1.0f, 1.0f, 1.0f), c1 = c0;
+  float4 s0 = make_float4(0.0f, 0.0f, 0.0f, 0.0f), s1 = s0;
+  if (rotates) {  // this token's cos / sin, requested while the row is still in flight
+    const uint32_t token = div_magic(row, sel ? a.heads1 : a.heads0, sel ? a.magic1 : a.magic0);
+    const float* tc = a.table + static_cast<size_t>(token) * a.rot + ((low ? lir : lir - hp) << 3);
+    const float* ts = tc + (a.rot >> 1);
+    const float sign = low ? -1.0f : 1.0f;  // first halves take -sin, second halves +sin (exact)
+    c0 = __ldg(reinterpret_cast<const float4*>(tc)), c1 = __ldg(reinterpret_cast<const float4*>(tc + 4));
+    s0 = scale4(__ldg(reinterpret_cast<const float4*>(ts)), sign);
+    s1 = scale4(__ldg(reinterpret_cast<const float4*>(ts + 4)), sign);
+  }
+  Oct x[K];
+  float2 acc = make_float2(0.0f, 0.0f);
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    x[k] = raw_unpack(rx[k]);
+    acc = oct_sumsq(x[k], acc);
+  }
+  const float ss = group_sum_narrow(acc.x + acc.y, g);
+  const float scale = rsqrtf(__fmaf_rn(ss, a.inv_d, a.eps));
+#pragma unroll
+  for (int k = 0; k < K; ++k) x[k] = oct_mul(oct_scale(x[k], scale), gm[k]);
+  const Oct o = shuffle_oct(x[0], src_lane);
+  if (rotates) rotate8(x[0], o, c0, c1, s0, s1);
+  OT* dst = static_cast<OT*>(sel ? a.out1 : a.out0) + off;
+#pragma unroll
+  for (int k = 0; k < K; ++k) oct_store(dst + (((k << lg) + lir) << 3), x[k]);
+}
+
+// One thread per (token, frequency): the rotation table of a step, shared by every layer.
+__global__ void __launch_bounds__(kBlock) rope_table_kernel(const RopeTableArgs a, const __grid_constant__ InvFreq f) {
+  const uint32_t half = a.rot / 2;
+  const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x;
+  const uint32_t t = static_cast<uint32_t>(idx / half), i = static_cast<uint32_t>(idx % half);
+  if (t >= a.tokens) return;
+  const uint32_t pos = token_pos(a.pos, t);
+  const float angle = __fmul_rn(static_cast<float>(pos), f.f[i]);
+  float sn, c;
+  sincosf(angle, &sn, &c);
+  a.table[static_cast<size_t>(t) * a.rot + i] = c;
+  a.table[static_cast<size_t>(t) * a.rot + half + i] = sn;
+  if (i == 0 && a.pos_out) a.pos_out[t] = pos;
 }
 
 template <typename T>
@@ -313,15 +433,40 @@ cudaError_t LaunchNormRopeT(const NormRopeArgs& a, const InvFreq& f, cudaStream_
   const unsigned ctas2 = static_cast<unsigned>((rows2 + rows_per_cta - 1) / rows_per_cta);
   const unsigned min_heads = a.heads2 && a.heads2 < a.heads ? a.heads2 : a.heads;
   const unsigned max_tok = rows_per_cta / min_heads + 2;  // tokens a CTA's rows can touch
-  const size_t smem = 3 * static_cast<size_t>(max_tok) * (a.rot / 2) * sizeof(float);
+  const size_t smem = a.table ? 0 : 2 * static_cast<size_t>(max_tok) * (a.rot / 2) * sizeof(float);
   if (smem > 48u * 1024u) return cudaErrorInvalidValue;
   const float inv_d = 1.0f / static_cast<float>(a.d);
   const uint32_t m1 = Magic(a.heads, a.rows), m2 = a.heads2 ? Magic(a.heads2, rows2) : 0u;
   const unsigned grid = ctas1 + ctas2;
-  if (k == 2 && rows_in_flight == 4) norm_rope_kernel<IT, OT, 2, 4><<<grid, kBlock, smem, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
-  else if (k == 2) norm_rope_kernel<IT, OT, 2, 2><<<grid, kBlock, smem, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
-  else if (rows_in_flight == 4) norm_rope_kernel<IT, OT, 1, 4><<<grid, kBlock, smem, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
-  else norm_rope_kernel<IT, OT, 1, 2><<<grid, kBlock, smem, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
+  const unsigned rpc1 = kBlock / g;  // rows per CTA of the lean kernel (one row per thread group)
+  const bool lean = a.table && octs == static_cast<unsigned>(k) * g && a.w && a.gate == nullptr && a.cache == nullptr &&
+                    a.cache2 == nullptr && a.in_row_stride == a.d && a.rows % rpc1 == 0 &&
+                    (a.heads2 == 0 || (a.w2 && a.in_row_stride2 == a.d && rows2 % rpc1 == 0)) && !a.force_general;
+  if (lean) {
+    RopeLeanArgs l = {};
+    l.in0 = a.in, l.out0 = a.out, l.w0 = a.w, l.heads0 = a.heads, l.magic0 = m1;
+    l.in1 = a.in2, l.out1 = a.out2, l.w1 = a.w2, l.heads1 = a.heads2 ? a.heads2 : 1, l.magic1 = m2;
+    l.ctas0 = a.rows / rpc1;
+    l.d = a.d, l.rot = a.rot, l.lg = lg, l.eps = a.eps, l.inv_d = inv_d, l.table = a.table;
+    const unsigned lgrid = l.ctas0 + static_cast<unsigned>(rows2 / rpc1);
+    if (k == 2) {
+      if (a.one_plus) norm_rope_lean_kernel<IT, OT, 2, true><<<lgrid, kBlock, 0, s>>>(l);
+      else norm_rope_lean_kernel<IT, OT, 2, false><<<lgrid, kBlock, 0, s>>>(l);
+    } else {
+      if (a.one_plus) norm_rope_lean_kernel<IT, OT, 1, true><<<lgrid, kBlock, 0, s>>>(l);
+      else norm_rope_lean_kernel<IT, OT, 1, false><<<lgrid, kBlock, 0, s>>>(l);
+    }
+    return cudaGetLastError();
+  }
+  if (a.table) {
+    if (k == 2 && rows_in_flight == 4) norm_rope_kernel<IT, OT, 2, 4, true><<<grid, kBlock, 0, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
+    else if (k == 2) norm_rope_kernel<IT, OT, 2, 2, true><<<grid, kBlock, 0, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
+    else norm_rope_kernel<IT, OT, 1, 2, true><<<grid, kBlock, 0, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
+  } else {
+    if (k == 2 && rows_in_flight == 4) norm_rope_kernel<IT, OT, 2, 4, false><<<grid, kBlock, smem, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
+    else if (k == 2) norm_rope_kernel<IT, OT, 2, 2, false><<<grid, kBlock, smem, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
+    else norm_rope_kernel<IT, OT, 1, 2, false><<<grid, kBlock, smem, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
+  }
   return cudaGetLastError();
 }
 
@@ -349,6 +494,15 @@ cudaError_t LaunchNormRope(const NormRopeArgs& a, const InvFreq& f, cudaStream_t
     case kF16 * 3 + kF16: return LaunchNormRopeT<f16, f16>(a, f, s);
   }
   return cudaErrorInvalidValue;
+}
+
+cudaError_t LaunchRopeTable(const RopeTableArgs& a, const InvFreq& f, cudaStream_t s) {
+  const uint64_t n = static_cast<uint64_t>(a.tokens) * (a.rot / 2);
+  if (n == 0) return cudaSuccess;
+  const uint64_t grid = (n + kBlock - 1) / kBlock;
+  if (grid > 0x7FFFFFFFull) return cudaErrorInvalidValue;
+  rope_table_kernel<<<static_cast<unsigned>(grid), kBlock, 0, s>>>(a, f);
+  return cudaGetLastError();
 }
 
 cudaError_t LaunchSplitQgate(const SplitArgs& a, cudaStream_t s) {

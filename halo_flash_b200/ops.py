@@ -149,6 +149,31 @@ def norm_rope_qk(q, k, w_q, w_k, eps, rot, theta, *, q_out=None, q_gate=None, k_
     return q_out, k
 
 
+def rope_table(table, rot, theta, *, pos0=0, params=None, pstride=0, slot=0, scale=1, pos_out=None):
+    """Fill table [T, 2, rot/2] fp32 with cos / sin of every token's rotation angles."""
+    _chk(table, "table", (torch.float32,)), _chk(params, "params", (torch.int32, torch.uint32))
+    _chk(pos_out, "pos_out", (torch.int32, torch.uint32))
+    tokens = table.numel() // rot if rot else 0
+    lib().call("rope_table_ex", _stream(), _p(table), tokens, rot, theta, _p(params), pstride, slot, pos0, scale,
+               _p(pos_out))
+    return table
+
+
+def norm_rope_qk_table(q, k, w_q, w_k, eps, rot, table, *, q_out=None, q_gate=None, k_cache=None, one_plus=True,
+                       q_row_stride=None):
+    """norm_rope_qk with the rotation table of rope_table() (k may be None)."""
+    _chk(q, "q", _ACT), _chk(k, "k", (q.dtype,)), _chk(w_q, "w_q", (torch.float32,)), _chk(w_k, "w_k", (torch.float32,))
+    _chk(table, "table", (torch.float32,))
+    q_out = q if q_out is None else _chk(q_out, "q_out", _ACT)
+    _chk(q_gate, "q_gate", (q.dtype,)), _chk(k_cache, "k_cache", (q_out.dtype,))
+    tokens, hq, d = q_out.shape
+    hk = 0 if k is None else k.shape[1]
+    stride = d if q_row_stride is None else q_row_stride
+    lib().call("norm_rope_qk_table_ex", _stream(), _p(q), stride, _p(q_out), _p(q_gate), _p(w_q), hq, _p(k), _p(k),
+               _p(k_cache), _p(w_k), hk, _code(q), _code(q_out), int(one_plus), eps, d, rot, tokens, _p(table))
+    return q_out, k
+
+
 # ---- group 4 ---------------------------------------------------------------
 def silu_mul(g, up, *, y=None):
     """y = SiLU(g) * up elementwise; y defaults to g (in place)."""

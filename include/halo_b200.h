@@ -212,6 +212,23 @@ int halo_b200_norm_rope_qk_ex(halo_b200_stream stream, const void* q_in, uint64_
                               const uint32_t* params, uint32_t pstride, uint32_t slot, uint32_t pos0, uint32_t scale,
                               uint32_t* pos_out, char* err, size_t errlen);
 
+/* The rotation table of one step: table[t][0][i] = cos, table[t][1][i] = sin of
+ * float(pos_t) * pow(theta, -2 i / rotary_dim), i < rotary_dim / 2 - the angle, cosf and sinf that
+ * RopeNeox (src/kernels/core.hip:275-288) evaluates per head and element - as tokens * rotary_dim
+ * floats, 16-byte aligned, caller-owned. Positions as in halo_b200_rope_ex. Every attention layer of a step rotates at
+ * the same positions, so the table is computed once and shared by all of them. */
+int halo_b200_rope_table_ex(halo_b200_stream stream, float* table, uint32_t tokens, uint32_t rotary_dim, float theta,
+                            const uint32_t* params, uint32_t pstride, uint32_t slot, uint32_t pos0, uint32_t scale,
+                            uint32_t* pos_out, char* err, size_t errlen);
+/* halo_b200_norm_rope_qk_ex (src/kernels/core.hip:368-443 for Q and K of one layer) reading
+ * (cos, sin) from a table made by halo_b200_rope_table_ex instead of computing them: same results bit for bit, no sincosf, shared memory or barrier in the kernel.
+ * k_heads may be 0 (Q only). */
+int halo_b200_norm_rope_qk_table_ex(halo_b200_stream stream, const void* q_in, uint64_t q_row_stride, void* q_out,
+                                    void* q_gate, const float* w_q, uint32_t q_heads, const void* k_in, void* k_out,
+                                    void* k_cache, const float* w_k, uint32_t k_heads, int in_dtype, int out_dtype,
+                                    int one_plus, float eps, uint32_t d, uint32_t rotary_dim, uint32_t tokens,
+                                    const float* table, char* err, size_t errlen);
+
 /* ---- group 4: SwiGLU ----------------------------------------------------------------- */
 
 /* halo_silu_mul, src/kernels/core.hip:321-325: g = SiLU(g) * up. */

@@ -85,3 +85,19 @@ def assert_bf16_within_1ulp(got_bits, want_f32, what=""):
     want_bits = oracle.bf16_bits(np.asarray(want_f32, dtype=np.float32))
     d = np.abs(bf16_ordinal(np.asarray(got_bits).reshape(-1)) - bf16_ordinal(want_bits.reshape(-1)))
     assert d.max() <= 1, f"{what}: {int((d > 1).sum())} values more than 1 bf16 ulp off (max {int(d.max())})"
+
+
+def assert_bf16_rope(got_bits, want_f32, what=""):
+    """bf16 contract for rotated values. A rotated value a*c - b*s can cancel to far below |a|, |b|,
+    where the fp32 contract (|diff| <= 1e-5 * max(|a|, |b|)) is many bf16 ulps of the small result.
+    So: within 1 bf16 ulp of bf16_rne(oracle), or within 1e-5 of the row's largest magnitude plus
+    the bf16 rounding of the value itself."""
+    import oracle
+    want = np.asarray(want_f32, dtype=np.float32)
+    got = oracle.bf16_to_f32(np.asarray(got_bits).reshape(want.shape))
+    want_bits = oracle.bf16_bits(want)
+    ulps = np.abs(bf16_ordinal(np.asarray(got_bits).reshape(-1)) - bf16_ordinal(want_bits.reshape(-1))).reshape(want.shape)
+    rowmax = np.abs(want).max(axis=-1, keepdims=True)
+    slack = 1e-5 * rowmax + np.abs(want) * 2.0 ** -8
+    bad = (ulps > 1) & (np.abs(got.astype(np.float64) - want) > slack)
+    assert not bad.any(), f"{what}: {int(bad.sum())} rotated values outside both bounds"

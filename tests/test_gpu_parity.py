@@ -11,7 +11,7 @@ import pytest
 import torch
 
 import oracle
-from conftest import assert_bf16_within_1ulp, assert_rows_close
+from conftest import assert_bf16_rope, assert_bf16_within_1ulp, assert_rows_close
 from halo_flash_b200 import HaloError, lib, ops, synth
 
 pytestmark = pytest.mark.gpu
@@ -326,8 +326,8 @@ def test_rope_q_and_k_random_positions(orc, shape, dtype):
         check_rope(to_f32(dq), wq, q, s.rot, "q")
         check_rope(to_f32(dk), wk, k, s.rot, "k")
     else:
-        assert_bf16_within_1ulp(bits16(dq), wq, "q bf16")
-        assert_bf16_within_1ulp(bits16(dk), wk, "k bf16")
+        assert_bf16_rope(bits16(dq), wq, "q bf16")
+        assert_bf16_rope(bits16(dk), wk, "k bf16")
         assert np.array_equal(bits16(dq)[..., s.rot:], oracle.bf16_bits(q)[..., s.rot:])
 
 
@@ -432,7 +432,7 @@ def test_fused_norm_rope_bf16(orc):
     want = orc.rope_rows(orc.rmsnorm_rows(x.copy(), ONE + w, s.eps).reshape(T, heads, hd), pos, s.rot, s.theta)
     dx = to_dev(x, "bf16")
     ops.norm_rope(dx, to_dev(w), s.eps, s.rot, s.theta, heads, params=to_dev(pos.view(np.int32)), pstride=1)
-    assert_bf16_within_1ulp(bits16(dx), want.reshape(-1, hd), "norm_rope bf16")
+    assert_bf16_rope(bits16(dx), want.reshape(-1, hd), "norm_rope bf16")
 
 
 # ---- group 4 ---------------------------------------------------------------------------
@@ -700,8 +700,8 @@ def test_q_and_k_norm_rope_in_one_launch(orc):
     pos = np.arange(pos0, pos0 + T, dtype=np.uint32)
     wantq = orc.rope_rows(orc.rmsnorm_rows(q.reshape(-1, hd).copy(), ONE + wq, s.eps).reshape(q.shape), pos, s.rot, s.theta)
     wantk = orc.rope_rows(orc.rmsnorm_rows(k.reshape(-1, hd).copy(), ONE + wk, s.eps).reshape(k.shape), pos, s.rot, s.theta)
-    assert_bf16_within_1ulp(bits16(q2), wantq, "q")
-    assert_bf16_within_1ulp(bits16(k2), wantk, "k")
+    assert_bf16_rope(bits16(q2), wantq, "q")
+    assert_bf16_rope(bits16(k2), wantk, "k")
     # fp32, interleaved q|gate rows, K cache append, tiny shapes (4 Q / 2 KV heads x 64, rot 16)
     c, T2 = synth.C1, 9
     qg = synth.act("t.qk.qg", T2 * c.q_heads, 2 * c.head_dim)
@@ -736,3 +736,49 @@ def test_swiglu_several_tensors_in_one_launch(orc):
     single = Guarded(shapes[0], torch.bfloat16)
     ops.silu_mul(to_dev(gs[0], "bf16"), to_dev(us[0], "bf16"), y=single.t)
     assert torch.equal(single.t, outs[0].t)
+
+
+def test_rotation_table_path_equals_in_kernel_sincos(orc):
+    """norm_rope_qk_table_ex (cos / sin read from a precomputed table) == norm_rope_qk_ex bit for bit;
+    the table itself holds cos / sin of float(pos) * inv_freq within 1e-6 of the CPU's libm."""
+    s, T, pos0 = synth.FULL, 37, 262144 - 37
+    q = rounded(synth.act("t.tb.q", T, s.q_heads, s.head_dim), "bf16")
+    k = rounded(synth.act("t.tb.k", T, s.kv_heads, s.head_dim), "bf16")
+    wq, wk = to_dev(synth.norm_w("t.tb.wq", s.head_dim)), to_dev(synth.norm_w("t.tb.wk", s.head_dim))
+    table = Guarded((T, 2, s.rot // 2), torch.float32)
+    used = torch.zeros(T, dtype=torch.int32, device=DEV)
+    ops.rope_table(table.t, s.rot, s.theta, pos0=pos0, pos_out=used)
+    table.check()
+    assert np.array_equal(used.cpu().numpy(), np.arange(pos0, pos0 + T))
+    inv = orc.rope_inv_freq(s.rot, s.theta)
+    ang = (np.arange(pos0, pos0 + T, dtype=np.uint32).astype(np.float32)[:, None] * inv[None, :]).astype(np.float32)
+    got = to_f32(table.t)
+    assert np.abs(got[:, 0] - np.cos(ang.astype(np.float64))).max() < 1e-6
+    assert np.abs(got[:, 1] - np.sin(ang.astype(np.float64))).max() < 1e-6
+    q1, k1 = to_dev(q, "bf16"), to_dev(k, "bf16")
+    ops.norm_rope_qk(q1, k1, wq, wk, s.eps, s.rot, s.theta, pos0=pos0)
+    q2, k2 = to_dev(q, "bf16"), to_dev(k, "bf16")
+    ops.norm_rope_qk_table(q2, k2, wq, wk, s.eps, s.rot, table.t)
+    assert torch.equal(q1, q2) and torch.equal(k1, k2)
+    q3 = to_dev(q, "bf16")
+    ops.norm_rope_qk_table(q3, None, wq, None, s.eps, s.rot, table.t)
+    assert torch.equal(q1, q3)
+    # T = 32 fills the lean kernel's grid exactly; its result equals the general kernel's
+    T2 = 32
+    qa = rounded(synth.act("t.tb.qa", T2, s.q_heads, s.head_dim), "bf16")
+    ka = rounded(synth.act("t.tb.ka", T2, s.kv_heads, s.head_dim), "bf16")
+    tab2 = ops.rope_table(torch.empty(T2, 2, s.rot // 2, device=DEV), s.rot, s.theta, pos0=100000)
+    res = []
+    for force in (0, 1):
+        lib().tune("norm_force_general", force)
+        try:
+            qd, kd = to_dev(qa, "bf16"), to_dev(ka, "bf16")
+            ops.norm_rope_qk_table(qd, kd, wq, wk, s.eps, s.rot, tab2)
+            res.append((qd, kd))
+        finally:
+            lib().tune("norm_force_general", 0)
+    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
+    pos = np.arange(100000, 100000 + T2, dtype=np.uint32)
+    wantq = orc.rope_rows(orc.rmsnorm_rows(qa.reshape(-1, s.head_dim).copy(), ONE + to_f32(wq), s.eps).reshape(qa.shape),
+                          pos, s.rot, s.theta)
+    assert_bf16_rope(bits16(res[0][0]), wantq, "lean norm+rope q")
