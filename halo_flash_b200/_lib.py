@@ -56,6 +56,8 @@ SIGNATURES: dict[str, list] = {
                                   _p, _u32, _u32, _u32, _u32, _p],
     "halo_b200_rope_table_ex": [_p, _u32, _u32, _f, _p, _u32, _u32, _u32, _u32, _p],
     "halo_b200_norm_rope_qk_table_ex": [_p, _u64, _p, _p, _p, _u32, _p, _p, _p, _p, _u32, _i, _i, _i, _f, _u32, _u32, _u32, _p],
+    "halo_b200_norm_rope_qk_noalloc": [_p, _u64, _p, _p, _p, _u32, _p, _p, _p, _p, _u32, _i, _i, _i, _f, _u32, _u32, _u32, _f,
+                                       _p, _u32, _u32, _u32, _u32, _p],
     "halo_b200_silu_mul": [_p, _p, _u32],
     "halo_b200_silu_mul_h": [_p, _p, _p, _u32],
     "halo_b200_silu_mul_ex": [_p, _p, _i, _p, _i, _u64],

@@ -229,6 +229,22 @@ int halo_b200_norm_rope_qk_table_ex(halo_b200_stream stream, const void* q_in, u
                                     int one_plus, float eps, uint32_t d, uint32_t rotary_dim, uint32_t tokens,
                                     const float* table, char* err, size_t errlen);
 
+/* No counterpart in the reference. halo_b200_norm_rope_qk_ex for callers that cannot allocate
+ * device memory and have no buffer to lend for the rotation table: an engine that committed and
+ * accounts for all of its device memory at load time, a serving loop that cannot afford cudaMalloc's
+ * device-wide synchronisation, a host that forbids allocation after start-up. Same arguments and
+ * results (bit for bit) as halo_b200_norm_rope_qk_ex; the rotation table lives in a fixed 4 MiB
+ * array inside the library (on every GPU that loads it, until exit) and nothing is allocated.
+ * Limits: tokens * rotary_dim <= 1048576, otherwise -1 with a message. Every call shares that
+ * array: calls on one stream are ordered, calls whose kernels overlap on the GPU race. The first
+ * call on each device resolves the array's address and must be made outside stream capture. */
+int halo_b200_norm_rope_qk_noalloc(halo_b200_stream stream, const void* q_in, uint64_t q_row_stride, void* q_out,
+                                   void* q_gate, const float* w_q, uint32_t q_heads, const void* k_in, void* k_out,
+                                   void* k_cache, const float* w_k, uint32_t k_heads, int in_dtype, int out_dtype,
+                                   int one_plus, float eps, uint32_t d, uint32_t rotary_dim, uint32_t tokens,
+                                   float theta, const uint32_t* params, uint32_t pstride, uint32_t slot,
+                                   uint32_t pos0, uint32_t scale, uint32_t* pos_out, char* err, size_t errlen);
+
 /* ---- group 4: SwiGLU ----------------------------------------------------------------- */
 
 /* halo_silu_mul, src/kernels/core.hip:321-325: g = SiLU(g) * up. */
