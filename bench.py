@@ -200,19 +200,12 @@ def time_graph(torch, fn_capture, replays: int):
     return e0.elapsed_time(e1) / replays
 
 
-def kernel_table(torch, shapes, T: int, peaks: dict) -> dict:
-    """Average duration of each kernel of the chain, launched back to back over a ring of distinct
-    buffer sets totalling >= 512 MB (so no launch finds its inputs in the 126 MB L2); one CUDA graph
-    per kernel, CUDA-event timed on the launching stream."""
+def op_specs(torch, shapes, T: int):
+    """(make buffers, run) for every launch shape of the chain, plus the Q8_0-epilogue form of the add + norm."""
     from halo_flash_b200 import chain as chain_mod, ops
     s, dev, bf = shapes, "cuda", torch.bfloat16
     bpt = chain_mod.bytes_per_token(s, 2)
     k = s.top_k
-
-    def ring(nbytes_per_set, make):
-        n = max(3, -(-512 * 2**20 // nbytes_per_set))
-        return [make() for _ in range(n)]
-
     r = lambda *shape: torch.randn(*shape, device=dev).to(bf)
     w_h = torch.randn(s.hidden, device=dev) * 0.1
     w_hd = torch.randn(s.head_dim, device=dev) * 0.1
@@ -235,12 +228,27 @@ def kernel_table(torch, shapes, T: int, peaks: dict) -> dict:
         "embed": (lambda: (torch.randint(0, 8192, (T,), device=dev, dtype=torch.int32),
                            torch.empty(T, s.hidden, device=dev, dtype=bf)),
                   lambda b: ops.embed_q8_0(table, b[0], s.hidden, b[1])),
+        # not in the chain: the add + norm whose only normalized output is Q8_0 blocks
+        "add_rmsnorm_q8": (lambda: (r(T, s.hidden), r(T, s.hidden),
+                                    torch.empty(T, s.q8_row_bytes, device=dev, dtype=torch.uint8)),
+                           lambda b: ops.add_rmsnorm(b[0], b[1], w_h, s.eps, q8_0=b[2])),
     }
+    nbytes = {"add_rmsnorm": bpt["add_rmsnorm"], "l2norm": bpt["l2norm"], "gated_norm": bpt["gated_norm"],
+              "norm_rope_qk": bpt["norm_rope"], "swiglu_moe": bpt["swiglu_shared"] + bpt["swiglu_routed"],
+              "embed": bpt["embed"], "add_rmsnorm_q8": 3 * 2 * s.hidden + s.q8_row_bytes}
+    return specs, {k_: v * T for k_, v in nbytes.items()}
+
+
+def kernel_table(torch, shapes, T: int, peaks: dict) -> dict:
+    """Average duration of each kernel of the chain, launched back to back over a ring of distinct
+    buffer sets totalling >= 512 MB (so no launch finds its inputs in the 126 MB L2); one CUDA graph
+    per kernel, CUDA-event timed on the launching stream."""
+    specs, nbytes_of = op_specs(torch, shapes, T)
     out = {}
     for name, (make, run) in specs.items():
-        nbytes = {"norm_rope_qk": bpt["norm_rope"], "swiglu_moe": bpt["swiglu_shared"] + bpt["swiglu_routed"]}.get(
-            name, bpt.get(name, 0)) * T
-        sets = ring(nbytes, make)
+        nbytes = nbytes_of[name]
+        n = max(3, -(-512 * 2**20 // nbytes))
+        sets = [make() for _ in range(n)]
         run(sets[0])
         torch.cuda.synchronize()
         reps = max(1, 60 // len(sets))
@@ -252,6 +260,21 @@ def kernel_table(torch, shapes, T: int, peaks: dict) -> dict:
         del sets
         torch.cuda.empty_cache()
     return out
+
+
+def profile_op(args) -> None:
+    """A few eager launches of ONE op over distinct buffer sets and nothing else: the small case a
+    profiler capture wants (ncu -k <kernel> -s 2 -c 1 python bench.py --profile-op <op>)."""
+    import torch
+    from halo_flash_b200 import synth
+    specs, _ = op_specs(torch, synth.FULL, args.tokens)
+    make, run = specs[args.profile_op]
+    sets = [make() for _ in range(6)]
+    torch.cuda.synchronize()
+    for b in sets:
+        run(b)
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_op": args.profile_op, "tokens": args.tokens, "launches": len(sets)}), flush=True)
 
 
 def run_e2e(torch, ch, steps: int) -> dict:
@@ -389,7 +412,7 @@ def run_ours(args) -> None:
         return
     table = kernel_table(torch, synth.FULL, T, peaks)
     launches = {"add_rmsnorm": 96, "l2norm": 36, "gated_norm": 36, "norm_rope_qk": 12, "swiglu_moe": 48, "embed": 1}
-    est = {k: v["us"] * launches[k] for k, v in table.items()}
+    est = {k: table[k]["us"] * n for k, n in launches.items()}
     step_bytes = chain_mod.chain_bytes_per_token(synth.FULL, 2) * T
     roofline = {"bound": "hbm", "kernel": "norm_rows_lean_kernel<bf16,bf16,K=2,ADD> (residual add + RMSNorm(1+w), H=2048)",
                 "achieved": table[top]["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -430,8 +453,12 @@ def main() -> None:
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
     ap.add_argument("--no-kernel-table", action="store_true", help="skip the per-kernel timing leg (profiler captures)")
+    ap.add_argument("--profile-op", default=None, help="run 6 eager launches of one op and exit (profiler captures): "
+                    "add_rmsnorm, add_rmsnorm_q8, l2norm, gated_norm, norm_rope_qk, swiglu_moe, embed")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile_op:
+        profile_op(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
