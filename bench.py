@@ -200,6 +200,11 @@ def time_graph(torch, fn_capture, replays: int):
     return e0.elapsed_time(e1) / replays
 
 
+# DRAM traffic per token of the add + RMSNorm kernel from its ncu capture (profiles/): equal to its
+# algorithmic bytes (2 rows read, 2 rows written, 2 bytes per element, H = 2048).
+TRAFFIC_PER_TOKEN = 16384
+
+
 def op_specs(torch, shapes, T: int):
     """(make buffers, run) for every launch shape of the chain, plus the Q8_0-epilogue form of the add + norm."""
     from halo_flash_b200 import chain as chain_mod, ops
@@ -417,7 +422,10 @@ def run_ours(args) -> None:
     roofline = {"bound": "hbm", "kernel": "norm_rows_lean_kernel<bf16,bf16,K=2,ADD> (residual add + RMSNorm(1+w), H=2048)",
                 "achieved": table[top]["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": round(table[top]["gbs"] / peaks["hbm_gbs"], 4), "peak_kind": peak_kind,
-                "frac_of_8000": table[top]["frac_8000"], "traffic": None, "us_per_launch": table[top]["us"],
+                "frac_of_8000": table[top]["frac_8000"], "traffic": TRAFFIC_PER_TOKEN * T,
+                "traffic_how": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at T=4096 "
+                               "(33.6 MB read; the write-back of the 33.6 MB written is deferred in L2 and is "
+                               "counted at its algorithmic size), scaled by tokens", "us_per_launch": table[top]["us"],
                 "bytes_per_launch": table[top]["bytes"],
                 "how": "CUDA events around one graph of back-to-back launches over a >=512 MB ring of buffer sets",
                 "chain": {"bytes_per_step": step_bytes, "gbs": round(step_bytes / (ms_step * 1e-3) / 1e9, 1),
@@ -432,8 +440,9 @@ def run_ours(args) -> None:
             "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": config_dict(synth.FULL, T, n_gpus), "clocks": clocks,
-            "e2e": {"value": round(T * n_gpus / (e2e_ms * 1e-3), 1), "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"],
-                    "d2h_bytes_per_step": e2e["d2h"], "ms_per_step": round(e2e_ms, 3)},
+            "e2e": None if args.no_e2e else
+            {"value": round(T * n_gpus / (e2e_ms * 1e-3), 1), "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"],
+             "d2h_bytes_per_step": e2e["d2h"], "ms_per_step": round(e2e_ms, 3)},
             "gpu_launches": launches_per_step * args.steps, "roofline": roofline, "cpu_baseline": cpu}
     print(json.dumps(line), flush=True)
     if dist is not None:

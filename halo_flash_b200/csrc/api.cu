@@ -19,6 +19,7 @@ std::atomic<int> g_norm_short_rows_k1{0};
 std::atomic<int> g_norm_force_general{0};
 std::atomic<int> g_rope_rows_per_group{0};
 std::atomic<int> g_gated_rows_per_group{0};
+std::atomic<int> g_pdl{1};
 
 int Fail(char* err, size_t errlen, const char* fmt, ...) {
   if (err && errlen) {
@@ -264,6 +265,10 @@ int RunNormRope(NormRopeArgs a, float theta, const char* what, halo_b200_stream 
 
 }  // namespace
 
+namespace halo_b200 {
+bool PdlEnabled() { return g_pdl.load(std::memory_order_relaxed) != 0; }
+}  // namespace halo_b200
+
 extern "C" {
 
 const char* halo_b200_version(void) { return "halo_b200 0.1 sm_100a"; }
@@ -288,6 +293,11 @@ int halo_b200_tune(const char* key, int value) {
   if (std::strcmp(key, "norm_force_general") == 0) {
     if (value != 0 && value != 1) return -1;
     g_norm_force_general.store(value, std::memory_order_relaxed);
+    return 0;
+  }
+  if (std::strcmp(key, "pdl") == 0) {
+    if (value != 0 && value != 1) return -1;
+    g_pdl.store(value, std::memory_order_relaxed);
     return 0;
   }
   if (std::strcmp(key, "norm_short_rows_k1") == 0) {

@@ -24,6 +24,18 @@ namespace halo_b200 {
 constexpr unsigned kFullMask = 0xFFFFFFFFu;
 constexpr int kBlock = 256;  // threads per CTA of every row kernel
 
+// Programmatic dependent launch. Every kernel of the library starts with pdl_begin(): it lets
+// the next kernel in the stream be scheduled as soon as all CTAs of this one are resident (its
+// CTAs then sit in their own pdl_begin() until this grid has completed and its writes are
+// visible), and it waits for the kernel before this one in the same way. Nothing is read or
+// written before the wait. The launch gap between two 12-microsecond kernels (CTA scheduling,
+// parameter fetch, index arithmetic) thereby overlaps the tail of the earlier kernel. Both
+// instructions are no-ops in a kernel launched without the attribute LaunchKernel() sets.
+__device__ __forceinline__ void pdl_begin() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 using bf16 = __nv_bfloat16;
 using f16 = __half;
 
@@ -352,33 +364,57 @@ __device__ __forceinline__ float quad_amax(const float (&v)[8]) {
   return m;
 }
 
+// q[i] = clamp(rint(v[i] / d), +-127) for 8 values as 8 packed two's-complement bytes, with the
+// results of the IEEE division but (almost always) without dividing. t = v * rcp(d) is within
+// 2.3e-5 of the real quotient for |t| <= 127.5 and the correctly rounded quotient within 8e-6,
+// so whenever t is farther than 1e-4 from a rounding boundary (n + 0.5) both round to the same
+// integer. Rounding to nearest-even is the add of 1.5 * 2^23, whose low mantissa byte is the
+// code. The fast path also skips the clamp: with |v| <= amax and d a normal half within 2^-11
+// of amax / 127 the quotient stays below 127.1. A thread redoes its 8 values with the division
+// and the clamp when one of them is within 1e-4 of a boundary (about 1 in 600) or is NaN (the
+// test is written so that NaN fails it), or when d is a subnormal half, infinite or NaN.
+// Clamping before the rounding equals clamping after it (the bounds are integers), and NaN
+// clamps to -127 either way. The fast path runs on packed fp32x2 instructions.
+__device__ __forceinline__ uint2 round_div_codes(const float (&v)[8], float d) {
+  constexpr float kMagic = 12582912.0f;
+  const float r = rcp_approx(d);
+  const float2 r2 = make_float2(r, r), magic2 = make_float2(kMagic, kMagic), neg2 = make_float2(-kMagic, -kMagic);
+  uint32_t bits[8];
+  bool ok = d >= 6.2e-5f && d < 1e30f;
+#pragma unroll
+  for (int i = 0; i < 8; i += 2) {
+    const float2 t = __fmul2_rn(make_float2(v[i], v[i + 1]), r2);
+    const float2 s = __fadd2_rn(t, magic2);
+    const float2 n = __fadd2_rn(s, neg2);
+    const float2 f = __fadd2_rn(t, make_float2(-n.x, -n.y));
+    ok = ok && fabsf(f.x) <= 0.4999f && fabsf(f.y) <= 0.4999f;
+    bits[i] = __float_as_uint(s.x);
+    bits[i + 1] = __float_as_uint(s.y);
+  }
+  if (!ok) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float t = fminf(fmaxf(__fdiv_rn(v[i], d), -127.0f), 127.0f);
+      bits[i] = __float_as_uint(__fadd_rn(t, kMagic));
+    }
+  }
+  return make_uint2(__byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410),
+                    __byte_perm(__byte_perm(bits[4], bits[5], 0x0040), __byte_perm(bits[6], bits[7], 0x0040), 0x5410));
+}
+
 // True Q8_0 (src/core/lowbit.cpp:285-298): d = half(amax / 127); q = clamp(rint(x / float(d)), +-127),
 // 0 when d == 0. Returns the 8 codes packed little-endian and the scale bits.
 __device__ __forceinline__ uint2 q8_0_codes(const float (&v)[8], float amax, uint16_t* dbits) {
   const f16 dh = __float2half_rn(amax / 127.0f);
   const float d = __half2float(dh);
   *dbits = __half_as_ushort(dh);
-  uint32_t w[2] = {0u, 0u};
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    float q = 0.0f;
-    if (d > 0.0f) q = fminf(fmaxf(rintf(v[i] / d), -127.0f), 127.0f);
-    const int qi = static_cast<int>(q);
-    w[i >> 2] |= (static_cast<uint32_t>(qi) & 0xFFu) << (8 * (i & 3));
-  }
-  return make_uint2(w[0], w[1]);
+  return d > 0.0f ? round_div_codes(v, d) : make_uint2(0u, 0u);
 }
 
 // int8 activation form (src/kernels/core.hip:3086-3101): scale = amax / 127 in fp32,
-// q = rint(v / scale), 0 when scale == 0.
+// q = rint(v / scale), 0 when scale == 0. (|v| <= amax keeps the quotient within +-127.)
 __device__ __forceinline__ uint2 i8_codes(const float (&v)[8], float scale) {
-  uint32_t w[2] = {0u, 0u};
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int qi = scale > 0.0f ? static_cast<int>(rintf(v[i] / scale)) : 0;
-    w[i >> 2] |= (static_cast<uint32_t>(qi) & 0xFFu) << (8 * (i & 3));
-  }
-  return make_uint2(w[0], w[1]);
+  return scale > 0.0f ? round_div_codes(v, scale) : make_uint2(0u, 0u);
 }
 
 // 8 code bytes to an address that is only 2-byte aligned (inside a 34-byte block).

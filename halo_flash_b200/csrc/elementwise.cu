@@ -58,6 +58,7 @@ struct VecSegments {
 // register count low enough for 5 resident CTAs per SM.
 template <typename IT, typename OT, int OP>
 __global__ void __launch_bounds__(kBlock, sizeof(IT) == 4 ? 3 : 5) elementwise_vec_kernel(const VecSegments v) {
+  pdl_begin();
   // Segment lookup by compare-and-select over constant indices: indexing the parameter arrays
   // with a run-time value would make the compiler copy them to local memory.
   const void* sa = v.a[0];
@@ -102,6 +103,7 @@ template <typename IT, typename OT, int OP>
 __global__ void __launch_bounds__(kBlock) elementwise_scalar_kernel(const IT* pa, const IT* pb, OT* py,
                                                                    const uint64_t begin, const uint64_t n,
                                                                    const float alpha) {
+  pdl_begin();
   for (uint64_t i = begin + static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x; i < n;
        i += static_cast<uint64_t>(gridDim.x) * kBlock)
     py[i] = from_f32<OT>(apply(OP, to_f32(pa[i]), to_f32(pb[i]), alpha));
@@ -130,7 +132,7 @@ cudaError_t LaunchOp(const EltArgs& a, cudaStream_t s) {
     v.first_cta[kMaxSegments] = static_cast<uint32_t>(ctas);
     for (int i = a.nseg; i < kMaxSegments; ++i) v.first_cta[i] = 0xFFFFFFFFu;  // never selected
     if (ctas) {
-      elementwise_vec_kernel<IT, OT, OP><<<static_cast<unsigned>(ctas), kBlock, 0, s>>>(v);
+      LaunchKernel(elementwise_vec_kernel<IT, OT, OP>, static_cast<unsigned>(ctas), kBlock, 0, s, v);
       const cudaError_t e = cudaGetLastError();
       if (e != cudaSuccess) return e;
     }
@@ -139,7 +141,7 @@ cudaError_t LaunchOp(const EltArgs& a, cudaStream_t s) {
     if (done[i] < a.seg[i].n) {
       uint64_t grid = (a.seg[i].n - done[i] + kBlock - 1) / kBlock;
       if (grid > 148u * 32u) grid = 148u * 32u;
-      elementwise_scalar_kernel<IT, OT, OP><<<static_cast<unsigned>(grid), kBlock, 0, s>>>(
+      LaunchKernel(elementwise_scalar_kernel<IT, OT, OP>, static_cast<unsigned>(grid), kBlock, 0, s, 
           static_cast<const IT*>(a.seg[i].a), static_cast<const IT*>(a.seg[i].b), static_cast<OT*>(a.seg[i].y), done[i],
           a.seg[i].n, a.alpha);
       const cudaError_t e = cudaGetLastError();

@@ -28,6 +28,7 @@ __device__ __forceinline__ void cp_async_wait_all() {
 template <typename OT>
 __global__ void __launch_bounds__(kBlock) embed_q8_0_kernel(const EmbedArgs a, const unsigned warps,
                                                            const unsigned row_smem) {
+  pdl_begin();
   extern __shared__ __align__(16) uint8_t stage[];
   const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   if (warp >= warps) return;
@@ -69,6 +70,7 @@ __global__ void __launch_bounds__(kBlock) embed_q8_0_kernel(const EmbedArgs a, c
 // One thread per element, byte loads: any alignment, any row_bytes.
 template <typename OT>
 __global__ void __launch_bounds__(kBlock) embed_q8_0_scalar_kernel(const EmbedArgs a) {
+  pdl_begin();
   OT* out = static_cast<OT*>(a.out);
   const size_t total = static_cast<size_t>(a.tokens) * a.cols;
   for (size_t idx = static_cast<size_t>(blockIdx.x) * kBlock + threadIdx.x; idx < total;
@@ -93,13 +95,13 @@ cudaError_t LaunchEmbedT(const EmbedArgs& a, cudaStream_t s) {
   if (a.vec && static_cast<size_t>(warps) * row_smem <= 48u * 1024u) {
     unsigned grid = (a.tokens + warps - 1) / warps;
     if (grid > 148u * 8u) grid = 148u * 8u;
-    embed_q8_0_kernel<OT><<<grid, kBlock, static_cast<size_t>(warps) * row_smem, s>>>(a, warps, row_smem);
+    LaunchKernel(embed_q8_0_kernel<OT>, grid, kBlock, static_cast<size_t>(warps) * row_smem, s, a, warps, row_smem);
     return cudaGetLastError();
   }
   const size_t total = static_cast<size_t>(a.tokens) * a.cols;
   size_t grid = (total + kBlock - 1) / kBlock;
   if (grid > 148u * 32u) grid = 148u * 32u;
-  embed_q8_0_scalar_kernel<OT><<<static_cast<unsigned>(grid), kBlock, 0, s>>>(a);
+  LaunchKernel(embed_q8_0_scalar_kernel<OT>, static_cast<unsigned>(grid), kBlock, 0, s, a);
   return cudaGetLastError();
 }
 

@@ -9,8 +9,33 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <utility>
 
 namespace halo_b200 {
+
+// True unless halo_b200_tune("pdl", 0) switched programmatic dependent launch off.
+bool PdlEnabled();
+
+// Every kernel launch of the library: a plain stream-ordered launch that additionally allows the
+// kernel to be scheduled while its predecessor in the stream drains (the kernels order
+// themselves with pdl_begin()). Safe next to foreign kernels: one that never signals lets its
+// successor start only at its completion, and a successor launched without the attribute waits
+// for full completion as usual. Capturable into CUDA graphs (a programmatic edge).
+template <typename... KArgs, typename... Args>
+inline cudaError_t LaunchKernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = PdlEnabled() ? 1u : 0u;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 enum DType : int { kF32 = 0, kF16 = 1, kBF16 = 2 };
 inline std::size_t DTypeSize(int t) { return t == kF32 ? 4 : 2; }

@@ -190,6 +190,7 @@ constexpr int MinCtas(int live) { return live <= 1 ? 6 : (live <= 2 ? 5 : (live 
 template <typename XT, typename YT, int K, int R, bool ADD>
 __global__ void __launch_bounds__(kBlock, MinCtas(K * R)) norm_rows_kernel(const NormArgs a, const unsigned lg,
                                                                           const float inv_d) {
+  pdl_begin();
   __shared__ float scratch[kBlock / 32];
   norm_rows_body<XT, YT, K, R, ADD, false>(a, lg, inv_d, scratch);
 }
@@ -212,6 +213,7 @@ struct LeanArgs {
   float eps, inv_d;
   uint32_t lg;
   int one_plus, l2;
+  int stage_q8;  // Q8_0 blocks leave through shared memory as 16-byte stores (see the kernel)
 };
 
 // WIDE: more than one warp per row (g > 32), the reduction crosses shared memory and a barrier.
@@ -220,7 +222,13 @@ struct LeanArgs {
 // cost these microsecond CTAs 3-4 % (12.6 vs 12.1 us on the add + norm of 4096 x 2048).
 template <typename XT, typename YT, int K, bool ADD, bool EPI, bool WIDE, int MODE>
 __global__ void __launch_bounds__(kBlock) norm_rows_lean_kernel(const LeanArgs a) {
+  pdl_begin();
   __shared__ float scratch[WIDE ? kBlock / 32 : 1];
+  // Q8_0 staging: the 32 octets of a warp's slab are 8 blocks = 272 contiguous output bytes that
+  // start on a 16-byte boundary (272 = 17 * 16), so the warp assembles them in shared memory
+  // with 2-byte stores and 17 lanes write them out as 16-byte stores; the 2-byte global stores
+  // this replaces cost 4-5 store instructions per thread, each touching 32 separate sectors.
+  __shared__ __align__(16) uint8_t stage[EPI ? kBlock / 32 : 1][EPI ? K : 1][EPI ? 272 : 16];
   const unsigned lg = a.lg, g = 1u << lg;
   const unsigned lir = threadIdx.x & (g - 1);
   const uint32_t row = blockIdx.x * (kBlock >> lg) + (threadIdx.x >> lg);
@@ -276,9 +284,23 @@ __global__ void __launch_bounds__(kBlock) norm_rows_lean_kernel(const LeanArgs a
       if (a.q8_0) {
         uint16_t dbits;
         const uint2 codes = q8_0_codes(arr, amax, &dbits);
-        uint8_t* blk = a.q8_0 + (static_cast<size_t>(row) * (a.d >> 5) + (c0 >> 5)) * 34;
-        if ((c0 & 31u) == 0) *reinterpret_cast<uint16_t*>(blk) = dbits;
-        store_codes_u16(blk + 2 + (c0 & 31u), codes);
+        const size_t blk_index = static_cast<size_t>(row) * (a.d >> 5) + (c0 >> 5);
+        if (a.stage_q8) {
+          const unsigned lane = threadIdx.x & 31u;
+          uint8_t* st = stage[threadIdx.x >> 5][k];
+          uint8_t* sb = st + (lane >> 2) * 34;
+          if ((lane & 3u) == 0) *reinterpret_cast<uint16_t*>(sb) = dbits;
+          store_codes_u16(sb + 2 + ((lane & 3u) << 3), codes);
+          __syncwarp();
+          if (lane < 17) {
+            uint8_t* out = a.q8_0 + (blk_index - (lane >> 2)) * 34;  // the warp's first block
+            reinterpret_cast<uint4*>(out)[lane] = reinterpret_cast<const uint4*>(st)[lane];
+          }
+        } else {
+          uint8_t* blk = a.q8_0 + blk_index * 34;
+          if ((c0 & 31u) == 0) *reinterpret_cast<uint16_t*>(blk) = dbits;
+          store_codes_u16(blk + 2 + (c0 & 31u), codes);
+        }
       }
       if (a.xq) {
         const float qs = amax / 127.0f;
@@ -293,6 +315,7 @@ __global__ void __launch_bounds__(kBlock) norm_rows_lean_kernel(const LeanArgs a
 // after the reduction. Correctness path for shapes the vector kernel refuses.
 template <typename XT, typename YT, bool ADD>
 __global__ void __launch_bounds__(kBlock) norm_rows_scalar_kernel(const NormArgs a) {
+  pdl_begin();
   __shared__ float scratch[kBlock / 32];
   __shared__ float total;
   const uint32_t row = blockIdx.x;
@@ -456,6 +479,7 @@ __device__ __forceinline__ void gated_norm_body(const GatedArgs& a, const unsign
 template <typename OT, typename ZT, typename YT, int K, int R, bool FULL>
 __global__ void __launch_bounds__(kBlock, K >= 4 ? 2 : (K * R <= 2 ? 4 : 3)) gated_norm_kernel(const GatedArgs a, const unsigned lg,
                                                                                const float inv_d) {
+  pdl_begin();
   __shared__ float scratch[kBlock / 32];
   gated_norm_body<OT, ZT, YT, K, R, FULL>(a, lg, inv_d, scratch);
 }
@@ -474,6 +498,7 @@ struct GatedLeanArgs {
 
 template <typename OT, typename ZT, typename YT>
 __global__ void __launch_bounds__(kBlock) gated_norm_lean_kernel(const GatedLeanArgs a) {
+  pdl_begin();
   const unsigned lg = a.lg, g = 1u << lg;
   const unsigned lir = threadIdx.x & (g - 1);
   const uint32_t row = blockIdx.x * (kBlock >> lg) + (threadIdx.x >> lg);
@@ -498,6 +523,7 @@ __global__ void __launch_bounds__(kBlock) gated_norm_lean_kernel(const GatedLean
 
 template <typename OT, typename ZT, typename YT>
 __global__ void __launch_bounds__(kBlock) gated_norm_scalar_kernel(const GatedArgs a) {
+  pdl_begin();
   __shared__ float scratch[kBlock / 32];
   __shared__ float total;
   const size_t off = static_cast<size_t>(blockIdx.x) * a.d;
@@ -579,18 +605,20 @@ cudaError_t LaunchLean(const NormArgs& a, const Shape& sh, unsigned grid, cudaSt
   l.lg = sh.lg;
   l.one_plus = a.one_plus;
   l.l2 = a.l2;
+  // a warp's 32 octets must be consecutive in the output: rows of at least a warp, or one octet per thread
+  l.stage_q8 = a.q8_0 && (reinterpret_cast<uintptr_t>(a.q8_0) & 15u) == 0 && (sh.lg >= 5 || K == 1);
   const bool epi = a.q8_0 || a.xq;
   const int mode = (!epi && a.w && a.y && !a.l2) ? (a.one_plus ? 2 : 1) : 0;
   if (sh.lg > 5) {
-    if (epi) norm_rows_lean_kernel<XT, YT, K, ADD, true, true, 0><<<grid, kBlock, 0, s>>>(l);
-    else if (mode == 2) norm_rows_lean_kernel<XT, YT, K, ADD, false, true, 2><<<grid, kBlock, 0, s>>>(l);
-    else if (mode == 1) norm_rows_lean_kernel<XT, YT, K, ADD, false, true, 1><<<grid, kBlock, 0, s>>>(l);
-    else norm_rows_lean_kernel<XT, YT, K, ADD, false, true, 0><<<grid, kBlock, 0, s>>>(l);
+    if (epi) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, true, 0>, grid, kBlock, 0, s, l);
+    else if (mode == 2) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, true, 2>, grid, kBlock, 0, s, l);
+    else if (mode == 1) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, true, 1>, grid, kBlock, 0, s, l);
+    else LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, true, 0>, grid, kBlock, 0, s, l);
   } else {
-    if (epi) norm_rows_lean_kernel<XT, YT, K, ADD, true, false, 0><<<grid, kBlock, 0, s>>>(l);
-    else if (mode == 2) norm_rows_lean_kernel<XT, YT, K, ADD, false, false, 2><<<grid, kBlock, 0, s>>>(l);
-    else if (mode == 1) norm_rows_lean_kernel<XT, YT, K, ADD, false, false, 1><<<grid, kBlock, 0, s>>>(l);
-    else norm_rows_lean_kernel<XT, YT, K, ADD, false, false, 0><<<grid, kBlock, 0, s>>>(l);
+    if (epi) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, false, 0>, grid, kBlock, 0, s, l);
+    else if (mode == 2) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, false, 2>, grid, kBlock, 0, s, l);
+    else if (mode == 1) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, false, 1>, grid, kBlock, 0, s, l);
+    else LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, false, 0>, grid, kBlock, 0, s, l);
   }
   return cudaGetLastError();
 }
@@ -598,7 +626,7 @@ cudaError_t LaunchLean(const NormArgs& a, const Shape& sh, unsigned grid, cudaSt
 template <typename XT, typename YT, bool ADD>
 cudaError_t LaunchNormT(const NormArgs& a, cudaStream_t s) {
   if (!a.vec) {
-    norm_rows_scalar_kernel<XT, YT, ADD><<<a.rows, kBlock, 0, s>>>(a);
+    LaunchKernel(norm_rows_scalar_kernel<XT, YT, ADD>, a.rows, kBlock, 0, s, a);
     return cudaGetLastError();
   }
   const Shape sh = PickShape(a.d / 8, a.rows, a.threads_per_row, (a.q8_0 || a.xq) ? 4u : 1u, a.short_rows_k1);
@@ -614,10 +642,10 @@ cudaError_t LaunchNormT(const NormArgs& a, cudaStream_t s) {
   }
   const float inv_d = 1.0f / static_cast<float>(a.d);
   switch (sh.k) {
-    case 1: norm_rows_kernel<XT, YT, 1, 1, ADD><<<grid, kBlock, 0, s>>>(a, sh.lg, inv_d); break;
-    case 2: norm_rows_kernel<XT, YT, 2, 1, ADD><<<grid, kBlock, 0, s>>>(a, sh.lg, inv_d); break;
-    case 4: norm_rows_kernel<XT, YT, 4, 1, ADD><<<grid, kBlock, 0, s>>>(a, sh.lg, inv_d); break;
-    case 8: norm_rows_kernel<XT, YT, 8, 1, ADD><<<grid, kBlock, 0, s>>>(a, sh.lg, inv_d); break;
+    case 1: LaunchKernel(norm_rows_kernel<XT, YT, 1, 1, ADD>, grid, kBlock, 0, s, a, sh.lg, inv_d); break;
+    case 2: LaunchKernel(norm_rows_kernel<XT, YT, 2, 1, ADD>, grid, kBlock, 0, s, a, sh.lg, inv_d); break;
+    case 4: LaunchKernel(norm_rows_kernel<XT, YT, 4, 1, ADD>, grid, kBlock, 0, s, a, sh.lg, inv_d); break;
+    case 8: LaunchKernel(norm_rows_kernel<XT, YT, 8, 1, ADD>, grid, kBlock, 0, s, a, sh.lg, inv_d); break;
     default: return cudaErrorInvalidValue;
   }
   return cudaGetLastError();
@@ -641,7 +669,7 @@ cudaError_t LaunchNormY(const NormArgs& a, cudaStream_t s) {
 template <typename OT, typename ZT, typename YT>
 cudaError_t LaunchGatedT(const GatedArgs& a, cudaStream_t s) {
   if (!a.vec) {
-    gated_norm_scalar_kernel<OT, ZT, YT><<<a.rows, kBlock, 0, s>>>(a);
+    LaunchKernel(gated_norm_scalar_kernel<OT, ZT, YT>, a.rows, kBlock, 0, s, a);
     return cudaGetLastError();
   }
   const float inv_d = 1.0f / static_cast<float>(a.d);
@@ -658,7 +686,7 @@ cudaError_t LaunchGatedT(const GatedArgs& a, cudaStream_t s) {
     l.mode = a.mode;
     l.eps = a.eps;
     l.inv_d = inv_d;
-    gated_norm_lean_kernel<OT, ZT, YT><<<a.rows / (kBlock / octs), kBlock, 0, s>>>(l);
+    LaunchKernel(gated_norm_lean_kernel<OT, ZT, YT>, a.rows / (kBlock / octs), kBlock, 0, s, l);
     return cudaGetLastError();
   }
   // One octet per thread on short rows: the layout of the lean kernel, so the two agree bit for bit.
@@ -666,21 +694,21 @@ cudaError_t LaunchGatedT(const GatedArgs& a, cudaStream_t s) {
   const unsigned grid = (a.rows + sh.rows_per_cta - 1) / sh.rows_per_cta;
   switch (sh.k) {
     case 1:
-      if (sh.full) gated_norm_kernel<OT, ZT, YT, 1, 1, true><<<grid, kBlock, 0, s>>>(a, sh.lg, inv_d);
-      else gated_norm_kernel<OT, ZT, YT, 1, 1, false><<<grid, kBlock, 0, s>>>(a, sh.lg, inv_d);
+      if (sh.full) LaunchKernel(gated_norm_kernel<OT, ZT, YT, 1, 1, true>, grid, kBlock, 0, s, a, sh.lg, inv_d);
+      else LaunchKernel(gated_norm_kernel<OT, ZT, YT, 1, 1, false>, grid, kBlock, 0, s, a, sh.lg, inv_d);
       break;
     case 2:
       if (sh.lg <= 5 && a.rows_per_group == 2) {  // short rows, two rows per thread group in flight
         const unsigned rpc2 = sh.rows_per_cta * 2;
         const unsigned grid2 = (a.rows + rpc2 - 1) / rpc2;
-        if (sh.full && a.rows % rpc2 == 0) gated_norm_kernel<OT, ZT, YT, 2, 2, true><<<grid2, kBlock, 0, s>>>(a, sh.lg, inv_d);
-        else gated_norm_kernel<OT, ZT, YT, 2, 2, false><<<grid2, kBlock, 0, s>>>(a, sh.lg, inv_d);
+        if (sh.full && a.rows % rpc2 == 0) LaunchKernel(gated_norm_kernel<OT, ZT, YT, 2, 2, true>, grid2, kBlock, 0, s, a, sh.lg, inv_d);
+        else LaunchKernel(gated_norm_kernel<OT, ZT, YT, 2, 2, false>, grid2, kBlock, 0, s, a, sh.lg, inv_d);
         break;
       }
-      if (sh.full) gated_norm_kernel<OT, ZT, YT, 2, 1, true><<<grid, kBlock, 0, s>>>(a, sh.lg, inv_d);
-      else gated_norm_kernel<OT, ZT, YT, 2, 1, false><<<grid, kBlock, 0, s>>>(a, sh.lg, inv_d);
+      if (sh.full) LaunchKernel(gated_norm_kernel<OT, ZT, YT, 2, 1, true>, grid, kBlock, 0, s, a, sh.lg, inv_d);
+      else LaunchKernel(gated_norm_kernel<OT, ZT, YT, 2, 1, false>, grid, kBlock, 0, s, a, sh.lg, inv_d);
       break;
-    case 4: gated_norm_kernel<OT, ZT, YT, 4, 1, false><<<grid, kBlock, 0, s>>>(a, sh.lg, inv_d); break;
+    case 4: LaunchKernel(gated_norm_kernel<OT, ZT, YT, 4, 1, false>, grid, kBlock, 0, s, a, sh.lg, inv_d); break;
     default: return cudaErrorInvalidValue;
   }
   return cudaGetLastError();

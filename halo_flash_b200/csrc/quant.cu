@@ -14,6 +14,7 @@ namespace {
 
 template <typename XT>
 __global__ void __launch_bounds__(kBlock) quantize_vec_kernel(const QuantArgs a) {
+  pdl_begin();
   const uint32_t opr = a.cols / 8;
   const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x;
   const uint32_t row = static_cast<uint32_t>(idx / opr), j = static_cast<uint32_t>(idx % opr);
@@ -70,6 +71,7 @@ __global__ void __launch_bounds__(kBlock) quantize_vec_kernel(const QuantArgs a)
 // One warp per 32-value block, one element per lane: any alignment.
 template <typename XT>
 __global__ void __launch_bounds__(kBlock) quantize_scalar_kernel(const QuantArgs a) {
+  pdl_begin();
   const uint32_t bpr = a.cols / 32;
   const uint32_t lane = threadIdx.x & 31u;
   const uint64_t nblk = static_cast<uint64_t>(a.rows) * bpr;
@@ -118,12 +120,12 @@ cudaError_t LaunchQuantT(const QuantArgs& a, cudaStream_t s) {
     const uint64_t octs = static_cast<uint64_t>(a.rows) * (a.cols / 8);
     const uint64_t grid = (octs + kBlock - 1) / kBlock;
     if (grid > 0x7FFFFFFFull) return cudaErrorInvalidValue;
-    quantize_vec_kernel<XT><<<static_cast<unsigned>(grid), kBlock, 0, s>>>(a);
+    LaunchKernel(quantize_vec_kernel<XT>, static_cast<unsigned>(grid), kBlock, 0, s, a);
   } else {
     const uint64_t nblk = static_cast<uint64_t>(a.rows) * (a.cols / 32);
     uint64_t grid = (nblk + kBlock / 32 - 1) / (kBlock / 32);
     if (grid > 148u * 32u) grid = 148u * 32u;
-    quantize_scalar_kernel<XT><<<static_cast<unsigned>(grid), kBlock, 0, s>>>(a);
+    LaunchKernel(quantize_scalar_kernel<XT>, static_cast<unsigned>(grid), kBlock, 0, s, a);
   }
   return cudaGetLastError();
 }

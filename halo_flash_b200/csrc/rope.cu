@@ -26,6 +26,7 @@ __device__ __forceinline__ uint32_t token_pos(const PosSpec& p, uint32_t t) {
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(kBlock) rope_kernel(const RopeArgs a, const __grid_constant__ InvFreq f,
                                                      const unsigned tpc) {
+  pdl_begin();
   extern __shared__ float2 cs[];  // [tpc][half]
   const uint32_t half = a.rot / 2;
   const uint32_t t0 = blockIdx.x * tpc;
@@ -273,6 +274,7 @@ __global__ void __launch_bounds__(kBlock, K * ROWS >= 8 ? 2 : 3) norm_rope_kerne
                                                              const unsigned lg, const uint32_t ctas1,
                                                              const float inv_d, const uint32_t magic1,
                                                              const uint32_t magic2) {
+  pdl_begin();
   extern __shared__ float rope_smem[];
   const unsigned slots = kBlock >> lg;
   const bool second = blockIdx.x >= ctas1;
@@ -304,6 +306,7 @@ struct RopeLeanArgs {  // scalar fields on purpose: indexing a parameter array b
 
 template <typename IT, typename OT, int K, bool ONEPLUS>
 __global__ void __launch_bounds__(kBlock) norm_rope_lean_kernel(const RopeLeanArgs a) {
+  pdl_begin();
   const bool sel = blockIdx.x >= a.ctas0;
   const uint32_t cta = blockIdx.x - (sel ? a.ctas0 : 0u);
   const unsigned lg = a.lg, g = 1u << lg;
@@ -361,6 +364,7 @@ __global__ void __launch_bounds__(kBlock) norm_rope_lean_kernel(const RopeLeanAr
 
 // One thread per (token, frequency): the rotation table of a step, shared by every layer.
 __global__ void __launch_bounds__(kBlock) rope_table_kernel(const RopeTableArgs a, const __grid_constant__ InvFreq f) {
+  pdl_begin();
   const uint32_t half = a.rot / 2;
   const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x;
   const uint32_t t = static_cast<uint32_t>(idx / half), i = static_cast<uint32_t>(idx % half);
@@ -376,6 +380,7 @@ __global__ void __launch_bounds__(kBlock) rope_table_kernel(const RopeTableArgs 
 
 template <typename T>
 __global__ void __launch_bounds__(kBlock) split_qgate_kernel(const SplitArgs a) {
+  pdl_begin();
   const size_t total = static_cast<size_t>(a.rows) * a.hd;
   const T* qg = static_cast<const T*>(a.qg);
   T* q = static_cast<T*>(a.q);
@@ -405,8 +410,8 @@ cudaError_t LaunchRopeT(const RopeArgs& a, const InvFreq& f, cudaStream_t s) {
   if (tpc > a.tokens) tpc = a.tokens;
   const unsigned grid = (a.tokens + tpc - 1) / tpc;
   const size_t smem = static_cast<size_t>(tpc) * half * sizeof(float2);
-  if (a.vec) rope_kernel<T, true><<<grid, kBlock, smem, s>>>(a, f, tpc);
-  else rope_kernel<T, false><<<grid, kBlock, smem, s>>>(a, f, tpc);
+  if (a.vec) LaunchKernel(rope_kernel<T, true>, grid, kBlock, smem, s, a, f, tpc);
+  else LaunchKernel(rope_kernel<T, false>, grid, kBlock, smem, s, a, f, tpc);
   return cudaGetLastError();
 }
 
@@ -450,22 +455,22 @@ cudaError_t LaunchNormRopeT(const NormRopeArgs& a, const InvFreq& f, cudaStream_
     l.d = a.d, l.rot = a.rot, l.lg = lg, l.eps = a.eps, l.inv_d = inv_d, l.table = a.table;
     const unsigned lgrid = l.ctas0 + static_cast<unsigned>(rows2 / rpc1);
     if (k == 2) {
-      if (a.one_plus) norm_rope_lean_kernel<IT, OT, 2, true><<<lgrid, kBlock, 0, s>>>(l);
-      else norm_rope_lean_kernel<IT, OT, 2, false><<<lgrid, kBlock, 0, s>>>(l);
+      if (a.one_plus) LaunchKernel(norm_rope_lean_kernel<IT, OT, 2, true>, lgrid, kBlock, 0, s, l);
+      else LaunchKernel(norm_rope_lean_kernel<IT, OT, 2, false>, lgrid, kBlock, 0, s, l);
     } else {
-      if (a.one_plus) norm_rope_lean_kernel<IT, OT, 1, true><<<lgrid, kBlock, 0, s>>>(l);
-      else norm_rope_lean_kernel<IT, OT, 1, false><<<lgrid, kBlock, 0, s>>>(l);
+      if (a.one_plus) LaunchKernel(norm_rope_lean_kernel<IT, OT, 1, true>, lgrid, kBlock, 0, s, l);
+      else LaunchKernel(norm_rope_lean_kernel<IT, OT, 1, false>, lgrid, kBlock, 0, s, l);
     }
     return cudaGetLastError();
   }
   if (a.table) {
-    if (k == 2 && rows_in_flight == 4) norm_rope_kernel<IT, OT, 2, 4, true><<<grid, kBlock, 0, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
-    else if (k == 2) norm_rope_kernel<IT, OT, 2, 2, true><<<grid, kBlock, 0, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
-    else norm_rope_kernel<IT, OT, 1, 2, true><<<grid, kBlock, 0, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
+    if (k == 2 && rows_in_flight == 4) LaunchKernel(norm_rope_kernel<IT, OT, 2, 4, true>, grid, kBlock, 0, s, a, f, lg, ctas1, inv_d, m1, m2);
+    else if (k == 2) LaunchKernel(norm_rope_kernel<IT, OT, 2, 2, true>, grid, kBlock, 0, s, a, f, lg, ctas1, inv_d, m1, m2);
+    else LaunchKernel(norm_rope_kernel<IT, OT, 1, 2, true>, grid, kBlock, 0, s, a, f, lg, ctas1, inv_d, m1, m2);
   } else {
-    if (k == 2 && rows_in_flight == 4) norm_rope_kernel<IT, OT, 2, 4, false><<<grid, kBlock, smem, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
-    else if (k == 2) norm_rope_kernel<IT, OT, 2, 2, false><<<grid, kBlock, smem, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
-    else norm_rope_kernel<IT, OT, 1, 2, false><<<grid, kBlock, smem, s>>>(a, f, lg, ctas1, inv_d, m1, m2);
+    if (k == 2 && rows_in_flight == 4) LaunchKernel(norm_rope_kernel<IT, OT, 2, 4, false>, grid, kBlock, smem, s, a, f, lg, ctas1, inv_d, m1, m2);
+    else if (k == 2) LaunchKernel(norm_rope_kernel<IT, OT, 2, 2, false>, grid, kBlock, smem, s, a, f, lg, ctas1, inv_d, m1, m2);
+    else LaunchKernel(norm_rope_kernel<IT, OT, 1, 2, false>, grid, kBlock, smem, s, a, f, lg, ctas1, inv_d, m1, m2);
   }
   return cudaGetLastError();
 }
@@ -501,7 +506,7 @@ cudaError_t LaunchRopeTable(const RopeTableArgs& a, const InvFreq& f, cudaStream
   if (n == 0) return cudaSuccess;
   const uint64_t grid = (n + kBlock - 1) / kBlock;
   if (grid > 0x7FFFFFFFull) return cudaErrorInvalidValue;
-  rope_table_kernel<<<static_cast<unsigned>(grid), kBlock, 0, s>>>(a, f);
+  LaunchKernel(rope_table_kernel, static_cast<unsigned>(grid), kBlock, 0, s, a, f);
   return cudaGetLastError();
 }
 
@@ -511,9 +516,9 @@ cudaError_t LaunchSplitQgate(const SplitArgs& a, cudaStream_t s) {
   size_t grid = (total + kBlock - 1) / kBlock;
   if (grid > 148u * 16u) grid = 148u * 16u;
   switch (a.dtype) {
-    case kF32: split_qgate_kernel<float><<<static_cast<unsigned>(grid), kBlock, 0, s>>>(a); break;
-    case kF16: split_qgate_kernel<f16><<<static_cast<unsigned>(grid), kBlock, 0, s>>>(a); break;
-    case kBF16: split_qgate_kernel<bf16><<<static_cast<unsigned>(grid), kBlock, 0, s>>>(a); break;
+    case kF32: LaunchKernel(split_qgate_kernel<float>, static_cast<unsigned>(grid), kBlock, 0, s, a); break;
+    case kF16: LaunchKernel(split_qgate_kernel<f16>, static_cast<unsigned>(grid), kBlock, 0, s, a); break;
+    case kBF16: LaunchKernel(split_qgate_kernel<bf16>, static_cast<unsigned>(grid), kBlock, 0, s, a); break;
     default: return cudaErrorInvalidValue;
   }
   return cudaGetLastError();

@@ -314,7 +314,9 @@ const char* halo_b200_kernel_name(size_t index);
  * "norm_short_rows_k1" (1 = rows of <= 256 elements use one 8-element chunk per thread; 0 = built-in choice),
  * "norm_force_general" (1 = the row norms always run their general kernel, never the lean one),
  * "gated_rows_per_group" (1 or 2 rows in flight per thread group of the gated norm on short rows; 0 = built-in),
- * "rope_rows_per_group" (2 or 4 rows in flight per thread group of the fused norm + RoPE kernel; 0 = built-in).
+ * "rope_rows_per_group" (2 or 4 rows in flight per thread group of the fused norm + RoPE kernel; 0 = built-in),
+ * "pdl" (1, the default = kernels are launched with programmatic stream serialization, so a kernel is scheduled
+ * while its predecessor in the stream drains and waits on the device for it to complete; 0 = plain launches).
  * Returns 0, or -1 for an unknown key or value. */
 int halo_b200_tune(const char* key, int value);
 
