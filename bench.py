@@ -215,6 +215,7 @@ def op_specs(torch, shapes, T: int):
     w_h = torch.randn(s.hidden, device=dev) * 0.1
     w_hd = torch.randn(s.head_dim, device=dev) * 0.1
     w_g = 1 + torch.randn(s.lin_dim, device=dev) * 0.1
+    w_hc = 1 + torch.randn(4, s.hidden, device=dev) * 0.1
     table = torch.randint(0, 255, (8192, s.q8_row_bytes), device=dev, dtype=torch.uint8)
     table.view(8192, -1, 34)[:, :, 1] = 0x3C  # finite fp16 scales
     rope_tab = ops.rope_table(torch.empty(T, 2, s.rot // 2, device=dev), s.rot, s.theta)
@@ -237,10 +238,15 @@ def op_specs(torch, shapes, T: int):
         "add_rmsnorm_q8": (lambda: (r(T, s.hidden), r(T, s.hidden),
                                     torch.empty(T, s.q8_row_bytes, device=dev, dtype=torch.uint8)),
                            lambda b: ops.add_rmsnorm(b[0], b[1], w_h, s.eps, q8_0=b[2])),
+        # not in the chain: Flash-Next's form of the residual op, 4 residual streams per token
+        "hc_combine_norm": (lambda: (r(T, 4, s.hidden), r(T, s.hidden), torch.randn(T, 4, device=dev),
+                                     torch.empty(T, 4, s.hidden, device=dev, dtype=bf)),
+                            lambda b: ops.hc_combine_norm(b[0], b[1], b[2], w_hc, s.eps, y=b[3])),
     }
     nbytes = {"add_rmsnorm": bpt["add_rmsnorm"], "l2norm": bpt["l2norm"], "gated_norm": bpt["gated_norm"],
               "norm_rope_qk": bpt["norm_rope"], "swiglu_moe": bpt["swiglu_shared"] + bpt["swiglu_routed"],
-              "embed": bpt["embed"], "add_rmsnorm_q8": 3 * 2 * s.hidden + s.q8_row_bytes}
+              "embed": bpt["embed"], "add_rmsnorm_q8": 3 * 2 * s.hidden + s.q8_row_bytes,
+              "hc_combine_norm": (3 * 4 + 1) * 2 * s.hidden + 16}  # read + write res, write y (4 streams), read out, logits
     return specs, {k_: v * T for k_, v in nbytes.items()}
 
 
@@ -463,7 +469,7 @@ def main() -> None:
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
     ap.add_argument("--no-kernel-table", action="store_true", help="skip the per-kernel timing leg (profiler captures)")
     ap.add_argument("--profile-op", default=None, help="run 6 eager launches of one op and exit (profiler captures): "
-                    "add_rmsnorm, add_rmsnorm_q8, l2norm, gated_norm, norm_rope_qk, swiglu_moe, embed")
+                    "add_rmsnorm, add_rmsnorm_q8, l2norm, gated_norm, norm_rope_qk, swiglu_moe, embed, hc_combine_norm")
     args = ap.parse_args()
     if args.profile_op:
         profile_op(args)

@@ -66,6 +66,25 @@ SIGNATURES: dict[str, list] = {
     "halo_b200_matvec_q8_0_embed": [_p, _p, _u32, _u32, _u64],
     "halo_b200_matvec_q8_0_embed_p": [_p, _p, _p, _u32, _u64],
     "halo_b200_matvec_q8_0_embed_rows": [_p, _p, _p, _u32, _u64, _u32],
+    "halo_b200_hc_combine_norm_rows": [_p, _i, _p, _p, _p, _p, _p, _u32, _u32, _f, _p, _p, _u32, _p, _u32, _u32],
+    "halo_b200_hc_combine_norm_rows_q8": [_p, _p, _p, _p, _p, _p, _u32, _u32, _f, _p, _p, _u32, _p, _u32, _p, _p, _u32],
+    "halo_b200_hc_combine_norm_tok": [_p, _i, _p, _p, _p, _p, _u32, _f, _p, _p, _u32, _p, _u32, _u32],
+    "halo_b200_hc_combine_norm_tok_moe": [_p, _i, _p, _p, _p, _p, _p, _u32, _p, _p, _p, _u32, _f, _p, _p, _u32, _p, _u32,
+                                          _u32],
+    "halo_b200_hc_combine_norm_ex": [_p, _i, _p, _i, _p, _p, _i, _p, _i, _p, _u32, _p, _p, _p, _u32, _p, _p, _u32, _u32, _f,
+                                     _u32],
+    "halo_b200_hc_combine_norm_moe_ex": [_p, _i, _p, _i, _p, _p, _p, _i, _p, _u32, _p, _p, _i, _p, _i, _p, _u32, _p, _p, _p,
+                                         _u32, _u32, _u32, _f, _u32],
+    "halo_b200_hc_combine_rows": [_p, _i, _p, _p, _u32, _u32, _u32],
+    "halo_b200_hc_combine_rows_ex": [_p, _i, _p, _i, _p, _u32, _u32, _u32],
+    "halo_b200_broadcast_rows": [_p, _i, _p, _u32, _u32, _u32],
+    "halo_b200_broadcast_rows_ex": [_p, _i, _p, _i, _u32, _u32, _u32],
+    "halo_b200_hc_mix_rows": [_p, _p, _p, _u32, _u32, _u32],
+    "halo_b200_hc_mix_rows_ex": [_p, _p, _p, _i, _u32, _u32, _u32],
+    "halo_b200_axpy_sigmoid_rows": [_p, _p, _p, _u32, _u32],
+    "halo_b200_inject_reduce": [_p, _p, _u32, _u32, _u32],
+    "halo_b200_res_to_f32": [_p, _p, _i, _u32],
+    "halo_b200_hc_norm_scales": [_p, _p, _u32, _f, _u32],
     "halo_b200_embed_q8_0_ex": [_p, _u64, _u32, _p, _u32, _u32, _u32, _p, _i, _u32],
 }
 

@@ -263,6 +263,61 @@ int RunNormRope(NormRopeArgs a, float theta, const char* what, halo_b200_stream 
   return Done(LaunchRope(r, f, S(stream)), what, err, errlen);
 }
 
+
+std::atomic<int> g_hc_row_level{0};
+std::atomic<int> g_hc_token_k{0};
+
+int RunHc(HcArgs a, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+  if (a.tokens == 0) return Done(cudaSuccess, what, err, errlen);  // an empty chunk is a no-op
+  REQUIRE(a.res != nullptr && a.w != nullptr, "%s: null pointer", what);
+  REQUIRE(a.hc >= 1 && a.h > 0, "%s: hc and h must be positive", what);
+  REQUIRE(!(a.out && a.yp), "%s: a stored block output and an expert sum exclude each other", what);
+  const bool combine = a.out || a.yp;
+  REQUIRE(combine == (a.inject != nullptr), "%s: inject goes with a block output", what);
+  if (a.yp) REQUIRE(a.pos && a.mw && a.sx && a.sg && a.k >= 1, "%s: expert sum needs pos, mw, sx, sg and k >= 1", what);
+  REQUIRE(ValidDType(a.res_dtype) && ValidDType(a.out_dtype) && ValidDType(a.y_dtype), "%s: unknown dtype", what);
+  REQUIRE(a.y || a.y16 || a.rscale || a.yq || a.iw || combine, "%s: no output", what);
+  REQUIRE(a.irows <= 8, "%s: at most 8 inject rows (irows = %u)", what, a.irows);
+  if (a.iw) REQUIRE(a.ipart != nullptr && a.irows >= 1, "%s: iw needs ipart and irows >= 1", what);
+  else a.irows = 0;
+  REQUIRE((a.yq == nullptr) == (a.yd == nullptr), "%s: yq and yd go together", what);
+  if (a.yq) REQUIRE(a.h % 32 == 0 && a.y16_tokens >= a.tokens, "%s: the int8 copy needs h %% 32 == 0 and y16_tokens >= tokens", what);
+  if (a.y16_tokens) REQUIRE((static_cast<uint64_t>(a.hc) * a.h) % 64 == 0 && a.y16_tokens >= a.tokens,
+                            "%s: K-blocked layouts need hc * h %% 64 == 0 and y16_tokens >= tokens", what);
+  const size_t rs = DTypeSize(a.res_dtype), os = DTypeSize(a.out_dtype), ys = DTypeSize(a.y_dtype);
+  REQUIRE(Aligned(a.res, rs) && Aligned(a.out, os) && Aligned(a.yp, os) && Aligned(a.y, ys) && Aligned(a.y16, 2) &&
+              Aligned(a.w, 4) && Aligned(a.inject, 4) && Aligned(a.iw, 4) && Aligned(a.ipart, 4) &&
+              Aligned(a.rscale, 4) && Aligned(a.yd, 4) && Aligned(a.sx, a.sx_is_f32 ? 4 : os),
+          "%s: pointer not aligned to its element type", what);
+  a.vec = a.h % 8 == 0 && a.h >= 32 && a.h <= 256u * 8u * 8u && Aligned(a.res, 16) && Aligned(a.out, 16) &&
+          Aligned(a.yp, 16) && Aligned(a.sx, 16) && Aligned(a.y, 16) && Aligned(a.y16, 16) && Aligned(a.w, 16) &&
+          Aligned(a.iw, 16) && Aligned(a.yq, 8);
+  if (!a.vec) REQUIRE(!a.yp && !a.yq && (a.out || !combine),
+                      "%s: the expert sum and the int8 copy need h %% 8 == 0, 32 <= h <= 16384 and 16-byte aligned buffers", what);
+  if (!a.vec && !combine) return Fail(err, errlen, "%s: the norm-only form needs h %% 8 == 0 and 16-byte aligned buffers", what);
+  if (!a.y)  // no y: any y type of a supported (res, out, y) triple will do
+    a.y_dtype = (a.out_dtype == a.res_dtype && a.res_dtype != kF32) ? a.res_dtype : kF32;
+  a.row_level = g_hc_row_level.load(std::memory_order_relaxed);
+  a.token_k = g_hc_token_k.load(std::memory_order_relaxed);
+  const cudaError_t e = LaunchHcCombineNorm(a, S(stream));
+  if (e == cudaErrorInvalidValue) return Fail(err, errlen, "%s: unsupported (res, out, y) dtype combination or shape", what);
+  return Done(e, what, err, errlen);
+}
+
+int RunHcElt(HcEltArgs a, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+  if (a.tokens == 0 || a.h == 0) return Done(cudaSuccess, what, err, errlen);
+  REQUIRE(a.a != nullptr && a.b != nullptr, "%s: null pointer", what);
+  REQUIRE(a.op == kHcBroadcast || a.op == kInjectReduce || a.c != nullptr, "%s: null pointer", what);
+  REQUIRE(a.hc >= 1, "%s: hc is 0", what);
+  REQUIRE(ValidDType(a.a_dtype) && ValidDType(a.b_dtype), "%s: unknown dtype", what);
+  REQUIRE(Aligned(a.a, DTypeSize(a.a_dtype)) && Aligned(a.b, DTypeSize(a.b_dtype)) && Aligned(a.c, a.op == kHcMix ? DTypeSize(a.b_dtype) : 4),
+          "%s: pointer not aligned to its element type", what);
+  a.vec = a.h % 8 == 0 && Aligned(a.a, 16) && Aligned(a.b, 16) && (a.op != kHcMix || Aligned(a.c, 16));
+  const cudaError_t e = LaunchHcElt(a, S(stream));
+  if (e == cudaErrorInvalidValue) return Fail(err, errlen, "%s: unsupported dtype combination", what);
+  return Done(e, what, err, errlen);
+}
+
 }  // namespace
 
 namespace halo_b200 {
@@ -293,6 +348,16 @@ int halo_b200_tune(const char* key, int value) {
   if (std::strcmp(key, "norm_force_general") == 0) {
     if (value != 0 && value != 1) return -1;
     g_norm_force_general.store(value, std::memory_order_relaxed);
+    return 0;
+  }
+  if (std::strcmp(key, "hc_token_k") == 0) {
+    if (value != 0 && value != 1 && value != 2) return -1;
+    g_hc_token_k.store(value, std::memory_order_relaxed);
+    return 0;
+  }
+  if (std::strcmp(key, "hc_row_level") == 0) {
+    if (value != 0 && value != 1) return -1;
+    g_hc_row_level.store(value, std::memory_order_relaxed);
     return 0;
   }
   if (std::strcmp(key, "pdl") == 0) {
@@ -387,11 +452,30 @@ int halo_b200_rmsnorm_rows_h(halo_b200_stream stream, const void* x, int x_dtype
                              uint16_t* y16, uint32_t d, float eps, uint32_t w_stride, uint32_t w_period,
                              const float* iw, float* ipart, uint32_t irows, uint32_t y16_tokens, uint32_t rows,
                              char* err, size_t errlen) {
-  (void)ipart;
-  (void)irows;
-  REQUIRE(iw == nullptr, "halo_rmsnorm_rows_h: inject partial products (iw) are not implemented");
   REQUIRE(rows == 0 || (w_all && y && y16), "halo_rmsnorm_rows_h: null pointer");
   REQUIRE(w_period > 0, "halo_rmsnorm_rows_h: w_period is 0");
+  if (iw) {
+    // with the next projection's partial products: the grouped-norm kernel without a combine
+    REQUIRE(w_period == 1 || w_stride == d, "halo_rmsnorm_rows_h: iw needs gamma rows d apart (w_stride == d)");
+    REQUIRE(rows % w_period == 0, "halo_rmsnorm_rows_h: rows must be a multiple of w_period");
+    HcArgs h{};
+    h.res = const_cast<void*>(x);
+    h.res_dtype = x_dtype;
+    h.out_dtype = kF32;
+    h.w = w_all;
+    h.y = y;
+    h.y_dtype = kF32;
+    h.y16 = y16;
+    h.y16_tokens = y16_tokens;
+    h.iw = iw;
+    h.ipart = ipart;
+    h.irows = irows;
+    h.hc = w_period;
+    h.h = d;
+    h.tokens = rows / w_period;
+    h.eps = eps;
+    return RunHc(h, "halo_rmsnorm_rows_h", stream, err, errlen);
+  }
   NormArgs a;
   a.x = x;
   a.x_dtype = x_dtype;
@@ -900,5 +984,224 @@ int halo_b200_matvec_q8_0_embed_rows(halo_b200_stream stream, const uint8_t* w, 
   a.out = out;
   return RunEmbed(a, "halo_matvec_q8_0_embed_rows", stream, err, errlen);
 }
+
+// ---- hyper-connection residual ---------------------------------------------------------------
+int halo_b200_hc_combine_norm_ex(halo_b200_stream stream, void* res, int res_dtype, const void* out, int out_dtype,
+                                 const float* inject, const float* w_all, int one_plus, void* y, int y_dtype,
+                                 uint16_t* y16, uint32_t y16_tokens, float* rscale, const float* iw, float* ipart,
+                                 uint32_t irows, int8_t* yq, float* yd, uint32_t hc, uint32_t h, float eps,
+                                 uint32_t tokens, char* err, size_t errlen) {
+  HcArgs a{};
+  a.res = res;
+  a.res_dtype = res_dtype;
+  a.out = out;
+  a.out_dtype = out_dtype;
+  a.inject = inject;
+  a.w = w_all;
+  a.one_plus = one_plus;
+  a.y = y;
+  a.y_dtype = y_dtype;
+  a.y16 = y16;
+  a.y16_tokens = y16_tokens;
+  a.rscale = rscale;
+  a.iw = iw;
+  a.ipart = ipart;
+  a.irows = irows;
+  a.yq = yq;
+  a.yd = yd;
+  a.hc = hc;
+  a.h = h;
+  a.eps = eps;
+  a.tokens = tokens;
+  return RunHc(a, "halo_b200_hc_combine_norm_ex", stream, err, errlen);
+}
+
+int halo_b200_hc_combine_norm_moe_ex(halo_b200_stream stream, void* res, int res_dtype, const void* yp, int yp_dtype,
+                                     const uint32_t* pos, const float* mw, const void* sx, int sx_dtype,
+                                     const float* sg, uint32_t k, const float* inject, const float* w_all,
+                                     int one_plus, void* y, int y_dtype, uint16_t* y16, uint32_t y16_tokens,
+                                     float* rscale, const float* iw, float* ipart, uint32_t irows, uint32_t hc,
+                                     uint32_t h, float eps, uint32_t tokens, char* err, size_t errlen) {
+  REQUIRE(sx_dtype == kF32 || sx_dtype == yp_dtype, "halo_b200_hc_combine_norm_moe_ex: sx must be fp32 or of yp's type");
+  HcArgs a{};
+  a.res = res;
+  a.res_dtype = res_dtype;
+  a.yp = yp;
+  a.out_dtype = yp_dtype;
+  a.pos = pos;
+  a.mw = mw;
+  a.sx = sx;
+  a.sx_is_f32 = sx_dtype == kF32;
+  a.sg = sg;
+  a.k = k;
+  a.inject = inject;
+  a.w = w_all;
+  a.one_plus = one_plus;
+  a.y = y;
+  a.y_dtype = y_dtype;
+  a.y16 = y16;
+  a.y16_tokens = y16_tokens;
+  a.rscale = rscale;
+  a.iw = iw;
+  a.ipart = ipart;
+  a.irows = irows;
+  a.hc = hc;
+  a.h = h;
+  a.eps = eps;
+  a.tokens = tokens;
+  return RunHc(a, "halo_b200_hc_combine_norm_moe_ex", stream, err, errlen);
+}
+
+int halo_b200_hc_combine_norm_rows(halo_b200_stream stream, void* res, int res_dtype, const float* out,
+                                   const float* inject, const float* w_all, float* y, uint16_t* y16, uint32_t hc,
+                                   uint32_t h, float eps, const float* iw, float* ipart, uint32_t irows,
+                                   float* rscale, uint32_t y16_tokens, uint32_t rows, char* err, size_t errlen) {
+  REQUIRE(hc > 0 && rows % hc == 0, "halo_hc_combine_norm_rows: the grid must hold hc rows per token");
+  REQUIRE(rows == 0 || (out && inject), "halo_hc_combine_norm_rows: null pointer");
+  return halo_b200_hc_combine_norm_ex(stream, res, res_dtype, out, kF32, inject, w_all, 0, y, kF32, y16, y16_tokens,
+                                      rscale, iw, ipart, irows, nullptr, nullptr, hc, h, eps, rows / hc, err, errlen);
+}
+
+int halo_b200_hc_combine_norm_rows_q8(halo_b200_stream stream, float* res, const float* out, const float* inject,
+                                      const float* w_all, float* y, uint16_t* y16, uint32_t hc, uint32_t h, float eps,
+                                      const float* iw, float* ipart, uint32_t irows, float* rscale,
+                                      uint32_t y16_tokens, int8_t* yq, float* yd, uint32_t rows, char* err,
+                                      size_t errlen) {
+  REQUIRE(hc > 0 && rows % hc == 0, "halo_hc_combine_norm_rows_q8: the grid must hold hc rows per token");
+  REQUIRE(rows == 0 || (out && inject && yq && yd), "halo_hc_combine_norm_rows_q8: null pointer");
+  return halo_b200_hc_combine_norm_ex(stream, res, kF32, out, kF32, inject, w_all, 0, y, kF32, y16, y16_tokens, rscale,
+                                      iw, ipart, irows, yq, yd, hc, h, eps, rows / hc, err, errlen);
+}
+
+int halo_b200_hc_combine_norm_tok(halo_b200_stream stream, void* res, int res_dtype, const float* out,
+                                  const float* inject, const float* w_all, uint16_t* y16, uint32_t h, float eps,
+                                  const float* iw, float* ipart, uint32_t irows, float* rscale, uint32_t y16_tokens,
+                                  uint32_t tokens, char* err, size_t errlen) {
+  REQUIRE(tokens == 0 || (out && inject), "halo_hc_combine_norm_tok: null pointer");
+  return halo_b200_hc_combine_norm_ex(stream, res, res_dtype, out, kF32, inject, w_all, 0, nullptr, kF32, y16,
+                                      y16_tokens, rscale, iw, ipart, irows, nullptr, nullptr, 4, h, eps, tokens, err,
+                                      errlen);
+}
+
+int halo_b200_hc_combine_norm_tok_moe(halo_b200_stream stream, void* res, int res_dtype, const uint16_t* yp,
+                                      const uint32_t* pos, const float* mw, const float* sx, const float* sg,
+                                      uint32_t k, const float* inject, const float* w_all, uint16_t* y16, uint32_t h,
+                                      float eps, const float* iw, float* ipart, uint32_t irows, float* rscale,
+                                      uint32_t y16_tokens, uint32_t tokens, char* err, size_t errlen) {
+  REQUIRE(tokens == 0 || (yp && inject), "halo_hc_combine_norm_tok_moe: null pointer");
+  return halo_b200_hc_combine_norm_moe_ex(stream, res, res_dtype, yp, kF16, pos, mw, sx, kF32, sg, k, inject, w_all, 0,
+                                          nullptr, kF32, y16, y16_tokens, rscale, iw, ipart, irows, 4, h, eps, tokens,
+                                          err, errlen);
+}
+
+int halo_b200_hc_combine_rows_ex(halo_b200_stream stream, void* res, int res_dtype, const void* out, int out_dtype,
+                                 const float* inject, uint32_t hc, uint32_t h, uint32_t tokens, char* err,
+                                 size_t errlen) {
+  HcEltArgs a{};
+  a.op = kHcCombine;
+  a.a = res;
+  a.a_dtype = res_dtype;
+  a.b = out;
+  a.b_dtype = out_dtype;
+  a.c = inject;
+  a.hc = hc;
+  a.h = h;
+  a.tokens = tokens;
+  return RunHcElt(a, "halo_hc_combine_rows", stream, err, errlen);
+}
+
+int halo_b200_hc_combine_rows(halo_b200_stream stream, void* res, int res_dtype, const float* out, const float* inject,
+                              uint32_t hc, uint32_t h, uint32_t tokens, char* err, size_t errlen) {
+  return halo_b200_hc_combine_rows_ex(stream, res, res_dtype, out, kF32, inject, hc, h, tokens, err, errlen);
+}
+
+int halo_b200_broadcast_rows_ex(halo_b200_stream stream, void* res, int res_dtype, const void* x, int x_dtype,
+                                uint32_t hc, uint32_t h, uint32_t tokens, char* err, size_t errlen) {
+  HcEltArgs a{};
+  a.op = kHcBroadcast;
+  a.a = res;
+  a.a_dtype = res_dtype;
+  a.b = x;
+  a.b_dtype = x_dtype;
+  a.hc = hc;
+  a.h = h;
+  a.tokens = tokens;
+  return RunHcElt(a, "halo_broadcast_rows", stream, err, errlen);
+}
+
+int halo_b200_broadcast_rows(halo_b200_stream stream, void* res, int res_dtype, const float* x, uint32_t hc,
+                             uint32_t h, uint32_t tokens, char* err, size_t errlen) {
+  return halo_b200_broadcast_rows_ex(stream, res, res_dtype, x, kF32, hc, h, tokens, err, errlen);
+}
+
+int halo_b200_hc_mix_rows_ex(halo_b200_stream stream, const void* xn, const void* gate, void* mixed, int dtype,
+                             uint32_t hc, uint32_t h, uint32_t tokens, char* err, size_t errlen) {
+  HcEltArgs a{};
+  a.op = kHcMix;
+  a.a = mixed;
+  a.a_dtype = dtype;
+  a.b = xn;
+  a.b_dtype = dtype;
+  a.c = gate;
+  a.hc = hc;
+  a.h = h;
+  a.tokens = tokens;
+  return RunHcElt(a, "halo_hc_mix_rows", stream, err, errlen);
+}
+
+int halo_b200_hc_mix_rows(halo_b200_stream stream, const float* xn, const float* gate, float* mixed, uint32_t hc,
+                          uint32_t h, uint32_t tokens, char* err, size_t errlen) {
+  return halo_b200_hc_mix_rows_ex(stream, xn, gate, mixed, kF32, hc, h, tokens, err, errlen);
+}
+
+int halo_b200_axpy_sigmoid_rows(halo_b200_stream stream, float* y, const float* x, const float* g, uint32_t n,
+                                uint32_t tokens, char* err, size_t errlen) {
+  HcEltArgs a{};
+  a.op = kAxpySigmoidRows;
+  a.a = y;
+  a.a_dtype = kF32;
+  a.b = x;
+  a.b_dtype = kF32;
+  a.c = g;
+  a.hc = 1;
+  a.h = n;
+  a.tokens = tokens;
+  return RunHcElt(a, "halo_axpy_sigmoid_rows", stream, err, errlen);
+}
+
+int halo_b200_inject_reduce(halo_b200_stream stream, const float* ipart, float* inject, uint32_t hc, uint32_t irows,
+                            uint32_t tokens, char* err, size_t errlen) {
+  if (tokens == 0 || irows == 0) return Done(cudaSuccess, "halo_inject_reduce", err, errlen);
+  HcEltArgs a{};
+  a.op = kInjectReduce;
+  a.a = inject;
+  a.a_dtype = kF32;
+  a.b = ipart;
+  a.b_dtype = kF32;
+  a.hc = hc;
+  a.h = 1;
+  a.irows = irows;
+  a.tokens = tokens;
+  return RunHcElt(a, "halo_inject_reduce", stream, err, errlen);
+}
+
+int halo_b200_res_to_f32(halo_b200_stream stream, float* y, const void* x, int x_dtype, uint32_t n, char* err,
+                         size_t errlen) {
+  REQUIRE(x_dtype == kF16 || x_dtype == kBF16, "halo_res_to_f32: x must be fp16 or bf16");
+  return halo_b200_broadcast_rows_ex(stream, y, kF32, x, x_dtype, 1, n, 1, err, errlen);
+}
+
+int halo_b200_hc_norm_scales(halo_b200_stream stream, const float* res, float* scale, uint32_t h, float eps,
+                             uint32_t rows, char* err, size_t errlen) {
+  REQUIRE(rows == 0 || scale != nullptr, "halo_hc_norm_scales: scale is null");
+  NormArgs a;
+  a.x = res;
+  a.rscale = scale;
+  a.d = h;
+  a.eps = eps;
+  a.rows = rows;
+  return RunNorm(a, "halo_hc_norm_scales", stream, err, errlen);
+}
+
 
 }  // extern "C"

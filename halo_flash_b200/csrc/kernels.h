@@ -231,6 +231,59 @@ struct QuantArgs {
 };
 cudaError_t LaunchQuantize(const QuantArgs& a, cudaStream_t s);
 
+
+// Hyper-connection residual (hc streams of h per token): combine + grouped RMSNorm and the
+// elementwise stream ops around it (src/kernels/core.hip:601-625, 4105-4496, 4634-4714).
+struct HcArgs {
+  void* res;            // [tokens][hc][h], res_dtype; updated in place
+  const void* out;      // [tokens][h], out_dtype (null when the block output is built from the experts)
+  const float* inject;  // [tokens][hc] scatter logits
+  const float* w;       // [hc][h] gammas
+  void* y;              // [tokens][hc][h], y_dtype; may be null
+  void* y16;            // fp16 copy; row-major, or K-blocked [hc h / 64][y16_tokens][64]; may be null
+  float* rscale;        // [tokens][hc] row scales; may be null
+  const float* iw;      // [irows][hc h] fp32 rows whose partial products with y go to ipart; may be null
+  float* ipart;         // [tokens][hc][irows]
+  int8_t* yq;           // K-blocked int8 copy [hc h / 64][y16_tokens][64]; may be null
+  float* yd;            // its scales [hc h / 32][y16_tokens]
+  // block output built in the kernel: sum over k slots of mw * yp[pos] + sigmoid(sg) * sx
+  const void* yp;       // expert output rows [pairs][h], out_dtype (fp16 in the reference)
+  const uint32_t* pos;  // [tokens][k] row of yp holding (token, slot)
+  const float* mw;      // [tokens][k] routing weights
+  const void* sx;       // [tokens][h] shared-expert output, fp32 or out_dtype
+  const float* sg;      // [tokens] shared-expert gate logit
+  uint32_t k;
+  int sx_is_f32;
+  uint32_t hc, h, tokens, irows, y16_tokens;
+  float eps;
+  int one_plus;
+  int res_dtype, out_dtype, y_dtype;
+  int vec;
+  int token_k;    // tuning: 2 = token-level shapes take two octets per stream per thread where they fit
+  int row_level;  // tuning: 1 = one thread group per (token, stream) row even where a token-level shape exists
+};
+cudaError_t LaunchHcCombineNorm(const HcArgs& a, cudaStream_t s);
+
+enum HcEltOp : int {
+  kHcCombine = 0,     // res[t][s][i] += out[t][i] * 2 sigmoid(inject[t][s] / hc)
+  kHcBroadcast = 1,   // res[t][s][i] = x[t][i]
+  kHcMix = 2,         // mixed[t][i] = (sum_s xn[t][s][i] * sigmoid(gate[t][s][i])) / hc
+  kAxpySigmoidRows = 3,  // y[t][i] += sigmoid(g[t]) * x[t][i]
+  kInjectReduce = 4,  // inject[t][r] = sum_s ipart[(t hc + s) irows + r]
+  kHcNormScales = 5,  // scale[row] = 1 / sqrt(mean(res_row^2) + eps)
+};
+struct HcEltArgs {
+  int op;
+  void* a;        // res / mixed / y / inject / scale (written)
+  const void* b;  // out / x / xn / ipart / res
+  const void* c;  // inject / gate / g
+  int a_dtype, b_dtype;
+  uint32_t hc, h, tokens, irows;
+  float eps;
+  int vec;
+};
+cudaError_t LaunchHcElt(const HcEltArgs& a, cudaStream_t s);
+
 }  // namespace halo_b200
 
 #endif  // HALO_B200_KERNELS_H_

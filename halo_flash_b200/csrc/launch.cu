@@ -260,6 +260,98 @@ HANDLER(H_embed_rows) {
   return halo_b200_matvec_q8_0_embed_rows(c.s, w, out, params, cols, rb, c.grid[1], c.err, c.errlen);
 }
 
+template <int DT>
+HANDLER(H_hc_combine_norm_rows) {
+  auto* res = r.ptr<void>(); auto* out = r.ptr<const float>(); auto* inject = r.ptr<const float>();
+  auto* w = r.ptr<const float>(); auto* y = r.ptr<float>(); auto* y16 = r.ptr<uint16_t>();
+  const uint32_t hc = r.u32(), h = r.u32(); const float eps = r.f32();
+  auto* iw = r.ptr<const float>(); auto* ipart = r.ptr<float>(); const uint32_t irows = r.u32();
+  auto* rscale = r.ptr<float>(); const uint32_t y16_tokens = r.u32();
+  CHECK_ARGS("halo_hc_combine_norm_rows");
+  return halo_b200_hc_combine_norm_rows(c.s, res, DT, out, inject, w, y, y16, hc, h, eps, iw, ipart, irows, rscale,
+                                        y16_tokens, c.grid[0], c.err, c.errlen);
+}
+HANDLER(H_hc_combine_norm_rows_q8) {
+  auto* res = r.ptr<float>(); auto* out = r.ptr<const float>(); auto* inject = r.ptr<const float>();
+  auto* w = r.ptr<const float>(); auto* y = r.ptr<float>(); auto* y16 = r.ptr<uint16_t>();
+  const uint32_t hc = r.u32(), h = r.u32(); const float eps = r.f32();
+  auto* iw = r.ptr<const float>(); auto* ipart = r.ptr<float>(); const uint32_t irows = r.u32();
+  auto* rscale = r.ptr<float>(); const uint32_t y16_tokens = r.u32();
+  auto* yq = r.ptr<int8_t>(); auto* yd = r.ptr<float>();
+  CHECK_ARGS("halo_hc_combine_norm_rows_q8");
+  return halo_b200_hc_combine_norm_rows_q8(c.s, res, out, inject, w, y, y16, hc, h, eps, iw, ipart, irows, rscale,
+                                           y16_tokens, yq, yd, c.grid[0], c.err, c.errlen);
+}
+template <int DT>
+HANDLER(H_hc_combine_norm_tok) {
+  auto* res = r.ptr<void>(); auto* out = r.ptr<const float>(); auto* inject = r.ptr<const float>();
+  auto* w = r.ptr<const float>(); auto* y16 = r.ptr<uint16_t>();
+  const uint32_t h = r.u32(); const float eps = r.f32();
+  auto* iw = r.ptr<const float>(); auto* ipart = r.ptr<float>(); const uint32_t irows = r.u32();
+  auto* rscale = r.ptr<float>(); const uint32_t y16_tokens = r.u32();
+  CHECK_ARGS("halo_hc_combine_norm_tok");
+  return halo_b200_hc_combine_norm_tok(c.s, res, DT, out, inject, w, y16, h, eps, iw, ipart, irows, rscale, y16_tokens,
+                                       c.grid[0], c.err, c.errlen);
+}
+template <int DT>
+HANDLER(H_hc_combine_norm_tok_moe) {
+  auto* res = r.ptr<void>(); auto* yp = r.ptr<const uint16_t>(); auto* pos = r.ptr<const uint32_t>();
+  auto* mw = r.ptr<const float>(); auto* sx = r.ptr<const float>(); auto* sg = r.ptr<const float>();
+  const uint32_t k = r.u32();
+  auto* inject = r.ptr<const float>(); auto* w = r.ptr<const float>(); auto* y16 = r.ptr<uint16_t>();
+  const uint32_t h = r.u32(); const float eps = r.f32();
+  auto* iw = r.ptr<const float>(); auto* ipart = r.ptr<float>(); const uint32_t irows = r.u32();
+  auto* rscale = r.ptr<float>(); const uint32_t y16_tokens = r.u32();
+  CHECK_ARGS("halo_hc_combine_norm_tok_moe");
+  return halo_b200_hc_combine_norm_tok_moe(c.s, res, DT, yp, pos, mw, sx, sg, k, inject, w, y16, h, eps, iw, ipart,
+                                           irows, rscale, y16_tokens, c.grid[0], c.err, c.errlen);
+}
+template <int DT, bool ROWS>
+HANDLER(H_hc_combine) {
+  auto* res = r.ptr<void>(); auto* out = r.ptr<const float>(); auto* inject = r.ptr<const float>();
+  const uint32_t hc = r.u32(), h = r.u32(); const uint32_t tokens = ROWS ? r.u32() : 1u;
+  CHECK_ARGS("halo_hc_combine");
+  return halo_b200_hc_combine_rows(c.s, res, DT, out, inject, hc, h, tokens, c.err, c.errlen);
+}
+template <int DT, bool ROWS>
+HANDLER(H_broadcast) {
+  auto* res = r.ptr<void>(); auto* x = r.ptr<const float>();
+  const uint32_t hc = r.u32(), h = r.u32(); const uint32_t tokens = ROWS ? r.u32() : 1u;
+  CHECK_ARGS("halo_broadcast");
+  return halo_b200_broadcast_rows(c.s, res, DT, x, hc, h, tokens, c.err, c.errlen);
+}
+template <bool ROWS>
+HANDLER(H_hc_mix) {
+  auto* xn = r.ptr<const float>(); auto* gate = r.ptr<const float>(); auto* mixed = r.ptr<float>();
+  const uint32_t hc = r.u32(), h = r.u32(); const uint32_t tokens = ROWS ? r.u32() : 1u;
+  CHECK_ARGS("halo_hc_mix");
+  return halo_b200_hc_mix_rows(c.s, xn, gate, mixed, hc, h, tokens, c.err, c.errlen);
+}
+template <bool ROWS>
+HANDLER(H_axpy_sigmoid) {
+  auto* y = r.ptr<float>(); auto* x = r.ptr<const float>(); auto* g = r.ptr<const float>();
+  const uint32_t n = r.u32(); const uint32_t tokens = ROWS ? r.u32() : 1u;
+  CHECK_ARGS("halo_axpy_sigmoid");
+  return halo_b200_axpy_sigmoid_rows(c.s, y, x, g, n, tokens, c.err, c.errlen);
+}
+HANDLER(H_inject_reduce) {
+  auto* ipart = r.ptr<const float>(); auto* inject = r.ptr<float>();
+  const uint32_t hc = r.u32(), irows = r.u32(), tokens = r.u32();
+  CHECK_ARGS("halo_inject_reduce");
+  return halo_b200_inject_reduce(c.s, ipart, inject, hc, irows, tokens, c.err, c.errlen);
+}
+template <int DT>
+HANDLER(H_res_to_f32) {
+  auto* y = r.ptr<float>(); auto* x = r.ptr<const void>(); const uint32_t n = r.u32();
+  CHECK_ARGS("halo_res_to_f32");
+  return halo_b200_res_to_f32(c.s, y, x, DT, n, c.err, c.errlen);
+}
+HANDLER(H_hc_norm_scales) {
+  auto* res = r.ptr<const float>(); auto* scale = r.ptr<float>(); const uint32_t h = r.u32(); const float eps = r.f32();
+  CHECK_ARGS("halo_hc_norm_scales");
+  return halo_b200_hc_norm_scales(c.s, res, scale, h, eps, c.grid[0], c.err, c.errlen);
+}
+
 struct Entry {
   const char* name;
   Handler fn;
@@ -300,6 +392,36 @@ const Entry kTable[] = {
     {"halo_matvec_q8_0_embed", H_embed},
     {"halo_matvec_q8_0_embed_p", H_embed_p},
     {"halo_matvec_q8_0_embed_rows", H_embed_rows},
+    {"halo_hc_combine_norm_rows", H_hc_combine_norm_rows<HALO_B200_F32>},
+    {"halo_hc_combine_norm_rows_r16", H_hc_combine_norm_rows<HALO_B200_F16>},
+    {"halo_hc_combine_norm_rows_rb", H_hc_combine_norm_rows<HALO_B200_BF16>},
+    {"halo_hc_combine_norm_rows_q8", H_hc_combine_norm_rows_q8},
+    {"halo_hc_combine_norm_tok", H_hc_combine_norm_tok<HALO_B200_F32>},
+    {"halo_hc_combine_norm_tok_r16", H_hc_combine_norm_tok<HALO_B200_F16>},
+    {"halo_hc_combine_norm_tok_rb", H_hc_combine_norm_tok<HALO_B200_BF16>},
+    {"halo_hc_combine_norm_tok_moe", H_hc_combine_norm_tok_moe<HALO_B200_F32>},
+    {"halo_hc_combine_norm_tok_moe_r16", H_hc_combine_norm_tok_moe<HALO_B200_F16>},
+    {"halo_hc_combine_norm_tok_moe_rb", H_hc_combine_norm_tok_moe<HALO_B200_BF16>},
+    {"halo_hc_combine_norm_tok_moev", H_hc_combine_norm_tok_moe<HALO_B200_F32>},
+    {"halo_hc_combine_norm_tok_moev_r16", H_hc_combine_norm_tok_moe<HALO_B200_F16>},
+    {"halo_hc_combine_norm_tok_moev_rb", H_hc_combine_norm_tok_moe<HALO_B200_BF16>},
+    {"halo_hc_combine", H_hc_combine<HALO_B200_F32, false>},
+    {"halo_hc_combine_rows", H_hc_combine<HALO_B200_F32, true>},
+    {"halo_hc_combine_rows_r16", H_hc_combine<HALO_B200_F16, true>},
+    {"halo_hc_combine_rows_rb", H_hc_combine<HALO_B200_BF16, true>},
+    {"halo_broadcast", H_broadcast<HALO_B200_F32, false>},
+    {"halo_broadcast_rows", H_broadcast<HALO_B200_F32, true>},
+    {"halo_broadcast_rows_r16", H_broadcast<HALO_B200_F16, true>},
+    {"halo_broadcast_rows_rb", H_broadcast<HALO_B200_BF16, true>},
+    {"halo_hc_mix", H_hc_mix<false>},
+    {"halo_hc_mix_rows", H_hc_mix<true>},
+    {"halo_axpy_sigmoid", H_axpy_sigmoid<false>},
+    {"halo_axpy_sigmoid_rows", H_axpy_sigmoid<true>},
+    {"halo_inject_reduce", H_inject_reduce},
+    {"halo_res_to_f32_r16", H_res_to_f32<HALO_B200_F16>},
+    {"halo_res_to_f32_rb", H_res_to_f32<HALO_B200_BF16>},
+    {"halo_hc_norm_scales", H_hc_norm_scales},
+    {"halo_hc_norm_scales_u", H_hc_norm_scales},
 };
 constexpr size_t kCount = sizeof(kTable) / sizeof(kTable[0]);
 

@@ -206,3 +206,78 @@ def embed_q8_0(table, ids, cols, out, *, id_stride=1, id_slot=0, vocab=0):
     lib().call("embed_q8_0_ex", _stream(), _p(table), table.shape[-1], vocab, _p(ids), id_stride, id_slot, tokens,
                _p(out), _code(out), cols)
     return out
+
+
+# ---- hyper-connection residual (hc streams of h values per token) -----------------------------
+def hc_combine_norm(res, out, inject, w, eps, *, one_plus=False, y=None, y16=None, y16_tokens=0, rscale=None, iw=None,
+                    ipart=None, yq=None, yd=None):
+    """res [T, hc, h] += out [T, h] * 2 sigmoid(inject [T, hc] / hc), stored in res' dtype; then the
+    grouped RMSNorm of the stored streams (gamma w [hc, h]) into any of y, y16 (fp16; K-blocked when
+    y16_tokens > 0), rscale [T, hc], yq / yd (K-blocked int8 + scales), ipart [T, hc, irows] = partial
+    products with iw [irows, hc*h]. out = inject = None: grouped norm only."""
+    _chk(res, "res", _ACT), _chk(out, "out", _ACT), _chk(inject, "inject", (torch.float32,))
+    _chk(w, "w", (torch.float32,)), _chk(y, "y", _ACT), _chk(y16, "y16", (torch.float16,))
+    _chk(rscale, "rscale", (torch.float32,)), _chk(iw, "iw", (torch.float32,)), _chk(ipart, "ipart", (torch.float32,))
+    _chk(yq, "yq", (torch.int8,)), _chk(yd, "yd", (torch.float32,))
+    tokens, hc, h = res.shape
+    lib().call("hc_combine_norm_ex", _stream(), _p(res), _code(res), _p(out), _code(out) if out is not None else F32,
+               _p(inject), _p(w), int(one_plus), _p(y), _code(y) if y is not None else F32, _p(y16), y16_tokens,
+               _p(rscale), _p(iw), _p(ipart), iw.shape[0] if iw is not None else 0, _p(yq), _p(yd), hc, h, eps, tokens)
+    return y
+
+
+def hc_combine_norm_moe(res, yp, pos, mw, sx, sg, inject, w, eps, *, one_plus=False, y=None, y16=None, y16_tokens=0,
+                        rscale=None, iw=None, ipart=None):
+    """hc_combine_norm whose block output is built in the kernel: sum over the k slots of
+    mw[t, s] * yp[pos[t, s]] (expert output rows), then + sigmoid(sg[t]) * sx[t] (shared expert)."""
+    _chk(res, "res", _ACT), _chk(yp, "yp", (torch.float16, torch.bfloat16)), _chk(pos, "pos", (torch.int32, torch.uint32))
+    _chk(mw, "mw", (torch.float32,)), _chk(sx, "sx", (torch.float32, yp.dtype)), _chk(sg, "sg", (torch.float32,))
+    _chk(inject, "inject", (torch.float32,)), _chk(w, "w", (torch.float32,)), _chk(y, "y", _ACT)
+    _chk(y16, "y16", (torch.float16,)), _chk(rscale, "rscale", (torch.float32,)), _chk(iw, "iw", (torch.float32,))
+    _chk(ipart, "ipart", (torch.float32,))
+    tokens, hc, h = res.shape
+    lib().call("hc_combine_norm_moe_ex", _stream(), _p(res), _code(res), _p(yp), _code(yp), _p(pos), _p(mw), _p(sx),
+               _code(sx), _p(sg), pos.shape[1], _p(inject), _p(w), int(one_plus), _p(y),
+               _code(y) if y is not None else F32, _p(y16), y16_tokens, _p(rscale), _p(iw), _p(ipart),
+               iw.shape[0] if iw is not None else 0, hc, h, eps, tokens)
+    return y
+
+
+def hc_combine_rows(res, out, inject):
+    """res [T, hc, h] += out [T, h] * 2 sigmoid(inject [T, hc] / hc)."""
+    _chk(res, "res", _ACT), _chk(out, "out", _ACT), _chk(inject, "inject", (torch.float32,))
+    tokens, hc, h = res.shape
+    lib().call("hc_combine_rows_ex", _stream(), _p(res), _code(res), _p(out), _code(out), _p(inject), hc, h, tokens)
+    return res
+
+
+def broadcast_rows(res, x):
+    """res [T, hc, h] = x [T, h] in every stream."""
+    _chk(res, "res", _ACT), _chk(x, "x", _ACT)
+    tokens, hc, h = res.shape
+    lib().call("broadcast_rows_ex", _stream(), _p(res), _code(res), _p(x), _code(x), hc, h, tokens)
+    return res
+
+
+def hc_mix_rows(xn, gate, mixed):
+    """mixed [T, h] = mean over streams of xn [T, hc, h] * sigmoid(gate [T, hc, h])."""
+    _chk(xn, "xn", _ACT), _chk(gate, "gate", (xn.dtype,)), _chk(mixed, "mixed", (xn.dtype,))
+    tokens, hc, h = xn.shape
+    lib().call("hc_mix_rows_ex", _stream(), _p(xn), _p(gate), _p(mixed), _code(xn), hc, h, tokens)
+    return mixed
+
+
+def axpy_sigmoid_rows(y, x, g):
+    """y [T, n] += sigmoid(g [T]) * x [T, n]."""
+    _chk(y, "y", (torch.float32,)), _chk(x, "x", (torch.float32,)), _chk(g, "g", (torch.float32,))
+    tokens, n = y.shape
+    lib().call("axpy_sigmoid_rows", _stream(), _p(y), _p(x), _p(g), n, tokens)
+    return y
+
+
+def inject_reduce(ipart, inject):
+    """inject [T, irows] = sum over streams of ipart [T, hc, irows]."""
+    _chk(ipart, "ipart", (torch.float32,)), _chk(inject, "inject", (torch.float32,))
+    tokens, hc, irows = ipart.shape
+    lib().call("inject_reduce", _stream(), _p(ipart), _p(inject), hc, irows, tokens)
+    return inject

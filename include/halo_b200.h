@@ -71,9 +71,10 @@ int halo_b200_rmsnorm_rows_rb(halo_b200_stream stream, const uint16_t* x, const 
                               float eps, uint32_t w_stride, uint32_t w_period, uint32_t rows, char* err,
                               size_t errlen);
 /* halo_rmsnorm_rows_h (+ _r16, _rb), src/kernels/core.hip:4502-4552: also writes an fp16
- * copy y16, row-major or (y16_tokens > 0) K-blocked [cols / 64][y16_tokens][64]. The fused
- * inject partial products (iw / ipart / irows) belong to Flash-Next's hyper-connection
- * mixer and are not implemented: iw must be NULL. x_dtype selects the variant. */
+ * copy y16, row-major or (y16_tokens > 0) K-blocked [cols / 64][y16_tokens][64]. With iw
+ * (irows <= 8 fp32 rows of w_period * d) it also writes the partial products
+ * ipart[row * irows + r] = <y_row, iw[r][(row % w_period) d ..]>; that form needs w_stride == d and
+ * rows % w_period == 0. x_dtype selects the variant. */
 int halo_b200_rmsnorm_rows_h(halo_b200_stream stream, const void* x, int x_dtype, const float* w_all, float* y,
                              uint16_t* y16, uint32_t d, float eps, uint32_t w_stride, uint32_t w_period,
                              const float* iw, float* ipart, uint32_t irows, uint32_t y16_tokens, uint32_t rows,
@@ -285,6 +286,89 @@ int halo_b200_embed_q8_0_ex(halo_b200_stream stream, const uint8_t* w, uint64_t 
                             const uint32_t* ids, uint32_t id_stride, uint32_t id_slot, uint32_t tokens, void* out,
                             int out_dtype, uint32_t cols, char* err, size_t errlen);
 
+/* ---- hyper-connection residual (Flash-Next: hc streams of h values per token) ----------------- */
+
+/* halo_hc_combine_norm_rows (+ _r16, _rb: res_dtype), src/kernels/core.hip:4105-4230; CPU operators
+ * HcCombine + GroupedNorm, src/model/reference.cpp:151-202. Per (token t, stream s) row:
+ * res += out[t] * 2 sigmoid(inject[t][s] / hc), stored in res' type; y = RMSNorm of the stored row with
+ * gamma w_all[s]; optional fp16 copy y16 (row-major, or K-blocked [hc h / 64][y16_tokens][64] when
+ * y16_tokens > 0), optional row scales rscale[t hc + s], optional partial products
+ * ipart[(t hc + s) irows + r] = <y, iw[r][s h ..]> (irows <= 8). y may be NULL. rows = grid.x = tokens * hc. */
+int halo_b200_hc_combine_norm_rows(halo_b200_stream stream, void* res, int res_dtype, const float* out,
+                                   const float* inject, const float* w_all, float* y, uint16_t* y16, uint32_t hc,
+                                   uint32_t h, float eps, const float* iw, float* ipart, uint32_t irows,
+                                   float* rscale, uint32_t y16_tokens, uint32_t rows, char* err, size_t errlen);
+/* halo_hc_combine_norm_rows_q8, src/kernels/core.hip:4231-4238: also the K-blocked int8 copy
+ * yq [hc h / 64][y16_tokens][64] with fp32 scales yd [hc h / 32][y16_tokens] (amax / 127, round to even). */
+int halo_b200_hc_combine_norm_rows_q8(halo_b200_stream stream, float* res, const float* out, const float* inject,
+                                      const float* w_all, float* y, uint16_t* y16, uint32_t hc, uint32_t h, float eps,
+                                      const float* iw, float* ipart, uint32_t irows, float* rscale,
+                                      uint32_t y16_tokens, int8_t* yq, float* yd, uint32_t rows, char* err,
+                                      size_t errlen);
+/* halo_hc_combine_norm_tok (+ _r16, _rb), src/kernels/core.hip:4240-4435: hc = 4, one launch unit per
+ * token, no fp32 y. tokens = grid.x. */
+int halo_b200_hc_combine_norm_tok(halo_b200_stream stream, void* res, int res_dtype, const float* out,
+                                  const float* inject, const float* w_all, uint16_t* y16, uint32_t h, float eps,
+                                  const float* iw, float* ipart, uint32_t irows, float* rscale, uint32_t y16_tokens,
+                                  uint32_t tokens, char* err, size_t errlen);
+/* halo_hc_combine_norm_tok_moe and _moev (+ _r16, _rb), src/kernels/core.hip:4437-4485: the block output
+ * is built in the kernel as halo_moe_combine_shared builds it (core.hip:5466-5480; CPU operator
+ * src/model/reference.cpp:558-578): out[t] = sum over slots, in order, of mw[t k + s] * yp[pos[t k + s]]
+ * (fp16 rows), then + sigmoid(sg[t]) * sx[t]. */
+int halo_b200_hc_combine_norm_tok_moe(halo_b200_stream stream, void* res, int res_dtype, const uint16_t* yp,
+                                      const uint32_t* pos, const float* mw, const float* sx, const float* sg,
+                                      uint32_t k, const float* inject, const float* w_all, uint16_t* y16, uint32_t h,
+                                      float eps, const float* iw, float* ipart, uint32_t irows, float* rscale,
+                                      uint32_t y16_tokens, uint32_t tokens, char* err, size_t errlen);
+/* Typed forms of the two above (the arithmetic of src/kernels/core.hip:4105-4230): block output and y in
+ * fp32, fp16 or bf16 (supported (res, out, y) triples: (any, f32 | f16, f32), (bf16, bf16, bf16),
+ * (f16, f16, f16)), gamma w or 1 + w, any hc. inject == NULL and out == NULL: grouped norm only, res is
+ * read and not written. */
+int halo_b200_hc_combine_norm_ex(halo_b200_stream stream, void* res, int res_dtype, const void* out, int out_dtype,
+                                 const float* inject, const float* w_all, int one_plus, void* y, int y_dtype,
+                                 uint16_t* y16, uint32_t y16_tokens, float* rscale, const float* iw, float* ipart,
+                                 uint32_t irows, int8_t* yq, float* yd, uint32_t hc, uint32_t h, float eps,
+                                 uint32_t tokens, char* err, size_t errlen);
+int halo_b200_hc_combine_norm_moe_ex(halo_b200_stream stream, void* res, int res_dtype, const void* yp, int yp_dtype,
+                                     const uint32_t* pos, const float* mw, const void* sx, int sx_dtype,
+                                     const float* sg, uint32_t k, const float* inject, const float* w_all,
+                                     int one_plus, void* y, int y_dtype, uint16_t* y16, uint32_t y16_tokens,
+                                     float* rscale, const float* iw, float* ipart, uint32_t irows, uint32_t hc,
+                                     uint32_t h, float eps, uint32_t tokens, char* err, size_t errlen);
+/* halo_hc_combine and halo_hc_combine_rows (+ _r16, _rb), src/kernels/core.hip:610-617, 4649-4673:
+ * res [tokens][hc][h] += out [tokens][h] * 2 sigmoid(inject [tokens][hc] / hc). */
+int halo_b200_hc_combine_rows(halo_b200_stream stream, void* res, int res_dtype, const float* out, const float* inject,
+                              uint32_t hc, uint32_t h, uint32_t tokens, char* err, size_t errlen);
+int halo_b200_hc_combine_rows_ex(halo_b200_stream stream, void* res, int res_dtype, const void* out, int out_dtype,
+                                 const float* inject, uint32_t hc, uint32_t h, uint32_t tokens, char* err,
+                                 size_t errlen);
+/* halo_broadcast and halo_broadcast_rows (+ _r16, _rb), src/kernels/core.hip:619-623, 4675-4697:
+ * res [tokens][hc][h] = x [tokens][h]. */
+int halo_b200_broadcast_rows(halo_b200_stream stream, void* res, int res_dtype, const float* x, uint32_t hc,
+                             uint32_t h, uint32_t tokens, char* err, size_t errlen);
+int halo_b200_broadcast_rows_ex(halo_b200_stream stream, void* res, int res_dtype, const void* x, int x_dtype,
+                                uint32_t hc, uint32_t h, uint32_t tokens, char* err, size_t errlen);
+/* halo_hc_mix and halo_hc_mix_rows, src/kernels/core.hip:600-608, 4634-4647; CPU operator
+ * src/model/reference.cpp:179-188: mixed[t][i] = (sum over s of xn[t][s][i] * sigmoid(gate[t][s][i])) / hc. */
+int halo_b200_hc_mix_rows(halo_b200_stream stream, const float* xn, const float* gate, float* mixed, uint32_t hc,
+                          uint32_t h, uint32_t tokens, char* err, size_t errlen);
+int halo_b200_hc_mix_rows_ex(halo_b200_stream stream, const void* xn, const void* gate, void* mixed, int dtype,
+                             uint32_t hc, uint32_t h, uint32_t tokens, char* err, size_t errlen);
+/* halo_axpy_sigmoid and halo_axpy_sigmoid_rows, src/kernels/core.hip:1129-1133, 4707-4714:
+ * y [tokens][n] += sigmoid(g [tokens]) * x [tokens][n] (the shared expert's gated add). */
+int halo_b200_axpy_sigmoid_rows(halo_b200_stream stream, float* y, const float* x, const float* g, uint32_t n,
+                                uint32_t tokens, char* err, size_t errlen);
+/* halo_inject_reduce, src/kernels/core.hip:4486-4496: inject[t][r] = sum over streams, in order, of
+ * ipart[(t hc + s) irows + r]. */
+int halo_b200_inject_reduce(halo_b200_stream stream, const float* ipart, float* inject, uint32_t hc, uint32_t irows,
+                            uint32_t tokens, char* err, size_t errlen);
+/* halo_res_to_f32_r16 and _rb, src/kernels/core.hip:4698-4705: y[i] = float(x[i]). */
+int halo_b200_res_to_f32(halo_b200_stream stream, float* y, const void* x, int x_dtype, uint32_t n, char* err,
+                         size_t errlen);
+/* halo_hc_norm_scales and _u, src/kernels/core.hip:2768-2776, 9383-9400: scale[row] = 1 / sqrt(mean(res_row^2) + eps). */
+int halo_b200_hc_norm_scales(halo_b200_stream stream, const float* res, float* scale, uint32_t h, float eps,
+                             uint32_t rows, char* err, size_t errlen);
+
 /* ---- launch by kernel name -------------------------------------------------------------- */
 
 /* One launch argument, as rt::Arg (src/rt/device.hpp:35-59): a device pointer (buffer base +
@@ -315,6 +399,7 @@ const char* halo_b200_kernel_name(size_t index);
  * "norm_force_general" (1 = the row norms always run their general kernel, never the lean one),
  * "gated_rows_per_group" (1 or 2 rows in flight per thread group of the gated norm on short rows; 0 = built-in),
  * "rope_rows_per_group" (2 or 4 rows in flight per thread group of the fused norm + RoPE kernel; 0 = built-in),
+ * "hc_row_level" (1 = the hyper-connection combine + norm always runs one (token, stream) row per thread group),
  * "pdl" (1, the default = kernels are launched with programmatic stream serialization, so a kernel is scheduled
  * while its predecessor in the stream drains and waits on the device for it to complete; 0 = plain launches).
  * Returns 0, or -1 for an unknown key or value. */

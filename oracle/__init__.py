@@ -52,6 +52,10 @@ _SIGS = {
     "orc_quantize_i8_rows": (None, [_p, _sz, _sz, _p, _p, _int]),
     "orc_round_bf16": (None, [_p, _sz]),
     "orc_round_fp16": (None, [_p, _sz]),
+    "orc_hc_combine_norm": (None, [_p, _p, _p, _p, _p, _sz, _sz, _sz, _f32, _int, _int]),
+    "orc_hc_inject": (None, [_p, _p, _p, _sz, _sz, _sz, _int]),
+    "orc_hc_mix": (None, [_p, _p, _p, _sz, _sz, _sz, _int]),
+    "orc_moe_combine": (None, [_p, _p, _p, _p, _p, _p, _sz, _sz, _sz, _int]),
 }
 
 
@@ -202,6 +206,47 @@ class Oracle:
         xd = np.empty((rows, cols // 32), dtype=np.float32)
         self._call("orc_quantize_i8_rows", _ptr(x), rows, cols, _ptr(xq), _ptr(xd), threads)
         return xq, xd
+
+    # --- hyper-connection residual --------------------------------------------
+    def hc_combine_norm(self, res, out, inject, w, eps, round=0, threads=1):
+        """res [T, hc, h] updated in place (out None: left as is), returns y = grouped norm of the stored res.
+        round: 0 fp32 residual, 1 bf16, 2 fp16 storage."""
+        res = _f32arr(res, True)
+        tokens, hc, h = res.shape
+        w = _f32arr(w)
+        y = np.empty_like(res)
+        op = ip = None
+        if out is not None:
+            out, inject = _f32arr(out), _f32arr(inject)
+            assert out.size == tokens * h and inject.size == tokens * hc
+            op, ip = _ptr(out), _ptr(inject)
+        self._call("orc_hc_combine_norm", _ptr(res), op, ip, _ptr(w), _ptr(y), tokens, hc, h, eps, round, threads)
+        return y
+
+    def hc_inject(self, xn, iw, threads=1):
+        """xn [T, hc*h], iw [irows, hc*h] -> inject [T, irows]."""
+        xn, iw = _f32arr(xn), _f32arr(iw)
+        tokens, cols = xn.reshape(xn.shape[0], -1).shape
+        irows = iw.shape[0]
+        out = np.empty((tokens, irows), dtype=np.float32)
+        self._call("orc_hc_inject", _ptr(xn), _ptr(iw), _ptr(out), tokens, cols, irows, threads)
+        return out
+
+    def hc_mix(self, xn, gate, threads=1):
+        xn, gate = _f32arr(xn), _f32arr(gate)
+        tokens, hc, h = xn.shape
+        out = np.empty((tokens, h), dtype=np.float32)
+        self._call("orc_hc_mix", _ptr(xn), _ptr(gate), _ptr(out), tokens, hc, h, threads)
+        return out
+
+    def moe_combine(self, yp, pos, mw, sx, sg, threads=1):
+        yp, mw, sx, sg = _f32arr(yp), _f32arr(mw), _f32arr(sx), _f32arr(sg)
+        pos = np.ascontiguousarray(pos, dtype=np.uint32)
+        tokens, k = pos.shape
+        h = yp.shape[-1]
+        out = np.empty((tokens, h), dtype=np.float32)
+        self._call("orc_moe_combine", _ptr(yp), _ptr(pos), _ptr(mw), _ptr(sx), _ptr(sg), _ptr(out), tokens, k, h, threads)
+        return out
 
     def round_bf16(self, x):
         x = _f32arr(x, True)

@@ -287,4 +287,78 @@ void orc_round_fp16(float* x, std::size_t n) {
   for (std::size_t i = 0; i < n; ++i) x[i] = RoundToHalf(x[i]);
 }
 
+// ---- hyper-connection residual (Flash-Next) ------------------------------------------------
+// res [T][hc][h] += out [T][h] * 2 sigmoid(inject [T][hc] / hc) (ReferenceModel::HcCombine,
+// src/model/reference.cpp:189-202); the stored residual is then rounded as a 16-bit buffer would
+// hold it (round: 0 none, 1 bf16, 2 fp16; src/kernels/core.hip:4132-4135) and y = GroupedNorm of the
+// stored values: each stream normalized on its own under its slice of the [hc h] gamma
+// (reference.cpp:151-160). out == NULL skips the combine. y may alias nothing else.
+void orc_hc_combine_norm(float* res, const float* out, const float* inject, const float* w, float* y,
+                         std::size_t tokens, std::size_t hc, std::size_t h, float eps, int round, int threads) {
+  ForRows(tokens, threads, [=](std::size_t b, std::size_t e) {
+    for (std::size_t t = b; t < e; ++t)
+      for (std::size_t s = 0; s < hc; ++s) {
+        float* dst = res + (t * hc + s) * h;
+        if (out != nullptr) {
+          const float a = 2.0F * SigmoidF(inject[t * hc + s] / static_cast<float>(hc));
+          for (std::size_t i = 0; i < h; ++i) dst[i] += out[t * h + i] * a;
+        }
+        if (round == 1) orc_round_bf16(dst, h);
+        if (round == 2) orc_round_fp16(dst, h);
+        float* yr = y + (t * hc + s) * h;
+        for (std::size_t i = 0; i < h; ++i) yr[i] = dst[i];
+        RmsNormRow(yr, h, w + s * h, eps);
+      }
+  });
+}
+
+// inject [T][irows] = iw [irows][hc h] . xn [T][hc h], double accumulation (MatVec(m.inject, 0, xn,
+// inject), reference.cpp:185-187 through src/model/cpu_ops.cpp:108-118).
+void orc_hc_inject(const float* xn, const float* iw, float* inject, std::size_t tokens, std::size_t cols,
+                   std::size_t irows, int threads) {
+  ForRows(tokens, threads, [=](std::size_t b, std::size_t e) {
+    for (std::size_t t = b; t < e; ++t)
+      for (std::size_t r = 0; r < irows; ++r) {
+        double acc = 0.0;
+        for (std::size_t i = 0; i < cols; ++i) acc += static_cast<double>(iw[r * cols + i]) * xn[t * cols + i];
+        inject[t * irows + r] = static_cast<float>(acc);
+      }
+  });
+}
+
+// mixed [T][h] = (sum over s of xn[t][s][i] * sigmoid(gate[t][s][i])) / hc (reference.cpp:179-188).
+void orc_hc_mix(const float* xn, const float* gate, float* mixed, std::size_t tokens, std::size_t hc, std::size_t h,
+                int threads) {
+  ForRows(tokens, threads, [=](std::size_t b, std::size_t e) {
+    for (std::size_t t = b; t < e; ++t) {
+      float* m = mixed + t * h;
+      for (std::size_t i = 0; i < h; ++i) m[i] = 0.0F;
+      for (std::size_t s = 0; s < hc; ++s) {
+        const std::size_t base = (t * hc + s) * h;
+        for (std::size_t i = 0; i < h; ++i) m[i] += xn[base + i] * SigmoidF(gate[base + i]);
+      }
+      for (std::size_t i = 0; i < h; ++i) m[i] /= static_cast<float>(hc);
+    }
+  });
+}
+
+// out [T][h] = sum over slots, in order, of mw[t k + s] * yp[pos[t k + s]], then + sigmoid(sg[t]) * sx[t]
+// (ReferenceModel::Moe, reference.cpp:558-578; rows of yp are the experts' down projections).
+void orc_moe_combine(const float* yp, const std::uint32_t* pos, const float* mw, const float* sx, const float* sg,
+                     float* out, std::size_t tokens, std::size_t k, std::size_t h, int threads) {
+  ForRows(tokens, threads, [=](std::size_t b, std::size_t e) {
+    for (std::size_t t = b; t < e; ++t) {
+      float* o = out + t * h;
+      for (std::size_t i = 0; i < h; ++i) o[i] = 0.0F;
+      for (std::size_t s = 0; s < k; ++s) {
+        const float weight = mw[t * k + s];
+        const float* down = yp + static_cast<std::size_t>(pos[t * k + s]) * h;
+        for (std::size_t j = 0; j < h; ++j) o[j] += weight * down[j];
+      }
+      const float g = SigmoidF(sg[t]);
+      for (std::size_t j = 0; j < h; ++j) o[j] += g * sx[t * h + j];
+    }
+  });
+}
+
 }  // extern "C"

@@ -10,6 +10,7 @@
 #include <algorithm>
 #include <cstddef>
 #include <cstdint>
+#include <cstring>
 #include <span>
 #include <thread>
 #include <vector>
@@ -17,6 +18,7 @@
 #include "core/lowbit.hpp"
 #include "core/quant.hpp"
 #include "model/cpu_ops.hpp"
+#include "model/weights.hpp"
 
 namespace {
 
@@ -33,6 +35,16 @@ void ForRows(std::size_t rows, int threads, Fn fn) {
   std::vector<std::thread> pool;
   for (std::size_t b = 0; b < rows; b += chunk) pool.emplace_back(fn, b, std::min(rows, b + chunk));
   for (auto& t : pool) t.join();
+}
+
+// What a bf16 residual buffer holds after a store of v: round to nearest even on the upper 16 bits
+// (the GPU side's HaloBf16 store, src/kernels/core.hip:62-73), decoded by the reference's Bf16ToFloat.
+float StoredBf16(float v) {
+  std::uint32_t u;
+  std::memcpy(&u, &v, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return v;
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return halo::quant::Bf16ToFloat(static_cast<std::uint16_t>(u >> 16));
 }
 
 }  // namespace
@@ -120,6 +132,78 @@ void orc_encode_q8_0_rows(const float* x, std::size_t rows, std::size_t cols, st
   ForRows(rows, threads, [=](std::size_t b, std::size_t e) {
     for (std::size_t r = b; r < e; ++r)
       halo::quant::lowbit::EncodeQ8_0(x + r * cols, cols, out + r * (cols / 32) * 34);
+  });
+}
+
+// ---- hyper-connection residual (Flash-Next) ------------------------------------------------
+// ReferenceModel::HcCombine, GroupedNorm, HcMix and Moe (src/model/reference.cpp:151-202, 529-578) are
+// members (or file-local helpers) of a class that needs a loaded model, so they cannot be called from
+// here. These four functions repeat their loops around the reference's own scalar operators: the norm is
+// cpu::RmsNorm, the gates are cpu::Sigmoid, the inject projection is cpu::MatVec over an F32 TensorRef;
+// the only arithmetic written here is the `dst += out * a` / `m += x * gate` accumulation of those loops.
+void orc_hc_combine_norm(float* res, const float* out, const float* inject, const float* w, float* y,
+                         std::size_t tokens, std::size_t hc, std::size_t h, float eps, int round, int threads) {
+  ForRows(tokens, threads, [=](std::size_t b, std::size_t e) {
+    for (std::size_t t = b; t < e; ++t)
+      for (std::size_t s = 0; s < hc; ++s) {
+        float* dst = res + (t * hc + s) * h;
+        if (out != nullptr) {
+          const float a = 2.0F * cpu::Sigmoid(inject[t * hc + s] / static_cast<float>(hc));
+          for (std::size_t i = 0; i < h; ++i) dst[i] += out[t * h + i] * a;
+        }
+        if (round == 1)
+          for (std::size_t i = 0; i < h; ++i) dst[i] = StoredBf16(dst[i]);
+        if (round == 2)
+          for (std::size_t i = 0; i < h; ++i) dst[i] = static_cast<float>(static_cast<_Float16>(dst[i]));
+        float* yr = y + (t * hc + s) * h;
+        std::copy(dst, dst + h, yr);
+        cpu::RmsNorm(std::span<float>(yr, h), w + s * h, eps);
+      }
+  });
+}
+
+void orc_hc_inject(const float* xn, const float* iw, float* inject, std::size_t tokens, std::size_t cols,
+                   std::size_t irows, int threads) {
+  halo::model::TensorRef ref;
+  ref.data = iw;
+  ref.type = halo::core::GgmlType::kF32;
+  ref.cols = cols;
+  ref.rows = irows;
+  ForRows(tokens, threads, [=](std::size_t b, std::size_t e) {
+    for (std::size_t t = b; t < e; ++t)
+      cpu::MatVec(ref, 0, std::span<const float>(xn + t * cols, cols), std::span<float>(inject + t * irows, irows));
+  });
+}
+
+void orc_hc_mix(const float* xn, const float* gate, float* mixed, std::size_t tokens, std::size_t hc, std::size_t h,
+                int threads) {
+  ForRows(tokens, threads, [=](std::size_t b, std::size_t e) {
+    for (std::size_t t = b; t < e; ++t) {
+      float* m = mixed + t * h;
+      std::fill(m, m + h, 0.0F);
+      for (std::size_t s = 0; s < hc; ++s) {
+        const std::size_t base = (t * hc + s) * h;
+        for (std::size_t i = 0; i < h; ++i) m[i] += xn[base + i] * cpu::Sigmoid(gate[base + i]);
+      }
+      for (std::size_t i = 0; i < h; ++i) m[i] /= static_cast<float>(hc);
+    }
+  });
+}
+
+void orc_moe_combine(const float* yp, const std::uint32_t* pos, const float* mw, const float* sx, const float* sg,
+                     float* out, std::size_t tokens, std::size_t k, std::size_t h, int threads) {
+  ForRows(tokens, threads, [=](std::size_t b, std::size_t e) {
+    for (std::size_t t = b; t < e; ++t) {
+      float* o = out + t * h;
+      std::fill(o, o + h, 0.0F);
+      for (std::size_t s = 0; s < k; ++s) {
+        const float weight = mw[t * k + s];
+        const float* down = yp + static_cast<std::size_t>(pos[t * k + s]) * h;
+        for (std::size_t j = 0; j < h; ++j) o[j] += weight * down[j];
+      }
+      const float g = cpu::Sigmoid(sg[t]);
+      for (std::size_t j = 0; j < h; ++j) o[j] += g * sx[t * h + j];
+    }
   });
 }
 

@@ -66,7 +66,11 @@ def test_bad_arguments_are_rejected_with_a_message():
     assert "rotary_dim" in _err_call("rope_neox", 256, 64, 15, 0, 1e7, 4)
     assert "cols % 32" in _err_call("matvec_q8_0_embed", 256, 256, 0, 48, 51)
     assert "row_bytes" in _err_call("matvec_q8_0_embed", 256, 256, 0, 64, 34)
-    assert "iw" in _err_call("rmsnorm_rows_h", 256, 0, 256, 256, 256, 64, 1e-6, 0, 1, 256, 256, 1, 0, 4)
+    assert "iw needs gamma rows" in _err_call("rmsnorm_rows_h", 256, 0, 256, 256, 256, 64, 1e-6, 0, 2, 256, 256, 1, 0, 4)
+    assert "inject goes with" in _err_call("hc_combine_norm_ex", 256, 0, 256, 0, None, 256, 0, 256, 0, None, 0, None, None,
+                                           None, 0, None, None, 4, 64, 1e-6, 2)
+    assert "hc rows per token" in _err_call("hc_combine_norm_rows", 256, 0, 256, 256, 256, 256, None, 4, 64, 1e-6, None,
+                                            None, 0, None, 0, 7)
     assert "aligned" in _err_call("silu_mul", 258, 256, 8)  # fp32 pointer off by 2 bytes
     assert "1..256" in _err_call("norm_rope_rows", 256, 256, 1e-6, 512, 64, 0, 2, 1e7, None, 4)
 
