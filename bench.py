@@ -216,6 +216,8 @@ def op_specs(torch, shapes, T: int):
     w_hd = torch.randn(s.head_dim, device=dev) * 0.1
     w_g = 1 + torch.randn(s.lin_dim, device=dev) * 0.1
     w_hc = 1 + torch.randn(4, s.hidden, device=dev) * 0.1
+    conv_c = (2 * s.k_heads + s.v_heads) * s.lin_dim
+    conv_w, conv_state = torch.randn(conv_c, 4, device=dev) * 0.5, torch.randn(3, conv_c, device=dev)
     table = torch.randint(0, 255, (8192, s.q8_row_bytes), device=dev, dtype=torch.uint8)
     table.view(8192, -1, 34)[:, :, 1] = 0x3C  # finite fp16 scales
     rope_tab = ops.rope_table(torch.empty(T, 2, s.rot // 2, device=dev), s.rot, s.theta)
@@ -242,11 +244,16 @@ def op_specs(torch, shapes, T: int):
         "hc_combine_norm": (lambda: (r(T, 4, s.hidden), r(T, s.hidden), torch.randn(T, 4, device=dev),
                                      torch.empty(T, 4, s.hidden, device=dev, dtype=bf)),
                             lambda b: ops.hc_combine_norm(b[0], b[1], b[2], w_hc, s.eps, y=b[3])),
+        # not in the chain: the DeltaNet conv(4) + SiLU + q/k L2 norm over the 8192 conv channels
+        "conv_l2norm": (lambda: (r(T, conv_c), torch.empty(T, conv_c, device=dev, dtype=bf)),
+                        lambda b: ops.conv_l2norm(b[0], conv_state, conv_w, b[1], l2_channels=2 * s.k_heads * s.lin_dim,
+                                                  d=s.lin_dim, eps=s.eps)),
     }
     nbytes = {"add_rmsnorm": bpt["add_rmsnorm"], "l2norm": bpt["l2norm"], "gated_norm": bpt["gated_norm"],
               "norm_rope_qk": bpt["norm_rope"], "swiglu_moe": bpt["swiglu_shared"] + bpt["swiglu_routed"],
               "embed": bpt["embed"], "add_rmsnorm_q8": 3 * 2 * s.hidden + s.q8_row_bytes,
-              "hc_combine_norm": (3 * 4 + 1) * 2 * s.hidden + 16}  # read + write res, write y (4 streams), read out, logits
+              "hc_combine_norm": (3 * 4 + 1) * 2 * s.hidden + 16,
+              "conv_l2norm": 2 * 2 * (2 * s.k_heads + s.v_heads) * s.lin_dim}  # read x, write out  # read + write res, write y (4 streams), read out, logits
     return specs, {k_: v * T for k_, v in nbytes.items()}
 
 
@@ -469,7 +476,7 @@ def main() -> None:
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
     ap.add_argument("--no-kernel-table", action="store_true", help="skip the per-kernel timing leg (profiler captures)")
     ap.add_argument("--profile-op", default=None, help="run 6 eager launches of one op and exit (profiler captures): "
-                    "add_rmsnorm, add_rmsnorm_q8, l2norm, gated_norm, norm_rope_qk, swiglu_moe, embed, hc_combine_norm")
+                    "add_rmsnorm, add_rmsnorm_q8, l2norm, gated_norm, norm_rope_qk, swiglu_moe, embed, hc_combine_norm, conv_l2norm")
     args = ap.parse_args()
     if args.profile_op:
         profile_op(args)

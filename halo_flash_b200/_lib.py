@@ -85,6 +85,12 @@ SIGNATURES: dict[str, list] = {
     "halo_b200_inject_reduce": [_p, _p, _u32, _u32, _u32],
     "halo_b200_res_to_f32": [_p, _p, _i, _u32],
     "halo_b200_hc_norm_scales": [_p, _p, _u32, _f, _u32],
+    "halo_b200_conv_l2norm_prefill": [_p, _p, _p, _p, _u32, _u32, _u32, _f, _u32, _u32],
+    "halo_b200_conv_l2norm_prefill8": [_p, _i, _p, _p, _p, _i, _u32, _u32, _u32, _f, _u32],
+    "halo_b200_conv_l2norm_ex": [_p, _i, _p, _p, _p, _i, _u32, _u32, _u32, _u32, _f, _u32],
+    "halo_b200_conv_state_advance": [_p, _i, _p, _u32, _u32, _u32],
+    "halo_b200_conv_l2norm": [_p, _p, _p, _p, _u32, _u32, _u32, _f, _u32],
+    "halo_b200_conv_step": [_p, _p, _p, _p, _u32, _u32],
     "halo_b200_embed_q8_0_ex": [_p, _u64, _u32, _p, _u32, _u32, _u32, _p, _i, _u32],
 }
 

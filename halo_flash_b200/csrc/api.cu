@@ -266,6 +266,7 @@ int RunNormRope(NormRopeArgs a, float theta, const char* what, halo_b200_stream 
 
 std::atomic<int> g_hc_row_level{0};
 std::atomic<int> g_hc_token_k{0};
+std::atomic<int> g_conv_tile{0};
 
 int RunHc(HcArgs a, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
   if (a.tokens == 0) return Done(cudaSuccess, what, err, errlen);  // an empty chunk is a no-op
@@ -318,6 +319,31 @@ int RunHcElt(HcEltArgs a, const char* what, halo_b200_stream stream, char* err, 
   return Done(e, what, err, errlen);
 }
 
+
+int RunConv(ConvArgs a, bool advance_only, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+  if (a.tokens == 0 || a.channels == 0) return Done(cudaSuccess, what, err, errlen);  // an empty chunk is a no-op
+  REQUIRE(a.in != nullptr, "%s: in is null", what);
+  REQUIRE(a.kern >= 1 && a.kern <= 9, "%s: conv kernel length %u outside 1..9", what, a.kern);
+  REQUIRE(ValidDType(a.in_dtype) && ValidDType(a.out_dtype), "%s: unknown dtype", what);
+  REQUIRE(Aligned(a.in, DTypeSize(a.in_dtype)) && Aligned(a.state, 4), "%s: pointer not aligned to its element type", what);
+  if (advance_only) {
+    REQUIRE(a.state != nullptr || a.kern < 2, "%s: state is null", what);
+    return Done(LaunchConvStateAdvance(a, S(stream)), what, err, errlen);
+  }
+  REQUIRE(a.w != nullptr && a.out != nullptr, "%s: null pointer", what);
+  REQUIRE(a.in != a.out, "%s: in and out must not be the same buffer (a token reads its predecessors' inputs)", what);
+  REQUIRE(Aligned(a.out, DTypeSize(a.out_dtype)) && Aligned(a.w, 4), "%s: pointer not aligned to its element type", what);
+  REQUIRE(a.l2_channels <= a.channels, "%s: l2_channels exceeds channels", what);
+  if (a.l2_channels) REQUIRE(a.d >= 1 && a.d <= 1024 && a.l2_channels % a.d == 0,
+                             "%s: the normalized channels must be whole heads of d <= 1024 channels", what);
+  if (a.d == 0) a.d = 128;
+  a.vec = a.channels % 8 == 0 && Aligned(a.in, 16) && Aligned(a.out, 16) && Aligned(a.w, 16) && Aligned(a.state, 16);
+  a.tile = g_conv_tile.load(std::memory_order_relaxed);
+  const cudaError_t e = LaunchConvL2norm(a, S(stream));
+  if (e == cudaErrorInvalidValue) return Fail(err, errlen, "%s: unsupported (in, out) dtype pair or chunk too long", what);
+  return Done(e, what, err, errlen);
+}
+
 }  // namespace
 
 namespace halo_b200 {
@@ -348,6 +374,11 @@ int halo_b200_tune(const char* key, int value) {
   if (std::strcmp(key, "norm_force_general") == 0) {
     if (value != 0 && value != 1) return -1;
     g_norm_force_general.store(value, std::memory_order_relaxed);
+    return 0;
+  }
+  if (std::strcmp(key, "conv_tile") == 0) {
+    if (value != 0 && value != 4 && value != 8) return -1;
+    g_conv_tile.store(value, std::memory_order_relaxed);
     return 0;
   }
   if (std::strcmp(key, "hc_token_k") == 0) {
@@ -1201,6 +1232,68 @@ int halo_b200_hc_norm_scales(halo_b200_stream stream, const float* res, float* s
   a.eps = eps;
   a.rows = rows;
   return RunNorm(a, "halo_hc_norm_scales", stream, err, errlen);
+}
+
+
+// ---- DeltaNet causal conv + SiLU + L2 norm ------------------------------------------------------
+int halo_b200_conv_l2norm_ex(halo_b200_stream stream, const void* in, int in_dtype, const float* state, const float* w,
+                             void* out, int out_dtype, uint32_t channels, uint32_t kern, uint32_t l2_channels,
+                             uint32_t d, float eps, uint32_t tokens, char* err, size_t errlen) {
+  ConvArgs a{};
+  a.in = in;
+  a.in_dtype = in_dtype;
+  a.state = const_cast<float*>(state);
+  a.w = w;
+  a.out = out;
+  a.out_dtype = out_dtype;
+  a.channels = channels;
+  a.kern = kern;
+  a.l2_channels = l2_channels;
+  a.d = d;
+  a.eps = eps;
+  a.tokens = tokens;
+  return RunConv(a, false, "halo_conv_l2norm_prefill", stream, err, errlen);
+}
+
+int halo_b200_conv_state_advance(halo_b200_stream stream, const void* in, int in_dtype, float* state,
+                                 uint32_t channels, uint32_t kern, uint32_t tokens, char* err, size_t errlen) {
+  ConvArgs a{};
+  a.in = in;
+  a.in_dtype = in_dtype;
+  a.out_dtype = kF32;
+  a.state = state;
+  a.channels = channels;
+  a.kern = kern;
+  a.tokens = tokens;
+  return RunConv(a, true, "halo_conv_state_advance", stream, err, errlen);
+}
+
+int halo_b200_conv_l2norm_prefill(halo_b200_stream stream, const float* in, const float* state, const float* w,
+                                  float* out, uint32_t channels, uint32_t kern, uint32_t l2_channels, float eps,
+                                  uint32_t d, uint32_t tokens, char* err, size_t errlen) {
+  return halo_b200_conv_l2norm_ex(stream, in, kF32, state, w, out, kF32, channels, kern, l2_channels, d, eps, tokens, err,
+                                  errlen);
+}
+
+int halo_b200_conv_l2norm_prefill8(halo_b200_stream stream, const void* in, int in_dtype, const float* state,
+                                   const float* w, void* out, int out_dtype, uint32_t channels, uint32_t tokens,
+                                   uint32_t l2_channels, float eps, uint32_t d, char* err, size_t errlen) {
+  return halo_b200_conv_l2norm_ex(stream, in, in_dtype, state, w, out, out_dtype, channels, 4, l2_channels, d, eps, tokens,
+                                  err, errlen);
+}
+
+int halo_b200_conv_l2norm(halo_b200_stream stream, const float* in, float* state, const float* w, float* out,
+                          uint32_t channels, uint32_t kern, uint32_t l2_channels, float eps, uint32_t d, char* err,
+                          size_t errlen) {
+  const int rc = halo_b200_conv_l2norm_ex(stream, in, kF32, state, w, out, kF32, channels, kern, l2_channels, d, eps, 1,
+                                          err, errlen);
+  if (rc != 0) return rc;
+  return halo_b200_conv_state_advance(stream, in, kF32, state, channels, kern, 1, err, errlen);
+}
+
+int halo_b200_conv_step(halo_b200_stream stream, const float* in, float* state, const float* w, float* out,
+                        uint32_t channels, uint32_t kern, char* err, size_t errlen) {
+  return halo_b200_conv_l2norm(stream, in, state, w, out, channels, kern, 0, 0.0f, 128, err, errlen);
 }
 
 

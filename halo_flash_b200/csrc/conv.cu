@@ -1,0 +1,232 @@
+// Causal depthwise conv (kernel 4) + SiLU + per-head L2 norm for sm_100a: the step of a Gated
+// DeltaNet layer just before the q / k L2 norm, fused with it. Replaces halo_conv_step,
+// halo_conv_l2norm, halo_conv_l2norm_prefill, halo_conv_l2norm_prefill8(_h, _hh) and
+// halo_conv_state_advance(_h) (src/kernels/core.hip:445-456, 3002-3028, 3486-3611); arithmetic
+// follows Qwen35Reference::Linear, src/model/qwen35.cpp:180-198.
+//
+// in, out are [tokens][channels]; channel ch of token t sees the inputs t-3 .. t, the ones before
+// the chunk from the conv state [3][channels] (oldest first, fp32). The first l2_channels channels
+// (q and k) are L2-normalized per head of d channels; the rest (v) are only convolved.
+//
+// A thread owns one octet of channels for kTile consecutive tokens: the window slides through its
+// registers (kTile + 3 loads for kTile outputs; the 3 halo rows are the neighbour tile's own rows, so
+// they come from L2), all loads are issued first, and a head of d channels is d / 8 neighbouring
+// lanes, so each token's sum of squares is a shuffle reduction with no barrier.
+#include <type_traits>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace halo_b200 {
+namespace {
+
+constexpr int kTaps = 4;
+
+// acc = w[3] x[t]; acc += w[0] x[t-3]; += w[1] x[t-2]; += w[2] x[t-1] (the order of qwen35.cpp:183-186),
+// each step one packed FMA. The step, prefill and scalar kernels all use this one recipe, so a token's
+// output does not depend on how the chunk was tiled.
+__device__ __forceinline__ Oct conv4(const Oct (&w)[kTaps], const Oct& x0, const Oct& x1, const Oct& x2, const Oct& x3) {
+  Oct acc;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 v = __fmul2_rn(w[3].p[i], x3.p[i]);
+    v = __ffma2_rn(w[0].p[i], x0.p[i], v);
+    v = __ffma2_rn(w[1].p[i], x1.p[i], v);
+    v = __ffma2_rn(w[2].p[i], x2.p[i], v);
+    acc.p[i] = v;
+  }
+  return acc;
+}
+
+// HL: lanes per head (d / 8), a compile-time constant so that the shuffle steps carry no branch and the
+// eight tokens' reductions, which are independent, interleave. FULL: the tile and its three rows of
+// history lie inside the chunk and the thread owns a real octet, so nothing is predicated and the row
+// addresses are one pointer stepped by `channels` (the predicated form spent more instructions on
+// address arithmetic and guards than on the convolution).
+template <typename IT, typename OT, unsigned HL, int kTile, bool FULL>
+__device__ __forceinline__ void conv_tile(const ConvArgs& a, const unsigned c0, const uint32_t t0, const bool live) {
+  const IT* in = static_cast<const IT*>(a.in);
+  // window rows j = 0 .. kTile + 2 hold input t0 - 3 + j
+  Raw<IT> raw[kTile + 3];
+  if constexpr (FULL) {
+    const IT* p = in + static_cast<size_t>(t0 - 3) * a.channels + c0;
+#pragma unroll
+    for (int j = 0; j < kTile + 3; ++j, p += a.channels) raw[j] = raw_load(p);
+  } else {
+#pragma unroll
+    for (int j = 0; j < kTile + 3; ++j) {
+      const int64_t i = static_cast<int64_t>(t0) - 3 + j;
+      const bool from_chunk = live && i >= 0 && i < static_cast<int64_t>(a.tokens);
+      if (from_chunk) raw[j] = raw_load(in + static_cast<size_t>(i) * a.channels + c0);
+      else if constexpr (std::is_same_v<IT, float>) raw[j].a = raw[j].b = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      else raw[j].u = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+  // taps: w[ch][4] -> four octets, tap k of the thread's 8 channels
+  Oct w[kTaps];
+  {
+    float4 wl[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+      wl[c] = (FULL || live) ? __ldg(reinterpret_cast<const float4*>(a.w + static_cast<size_t>(c0 + c) * kTaps))
+                             : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      w[0].p[i] = make_float2(wl[2 * i].x, wl[2 * i + 1].x);
+      w[1].p[i] = make_float2(wl[2 * i].y, wl[2 * i + 1].y);
+      w[2].p[i] = make_float2(wl[2 * i].z, wl[2 * i + 1].z);
+      w[3].p[i] = make_float2(wl[2 * i].w, wl[2 * i + 1].w);
+    }
+  }
+  // the three rows of history before the tile: from the chunk, or for the first tile from the conv state
+  Oct x0 = raw_unpack(raw[0]), x1 = raw_unpack(raw[1]), x2 = raw_unpack(raw[2]);
+  if constexpr (!FULL) {
+    if (t0 == 0 && live && a.state) {
+      x0 = oct_load(a.state + c0);
+      x1 = oct_load(a.state + static_cast<size_t>(a.channels) + c0);
+      x2 = oct_load(a.state + 2 * static_cast<size_t>(a.channels) + c0);
+    }
+  }
+  const bool l2 = c0 < a.l2_channels;
+  OT* out = static_cast<OT*>(a.out) + static_cast<size_t>(t0) * a.channels + c0;
+#pragma unroll
+  for (int t = 0; t < kTile; ++t, out += a.channels) {
+    const Oct x3 = raw_unpack(raw[t + 3]);
+    Oct v = conv4(w, x0, x1, x2, x3);
+    x0 = x1, x1 = x2, x2 = x3;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v.p[i] = silu2_f(v.p[i]);
+    if constexpr (HL > 0) {
+      // all lanes shuffle (a warp may hold normalized and plain heads); only q / k lanes use the sum
+      const float2 acc = oct_sumsq(v, make_float2(0.0f, 0.0f));
+      float ss = acc.x + acc.y;
+#pragma unroll
+      for (unsigned of = 16; of > 0; of >>= 1)
+        if (of < HL) ss += __shfl_xor_sync(kFullMask, ss, of);
+      if (l2) v = oct_scale(v, rsqrtf(ss + a.eps));
+    }
+    if (FULL || (live && t0 + t < a.tokens)) oct_store(out, v);
+  }
+}
+
+template <typename IT, typename OT, unsigned HL, int kTile>
+__global__ void __launch_bounds__(kBlock, kTile >= 8 ? 2 : 3) conv_l2norm_kernel(const ConvArgs a) {
+  pdl_begin();
+  const unsigned oc = blockIdx.x * kBlock + threadIdx.x;  // channel octet
+  const bool live = oc < (a.channels >> 3);
+  const unsigned c0 = (live ? oc : 0u) << 3;
+  const uint32_t t0 = blockIdx.y * kTile;
+  // CTA-uniform except in the last CTA of a row of the grid; a warp there may run both forms in turn
+  // (the shuffles of a head stay together: heads do not straddle the live / dead boundary)
+  const bool full = t0 >= 3 && t0 + kTile <= a.tokens && (blockIdx.x + 1) * kBlock <= (a.channels >> 3);
+  if (full) conv_tile<IT, OT, HL, kTile, true>(a, c0, t0, true);
+  else conv_tile<IT, OT, HL, kTile, false>(a, c0, t0, live);
+}
+
+// Any kernel length, head size and alignment: one CTA per (head, token), one channel per thread.
+template <typename IT, typename OT>
+__global__ void __launch_bounds__(1024) conv_l2norm_scalar_kernel(const ConvArgs a) {
+  pdl_begin();
+  __shared__ float scratch[32];
+  __shared__ float total;
+  const uint32_t t = blockIdx.y;
+  const uint32_t ch = blockIdx.x * a.d + threadIdx.x;
+  const bool live = threadIdx.x < a.d && ch < a.channels;
+  const IT* in = static_cast<const IT*>(a.in);
+  float v = 0.0f;
+  if (live) {
+    const float* w = a.w + static_cast<size_t>(ch) * a.kern;
+    float acc = __fmul_rn(w[a.kern - 1], to_f32(in[static_cast<size_t>(t) * a.channels + ch]));
+    for (uint32_t k = 0; k + 1 < a.kern; ++k) {
+      const int64_t i = static_cast<int64_t>(t) - static_cast<int64_t>(a.kern - 1) + k;  // window slot k
+      float x = 0.0f;
+      if (i >= 0) x = to_f32(in[static_cast<size_t>(i) * a.channels + ch]);
+      else if (a.state) x = a.state[static_cast<size_t>(i + a.kern - 1) * a.channels + ch];
+      acc = __fmaf_rn(w[k], x, acc);
+    }
+    v = silu_f(acc);
+  }
+  if (blockIdx.x * a.d < a.l2_channels) {  // CTA-uniform
+    float ss = warp_sum(live ? __fmul_rn(v, v) : 0.0f);
+    if ((threadIdx.x & 31u) == 0) scratch[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float s = 0.0f;
+      for (unsigned i = 0; i < (blockDim.x + 31) / 32; ++i) s += scratch[i];
+      total = s;
+    }
+    __syncthreads();
+    v *= rsqrtf(total + a.eps);
+  }
+  if (live) static_cast<OT*>(a.out)[static_cast<size_t>(t) * a.channels + ch] = from_f32<OT>(v);
+}
+
+// The conv state after a chunk: the last kern - 1 inputs, the older ones from the previous state when
+// the chunk is shorter than that (src/kernels/core.hip:3578-3611). One thread per channel.
+template <typename IT>
+__global__ void __launch_bounds__(kBlock) conv_state_advance_kernel(const ConvArgs a) {
+  pdl_begin();
+  const uint32_t ch = blockIdx.x * kBlock + threadIdx.x;
+  if (ch >= a.channels || a.kern < 2) return;
+  const IT* in = static_cast<const IT*>(a.in);
+  float next[8];  // kern <= 9: every row is read before any is written
+  for (uint32_t k = 0; k + 1 < a.kern; ++k) {
+    const int64_t i = static_cast<int64_t>(a.tokens) - static_cast<int64_t>(a.kern - 1) + k;
+    next[k] = i >= 0 ? to_f32(in[static_cast<size_t>(i) * a.channels + ch])
+                     : a.state[static_cast<size_t>(i + a.kern - 1) * a.channels + ch];
+  }
+  for (uint32_t k = 0; k + 1 < a.kern; ++k) a.state[static_cast<size_t>(k) * a.channels + ch] = next[k];
+}
+
+template <typename IT, typename OT, int TILE>
+cudaError_t LaunchConvTile(const ConvArgs& a, unsigned head_octs, cudaStream_t s) {
+  const dim3 grid((a.channels / 8 + kBlock - 1) / kBlock, (a.tokens + TILE - 1) / TILE);
+  if (grid.y > 65535u) return cudaErrorInvalidValue;
+  switch (a.l2_channels ? head_octs : 0u) {
+    case 0: return LaunchKernel(conv_l2norm_kernel<IT, OT, 0, TILE>, grid, kBlock, 0, s, a);
+    case 1: return LaunchKernel(conv_l2norm_kernel<IT, OT, 1, TILE>, grid, kBlock, 0, s, a);
+    case 2: return LaunchKernel(conv_l2norm_kernel<IT, OT, 2, TILE>, grid, kBlock, 0, s, a);
+    case 4: return LaunchKernel(conv_l2norm_kernel<IT, OT, 4, TILE>, grid, kBlock, 0, s, a);
+    case 8: return LaunchKernel(conv_l2norm_kernel<IT, OT, 8, TILE>, grid, kBlock, 0, s, a);
+    case 16: return LaunchKernel(conv_l2norm_kernel<IT, OT, 16, TILE>, grid, kBlock, 0, s, a);
+    default: return LaunchKernel(conv_l2norm_kernel<IT, OT, 32, TILE>, grid, kBlock, 0, s, a);
+  }
+}
+
+template <typename IT, typename OT>
+cudaError_t LaunchConvT(const ConvArgs& a, cudaStream_t s) {
+  const unsigned head_octs = a.d / 8;
+  const bool head_pow2 = head_octs >= 1 && head_octs <= 32 && (head_octs & (head_octs - 1)) == 0 && a.d % 8 == 0;
+  if (a.vec && a.kern == kTaps && (a.l2_channels == 0 || head_pow2)) {
+    return a.tile == 4 ? LaunchConvTile<IT, OT, 4>(a, head_octs, s) : LaunchConvTile<IT, OT, 8>(a, head_octs, s);
+  }
+  if (a.d == 0 || a.d > 1024 || a.tokens > 65535u) return cudaErrorInvalidValue;
+  const dim3 grid((a.channels + a.d - 1) / a.d, a.tokens);
+  return LaunchKernel(conv_l2norm_scalar_kernel<IT, OT>, grid, dim3((a.d + 31) / 32 * 32), 0, s, a);
+}
+
+}  // namespace
+
+cudaError_t LaunchConvL2norm(const ConvArgs& a, cudaStream_t s) {
+  if (a.tokens == 0 || a.channels == 0) return cudaSuccess;
+  const int i = a.in_dtype, o = a.out_dtype;
+  if (i == kF32 && o == kF32) return LaunchConvT<float, float>(a, s);
+  if (i == kF16 && o == kF32) return LaunchConvT<f16, float>(a, s);
+  if (i == kF16 && o == kF16) return LaunchConvT<f16, f16>(a, s);
+  if (i == kBF16 && o == kBF16) return LaunchConvT<bf16, bf16>(a, s);
+  if (i == kBF16 && o == kF32) return LaunchConvT<bf16, float>(a, s);
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t LaunchConvStateAdvance(const ConvArgs& a, cudaStream_t s) {
+  if (a.channels == 0 || a.kern < 2) return cudaSuccess;
+  const unsigned grid = (a.channels + kBlock - 1) / kBlock;
+  switch (a.in_dtype) {
+    case kF32: return LaunchKernel(conv_state_advance_kernel<float>, grid, kBlock, 0, s, a);
+    case kF16: return LaunchKernel(conv_state_advance_kernel<f16>, grid, kBlock, 0, s, a);
+    case kBF16: return LaunchKernel(conv_state_advance_kernel<bf16>, grid, kBlock, 0, s, a);
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace halo_b200

@@ -284,6 +284,23 @@ struct HcEltArgs {
 };
 cudaError_t LaunchHcElt(const HcEltArgs& a, cudaStream_t s);
 
+// Causal depthwise conv + SiLU + per-head L2 norm of a Gated DeltaNet layer (src/kernels/core.hip:
+// 445-456, 3002-3028, 3486-3611).
+struct ConvArgs {
+  const void* in;   // [tokens][channels], in_dtype
+  float* state;     // [kern - 1][channels] fp32, oldest first; read by the conv, written by the advance
+  const float* w;   // [channels][kern]
+  void* out;        // [tokens][channels], out_dtype
+  uint32_t channels, kern, l2_channels, d, tokens;
+  float eps;
+  int in_dtype, out_dtype;
+  int vec;
+  int tile;  // tuning: tokens per thread, 4 or 8 (0 = built-in choice)
+};
+cudaError_t LaunchConvL2norm(const ConvArgs& a, cudaStream_t s);
+cudaError_t LaunchConvStateAdvance(const ConvArgs& a, cudaStream_t s);
+
+
 }  // namespace halo_b200
 
 #endif  // HALO_B200_KERNELS_H_

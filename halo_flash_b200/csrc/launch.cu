@@ -352,6 +352,44 @@ HANDLER(H_hc_norm_scales) {
   return halo_b200_hc_norm_scales(c.s, res, scale, h, eps, c.grid[0], c.err, c.errlen);
 }
 
+HANDLER(H_conv_step) {
+  auto* in = r.ptr<const float>(); auto* state = r.ptr<float>(); auto* w = r.ptr<const float>(); auto* out = r.ptr<float>();
+  const uint32_t channels = r.u32(), kern = r.u32();
+  CHECK_ARGS("halo_conv_step");
+  return halo_b200_conv_step(c.s, in, state, w, out, channels, kern, c.err, c.errlen);
+}
+HANDLER(H_conv_l2norm) {
+  auto* in = r.ptr<const float>(); auto* state = r.ptr<float>(); auto* w = r.ptr<const float>(); auto* out = r.ptr<float>();
+  const uint32_t channels = r.u32(), kern = r.u32(), l2 = r.u32(); const float eps = r.f32();
+  CHECK_ARGS("halo_conv_l2norm");
+  return halo_b200_conv_l2norm(c.s, in, state, w, out, channels, kern, l2, eps, c.block[0], c.err, c.errlen);
+}
+HANDLER(H_conv_l2norm_prefill) {
+  auto* in = r.ptr<const float>(); auto* state = r.ptr<const float>(); auto* w = r.ptr<const float>();
+  auto* out = r.ptr<float>();
+  const uint32_t channels = r.u32(), kern = r.u32(), l2 = r.u32(); const float eps = r.f32();
+  CHECK_ARGS("halo_conv_l2norm_prefill");
+  return halo_b200_conv_l2norm_prefill(c.s, in, state, w, out, channels, kern, l2, eps, c.block[0], c.grid[1], c.err,
+                                       c.errlen);
+}
+template <int IN, int OUT>
+HANDLER(H_conv_l2norm_prefill8) {
+  auto* in = r.ptr<const void>(); auto* state = r.ptr<const float>(); auto* w = r.ptr<const float>();
+  auto* out = r.ptr<void>();
+  const uint32_t channels = r.u32(), tokens = r.u32(), l2 = r.u32(); const float eps = r.f32();
+  CHECK_ARGS("halo_conv_l2norm_prefill8");
+  if ((tokens + 7) / 8 != c.grid[1]) return BadArgs(c, "halo_conv_l2norm_prefill8 (grid.y != ceil(tokens / 8))");
+  return halo_b200_conv_l2norm_prefill8(c.s, in, IN, state, w, out, OUT, channels, tokens, l2, eps, c.block[0], c.err,
+                                        c.errlen);
+}
+template <int IN>
+HANDLER(H_conv_state_advance) {
+  auto* in = r.ptr<const void>(); auto* state = r.ptr<float>();
+  const uint32_t channels = r.u32(), kern = r.u32(), tokens = r.u32();
+  CHECK_ARGS("halo_conv_state_advance");
+  return halo_b200_conv_state_advance(c.s, in, IN, state, channels, kern, tokens, c.err, c.errlen);
+}
+
 struct Entry {
   const char* name;
   Handler fn;
@@ -422,6 +460,14 @@ const Entry kTable[] = {
     {"halo_res_to_f32_rb", H_res_to_f32<HALO_B200_BF16>},
     {"halo_hc_norm_scales", H_hc_norm_scales},
     {"halo_hc_norm_scales_u", H_hc_norm_scales},
+    {"halo_conv_step", H_conv_step},
+    {"halo_conv_l2norm", H_conv_l2norm},
+    {"halo_conv_l2norm_prefill", H_conv_l2norm_prefill},
+    {"halo_conv_l2norm_prefill8", H_conv_l2norm_prefill8<HALO_B200_F32, HALO_B200_F32>},
+    {"halo_conv_l2norm_prefill8_h", H_conv_l2norm_prefill8<HALO_B200_F16, HALO_B200_F32>},
+    {"halo_conv_l2norm_prefill8_hh", H_conv_l2norm_prefill8<HALO_B200_F16, HALO_B200_F16>},
+    {"halo_conv_state_advance", H_conv_state_advance<HALO_B200_F32>},
+    {"halo_conv_state_advance_h", H_conv_state_advance<HALO_B200_F16>},
 };
 constexpr size_t kCount = sizeof(kTable) / sizeof(kTable[0]);
 

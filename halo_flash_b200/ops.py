@@ -281,3 +281,23 @@ def inject_reduce(ipart, inject):
     tokens, hc, irows = ipart.shape
     lib().call("inject_reduce", _stream(), _p(ipart), _p(inject), hc, irows, tokens)
     return inject
+
+
+# ---- Gated DeltaNet causal conv + SiLU + per-head L2 norm -------------------------------------
+def conv_l2norm(x, state, w, out, *, l2_channels, d, eps):
+    """out [T, C] = SiLU(causal depthwise conv of x [T, C] with taps w [C, kern]); history before the chunk
+    from state [kern - 1, C] (fp32, oldest first; None = zeros). The first l2_channels channels are
+    L2-normalized per head of d channels. The state is not written: see conv_state_advance."""
+    _chk(x, "x", _ACT), _chk(state, "state", (torch.float32,)), _chk(w, "w", (torch.float32,)), _chk(out, "out", _ACT)
+    tokens, channels = x.shape
+    lib().call("conv_l2norm_ex", _stream(), _p(x), _code(x), _p(state), _p(w), _p(out), _code(out), channels, w.shape[1],
+               l2_channels, d, eps, tokens)
+    return out
+
+
+def conv_state_advance(x, state):
+    """state [kern - 1, C] <- the last kern - 1 rows of (state rows, then x rows)."""
+    _chk(x, "x", _ACT), _chk(state, "state", (torch.float32,))
+    tokens, channels = x.shape
+    lib().call("conv_state_advance", _stream(), _p(x), _code(x), _p(state), channels, state.shape[0] + 1, tokens)
+    return state

@@ -369,6 +369,38 @@ int halo_b200_res_to_f32(halo_b200_stream stream, float* y, const void* x, int x
 int halo_b200_hc_norm_scales(halo_b200_stream stream, const float* res, float* scale, uint32_t h, float eps,
                              uint32_t rows, char* err, size_t errlen);
 
+/* ---- Gated DeltaNet causal conv + SiLU + per-head L2 norm ---------------------------------------- */
+
+/* halo_conv_l2norm_prefill, src/kernels/core.hip:3486-3509; CPU operator Qwen35Reference::Linear,
+ * src/model/qwen35.cpp:180-198. in, out [tokens][channels]; out[t][ch] = SiLU(w[ch][kern-1] in[t][ch] +
+ * sum over k < kern-1 of w[ch][k] x(t - (kern-1) + k)), inputs before the chunk taken from the conv state
+ * [kern-1][channels] (oldest first; NULL = zeros); the first l2_channels channels are then L2-normalized per
+ * head of d channels (x / sqrt(sum x^2 + eps)). The state is not written. d = block.x, tokens = grid.y.
+ * in and out must be different buffers. */
+int halo_b200_conv_l2norm_prefill(halo_b200_stream stream, const float* in, const float* state, const float* w,
+                                  float* out, uint32_t channels, uint32_t kern, uint32_t l2_channels, float eps,
+                                  uint32_t d, uint32_t tokens, char* err, size_t errlen);
+/* halo_conv_l2norm_prefill8 (+ _h: fp16 in, _hh: fp16 in and out), src/kernels/core.hip:3511-3576: kern = 4. */
+int halo_b200_conv_l2norm_prefill8(halo_b200_stream stream, const void* in, int in_dtype, const float* state,
+                                   const float* w, void* out, int out_dtype, uint32_t channels, uint32_t tokens,
+                                   uint32_t l2_channels, float eps, uint32_t d, char* err, size_t errlen);
+/* Typed form of the two above: (in, out) in (f32, f32), (f16, f32), (f16, f16), (bf16, bf16), (bf16, f32). */
+int halo_b200_conv_l2norm_ex(halo_b200_stream stream, const void* in, int in_dtype, const float* state, const float* w,
+                             void* out, int out_dtype, uint32_t channels, uint32_t kern, uint32_t l2_channels,
+                             uint32_t d, float eps, uint32_t tokens, char* err, size_t errlen);
+/* halo_conv_state_advance (+ _h), src/kernels/core.hip:3578-3611: the state after a chunk of `tokens`
+ * inputs = its last kern - 1 inputs (older rows from the previous state when the chunk is shorter). */
+int halo_b200_conv_state_advance(halo_b200_stream stream, const void* in, int in_dtype, float* state,
+                                 uint32_t channels, uint32_t kern, uint32_t tokens, char* err, size_t errlen);
+/* halo_conv_l2norm, src/kernels/core.hip:3002-3028: one decode step (conv of one token, then the state
+ * shifts by it). d = block.x. Two launches: the conv, then the advance. */
+int halo_b200_conv_l2norm(halo_b200_stream stream, const float* in, float* state, const float* w, float* out,
+                          uint32_t channels, uint32_t kern, uint32_t l2_channels, float eps, uint32_t d, char* err,
+                          size_t errlen);
+/* halo_conv_step, src/kernels/core.hip:445-456: the same without the L2 norm. */
+int halo_b200_conv_step(halo_b200_stream stream, const float* in, float* state, const float* w, float* out,
+                        uint32_t channels, uint32_t kern, char* err, size_t errlen);
+
 /* ---- launch by kernel name -------------------------------------------------------------- */
 
 /* One launch argument, as rt::Arg (src/rt/device.hpp:35-59): a device pointer (buffer base +

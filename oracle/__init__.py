@@ -55,6 +55,7 @@ _SIGS = {
     "orc_hc_combine_norm": (None, [_p, _p, _p, _p, _p, _sz, _sz, _sz, _f32, _int, _int]),
     "orc_hc_inject": (None, [_p, _p, _p, _sz, _sz, _sz, _int]),
     "orc_hc_mix": (None, [_p, _p, _p, _sz, _sz, _sz, _int]),
+    "orc_conv_l2norm": (None, [_p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _f32]),
     "orc_moe_combine": (None, [_p, _p, _p, _p, _p, _p, _sz, _sz, _sz, _int]),
 }
 
@@ -246,6 +247,16 @@ class Oracle:
         h = yp.shape[-1]
         out = np.empty((tokens, h), dtype=np.float32)
         self._call("orc_moe_combine", _ptr(yp), _ptr(pos), _ptr(mw), _ptr(sx), _ptr(sg), _ptr(out), tokens, k, h, threads)
+        return out
+
+    def conv_l2norm(self, x, state, w, l2_channels, d, eps):
+        """x [T, C], state [kern-1, C] (updated in place), w [C, kern] -> out [T, C]."""
+        x, w = _f32arr(x), _f32arr(w)
+        state = _f32arr(state, True)
+        tokens, channels = x.shape
+        out = np.empty_like(x)
+        self._call("orc_conv_l2norm", _ptr(x), _ptr(state), _ptr(w), _ptr(out), tokens, channels, w.shape[1], l2_channels,
+                   d, eps)
         return out
 
     def round_bf16(self, x):

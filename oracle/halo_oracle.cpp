@@ -361,4 +361,26 @@ void orc_moe_combine(const float* yp, const std::uint32_t* pos, const float* mw,
   });
 }
 
+// Gated DeltaNet conv step for `tokens` tokens in sequence (Qwen35Reference::Linear,
+// src/model/qwen35.cpp:180-198): per channel acc = w[kern-1] * x; acc += w[k] * state[k] (k < kern-1),
+// SiLU, the state shifts by the token, then the first l2_channels channels are L2-normalized per head
+// of d channels (cpu::L2Norm with the eps passed). state [kern-1][channels] is updated in place.
+void orc_conv_l2norm(const float* in, float* state, const float* w, float* out, std::size_t tokens,
+                     std::size_t channels, std::size_t kern, std::size_t l2_channels, std::size_t d, float eps) {
+  for (std::size_t t = 0; t < tokens; ++t) {
+    const float* x = in + t * channels;
+    float* o = out + t * channels;
+    for (std::size_t ch = 0; ch < channels; ++ch) {
+      float acc = w[ch * kern + kern - 1] * x[ch];
+      for (std::size_t k = 0; k + 1 < kern; ++k) acc += w[ch * kern + k] * state[k * channels + ch];
+      o[ch] = SiluF(acc);
+    }
+    if (kern > 1) {
+      std::copy(state + channels, state + (kern - 1) * channels, state);
+      std::copy(x, x + channels, state + (kern - 2) * channels);
+    }
+    for (std::size_t h = 0; h * d < l2_channels; ++h) L2NormRow(o + h * d, d, eps);
+  }
+}
+
 }  // extern "C"
