@@ -91,6 +91,10 @@ SIGNATURES: dict[str, list] = {
     "halo_b200_conv_state_advance": [_p, _i, _p, _u32, _u32, _u32],
     "halo_b200_conv_l2norm": [_p, _p, _p, _p, _u32, _u32, _u32, _f, _u32],
     "halo_b200_conv_step": [_p, _p, _p, _p, _u32, _u32],
+    "halo_b200_copy_at": [_p, _i, _p, _p, _u32, _u32, _u32],
+    "halo_b200_copy": [_p, _p, _u32],
+    "halo_b200_f16_rows": [_p, _p, _u32],
+    "halo_b200_scale_silu": [_p, _p, _i, _f, _u32],
     "halo_b200_embed_q8_0_ex": [_p, _u64, _u32, _p, _u32, _u32, _u32, _p, _i, _u32],
 }
 

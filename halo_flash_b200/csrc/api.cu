@@ -308,12 +308,13 @@ int RunHc(HcArgs a, const char* what, halo_b200_stream stream, char* err, size_t
 int RunHcElt(HcEltArgs a, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
   if (a.tokens == 0 || a.h == 0) return Done(cudaSuccess, what, err, errlen);
   REQUIRE(a.a != nullptr && a.b != nullptr, "%s: null pointer", what);
-  REQUIRE(a.op == kHcBroadcast || a.op == kInjectReduce || a.c != nullptr, "%s: null pointer", what);
+  REQUIRE(a.op == kHcBroadcast || a.op == kInjectReduce || a.op == kScaleSilu || a.c != nullptr, "%s: null pointer", what);
   REQUIRE(a.hc >= 1, "%s: hc is 0", what);
   REQUIRE(ValidDType(a.a_dtype) && ValidDType(a.b_dtype), "%s: unknown dtype", what);
   REQUIRE(Aligned(a.a, DTypeSize(a.a_dtype)) && Aligned(a.b, DTypeSize(a.b_dtype)) && Aligned(a.c, a.op == kHcMix ? DTypeSize(a.b_dtype) : 4),
           "%s: pointer not aligned to its element type", what);
-  a.vec = a.h % 8 == 0 && Aligned(a.a, 16) && Aligned(a.b, 16) && (a.op != kHcMix || Aligned(a.c, 16));
+  a.vec = a.h % 8 == 0 && Aligned(a.a, 16) && Aligned(a.b, 16) && (a.op != kHcMix || Aligned(a.c, 16)) &&
+          (a.at_params == nullptr || (a.at_stride * DTypeSize(a.a_dtype)) % 16 == 0);
   const cudaError_t e = LaunchHcElt(a, S(stream));
   if (e == cudaErrorInvalidValue) return Fail(err, errlen, "%s: unsupported dtype combination", what);
   return Done(e, what, err, errlen);
@@ -1294,6 +1295,51 @@ int halo_b200_conv_l2norm(halo_b200_stream stream, const float* in, float* state
 int halo_b200_conv_step(halo_b200_stream stream, const float* in, float* state, const float* w, float* out,
                         uint32_t channels, uint32_t kern, char* err, size_t errlen) {
   return halo_b200_conv_l2norm(stream, in, state, w, out, channels, kern, 0, 0.0f, 128, err, errlen);
+}
+
+
+// ---- row copies and conversions around the attention block ------------------------------------
+int halo_b200_copy_at(halo_b200_stream stream, void* dst, int dst_dtype, const float* src, const uint32_t* params,
+                      uint32_t slot, uint32_t stride, uint32_t n, char* err, size_t errlen) {
+  REQUIRE(n == 0 || params != nullptr, "halo_copy_at: params is null");
+  REQUIRE(dst_dtype == kF32 || dst_dtype == kF16 || dst_dtype == kBF16, "halo_copy_at: unknown dtype");
+  HcEltArgs a{};
+  a.op = kHcBroadcast;
+  a.a = dst;
+  a.a_dtype = dst_dtype;
+  a.b = src;
+  a.b_dtype = kF32;
+  a.hc = 1;
+  a.h = n;
+  a.tokens = 1;
+  a.at_params = params;
+  a.at_slot = slot;
+  a.at_stride = stride;
+  return RunHcElt(a, "halo_copy_at", stream, err, errlen);
+}
+
+int halo_b200_copy(halo_b200_stream stream, float* dst, const float* src, uint32_t n, char* err, size_t errlen) {
+  return halo_b200_broadcast_rows_ex(stream, dst, kF32, src, kF32, 1, n, 1, err, errlen);
+}
+
+int halo_b200_f16_rows(halo_b200_stream stream, const float* x, uint16_t* y, uint32_t n, char* err, size_t errlen) {
+  return halo_b200_broadcast_rows_ex(stream, y, kF16, x, kF32, 1, n, 1, err, errlen);
+}
+
+int halo_b200_scale_silu(halo_b200_stream stream, const float* x, void* y, int y_dtype, float scale, uint32_t n,
+                         char* err, size_t errlen) {
+  REQUIRE(y_dtype == kF32 || y_dtype == kF16, "halo_scale_silu: y must be fp32 or fp16");
+  HcEltArgs a{};
+  a.op = kScaleSilu;
+  a.a = y;
+  a.a_dtype = y_dtype;
+  a.b = x;
+  a.b_dtype = kF32;
+  a.hc = 1;
+  a.h = n;
+  a.tokens = 1;
+  a.alpha = scale;
+  return RunHcElt(a, "halo_scale_silu", stream, err, errlen);
 }
 
 

@@ -396,7 +396,14 @@ __global__ void __launch_bounds__(kBlock) hc_elt_vec_kernel(const HcEltArgs a, c
     if (!ok) return;
     const Oct x = oct_load(static_cast<const BT*>(a.b) + static_cast<size_t>(t) * a.h + j * 8);
     AT* res = static_cast<AT*>(a.a) + static_cast<size_t>(t) * a.hc * a.h + j * 8;
+    if (a.at_params) res += static_cast<size_t>(a.at_params[a.at_slot]) * a.at_stride;  // row append (halo_copy_at)
     for (uint32_t s = 0; s < a.hc; ++s) oct_store(res + static_cast<size_t>(s) * a.h, x);
+  } else if constexpr (OP == kScaleSilu) {
+    if (!ok) return;
+    Oct x = oct_scale(oct_load(static_cast<const BT*>(a.b) + static_cast<size_t>(t) * a.h + j * 8), a.alpha);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) x.p[i] = silu2_f(x.p[i]);
+    oct_store(static_cast<AT*>(a.a) + static_cast<size_t>(t) * a.h + j * 8, x);
   } else if constexpr (OP == kHcMix) {
     if (!ok) return;
     const size_t base = static_cast<size_t>(t) * a.hc * a.h + j * 8;
@@ -429,11 +436,14 @@ template <typename AT, typename BT>
 __global__ void __launch_bounds__(kBlock) hc_elt_scalar_kernel(const HcEltArgs a) {
   pdl_begin();
   const float fhc = static_cast<float>(a.hc);
-  const bool per_token = a.op == kHcMix || a.op == kAxpySigmoidRows;
+  const bool per_token = a.op == kHcMix || a.op == kAxpySigmoidRows || a.op == kScaleSilu;
   const size_t n = static_cast<size_t>(a.tokens) * (per_token ? 1u : a.hc) * a.h;
+  const size_t at = a.at_params ? static_cast<size_t>(a.at_params[a.at_slot]) * a.at_stride : 0;
   for (size_t idx = static_cast<size_t>(blockIdx.x) * kBlock + threadIdx.x; idx < n;
        idx += static_cast<size_t>(gridDim.x) * kBlock) {
-    if (a.op == kHcMix) {
+    if (a.op == kScaleSilu) {
+      static_cast<AT*>(a.a)[idx] = from_f32<AT>(silu_f(__fmul_rn(to_f32(static_cast<const BT*>(a.b)[idx]), a.alpha)));
+    } else if (a.op == kHcMix) {
       const size_t t = idx / a.h, i = idx % a.h;
       float acc = 0.0f;
       for (uint32_t s = 0; s < a.hc; ++s) {
@@ -449,7 +459,7 @@ __global__ void __launch_bounds__(kBlock) hc_elt_scalar_kernel(const HcEltArgs a
       const size_t per = static_cast<size_t>(a.hc) * a.h;
       const size_t t = idx / per, r = idx % per;
       const float x = to_f32(static_cast<const BT*>(a.b)[t * a.h + r % a.h]);
-      AT* p = static_cast<AT*>(a.a) + idx;
+      AT* p = static_cast<AT*>(a.a) + idx + at;
       if (a.op == kHcBroadcast) {
         *p = from_f32<AT>(x);
       } else {
@@ -558,10 +568,11 @@ cudaError_t LaunchHcEltT(const HcEltArgs& a, cudaStream_t s) {
       case kHcCombine: return LaunchKernel(hc_elt_vec_kernel<AT, BT, kHcCombine>, grid, kBlock, 0, s, a, chunks);
       case kHcBroadcast: return LaunchKernel(hc_elt_vec_kernel<AT, BT, kHcBroadcast>, grid, kBlock, 0, s, a, chunks);
       case kHcMix: return LaunchKernel(hc_elt_vec_kernel<AT, BT, kHcMix>, grid, kBlock, 0, s, a, chunks);
+      case kScaleSilu: return LaunchKernel(hc_elt_vec_kernel<AT, BT, kScaleSilu>, grid, kBlock, 0, s, a, chunks);
       default: return LaunchKernel(hc_elt_vec_kernel<AT, BT, kAxpySigmoidRows>, grid, kBlock, 0, s, a, chunks);
     }
   }
-  const bool per_token = a.op == kHcMix || a.op == kAxpySigmoidRows;
+  const bool per_token = a.op == kHcMix || a.op == kAxpySigmoidRows || a.op == kScaleSilu;
   const size_t n = static_cast<size_t>(a.tokens) * (per_token ? 1u : a.hc) * a.h;
   size_t grid = (n + kBlock - 1) / kBlock;
   if (grid > 148u * 32u) grid = 148u * 32u;

@@ -271,6 +271,7 @@ enum HcEltOp : int {
   kAxpySigmoidRows = 3,  // y[t][i] += sigmoid(g[t]) * x[t][i]
   kInjectReduce = 4,  // inject[t][r] = sum_s ipart[(t hc + s) irows + r]
   kHcNormScales = 5,  // scale[row] = 1 / sqrt(mean(res_row^2) + eps)
+  kScaleSilu = 6,     // a[i] = SiLU(b[i] * alpha)
 };
 struct HcEltArgs {
   int op;
@@ -281,6 +282,9 @@ struct HcEltArgs {
   uint32_t hc, h, tokens, irows;
   float eps;
   int vec;
+  const uint32_t* at_params;  // kHcBroadcast: the destination starts at a + at_params[at_slot] * at_stride elements
+  uint32_t at_slot, at_stride;
+  float alpha;
 };
 cudaError_t LaunchHcElt(const HcEltArgs& a, cudaStream_t s);
 

@@ -390,6 +390,34 @@ HANDLER(H_conv_state_advance) {
   return halo_b200_conv_state_advance(c.s, in, IN, state, channels, kern, tokens, c.err, c.errlen);
 }
 
+template <int DT>
+HANDLER(H_copy_at) {
+  auto* dst = r.ptr<void>(); auto* src = r.ptr<const float>(); auto* params = r.ptr<const uint32_t>();
+  const uint32_t slot = r.u32(), stride = r.u32(), n = r.u32();
+  CHECK_ARGS("halo_copy_at");
+  return halo_b200_copy_at(c.s, dst, DT, src, params, slot, stride, n, c.err, c.errlen);
+}
+HANDLER(H_copy) {
+  auto* dst = r.ptr<float>(); auto* src = r.ptr<const float>(); const uint32_t n = r.u32();
+  CHECK_ARGS("halo_copy");
+  return halo_b200_copy(c.s, dst, src, n, c.err, c.errlen);
+}
+HANDLER(H_f16_rows) {
+  auto* x = r.ptr<const float>(); auto* y = r.ptr<uint16_t>(); const uint32_t n = r.u32();
+  CHECK_ARGS("halo_f16_rows");
+  return halo_b200_f16_rows(c.s, x, y, n, c.err, c.errlen);
+}
+HANDLER(H_scale_silu) {
+  auto* x = r.ptr<float>(); const float scale = r.f32(); const uint32_t n = r.u32();
+  CHECK_ARGS("halo_scale_silu");
+  return halo_b200_scale_silu(c.s, x, x, HALO_B200_F32, scale, n, c.err, c.errlen);
+}
+HANDLER(H_scale_silu_h) {
+  auto* x = r.ptr<const float>(); auto* y = r.ptr<uint16_t>(); const float scale = r.f32(); const uint32_t n = r.u32();
+  CHECK_ARGS("halo_scale_silu_h");
+  return halo_b200_scale_silu(c.s, x, y, HALO_B200_F16, scale, n, c.err, c.errlen);
+}
+
 struct Entry {
   const char* name;
   Handler fn;
@@ -468,6 +496,12 @@ const Entry kTable[] = {
     {"halo_conv_l2norm_prefill8_hh", H_conv_l2norm_prefill8<HALO_B200_F16, HALO_B200_F16>},
     {"halo_conv_state_advance", H_conv_state_advance<HALO_B200_F32>},
     {"halo_conv_state_advance_h", H_conv_state_advance<HALO_B200_F16>},
+    {"halo_copy_at", H_copy_at<HALO_B200_F32>},
+    {"halo_copy_at_h", H_copy_at<HALO_B200_F16>},
+    {"halo_copy", H_copy},
+    {"halo_f16_rows", H_f16_rows},
+    {"halo_scale_silu", H_scale_silu},
+    {"halo_scale_silu_h", H_scale_silu_h},
 };
 constexpr size_t kCount = sizeof(kTable) / sizeof(kTable[0]);
 

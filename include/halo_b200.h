@@ -401,6 +401,22 @@ int halo_b200_conv_l2norm(halo_b200_stream stream, const float* in, float* state
 int halo_b200_conv_step(halo_b200_stream stream, const float* in, float* state, const float* w, float* out,
                         uint32_t channels, uint32_t kern, char* err, size_t errlen);
 
+/* ---- row copies and conversions around the attention block --------------------------------------- */
+
+/* halo_copy_at and halo_copy_at_h, src/kernels/core.hip:341-350, 921-927: dst[params[slot] * stride + i] =
+ * src[i] (appends one row to a K/V cache at a position read from device memory); dst fp32, or fp16 / bf16
+ * rounded to nearest even. */
+int halo_b200_copy_at(halo_b200_stream stream, void* dst, int dst_dtype, const float* src, const uint32_t* params,
+                      uint32_t slot, uint32_t stride, uint32_t n, char* err, size_t errlen);
+/* halo_copy, src/kernels/core.hip:352-354. */
+int halo_b200_copy(halo_b200_stream stream, float* dst, const float* src, uint32_t n, char* err, size_t errlen);
+/* halo_f16_rows, src/kernels/core.hip:8157-8161: y[i] = fp16(x[i]). */
+int halo_b200_f16_rows(halo_b200_stream stream, const float* x, uint16_t* y, uint32_t n, char* err, size_t errlen);
+/* halo_scale_silu and halo_scale_silu_h, src/kernels/core.hip:586-598: y = SiLU(x * scale), y fp32 (may be x)
+ * or fp16 (the hyper-connection mixer's silu(down(xn) / hc), src/model/reference.cpp:172-174). */
+int halo_b200_scale_silu(halo_b200_stream stream, const float* x, void* y, int y_dtype, float scale, uint32_t n,
+                         char* err, size_t errlen);
+
 /* ---- launch by kernel name -------------------------------------------------------------- */
 
 /* One launch argument, as rt::Arg (src/rt/device.hpp:35-59): a device pointer (buffer base +

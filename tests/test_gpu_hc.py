@@ -394,3 +394,41 @@ def test_rmsnorm_rows_h_with_inject_partials(dev, orc):
     want_inj = orc.hc_inject(got.reshape(T, -1), iw)
     bound = np.abs(got.reshape(T, 1, -1) * iw[None]).sum(axis=2)
     assert np.all(np.abs(ip.sum(axis=1) - want_inj) <= 1e-5 * bound)
+
+
+def test_row_copies_and_scale_silu_by_name(dev, orc):
+    """halo_copy_at(_h) appending a K row at a position held in device memory (src/engine/qwen35_gpu.cpp's
+    cache writes), halo_copy, halo_f16_rows, halo_scale_silu(_h)."""
+    n, stride, rows = 512, 512, 6
+    src = synth.act("t.cp.src", n)
+    params = np.zeros(16, np.uint32)
+    params[1] = 4  # kHaloPosition
+    b_src, b_par = up(dev, src), up(dev, params)
+    cache = np.full((rows, stride), 7.0, np.float32)
+    b_cache = up(dev, cache)
+    dev.launch(dev.kernel("halo_copy_at"), (2,), (256,), [Arg.Buf(b_cache), Arg.Buf(b_src), Arg.Buf(b_par), Arg.U32(1), Arg.U32(stride), Arg.U32(n)])
+    want = cache.copy()
+    want[4] = src
+    assert np.array_equal(dev.download(b_cache, 0, cache.nbytes, np.float32).reshape(rows, stride), want)
+    cache16 = np.full((rows, stride), 7.0, np.float16)
+    b_c16 = up(dev, cache16)
+    dev.launch(dev.kernel("halo_copy_at_h"), (2,), (256,), [Arg.Buf(b_c16), Arg.Buf(b_src), Arg.Buf(b_par), Arg.U32(1), Arg.U32(stride), Arg.U32(n)])
+    want16 = cache16.copy()
+    want16[4] = src.astype(np.float16)
+    assert np.array_equal(dev.download(b_c16, 0, cache16.nbytes, np.float16).reshape(rows, stride), want16)
+    b_dst = dev.alloc(n * 4)
+    dev.launch(dev.kernel("halo_copy"), (2,), (256,), [Arg.Buf(b_dst), Arg.Buf(b_src), Arg.U32(n)])
+    assert np.array_equal(dev.download(b_dst, 0, n * 4, np.float32), src)
+    b_h = dev.alloc(n * 2)
+    dev.launch(dev.kernel("halo_f16_rows"), (2,), (256,), [Arg.Buf(b_src), Arg.Buf(b_h), Arg.U32(n)])
+    assert np.array_equal(dev.download(b_h, 0, n * 2, np.float16), src.astype(np.float16))
+    # silu(x / hc), in place and as an fp16 copy; odd length takes the scalar kernel
+    for m in (n, 77):
+        x = synth.act("t.cp.x", m) * 4
+        wants = np.array([orc._call("orc_silu", float(np.float32(v) * np.float32(0.25))) for v in x], np.float32)
+        b_x, b_y = up(dev, x), dev.alloc(m * 2)
+        dev.launch(dev.kernel("halo_scale_silu_h"), (1,), (256,), [Arg.Buf(b_x), Arg.Buf(b_y), Arg.F32(0.25), Arg.U32(m)])
+        dev.launch(dev.kernel("halo_scale_silu"), (1,), (256,), [Arg.Buf(b_x), Arg.F32(0.25), Arg.U32(m)])
+        got = dev.download(b_x, 0, m * 4, np.float32)
+        assert np.all(np.abs(got - wants) <= 1e-5 * np.abs(wants) + 1e-30)
+        assert ulps16(dev.download(b_y, 0, m * 2, np.float16).astype(np.float32), wants.astype(np.float16).astype(np.float32), "f16").max() <= 1
