@@ -280,6 +280,46 @@ def kernel_table(torch, shapes, T: int, peaks: dict) -> dict:
     return out
 
 
+def decode_steps(args) -> None:
+    """Decode form of the chain (config 2): B tokens per step, the full 151 936-row Q8_0 table, token and
+    position of every batch entry read from device memory, one captured graph replayed after the host rewrites
+    those 64-byte parameter rows. Prints microseconds per step for B = 1 .. --decode-batch (a latency figure;
+    the step moves only ~5 MB per token, so it is bound by the 230 launches, not by HBM)."""
+    import torch
+    from halo_flash_b200 import chain as chain_mod, synth
+    out = {}
+    for B in sorted({1, 2, 4, args.decode_batch}):
+        if B > args.decode_batch:
+            continue
+        ch = chain_mod.LayerChain(synth.FULL, B, pos0=0, step_params=True)
+        ch.capture()
+        pos = torch.randint(0, synth.FULL.max_pos, (64, B), dtype=torch.int32)
+        tok = torch.randint(0, synth.FULL.vocab, (64, B), dtype=torch.int32)
+        host = torch.zeros(64, B, 16, dtype=torch.int32).pin_memory()
+        host[:, :, 0], host[:, :, 1] = tok, pos
+        for i in range(8):
+            ch.params.copy_(host[i], non_blocking=True)
+            ch.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n = 200
+        e0.record()
+        for i in range(n):
+            ch.params.copy_(host[i % 64], non_blocking=True)  # this step's tokens and positions
+            ch.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / n
+        out[str(B)] = {"us_per_step": round(us, 2), "us_per_launch": round(us / ch.launches_per_step, 3),
+                       "tokens_per_s": round(B / (us * 1e-6), 1)}
+        del ch
+        torch.cuda.empty_cache()
+    print(json.dumps({"metric": "decode_us_per_step_layer_op_chain", "unit": "us", "higher_is_better": False,
+                      "launches_per_step": 230, "vocab": synth.FULL.vocab, "batch": out,
+                      "how": "CUDA events around 200 steps; each step = a 64-byte-per-token parameter upload + one graph replay"}),
+          flush=True)
+
+
 def profile_op(args) -> None:
     """A few eager launches of ONE op over distinct buffer sets and nothing else: the small case a
     profiler capture wants (ncu -k <kernel> -s 2 -c 1 python bench.py --profile-op <op>)."""
@@ -476,10 +516,17 @@ def main() -> None:
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
     ap.add_argument("--no-kernel-table", action="store_true", help="skip the per-kernel timing leg (profiler captures)")
+    ap.add_argument("--no-pdl", action="store_true", help="plain stream-ordered launches (no programmatic dependent launch)")
+    ap.add_argument("--decode-batch", type=int, default=0, help="time the decode form of the chain for batch 1 .. B and exit")
     ap.add_argument("--profile-op", default=None, help="run 6 eager launches of one op and exit (profiler captures): "
                     "add_rmsnorm, add_rmsnorm_q8, l2norm, gated_norm, norm_rope_qk, swiglu_moe, embed, hc_combine_norm, conv_l2norm")
     args = ap.parse_args()
-    if args.profile_op:
+    if args.no_pdl:
+        from halo_flash_b200 import lib
+        lib().tune("pdl", 0)
+    if args.decode_batch:
+        decode_steps(args)
+    elif args.profile_op:
         profile_op(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -85,7 +85,7 @@ class BlockOutputs:
 
 class LayerChain:
     def __init__(self, shapes: Shapes, tokens: int, *, pos0: int = 0, device="cuda:0", dtype=torch.bfloat16,
-                 sets: int = 2, vocab: int | None = None, seed: int = synth.SEED):
+                 sets: int = 2, vocab: int | None = None, seed: int = synth.SEED, step_params: bool = False):
         if not torch.cuda.is_available():
             raise RuntimeError("LayerChain needs a CUDA device: halo_flash_b200 has no CPU path")
         self.s, self.T, self.pos0, self.dtype = shapes, tokens, pos0, dtype
@@ -133,6 +133,14 @@ class LayerChain:
         self.table = table.view(self.vocab, nb * 34)
         del codes, half, table
         self.ids = torch.randint(0, self.vocab, (T,), device=dev, generator=g, dtype=torch.int32)
+        # Decode form: token and position of every batch entry live in device memory, rows 16 uint32 apart
+        # (slot 0 = token, slot 1 = position: src/kernels/step_params.h), so a captured step replays at any
+        # position after the host rewrites this buffer.
+        self.params = None
+        if step_params:
+            self.params = torch.zeros(T, 16, device=dev, dtype=torch.int32)
+            self.params[:, 0] = self.ids
+            self.params[:, 1] = torch.arange(pos0, pos0 + T, device=dev, dtype=torch.int32)
         self.launches_per_step = 2 + 4 * synth.LAYERS + sum(not synth.layer_is_gqa(l) for l in range(synth.LAYERS))
         self._graph: torch.cuda.CUDAGraph | None = None
 
@@ -152,9 +160,13 @@ class LayerChain:
         """Enqueue one full step on the current stream: the embedding gather and the rotation table,
         then per DeltaNet layer 5 launches (add+norm, L2, gated norm, add+norm, SwiGLU shared+routed)
         and per GQA layer 4 (add+norm, Q/K norm+RoPE, add+norm, SwiGLU): 2 + 36*5 + 12*4 = 230."""
-        ops.embed_q8_0(self.table, self.ids, self.s.hidden, self.res, vocab=self.vocab)
         # every GQA layer rotates at the same positions: one cos / sin table per step
-        ops.rope_table(self.rope_tab, self.s.rot, self.s.theta, pos0=self.pos0)
+        if self.params is not None:
+            ops.embed_q8_0(self.table, self.params, self.s.hidden, self.res, id_stride=16, id_slot=0, vocab=self.vocab)
+            ops.rope_table(self.rope_tab, self.s.rot, self.s.theta, params=self.params, pstride=16, slot=1)
+        else:
+            ops.embed_q8_0(self.table, self.ids, self.s.hidden, self.res, vocab=self.vocab)
+            ops.rope_table(self.rope_tab, self.s.rot, self.s.theta, pos0=self.pos0)
         for l in range(synth.LAYERS):
             self.layer(l, self.sets[l % len(self.sets)])
 

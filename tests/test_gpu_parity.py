@@ -815,3 +815,51 @@ def test_dependent_launch_orders_the_chain():
     plain_g, overlapped_g = run(0, True), run(1, True)
     for a, b in zip(plain_g, overlapped_g):
         assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+def test_decode_batch_with_device_step_params(orc):
+    """Config 2: B = 8 decode tokens, the full-size 151 936-row Q8_0 table, token ids and positions up to
+    262 143 read from device memory (rows 16 uint32 apart), one captured chain step replayed after the
+    parameters change. The gather is bit-exact, the rotation matches the oracle at each entry's position."""
+    from halo_flash_b200.chain import LayerChain
+    s, B = synth.FULL, 8
+    ch = LayerChain(s, B, pos0=0, step_params=True)
+    ch.capture()
+    rng = synth.rng("t.decode")
+    table = ch.table.cpu().numpy()
+    for _ in range(3):
+        ids = rng.integers(0, s.vocab, size=B).astype(np.int32)
+        ids[0], ids[1] = 0, s.vocab - 1
+        pos = rng.integers(0, s.max_pos, size=B).astype(np.int32)
+        pos[0], pos[1] = s.max_pos - 1, 0
+        p = np.zeros((B, 16), np.int32)
+        p[:, 0], p[:, 1] = ids, pos
+        q0 = ch.sets[3 % len(ch.sets)].q.clone()  # layer 3 is the first GQA layer
+        ch.params.copy_(torch.from_numpy(p).to(DEV))
+        # the embedding gather alone, then one rotation through the step's table
+        ops.embed_q8_0(ch.table, ch.params, s.hidden, ch.res, id_stride=16, id_slot=0, vocab=s.vocab)
+        want = orc.embed_q8_0_rows(table, ids.view(np.uint32), s.hidden)
+        assert np.array_equal(bits16(ch.res), oracle.bf16_bits(want))
+        ops.rope_table(ch.rope_tab, s.rot, s.theta, params=ch.params, pstride=16, slot=1)
+        q = q0.float()
+        w_q = torch.zeros(s.head_dim, device=DEV)
+        qn = q.clone()
+        ops.norm_rope_qk_table(qn, None, w_q, w_q, s.eps, s.rot, ch.rope_tab, one_plus=True)
+        wantq = orc.rmsnorm_rows(to_f32(q).reshape(-1, s.head_dim).copy(), np.ones(s.head_dim, np.float32), s.eps)
+        wantq = orc.rope_rows(wantq.reshape(B, s.q_heads, s.head_dim), pos.view(np.uint32), s.rot, s.theta)
+        assert_rows_close(to_f32(qn).reshape(-1, s.head_dim), wantq.reshape(-1, s.head_dim), what="decode rope at device positions")
+        # the captured step at these parameters equals the eager step
+        sets0 = [[t.clone() for t in bo.inputs()] for bo in ch.sets]
+        ch.replay()
+        torch.cuda.synchronize()
+        got = (ch.res.clone(), ch.xn.clone(), ch.h_r.clone())
+        for bo, saved in zip(ch.sets, sets0):  # q / k / qk were normalized in place: restore, then run eagerly
+            for t, v in zip(bo.inputs(), saved):
+                t.copy_(v)
+        ch.step()
+        torch.cuda.synchronize()
+        for a, b in zip(got, (ch.res, ch.xn, ch.h_r)):
+            assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+        for bo, saved in zip(ch.sets, sets0):
+            for t, v in zip(bo.inputs(), saved):
+                t.copy_(v)
