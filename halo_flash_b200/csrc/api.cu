@@ -267,6 +267,7 @@ int RunNormRope(NormRopeArgs a, float theta, const char* what, halo_b200_stream 
 std::atomic<int> g_hc_row_level{0};
 std::atomic<int> g_hc_token_k{0};
 std::atomic<int> g_conv_tile{0};
+std::atomic<int> g_conv_staged{1};
 
 int RunHc(HcArgs a, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
   if (a.tokens == 0) return Done(cudaSuccess, what, err, errlen);  // an empty chunk is a no-op
@@ -340,6 +341,7 @@ int RunConv(ConvArgs a, bool advance_only, const char* what, halo_b200_stream st
   if (a.d == 0) a.d = 128;
   a.vec = a.channels % 8 == 0 && Aligned(a.in, 16) && Aligned(a.out, 16) && Aligned(a.w, 16) && Aligned(a.state, 16);
   a.tile = g_conv_tile.load(std::memory_order_relaxed);
+  a.staged = g_conv_staged.load(std::memory_order_relaxed);
   const cudaError_t e = LaunchConvL2norm(a, S(stream));
   if (e == cudaErrorInvalidValue) return Fail(err, errlen, "%s: unsupported (in, out) dtype pair or chunk too long", what);
   return Done(e, what, err, errlen);
@@ -375,6 +377,11 @@ int halo_b200_tune(const char* key, int value) {
   if (std::strcmp(key, "norm_force_general") == 0) {
     if (value != 0 && value != 1) return -1;
     g_norm_force_general.store(value, std::memory_order_relaxed);
+    return 0;
+  }
+  if (std::strcmp(key, "conv_staged") == 0) {
+    if (value != 0 && value != 1) return -1;
+    g_conv_staged.store(value, std::memory_order_relaxed);
     return 0;
   }
   if (std::strcmp(key, "conv_tile") == 0) {
@@ -1340,6 +1347,12 @@ int halo_b200_scale_silu(halo_b200_stream stream, const float* x, void* y, int y
   a.tokens = 1;
   a.alpha = scale;
   return RunHcElt(a, "halo_scale_silu", stream, err, errlen);
+}
+
+
+int halo_b200_conv_stage_timeouts(unsigned int* count, char* err, size_t errlen) {
+  REQUIRE(count != nullptr, "halo_b200_conv_stage_timeouts: count is null");
+  return Done(ReadConvStageTimeouts(count), "halo_b200_conv_stage_timeouts", err, errlen);
 }
 
 

@@ -123,6 +123,172 @@ __global__ void __launch_bounds__(kBlock, kTile >= 8 ? 2 : 3) conv_l2norm_kernel
   else conv_tile<IT, OT, HL, kTile, false>(a, c0, t0, live);
 }
 
+// ---- the same tile with its rows staged in shared memory by bulk asynchronous copies --------------
+// The register form above holds its eleven input rows in registers to keep enough loads in flight
+// (128 registers, 16 resident warps per SM) and then computes with nothing in flight: it measured
+// 36 % issue-active. Here a CTA is persistent: it walks over tiles, and while it computes tile n out of
+// one shared-memory buffer, the copy engine fills the other with tile n + 1 (cp.async.bulk, one 1-D copy
+// of the CTA's channel slice per row, completion counted on an mbarrier per buffer). Bytes in flight
+// cost no registers and the loads of the next tile overlap the arithmetic of this one.
+//
+// Every wait is bounded: kStageSpinLimit polls (seconds), after which the CTA counts a timeout in
+// g_conv_stage_timeouts and all of its threads return together without writing further tiles. Nothing
+// else in the library waits on a barrier object. Rows outside the chunk are not copied; their lanes
+// read zeros (or the conv state).
+__device__ unsigned int g_conv_stage_timeouts = 0;
+constexpr unsigned kStageSpinLimit = 1u << 22;
+
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
+
+template <typename IT, typename OT, unsigned HL, int kTile, int MODE>  // MODE 0: per-thread q/k test, 1: all q/k, 2: none
+__device__ __forceinline__ void conv_stage_compute(const ConvArgs& a, const Oct (&w)[kTaps], const IT* tile,
+                                                   const unsigned row_elems, const unsigned c0, const uint32_t t0,
+                                                   const bool live, const uint32_t first_row, const uint32_t last_row) {
+  const IT* mine = tile + threadIdx.x * 8;
+  // window row j holds input t0 - 3 + j; rows [first_row, last_row) were copied, the rest read as zero
+  auto row = [&](int j) -> Oct {
+    if (static_cast<uint32_t>(j) >= first_row && static_cast<uint32_t>(j) < last_row) {
+      if constexpr (std::is_same_v<IT, float>) {
+        const float4 lo = *reinterpret_cast<const float4*>(mine + static_cast<size_t>(j) * row_elems);
+        const float4 hi = *reinterpret_cast<const float4*>(mine + static_cast<size_t>(j) * row_elems + 4);
+        Oct o;
+        o.p[0] = make_float2(lo.x, lo.y), o.p[1] = make_float2(lo.z, lo.w);
+        o.p[2] = make_float2(hi.x, hi.y), o.p[3] = make_float2(hi.z, hi.w);
+        return o;
+      } else {
+        const uint4 u = *reinterpret_cast<const uint4*>(mine + static_cast<size_t>(j) * row_elems);
+        if constexpr (std::is_same_v<IT, bf16>) return oct_unpack_bf16(u);
+        else return oct_unpack_f16(u);
+      }
+    }
+    return oct_zero();
+  };
+  Oct x0 = row(0), x1 = row(1), x2 = row(2);
+  if (t0 == 0 && live && a.state) {
+    x0 = oct_load(a.state + c0);
+    x1 = oct_load(a.state + static_cast<size_t>(a.channels) + c0);
+    x2 = oct_load(a.state + 2 * static_cast<size_t>(a.channels) + c0);
+  }
+  const bool l2 = MODE == 1 || (MODE == 0 && c0 < a.l2_channels);
+  OT* out = static_cast<OT*>(a.out) + static_cast<size_t>(t0) * a.channels + c0;
+#pragma unroll
+  for (int t = 0; t < kTile; ++t, out += a.channels) {
+    const Oct x3 = row(t + 3);
+    Oct v = conv4(w, x0, x1, x2, x3);
+    x0 = x1, x1 = x2, x2 = x3;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v.p[i] = silu2_f(v.p[i]);
+    if constexpr (MODE != 2 && HL > 0) {
+      const float2 acc = oct_sumsq(v, make_float2(0.0f, 0.0f));
+      float ss = acc.x + acc.y;
+#pragma unroll
+      for (unsigned of = 16; of > 0; of >>= 1)
+        if (of < HL) ss += __shfl_xor_sync(kFullMask, ss, of);
+      if (l2) v = oct_scale(v, rsqrtf(ss + a.eps));
+    }
+    if (live && t0 + t < a.tokens) oct_store(out, v);
+  }
+}
+
+// Rows of tile (slice, by) wanted by the window: [first_row, last_row) of the kTile + 3 window rows.
+template <int kTile>
+__device__ __forceinline__ void tile_rows(uint32_t t0, uint32_t tokens, uint32_t* first_row, uint32_t* last_row) {
+  *first_row = t0 >= 3 ? 0u : 3u - t0;
+  const uint32_t avail = tokens + 3u - t0;  // window rows before the chunk's end
+  *last_row = avail < static_cast<uint32_t>(kTile + 3) ? avail : static_cast<uint32_t>(kTile + 3);
+}
+
+// grid.x = a multiple of `slices` (CTA c always works on channel slice c % slices, so its taps are loaded
+// once); CTA c takes the token tiles c / slices, c / slices + grid.x / slices, ...
+template <typename IT, typename OT, unsigned HL, int kTile>
+__global__ void __launch_bounds__(kBlock, 2) conv_l2norm_staged_kernel(const ConvArgs a, const uint32_t slices,
+                                                                    const uint32_t token_tiles) {
+  pdl_begin();
+  extern __shared__ __align__(128) uint8_t conv_smem[];
+  __shared__ __align__(8) unsigned long long bars[2];
+  const unsigned octs = a.channels >> 3;
+  const uint32_t slice = blockIdx.x % slices, lane_of_slice = blockIdx.x / slices, stride = gridDim.x / slices;
+  const unsigned oc0 = slice * kBlock;                           // first channel octet of the CTA's slice
+  const unsigned slice_octs = min(static_cast<unsigned>(kBlock), octs - oc0);
+  constexpr unsigned row_elems = kBlock * 8;                     // elements between two staged rows
+  constexpr unsigned buf_elems = (kTile + 3) * row_elems;
+  const bool live = threadIdx.x < slice_octs;
+  const unsigned c0 = (oc0 + (live ? threadIdx.x : 0u)) << 3;
+  IT* bufs = reinterpret_cast<IT*>(conv_smem);
+  const unsigned row_bytes = slice_octs * 8u * static_cast<unsigned>(sizeof(IT));  // a multiple of 16
+
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&bars[0])) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&bars[1])) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  // thread 0 asks the copy engine for the rows of token tile `by` into buffer `b`
+  auto request = [&](uint32_t by, unsigned b) {
+    uint32_t first_row, last_row;
+    tile_rows<kTile>(by * kTile, a.tokens, &first_row, &last_row);
+    const unsigned bar = smem_addr(&bars[b]);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((last_row - first_row) * row_bytes) : "memory");
+    const IT* src = static_cast<const IT*>(a.in) + static_cast<size_t>(by * kTile + first_row - 3u) * a.channels +
+                    (static_cast<size_t>(oc0) << 3);
+    unsigned dst = smem_addr(bufs + b * buf_elems + first_row * row_elems);
+    for (uint32_t j = first_row; j < last_row; ++j, src += a.channels, dst += row_elems * sizeof(IT))
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(dst), "l"(src), "r"(row_bytes), "r"(bar) : "memory");
+  };
+
+  uint32_t by = lane_of_slice;
+  if (by >= token_tiles) return;  // uniform: the whole CTA has no tile
+  if (threadIdx.x == 0) request(by, 0);
+
+  // taps: w[ch][4] -> four octets, tap k of the thread's 8 channels; loaded once, while the first tile arrives
+  Oct w[kTaps];
+  {
+    float4 wl[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+      wl[c] = live ? __ldg(reinterpret_cast<const float4*>(a.w + static_cast<size_t>(c0 + c) * kTaps))
+                   : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      w[0].p[i] = make_float2(wl[2 * i].x, wl[2 * i + 1].x);
+      w[1].p[i] = make_float2(wl[2 * i].y, wl[2 * i + 1].y);
+      w[2].p[i] = make_float2(wl[2 * i].z, wl[2 * i + 1].z);
+      w[3].p[i] = make_float2(wl[2 * i].w, wl[2 * i + 1].w);
+    }
+  }
+  const unsigned slice_lo = oc0 << 3, slice_hi = (oc0 + slice_octs) << 3;
+  const int mode = (HL == 0 || slice_lo >= a.l2_channels) ? 2 : (slice_hi <= a.l2_channels ? 1 : 0);
+
+  for (uint32_t n = 0; by < token_tiles; ++n, by += stride) {
+    const unsigned b = n & 1u;
+    // the other buffer was last read in iteration n - 1, which ended with a CTA barrier: refill it now
+    if (threadIdx.x == 0 && by + stride < token_tiles) request(by + stride, b ^ 1u);
+    // wait for this buffer's bytes: its (n / 2)-th use, so phase parity (n / 2) & 1; bounded polls
+    const unsigned bar = smem_addr(&bars[b]), parity = (n >> 1) & 1u;
+    unsigned done = 0;
+    for (unsigned spin = 0; spin < kStageSpinLimit && !done; ++spin) {
+      asm volatile(
+          "{\n.reg .pred p;\n"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+          "selp.u32 %0, 1, 0, p;\n}"
+          : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    }
+    if (!__syncthreads_and(static_cast<int>(done))) {  // never seen; all threads leave together
+      if (threadIdx.x == 0) atomicAdd(&g_conv_stage_timeouts, 1u);
+      return;
+    }
+    uint32_t first_row, last_row;
+    tile_rows<kTile>(by * kTile, a.tokens, &first_row, &last_row);
+    const IT* tile = bufs + b * buf_elems;
+    if (mode == 2) conv_stage_compute<IT, OT, HL, kTile, 2>(a, w, tile, row_elems, c0, by * kTile, live, first_row, last_row);
+    else if (mode == 1) conv_stage_compute<IT, OT, HL, kTile, 1>(a, w, tile, row_elems, c0, by * kTile, live, first_row, last_row);
+    else conv_stage_compute<IT, OT, HL, kTile, 0>(a, w, tile, row_elems, c0, by * kTile, live, first_row, last_row);
+    __syncthreads();  // every thread is done reading this buffer before it is refilled
+  }
+}
+
 // Any kernel length, head size and alignment: one CTA per (head, token), one channel per thread.
 template <typename IT, typename OT>
 __global__ void __launch_bounds__(1024) conv_l2norm_scalar_kernel(const ConvArgs a) {
@@ -193,11 +359,47 @@ cudaError_t LaunchConvTile(const ConvArgs& a, unsigned head_octs, cudaStream_t s
   }
 }
 
+template <typename IT, typename OT, unsigned HL>
+cudaError_t LaunchConvStagedHL(const ConvArgs& a, unsigned grid, uint32_t slices, uint32_t token_tiles, size_t smem,
+                               cudaStream_t s) {
+  auto kernel = conv_l2norm_staged_kernel<IT, OT, HL, 8>;
+  // more than 48 KB of dynamic shared memory has to be asked for
+  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  return LaunchKernel(kernel, grid, kBlock, smem, s, a, slices, token_tiles);
+}
+
+// Two persistent CTAs per SM (the two tile buffers of a CTA take 88 KB for 16-bit inputs, 176 KB for
+// fp32, where one CTA per SM fits), rounded to a multiple of the number of channel slices.
+template <typename IT, typename OT>
+cudaError_t LaunchConvStaged(const ConvArgs& a, unsigned head_octs, cudaStream_t s) {
+  const uint32_t slices = (a.channels / 8 + kBlock - 1) / kBlock, token_tiles = (a.tokens + 7) / 8;
+  const size_t smem = 2 * static_cast<size_t>(8 + 3) * kBlock * 8 * sizeof(IT);
+  const unsigned resident = 148u * (sizeof(IT) == 2 ? 2u : 1u);
+  if (slices > resident) return cudaErrorNotSupported;  // wider than the persistent grid: the register form runs
+  unsigned per_slice = resident / slices;
+  if (per_slice > token_tiles) per_slice = token_tiles;
+  const unsigned grid = per_slice * slices;
+  switch (a.l2_channels ? head_octs : 0u) {
+    case 0: return LaunchConvStagedHL<IT, OT, 0>(a, grid, slices, token_tiles, smem, s);
+    case 1: return LaunchConvStagedHL<IT, OT, 1>(a, grid, slices, token_tiles, smem, s);
+    case 2: return LaunchConvStagedHL<IT, OT, 2>(a, grid, slices, token_tiles, smem, s);
+    case 4: return LaunchConvStagedHL<IT, OT, 4>(a, grid, slices, token_tiles, smem, s);
+    case 8: return LaunchConvStagedHL<IT, OT, 8>(a, grid, slices, token_tiles, smem, s);
+    case 16: return LaunchConvStagedHL<IT, OT, 16>(a, grid, slices, token_tiles, smem, s);
+    default: return LaunchConvStagedHL<IT, OT, 32>(a, grid, slices, token_tiles, smem, s);
+  }
+}
+
 template <typename IT, typename OT>
 cudaError_t LaunchConvT(const ConvArgs& a, cudaStream_t s) {
   const unsigned head_octs = a.d / 8;
   const bool head_pow2 = head_octs >= 1 && head_octs <= 32 && (head_octs & (head_octs - 1)) == 0 && a.d % 8 == 0;
   if (a.vec && a.kern == kTaps && (a.l2_channels == 0 || head_pow2)) {
+    if (a.staged) {
+      const cudaError_t e = LaunchConvStaged<IT, OT>(a, head_octs, s);
+      if (e != cudaErrorNotSupported) return e;
+    }
     return a.tile == 4 ? LaunchConvTile<IT, OT, 4>(a, head_octs, s) : LaunchConvTile<IT, OT, 8>(a, head_octs, s);
   }
   if (a.d == 0 || a.d > 1024 || a.tokens > 65535u) return cudaErrorInvalidValue;
@@ -216,6 +418,10 @@ cudaError_t LaunchConvL2norm(const ConvArgs& a, cudaStream_t s) {
   if (i == kBF16 && o == kBF16) return LaunchConvT<bf16, bf16>(a, s);
   if (i == kBF16 && o == kF32) return LaunchConvT<bf16, float>(a, s);
   return cudaErrorInvalidValue;
+}
+
+cudaError_t ReadConvStageTimeouts(unsigned int* out) {
+  return cudaMemcpyFromSymbol(out, g_conv_stage_timeouts, sizeof(unsigned int));
 }
 
 cudaError_t LaunchConvStateAdvance(const ConvArgs& a, cudaStream_t s) {

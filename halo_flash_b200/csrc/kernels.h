@@ -299,8 +299,10 @@ struct ConvArgs {
   float eps;
   int in_dtype, out_dtype;
   int vec;
-  int tile;  // tuning: tokens per thread, 4 or 8 (0 = built-in choice)
+  int tile;    // tuning: tokens per thread of the register form, 4 or 8 (0 = built-in choice)
+  int staged;  // 1 = rows staged in shared memory by bulk asynchronous copies; 0 = rows held in registers
 };
+cudaError_t ReadConvStageTimeouts(unsigned int* out);
 cudaError_t LaunchConvL2norm(const ConvArgs& a, cudaStream_t s);
 cudaError_t LaunchConvStateAdvance(const ConvArgs& a, cudaStream_t s);
 

@@ -401,6 +401,11 @@ int halo_b200_conv_l2norm(halo_b200_stream stream, const float* in, float* state
 int halo_b200_conv_step(halo_b200_stream stream, const float* in, float* state, const float* w, float* out,
                         uint32_t channels, uint32_t kern, char* err, size_t errlen);
 
+/* No counterpart in the reference. The conv kernel stages its input rows in shared memory with asynchronous
+ * bulk copies and waits for them on a barrier object with a bounded number of polls; a CTA whose wait ran out
+ * (never observed) returns without writing and is counted. Reads the count (this call synchronizes). */
+int halo_b200_conv_stage_timeouts(unsigned int* count, char* err, size_t errlen);
+
 /* ---- row copies and conversions around the attention block --------------------------------------- */
 
 /* halo_copy_at and halo_copy_at_h, src/kernels/core.hip:341-350, 921-927: dst[params[slot] * stride + i] =
@@ -448,6 +453,9 @@ const char* halo_b200_kernel_name(size_t index);
  * "gated_rows_per_group" (1 or 2 rows in flight per thread group of the gated norm on short rows; 0 = built-in),
  * "rope_rows_per_group" (2 or 4 rows in flight per thread group of the fused norm + RoPE kernel; 0 = built-in),
  * "hc_row_level" (1 = the hyper-connection combine + norm always runs one (token, stream) row per thread group),
+ * "conv_staged" (1, the default = the conv kernel stages rows in shared memory by bulk asynchronous copies; 0 = rows in registers),
+ * "conv_tile" (tokens per thread of the register form of the conv kernel: 4 or 8; 0 = built-in), "hc_token_k" (2 = two
+ * chunks per stream per thread in the token-level hyper-connection kernel where they fit),
  * "pdl" (1, the default = kernels are launched with programmatic stream serialization, so a kernel is scheduled
  * while its predecessor in the stream drains and waits on the device for it to complete; 0 = plain launches).
  * Returns 0, or -1 for an unknown key or value. */

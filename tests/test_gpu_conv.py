@@ -13,7 +13,7 @@ import torch
 
 import oracle
 from conftest import assert_rows_close
-from halo_flash_b200 import HaloError, ops, synth
+from halo_flash_b200 import HaloError, lib, ops, synth
 from halo_flash_b200.device import Arg, Device
 
 pytestmark = pytest.mark.gpu
@@ -61,12 +61,18 @@ def check(got, want, d, odt, what):
                                            (29, 8192, 4096, 128, 4), (5, 384, 256, 128, 4), (6, 512, 0, 128, 4),
                                            (9, 200, 100, 50, 4), (6, 256, 128, 64, 3), (4, 256, 128, 64, 2), (3, 128, 64, 64, 1)])
 @pytest.mark.parametrize("idt,odt", [("f32", "f32"), ("f16", "f32"), ("f16", "f16"), ("bf16", "bf16"), ("bf16", "f32")])
-def test_conv_l2norm(orc, T, C, l2, d, kern, idt, odt):
+@pytest.mark.parametrize("staged", [1, 0])
+def test_conv_l2norm(orc, T, C, l2, d, kern, idt, odt, staged):
+    """staged: rows brought into shared memory by bulk asynchronous copies (the default), or held in registers."""
     x, state, w = make(f"t.conv.{T}.{C}.{kern}", T, C, kern)
     x = rounded(x, idt)
     out = torch.full((T, C), float("nan"), device=DEV, dtype=TDT[odt])
     d_state = to_dev(state) if kern > 1 else None
-    ops.conv_l2norm(to_dev(x, idt), d_state, to_dev(w), out, l2_channels=l2, d=d, eps=EPS)
+    lib().tune("conv_staged", staged)
+    try:
+        ops.conv_l2norm(to_dev(x, idt), d_state, to_dev(w), out, l2_channels=l2, d=d, eps=EPS)
+    finally:
+        lib().tune("conv_staged", 1)
     st = state.copy()
     want = orc.conv_l2norm(x, st, w, l2, d, EPS)
     check(out.float().cpu().numpy(), want, d if l2 else C, odt, "conv + SiLU + L2")
@@ -92,6 +98,25 @@ def test_chunk_in_pieces_equals_chunk_at_once(orc):
         parts.append(piece)
     assert torch.equal(torch.cat(parts).view(torch.int16), whole.view(torch.int16))
     assert np.array_equal(st.cpu().numpy(), oracle.round_bf16(x)[-3:])
+    # the register form of the kernel computes the same bits as the staged form
+    lib().tune("conv_staged", 0)
+    try:
+        regs = torch.empty(T, C, device=DEV, dtype=torch.bfloat16)
+        ops.conv_l2norm(dx, to_dev(state), dw, regs, l2_channels=l2, d=d, eps=EPS)
+    finally:
+        lib().tune("conv_staged", 1)
+    assert torch.equal(regs.view(torch.int16), whole.view(torch.int16))
+
+
+def test_no_staging_wait_ever_ran_out():
+    """The staged kernel's barrier wait is bounded; a wait that runs out is counted. After the tests above: zero."""
+    import ctypes as C
+    n = C.c_uint(123)
+    err = C.create_string_buffer(256)
+    f = lib().cdll.halo_b200_conv_stage_timeouts
+    f.restype, f.argtypes = C.c_int, [C.POINTER(C.c_uint), C.c_char_p, C.c_size_t]
+    assert f(C.byref(n), err, len(err)) == 0, err.value
+    assert n.value == 0
 
 
 def test_conv_rejects_bad_arguments():
