@@ -95,6 +95,11 @@ SIGNATURES: dict[str, list] = {
     "halo_b200_copy": [_p, _p, _u32],
     "halo_b200_f16_rows": [_p, _p, _u32],
     "halo_b200_scale_silu": [_p, _p, _i, _f, _u32],
+    "halo_b200_moe_combine_grouped": [_p, _p, _p, _p, _u32, _u32, _u32],
+    "halo_b200_moe_combine_shared": [_p, _p, _p, _p, _p, _p, _u32, _u32, _u32],
+    "halo_b200_moe_combine": [_p, _p, _p, _u32, _u32],
+    "halo_b200_axpy_slot": [_p, _p, _p, _u32, _u32],
+    "halo_b200_moe_combine_ex": [_p, _i, _p, _p, _p, _i, _p, _p, _i, _u32, _u32, _u32],
     "halo_b200_embed_q8_0_ex": [_p, _u64, _u32, _p, _u32, _u32, _u32, _p, _i, _u32],
 }
 

@@ -347,6 +347,22 @@ int RunConv(ConvArgs a, bool advance_only, const char* what, halo_b200_stream st
   return Done(e, what, err, errlen);
 }
 
+
+int RunMoeCombine(MoeCombineArgs a, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+  if (a.tokens == 0 || a.n == 0) return Done(cudaSuccess, what, err, errlen);
+  REQUIRE(a.yp && a.mw && a.out, "%s: null pointer", what);
+  REQUIRE((a.sx == nullptr) == (a.sg == nullptr), "%s: sx and sg go together", what);
+  REQUIRE(ValidDType(a.yp_dtype) && ValidDType(a.out_dtype), "%s: unknown dtype", what);
+  const size_t ys = DTypeSize(a.yp_dtype), os = DTypeSize(a.out_dtype);
+  REQUIRE(Aligned(a.yp, ys) && Aligned(a.out, os) && Aligned(a.mw, 4) && Aligned(a.pos, 4) && Aligned(a.sg, 4) &&
+              Aligned(a.sx, a.sx_is_f32 ? 4 : ys),
+          "%s: pointer not aligned to its element type", what);
+  a.vec = a.n % 8 == 0 && Aligned(a.yp, 16) && Aligned(a.out, 16) && Aligned(a.sx, 16);
+  const cudaError_t e = LaunchMoeCombine(a, S(stream));
+  if (e == cudaErrorInvalidValue) return Fail(err, errlen, "%s: unsupported (yp, out) dtype pair", what);
+  return Done(e, what, err, errlen);
+}
+
 }  // namespace
 
 namespace halo_b200 {
@@ -1353,6 +1369,62 @@ int halo_b200_scale_silu(halo_b200_stream stream, const float* x, void* y, int y
 int halo_b200_conv_stage_timeouts(unsigned int* count, char* err, size_t errlen) {
   REQUIRE(count != nullptr, "halo_b200_conv_stage_timeouts: count is null");
   return Done(ReadConvStageTimeouts(count), "halo_b200_conv_stage_timeouts", err, errlen);
+}
+
+
+// ---- MoE combine -----------------------------------------------------------------------------------
+int halo_b200_moe_combine_ex(halo_b200_stream stream, const void* yp, int yp_dtype, const uint32_t* pos, const float* mw,
+                             const void* sx, int sx_dtype, const float* sg, void* out, int out_dtype, uint32_t k,
+                             uint32_t n, uint32_t tokens, char* err, size_t errlen) {
+  REQUIRE(sx == nullptr || sx_dtype == kF32 || sx_dtype == yp_dtype, "halo_b200_moe_combine_ex: sx must be fp32 or of yp's type");
+  MoeCombineArgs a{};
+  a.yp = yp;
+  a.yp_dtype = yp_dtype;
+  a.pos = pos;
+  a.mw = mw;
+  a.sx = sx;
+  a.sx_is_f32 = sx_dtype == kF32;
+  a.sg = sg;
+  a.out = out;
+  a.out_dtype = out_dtype;
+  a.k = k;
+  a.n = n;
+  a.tokens = tokens;
+  return RunMoeCombine(a, "halo_moe_combine", stream, err, errlen);
+}
+
+int halo_b200_moe_combine_grouped(halo_b200_stream stream, const uint16_t* yp, const uint32_t* pos, const float* w,
+                                  float* out, uint32_t k, uint32_t n, uint32_t tokens, char* err, size_t errlen) {
+  return halo_b200_moe_combine_ex(stream, yp, kF16, pos, w, nullptr, kF32, nullptr, out, kF32, k, n, tokens, err, errlen);
+}
+
+int halo_b200_moe_combine_shared(halo_b200_stream stream, const uint16_t* yp, const uint32_t* pos, const float* w,
+                                 const float* x, const float* g, float* out, uint32_t k, uint32_t n, uint32_t tokens,
+                                 char* err, size_t errlen) {
+  REQUIRE(tokens == 0 || (x && g), "halo_moe_combine_shared: null pointer");
+  return halo_b200_moe_combine_ex(stream, yp, kF16, pos, w, x, kF32, g, out, kF32, k, n, tokens, err, errlen);
+}
+
+int halo_b200_moe_combine(halo_b200_stream stream, const float* part, const float* weights, float* out, uint32_t slots,
+                          uint32_t n, char* err, size_t errlen) {
+  return halo_b200_moe_combine_ex(stream, part, kF32, nullptr, weights, nullptr, kF32, nullptr, out, kF32, slots, n, 1, err,
+                                  errlen);
+}
+
+int halo_b200_axpy_slot(halo_b200_stream stream, float* y, const float* x, const float* weights, uint32_t slot,
+                        uint32_t n, char* err, size_t errlen) {
+  REQUIRE(n == 0 || weights != nullptr, "halo_axpy_slot: weights is null");
+  MoeCombineArgs a{};
+  a.yp = x;
+  a.yp_dtype = kF32;
+  a.mw = weights ? weights + slot : nullptr;
+  a.out = y;
+  a.out_dtype = kF32;
+  a.k = 1;
+  a.n = n;
+  a.tokens = 1;
+  a.accumulate = 1;
+  return RunMoeCombine(a, "halo_axpy_slot", stream, err, errlen);
 }
 
 

@@ -579,7 +579,92 @@ cudaError_t LaunchHcEltT(const HcEltArgs& a, cudaStream_t s) {
   return LaunchKernel(hc_elt_scalar_kernel<AT, BT>, static_cast<unsigned>(grid), kBlock, 0, s, a);
 }
 
+// ---- MoE combine -------------------------------------------------------------------------------------
+// One thread per octet of a token's n columns; the k expert rows of the token are requested together (up to
+// 16 loads in flight per thread), then summed in slot order with the product and the sum rounded
+// separately, then the gated shared expert is added (src/model/reference.cpp:558-578).
+template <typename YT, typename OT>
+__global__ void __launch_bounds__(kBlock) moe_combine_kernel(const MoeCombineArgs a, const uint32_t chunks) {
+  pdl_begin();
+  __shared__ float gate;
+  const uint32_t t = blockIdx.x / chunks, chunk = blockIdx.x - t * chunks;
+  const unsigned j = chunk * kBlock + threadIdx.x;
+  if (a.sx) {
+    if (threadIdx.x == 0) gate = sigmoid_ieee(a.sg[t]);
+    __syncthreads();
+  }
+  if (j >= (a.n >> 3)) return;
+  const YT* yp = static_cast<const YT*>(a.yp) + j * 8;
+  const float* ww = a.mw + static_cast<size_t>(t) * a.k;
+  Oct acc = oct_zero();
+  OT* out = static_cast<OT*>(a.out) + static_cast<size_t>(t) * a.n + j * 8;
+  if (a.accumulate) acc = oct_load(out);
+  for (uint32_t s0 = 0; s0 < a.k; s0 += 16) {
+    Raw<YT> rows[16];
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      const uint32_t s = s0 + u;
+      if (s < a.k) {
+        const size_t r = a.pos ? a.pos[static_cast<size_t>(t) * a.k + s] : static_cast<size_t>(t) * a.k + s;
+        rows[u] = raw_load(yp + r * a.n);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 16; ++u)
+      if (s0 + u < a.k) acc = oct_axpy_unfused(acc, raw_unpack(rows[u]), ww[s0 + u]);
+  }
+  if (a.sx) {
+    const size_t off = static_cast<size_t>(t) * a.n + j * 8;
+    const Oct x = a.sx_is_f32 ? oct_load(static_cast<const float*>(a.sx) + off) : oct_load(static_cast<const YT*>(a.sx) + off);
+    acc = oct_axpy_unfused(acc, x, gate);
+  }
+  oct_store(out, acc);
+}
+
+template <typename YT, typename OT>
+__global__ void __launch_bounds__(kBlock) moe_combine_scalar_kernel(const MoeCombineArgs a) {
+  pdl_begin();
+  const size_t total = static_cast<size_t>(a.tokens) * a.n;
+  for (size_t idx = static_cast<size_t>(blockIdx.x) * kBlock + threadIdx.x; idx < total;
+       idx += static_cast<size_t>(gridDim.x) * kBlock) {
+    const size_t t = idx / a.n, i = idx % a.n;
+    OT* out = static_cast<OT*>(a.out) + idx;
+    float acc = a.accumulate ? to_f32(*out) : 0.0f;
+    for (uint32_t s = 0; s < a.k; ++s) {
+      const size_t r = a.pos ? a.pos[t * a.k + s] : t * a.k + s;
+      acc = __fadd_rn(acc, __fmul_rn(a.mw[t * a.k + s], to_f32(static_cast<const YT*>(a.yp)[r * a.n + i])));
+    }
+    if (a.sx) {
+      const float x = a.sx_is_f32 ? static_cast<const float*>(a.sx)[idx] : to_f32(static_cast<const YT*>(a.sx)[idx]);
+      acc = __fadd_rn(acc, __fmul_rn(sigmoid_ieee(a.sg[t]), x));
+    }
+    *out = from_f32<OT>(acc);
+  }
+}
+
+template <typename YT, typename OT>
+cudaError_t LaunchMoeCombineT(const MoeCombineArgs& a, cudaStream_t s) {
+  if (a.vec) {
+    const uint32_t chunks = (a.n / 8 + kBlock - 1) / kBlock;
+    return LaunchKernel(moe_combine_kernel<YT, OT>, a.tokens * chunks, kBlock, 0, s, a, chunks);
+  }
+  size_t grid = (static_cast<size_t>(a.tokens) * a.n + kBlock - 1) / kBlock;
+  if (grid > 148u * 32u) grid = 148u * 32u;
+  return LaunchKernel(moe_combine_scalar_kernel<YT, OT>, static_cast<unsigned>(grid), kBlock, 0, s, a);
+}
+
 }  // namespace
+
+cudaError_t LaunchMoeCombine(const MoeCombineArgs& a, cudaStream_t s) {
+  if (a.tokens == 0 || a.n == 0) return cudaSuccess;
+  const int y = a.yp_dtype, o = a.out_dtype;
+  if (y == kF16 && o == kF32) return LaunchMoeCombineT<f16, float>(a, s);
+  if (y == kF32 && o == kF32) return LaunchMoeCombineT<float, float>(a, s);
+  if (y == kBF16 && o == kBF16) return LaunchMoeCombineT<bf16, bf16>(a, s);
+  if (y == kBF16 && o == kF32) return LaunchMoeCombineT<bf16, float>(a, s);
+  if (y == kF16 && o == kF16) return LaunchMoeCombineT<f16, f16>(a, s);
+  return cudaErrorInvalidValue;
+}
 
 // (res, out, y) type triples: the reference's (fp32 | fp16 | bf16 residual, fp32 block output and
 // fp32 y) and the all-16-bit forms of a bf16 / fp16 engine.

@@ -307,6 +307,24 @@ cudaError_t LaunchConvL2norm(const ConvArgs& a, cudaStream_t s);
 cudaError_t LaunchConvStateAdvance(const ConvArgs& a, cudaStream_t s);
 
 
+// out[t] = sum over k slots, in order, of mw[t k + s] * yp[pos[t k + s]] (+ sigmoid(sg[t]) * sx[t]): the routed
+// experts' outputs combined per token, optionally with the gated shared expert (src/kernels/core.hip:2372-2380,
+// 5456-5480). pos == NULL: slot s of token t is row t k + s of yp.
+struct MoeCombineArgs {
+  const void* yp;       // [rows][n], yp_dtype
+  const uint32_t* pos;  // [tokens][k] or NULL
+  const float* mw;      // [tokens][k]
+  const void* sx;       // [tokens][n] shared-expert output (fp32, or yp_dtype when sx_is_f32 == 0); NULL: none
+  const float* sg;      // [tokens] gate logits
+  void* out;            // [tokens][n], out_dtype
+  uint32_t k, n, tokens;
+  int yp_dtype, out_dtype, sx_is_f32;
+  int accumulate;       // 1: out += (halo_axpy_slot), 0: out =
+  int vec;
+};
+cudaError_t LaunchMoeCombine(const MoeCombineArgs& a, cudaStream_t s);
+
+
 }  // namespace halo_b200
 
 #endif  // HALO_B200_KERNELS_H_

@@ -418,6 +418,32 @@ HANDLER(H_scale_silu_h) {
   return halo_b200_scale_silu(c.s, x, y, HALO_B200_F16, scale, n, c.err, c.errlen);
 }
 
+HANDLER(H_moe_combine_grouped) {
+  auto* yp = r.ptr<const uint16_t>(); auto* pos = r.ptr<const uint32_t>(); auto* w = r.ptr<const float>();
+  auto* out = r.ptr<float>(); const uint32_t k = r.u32(), n = r.u32();
+  CHECK_ARGS("halo_moe_combine_grouped");
+  return halo_b200_moe_combine_grouped(c.s, yp, pos, w, out, k, n, c.grid[1], c.err, c.errlen);
+}
+HANDLER(H_moe_combine_shared) {
+  auto* yp = r.ptr<const uint16_t>(); auto* pos = r.ptr<const uint32_t>(); auto* w = r.ptr<const float>();
+  auto* x = r.ptr<const float>(); auto* g = r.ptr<const float>(); auto* out = r.ptr<float>();
+  const uint32_t k = r.u32(), n = r.u32();
+  CHECK_ARGS("halo_moe_combine_shared");
+  return halo_b200_moe_combine_shared(c.s, yp, pos, w, x, g, out, k, n, c.grid[1], c.err, c.errlen);
+}
+HANDLER(H_moe_combine) {
+  auto* part = r.ptr<const float>(); auto* w = r.ptr<const float>(); auto* out = r.ptr<float>();
+  const uint32_t slots = r.u32(), n = r.u32();
+  CHECK_ARGS("halo_moe_combine");
+  return halo_b200_moe_combine(c.s, part, w, out, slots, n, c.err, c.errlen);
+}
+HANDLER(H_axpy_slot) {
+  auto* y = r.ptr<float>(); auto* x = r.ptr<const float>(); auto* w = r.ptr<const float>();
+  const uint32_t slot = r.u32(), n = r.u32();
+  CHECK_ARGS("halo_axpy_slot");
+  return halo_b200_axpy_slot(c.s, y, x, w, slot, n, c.err, c.errlen);
+}
+
 struct Entry {
   const char* name;
   Handler fn;
@@ -502,6 +528,11 @@ const Entry kTable[] = {
     {"halo_f16_rows", H_f16_rows},
     {"halo_scale_silu", H_scale_silu},
     {"halo_scale_silu_h", H_scale_silu_h},
+    {"halo_moe_combine_grouped", H_moe_combine_grouped},
+    {"halo_moe_combine_shared", H_moe_combine_shared},
+    {"halo_moe_combine", H_moe_combine},
+    {"halo_moe_combine_u", H_moe_combine},
+    {"halo_axpy_slot", H_axpy_slot},
 };
 constexpr size_t kCount = sizeof(kTable) / sizeof(kTable[0]);
 

@@ -301,3 +301,16 @@ def conv_state_advance(x, state):
     tokens, channels = x.shape
     lib().call("conv_state_advance", _stream(), _p(x), _code(x), _p(state), channels, state.shape[0] + 1, tokens)
     return state
+
+
+# ---- MoE combine ----------------------------------------------------------------------------------
+def moe_combine(yp, pos, mw, out, *, sx=None, sg=None):
+    """out [T, n] = sum over the k slots of mw[t, s] * yp[pos[t, s]] (+ sigmoid(sg[t]) * sx[t]).
+    pos None: slot s of token t is row t*k + s of yp."""
+    _chk(yp, "yp", _ACT), _chk(pos, "pos", (torch.int32, torch.uint32)), _chk(mw, "mw", (torch.float32,))
+    _chk(out, "out", _ACT), _chk(sx, "sx", (torch.float32, yp.dtype)), _chk(sg, "sg", (torch.float32,))
+    tokens, k = mw.shape
+    n = out.shape[-1]
+    lib().call("moe_combine_ex", _stream(), _p(yp), _code(yp), _p(pos), _p(mw), _p(sx), _code(sx) if sx is not None else F32,
+               _p(sg), _p(out), _code(out), k, n, tokens)
+    return out

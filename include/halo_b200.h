@@ -406,6 +406,30 @@ int halo_b200_conv_step(halo_b200_stream stream, const float* in, float* state, 
  * (never observed) returns without writing and is counted. Reads the count (this call synchronizes). */
 int halo_b200_conv_stage_timeouts(unsigned int* count, char* err, size_t errlen);
 
+/* ---- MoE combine (the step after the routed experts' down projections) --------------------------- */
+
+/* halo_moe_combine_grouped, src/kernels/core.hip:5456-5464: out[t][i] = sum over slots s, in order, of
+ * w[t k + s] * yp[pos[t k + s]][i] (yp: fp16 rows of the per-pair down projections). tokens = grid.y. */
+int halo_b200_moe_combine_grouped(halo_b200_stream stream, const uint16_t* yp, const uint32_t* pos, const float* w,
+                                  float* out, uint32_t k, uint32_t n, uint32_t tokens, char* err, size_t errlen);
+/* halo_moe_combine_shared, src/kernels/core.hip:5466-5480 (CPU operator ReferenceModel::Moe,
+ * src/model/reference.cpp:558-578): the same, then + sigmoid(g[t]) * x[t][i] (the gated shared expert). */
+int halo_b200_moe_combine_shared(halo_b200_stream stream, const uint16_t* yp, const uint32_t* pos, const float* w,
+                                 const float* x, const float* g, float* out, uint32_t k, uint32_t n, uint32_t tokens,
+                                 char* err, size_t errlen);
+/* halo_moe_combine and halo_moe_combine_u, src/kernels/core.hip:2372-2380, 9401-9420: one token,
+ * out[i] = sum over slots of weights[s] * part[s][i] (fp32 rows). */
+int halo_b200_moe_combine(halo_b200_stream stream, const float* part, const float* weights, float* out, uint32_t slots,
+                          uint32_t n, char* err, size_t errlen);
+/* halo_axpy_slot, src/kernels/core.hip:1123-1127: y += weights[slot] * x. */
+int halo_b200_axpy_slot(halo_b200_stream stream, float* y, const float* x, const float* weights, uint32_t slot,
+                        uint32_t n, char* err, size_t errlen);
+/* Typed form: (yp, out) in (f16, f32), (f32, f32), (bf16, bf16), (bf16, f32), (f16, f16); sx (may be NULL, with
+ * sg) fp32 or of yp's type; pos == NULL: slot s of token t is row t k + s of yp. */
+int halo_b200_moe_combine_ex(halo_b200_stream stream, const void* yp, int yp_dtype, const uint32_t* pos, const float* mw,
+                             const void* sx, int sx_dtype, const float* sg, void* out, int out_dtype, uint32_t k,
+                             uint32_t n, uint32_t tokens, char* err, size_t errlen);
+
 /* ---- row copies and conversions around the attention block --------------------------------------- */
 
 /* halo_copy_at and halo_copy_at_h, src/kernels/core.hip:341-350, 921-927: dst[params[slot] * stride + i] =

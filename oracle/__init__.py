@@ -240,13 +240,18 @@ class Oracle:
         self._call("orc_hc_mix", _ptr(xn), _ptr(gate), _ptr(out), tokens, hc, h, threads)
         return out
 
-    def moe_combine(self, yp, pos, mw, sx, sg, threads=1):
-        yp, mw, sx, sg = _f32arr(yp), _f32arr(mw), _f32arr(sx), _f32arr(sg)
+    def moe_combine(self, yp, pos, mw, sx=None, sg=None, threads=1):
+        """sx / sg None: the routed experts' sum only."""
+        yp, mw = _f32arr(yp), _f32arr(mw)
         pos = np.ascontiguousarray(pos, dtype=np.uint32)
         tokens, k = pos.shape
         h = yp.shape[-1]
         out = np.empty((tokens, h), dtype=np.float32)
-        self._call("orc_moe_combine", _ptr(yp), _ptr(pos), _ptr(mw), _ptr(sx), _ptr(sg), _ptr(out), tokens, k, h, threads)
+        sp = gp = None
+        if sx is not None:
+            sx, sg = _f32arr(sx), _f32arr(sg)
+            sp, gp = _ptr(sx), _ptr(sg)
+        self._call("orc_moe_combine", _ptr(yp), _ptr(pos), _ptr(mw), sp, gp, _ptr(out), tokens, k, h, threads)
         return out
 
     def conv_l2norm(self, x, state, w, l2_channels, d, eps):

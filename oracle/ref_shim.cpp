@@ -201,6 +201,7 @@ void orc_moe_combine(const float* yp, const std::uint32_t* pos, const float* mw,
         const float* down = yp + static_cast<std::size_t>(pos[t * k + s]) * h;
         for (std::size_t j = 0; j < h; ++j) o[j] += weight * down[j];
       }
+      if (sx == nullptr) continue;  // routed experts only
       const float g = cpu::Sigmoid(sg[t]);
       for (std::size_t j = 0; j < h; ++j) o[j] += g * sx[t * h + j];
     }

@@ -432,3 +432,50 @@ def test_row_copies_and_scale_silu_by_name(dev, orc):
         got = dev.download(b_x, 0, m * 4, np.float32)
         assert np.all(np.abs(got - wants) <= 1e-5 * np.abs(wants) + 1e-30)
         assert ulps16(dev.download(b_y, 0, m * 2, np.float16).astype(np.float32), wants.astype(np.float16).astype(np.float32), "f16").max() <= 1
+
+
+@pytest.mark.parametrize("T,k,n", [(5, 10, 2048), (3, 10, 2560), (7, 2, 256), (4, 17, 512), (3, 3, 100)])
+@pytest.mark.parametrize("ydt,sdt,odt", [("f16", "f32", "f32"), ("f32", "f32", "f32"), ("bf16", "bf16", "bf16"), ("bf16", "f32", "f32")])
+def test_moe_combine(orc, T, k, n, ydt, sdt, odt):
+    """The routed experts' sum is bit-exact in fp32 (same products and sums in the same order as the CPU
+    operator); the gated shared expert adds a term scaled by the device's sigmoid."""
+    yp = rounded(synth.act(f"t.moe.yp.{n}", T * k, n), ydt)
+    pos = synth.rng(f"t.moe.pos.{n}.{k}").permutation(T * k).reshape(T, k).astype(np.uint32)
+    mw = synth.rng(f"t.moe.mw.{n}.{k}").random((T, k), dtype=np.float32)
+    sx, sg = rounded(synth.act(f"t.moe.sx.{n}", T, n), sdt), synth.act(f"t.moe.sg.{n}", T)
+    d_yp, d_pos, d_mw = to_dev(yp, ydt), torch.from_numpy(pos.view(np.int32)).to(DEV), to_dev(mw)
+    out = torch.full((T, n), float("nan"), device=DEV, dtype=TDT[odt])
+    ops.moe_combine(d_yp, d_pos, d_mw, out)
+    want = orc.moe_combine(yp, pos, mw)
+    if odt == "f32":
+        assert np.array_equal(to_f32(out), want), "routed sum"
+    else:
+        assert np.array_equal(oracle.bf16_bits(to_f32(out)), oracle.bf16_bits(want)), "routed sum, bf16 out"
+    ops.moe_combine(d_yp, d_pos, d_mw, out, sx=to_dev(sx, sdt), sg=to_dev(sg))
+    want2 = orc.moe_combine(yp, pos, mw, sx, sg)
+    gs = np.float32(1) / (np.float32(1) + np.exp(-sg, dtype=np.float32))
+    mag = np.abs(want) + np.abs(gs[:, None] * sx)
+    tol = 3e-7 * mag if odt == "f32" else 2.0 ** -8 * np.abs(want2) + 3e-7 * mag
+    assert np.all(np.abs(to_f32(out) - want2) <= tol + 1e-30), "with the shared expert"
+    # slots in place (pos None) and the single-slot accumulate of halo_axpy_slot, through the by-name launch
+    if ydt == "f32":
+        dev = Device.create(0)
+        part, w1 = yp[:k], mw[0]
+        b_part, b_w, b_out = up(dev, part), up(dev, w1), dev.alloc(n * 4)
+        dev.launch(dev.kernel("halo_moe_combine"), (1,), (256,), [Arg.Buf(b_part), Arg.Buf(b_w), Arg.Buf(b_out), Arg.U32(k), Arg.U32(n)])
+        acc = np.zeros(n, np.float32)
+        for s_ in range(k):
+            acc = acc + w1[s_] * part[s_]
+        assert np.array_equal(dev.download(b_out, 0, n * 4, np.float32), acc)
+        dev.launch(dev.kernel("halo_axpy_slot"), (1,), (256,), [Arg.Buf(b_out), Arg.Buf(b_part), Arg.Buf(b_w), Arg.U32(1), Arg.U32(n)])
+        assert np.array_equal(dev.download(b_out, 0, n * 4, np.float32), acc + w1[1] * part[0])
+    if ydt == "f16" and n % 8 == 0:
+        dev = Device.create(0)
+        b_yp, b_pos, b_mw, b_sx, b_sg = up(dev, yp.astype(np.float16)), up(dev, pos), up(dev, mw), up(dev, sx), up(dev, sg)
+        b_o = dev.alloc(T * n * 4)
+        dev.launch(dev.kernel("halo_moe_combine_grouped"), ((n + 255) // 256, T), (256,),
+                   [Arg.Buf(b_yp), Arg.Buf(b_pos), Arg.Buf(b_mw), Arg.Buf(b_o), Arg.U32(k), Arg.U32(n)])
+        assert np.array_equal(dev.download(b_o, 0, T * n * 4, np.float32).reshape(T, n), want)
+        dev.launch(dev.kernel("halo_moe_combine_shared"), ((n + 255) // 256, T), (256,),
+                   [Arg.Buf(b_yp), Arg.Buf(b_pos), Arg.Buf(b_mw), Arg.Buf(b_sx), Arg.Buf(b_sg), Arg.Buf(b_o), Arg.U32(k), Arg.U32(n)])
+        assert np.all(np.abs(dev.download(b_o, 0, T * n * 4, np.float32).reshape(T, n) - want2) <= 3e-7 * mag + 1e-30)
