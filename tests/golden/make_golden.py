@@ -12,6 +12,11 @@ reference checkout (default /root/reference):
    src/core/lowbit.cpp compiled unmodified) on the tiny configuration:
    hidden 256, 4 Q / 2 KV heads x 64, rot 16, theta 1e7, 4 value heads x 64,
    ff 128, vocab 4096 Q8_0, T = 32, fp32.
+3. ops_wide_c1.npz - the same for the ops around the five groups, on the tiny configuration with 4 residual
+   streams: hyper-connection combine + grouped norm, inject projection, mix, the experts' combine, and the
+   DeltaNet conv + SiLU + L2 norm. These CPU operators are members of model classes in the reference
+   (src/model/reference.cpp:151-202, 558-578; src/model/qwen35.cpp:180-198), so oracle/ref_shim.cpp repeats
+   their loops around the reference's own cpu::RmsNorm / L2Norm / Sigmoid / Silu / MatVec.
 """
 from __future__ import annotations
 
@@ -77,9 +82,49 @@ def make_ops() -> dict:
     return out
 
 
+def make_wide_ops() -> dict:
+    T = 12  # fewer tokens than the main fixture: these tensors are hc = 4 times wider
+    ref = oracle.load("reference")
+    assert ref.kind == "reference"
+    s, hc, k, irows = synth.C1, 4, 3, 4
+    out: dict[str, np.ndarray] = {}
+    res, blk = synth.act("w.res", T, hc, s.hidden), synth.act("w.out", T, s.hidden)
+    inject = synth.act("w.inject", T, hc) * 2
+    gamma = (np.float32(1.0) + np.float32(0.1) * synth.act("w.gamma", hc, s.hidden)).astype(np.float32)
+    out.update(hc_res=res, hc_out=blk, hc_inject=inject, hc_gamma=gamma)
+    for name, rnd in (("f32", 0), ("bf16", 1), ("f16", 2)):
+        r = res.copy()
+        if rnd == 1:
+            r = oracle.round_bf16(r)
+        if rnd == 2:
+            r = r.astype(np.float16).astype(np.float32)
+        y = ref.hc_combine_norm(r, blk, inject, gamma, s.eps, rnd)
+        out[f"hc_res_out_{name}"], out[f"hc_y_{name}"] = r, y
+    iw = (synth.act("w.iw", irows, hc * s.hidden) * 0.05).astype(np.float32)
+    out.update(hc_iw=iw, hc_inject_proj=ref.hc_inject(out["hc_y_f32"].reshape(T, -1), iw))
+    gate = synth.act("w.gate", T, hc, s.hidden) * 2
+    out.update(hc_gate=gate, hc_mixed=ref.hc_mix(out["hc_y_f32"], gate))
+    yp = synth.act("w.yp", T * k, s.hidden).astype(np.float16).astype(np.float32)
+    pos = synth.rng("w.pos").permutation(T * k).reshape(T, k).astype(np.uint32)
+    mw = synth.rng("w.mw").random((T, k), dtype=np.float32)
+    sx, sg = synth.act("w.sx", T, s.hidden), synth.act("w.sg", T)
+    out.update(moe_yp=yp, moe_pos=pos, moe_w=mw, moe_sx=sx, moe_sg=sg, moe_routed=ref.moe_combine(yp, pos, mw),
+               moe_out=ref.moe_combine(yp, pos, mw, sx, sg))
+    C, l2 = (2 * s.k_heads + s.v_heads) * s.lin_dim, 2 * s.k_heads * s.lin_dim
+    cx, cstate = synth.act("w.conv_x", T, C), synth.act("w.conv_state", 3, C)
+    cw = (synth.act("w.conv_w", C, 4) * 0.5).astype(np.float32)
+    st = cstate.copy()
+    out.update(conv_x=cx, conv_state=cstate, conv_w=cw, conv_out=ref.conv_l2norm(cx, st, cw, l2, s.lin_dim, s.eps),
+               conv_state_out=st)
+    return out
+
+
 if __name__ == "__main__":
     n = extract_quant_blocks()
     ops = make_ops()
     np.savez_compressed(HERE / "ops_c1.npz", **ops)
+    wide = make_wide_ops()
+    np.savez_compressed(HERE / "ops_wide_c1.npz", **wide)
     print(f"quant_blocks.tsv: {n} rows; ops_c1.npz: {len(ops)} arrays, "
-          f"{(HERE / 'ops_c1.npz').stat().st_size} bytes")
+          f"{(HERE / 'ops_c1.npz').stat().st_size} bytes; ops_wide_c1.npz: {len(wide)} arrays, "
+          f"{(HERE / 'ops_wide_c1.npz').stat().st_size} bytes")

@@ -479,3 +479,45 @@ def test_moe_combine(orc, T, k, n, ydt, sdt, odt):
         dev.launch(dev.kernel("halo_moe_combine_shared"), ((n + 255) // 256, T), (256,),
                    [Arg.Buf(b_yp), Arg.Buf(b_pos), Arg.Buf(b_mw), Arg.Buf(b_sx), Arg.Buf(b_sg), Arg.Buf(b_o), Arg.U32(k), Arg.U32(n)])
         assert np.all(np.abs(dev.download(b_o, 0, T * n * 4, np.float32).reshape(T, n) - want2) <= 3e-7 * mag + 1e-30)
+
+
+def test_committed_outputs_of_the_compiled_reference():
+    """The kernels against tests/golden/ops_wide_c1.npz: outputs of the reference's own CPU operators on the
+    tiny configuration (generated by tests/golden/make_golden.py where the reference checkout is present)."""
+    from conftest import GOLDEN
+    g, s = np.load(GOLDEN / "ops_wide_c1.npz"), synth.C1
+    T, hc, h = g["hc_res"].shape
+    for name, rdt in (("f32", "f32"), ("bf16", "bf16"), ("f16", "f16")):
+        d_res = to_dev(rounded(g["hc_res"], rdt), rdt)
+        y = torch.empty(T, hc, h, device=DEV)
+        ops.hc_combine_norm(d_res, to_dev(g["hc_out"]), to_dev(g["hc_inject"]), to_dev(g["hc_gamma"]), s.eps, y=y)
+        check_res(to_f32(d_res), g[f"hc_res_out_{name}"], rdt, f"golden residual {name}",
+                  np.abs(g["hc_res"]) + 2 * np.abs(g["hc_out"])[:, None, :])
+        if rdt == "f32":  # (16-bit residuals may differ from the fixture by an ulp, so their norms are checked two-stage elsewhere)
+            assert_rows_close(to_f32(y).reshape(-1, h), g["hc_y_f32"].reshape(-1, h), rel=2e-5, what="golden grouped norm")
+    y32 = to_dev(g["hc_y_f32"])
+    irows = g["hc_iw"].shape[0]
+    ipart, inj = torch.empty(T, hc, irows, device=DEV), torch.empty(T, irows, device=DEV)
+    # norm-only form on rows that are already the fixture's y: unit gammas keep y / rms(y), whose inject
+    # partials must add up to the fixture's projection of that y
+    yn = torch.empty(T, hc, h, device=DEV)
+    ops.hc_combine_norm(y32.clone(), None, None, torch.ones(hc, h, device=DEV), s.eps, y=yn, iw=to_dev(g["hc_iw"]), ipart=ipart)
+    ops.inject_reduce(ipart, inj)
+    want_inj = np.einsum("tc,rc->tr", to_f32(yn).reshape(T, -1).astype(np.float64), g["hc_iw"].astype(np.float64))
+    bound = np.abs(to_f32(yn).reshape(T, 1, -1) * g["hc_iw"][None]).sum(axis=2)
+    assert np.all(np.abs(to_f32(inj) - want_inj) <= 1e-5 * bound + 1e-30)
+    mixed = torch.empty(T, h, device=DEV)
+    ops.hc_mix_rows(y32, to_dev(g["hc_gate"]), mixed)
+    assert np.all(np.abs(to_f32(mixed) - g["hc_mixed"]) <= 1e-5 * np.abs(g["hc_y_f32"]).sum(axis=1) / hc + 1e-30)
+    out = torch.empty(T, h, device=DEV)
+    ops.moe_combine(to_dev(g["moe_yp"], "f16"), torch.from_numpy(g["moe_pos"].view(np.int32)).to(DEV), to_dev(g["moe_w"]), out)
+    assert np.array_equal(to_f32(out), g["moe_routed"])
+    ops.moe_combine(to_dev(g["moe_yp"], "f16"), torch.from_numpy(g["moe_pos"].view(np.int32)).to(DEV), to_dev(g["moe_w"]), out,
+                    sx=to_dev(g["moe_sx"]), sg=to_dev(g["moe_sg"]))
+    assert np.all(np.abs(to_f32(out) - g["moe_out"]) <= 3e-7 * (np.abs(g["moe_routed"]) + np.abs(g["moe_sx"])) + 1e-30)
+    C = g["conv_x"].shape[1]
+    cout, cst = torch.empty(T, C, device=DEV), to_dev(g["conv_state"])
+    ops.conv_l2norm(to_dev(g["conv_x"]), cst, to_dev(g["conv_w"]), cout, l2_channels=2 * s.k_heads * s.lin_dim, d=s.lin_dim, eps=s.eps)
+    assert_rows_close(to_f32(cout).reshape(-1, s.lin_dim), g["conv_out"].reshape(-1, s.lin_dim), what="golden conv")
+    ops.conv_state_advance(to_dev(g["conv_x"]), cst)
+    assert np.array_equal(cst.cpu().numpy(), g["conv_state_out"])

@@ -174,3 +174,63 @@ def test_bf16_helpers_match_port(port):
     want = np.array([port._call("orc_float_to_bf16", float(v)) for v in x[:512]], dtype=np.uint16)
     assert np.array_equal(oracle.bf16_bits(x[:512]), want)
     assert np.array_equal(port.round_bf16(x.copy()), oracle.round_bf16(x))
+
+
+# ---- the ops around the five groups: hyper-connection residual, experts' combine, DeltaNet conv -------
+@pytest.fixture(scope="module")
+def golden_wide():
+    return np.load(GOLDEN / "ops_wide_c1.npz")
+
+
+def _wide_outputs(orc, g):
+    s = synth.C1
+    out = {}
+    for name, rnd in (("f32", 0), ("bf16", 1), ("f16", 2)):
+        r = g["hc_res"].copy()
+        if rnd == 1:
+            r = oracle.round_bf16(r)
+        if rnd == 2:
+            r = r.astype(np.float16).astype(np.float32)
+        out[f"hc_y_{name}"] = orc.hc_combine_norm(r, g["hc_out"], g["hc_inject"], g["hc_gamma"], s.eps, rnd)
+        out[f"hc_res_out_{name}"] = r
+    T = g["hc_res"].shape[0]
+    out["hc_inject_proj"] = orc.hc_inject(out["hc_y_f32"].reshape(T, -1), g["hc_iw"])
+    out["hc_mixed"] = orc.hc_mix(out["hc_y_f32"], g["hc_gate"])
+    out["moe_routed"] = orc.moe_combine(g["moe_yp"], g["moe_pos"], g["moe_w"])
+    out["moe_out"] = orc.moe_combine(g["moe_yp"], g["moe_pos"], g["moe_w"], g["moe_sx"], g["moe_sg"])
+    st = g["conv_state"].copy()
+    l2, d = 2 * s.k_heads * s.lin_dim, s.lin_dim
+    out["conv_out"] = orc.conv_l2norm(g["conv_x"], st, g["conv_w"], l2, d, s.eps)
+    out["conv_state_out"] = st
+    return out
+
+
+@pytest.mark.parametrize("kind", ["port", "reference"])
+def test_committed_reference_outputs_of_the_widened_ops(kind, golden_wide):
+    """The port (and, where it is built, the compiled reference) reproduces the committed outputs bit for bit."""
+    if kind == "reference" and not oracle.have_reference():
+        pytest.skip("reference library not built here")
+    got = _wide_outputs(oracle.load(kind), golden_wide)
+    for name, value in got.items():
+        assert value.tobytes() == golden_wide[name].tobytes(), name
+
+
+def test_widened_op_identities(port, golden_wide):
+    """Relations the CPU operators satisfy by construction (src/model/reference.cpp:189-202, 151-160)."""
+    g, s = golden_wide, synth.C1
+    T, hc, h = g["hc_res"].shape
+    # zero logits: 2 sigmoid(0) = 1, the combine is a plain add into every stream
+    r = g["hc_res"].copy()
+    port.hc_combine_norm(r, g["hc_out"], np.zeros((T, hc), np.float32), g["hc_gamma"], s.eps, 0)
+    assert np.array_equal(r, g["hc_res"] + g["hc_out"][:, None, :])
+    # the grouped norm is the plain row norm with gamma row = stream index
+    y = port.hc_combine_norm(g["hc_res"].copy(), None, None, g["hc_gamma"], s.eps, 0)
+    rows = port.rmsnorm_rows(g["hc_res"].reshape(T * hc, h).copy(), g["hc_gamma"], s.eps, w_stride=h, w_period=hc)
+    assert np.array_equal(y.reshape(T * hc, h), rows)
+    # the conv of a chunk equals token-by-token stepping with the state carried along
+    st_a, st_b = g["conv_state"].copy(), g["conv_state"].copy()
+    l2, d = 2 * s.k_heads * s.lin_dim, s.lin_dim
+    whole = port.conv_l2norm(g["conv_x"], st_a, g["conv_w"], l2, d, s.eps)
+    steps = np.concatenate([port.conv_l2norm(g["conv_x"][t:t + 1], st_b, g["conv_w"], l2, d, s.eps) for t in range(T)])
+    assert np.array_equal(whole, steps) and np.array_equal(st_a, st_b)
+    assert np.array_equal(st_a, g["conv_x"][-3:])
