@@ -218,8 +218,9 @@ def op_specs(torch, shapes, T: int):
     w_hc = 1 + torch.randn(4, s.hidden, device=dev) * 0.1
     conv_c = (2 * s.k_heads + s.v_heads) * s.lin_dim
     conv_w, conv_state = torch.randn(conv_c, 4, device=dev) * 0.5, torch.randn(3, conv_c, device=dev)
-    table = torch.randint(0, 255, (8192, s.q8_row_bytes), device=dev, dtype=torch.uint8)
-    table.view(8192, -1, 34)[:, :, 1] = 0x3C  # finite fp16 scales
+    # the full-size 151 936-row table (330.6 MB): random ids then gather from HBM, not from a table that fits L2
+    table = torch.randint(0, 255, (s.vocab, s.q8_row_bytes), device=dev, dtype=torch.uint8)
+    table.view(s.vocab, -1, 34)[:, :, 1] = 0x3C  # finite fp16 scales
     rope_tab = ops.rope_table(torch.empty(T, 2, s.rot // 2, device=dev), s.rot, s.theta)
     specs = {
         "add_rmsnorm": (lambda: (r(T, s.hidden), r(T, s.hidden), torch.empty(T, s.hidden, device=dev, dtype=bf)),
@@ -233,7 +234,7 @@ def op_specs(torch, shapes, T: int):
         "swiglu_moe": (lambda: (r(T, s.ff), r(T, s.ff), torch.empty(T, s.ff, device=dev, dtype=bf),
                                 r(T * k, s.ff), r(T * k, s.ff), torch.empty(T * k, s.ff, device=dev, dtype=bf)),
                        lambda b: ops.silu_mul_multi([(b[0], b[1]), (b[3], b[4])], [b[2], b[5]])),
-        "embed": (lambda: (torch.randint(0, 8192, (T,), device=dev, dtype=torch.int32),
+        "embed": (lambda: (torch.randint(0, s.vocab, (T,), device=dev, dtype=torch.int32),
                            torch.empty(T, s.hidden, device=dev, dtype=bf)),
                   lambda b: ops.embed_q8_0(table, b[0], s.hidden, b[1])),
         # not in the chain: the add + norm whose only normalized output is Q8_0 blocks
