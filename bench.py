@@ -284,7 +284,8 @@ def kernel_table(torch, shapes, T: int, peaks: dict) -> dict:
 def decode_steps(args) -> None:
     """Decode form of the chain (config 2): B tokens per step, the full 151 936-row Q8_0 table, token and
     position of every batch entry read from device memory, one captured graph replayed after the host rewrites
-    those 64-byte parameter rows. Prints microseconds per step for B = 1 .. --decode-batch (a latency figure;
+    those 64-byte parameter rows; the add + norm writes its normalized row as Q8_0 blocks (the decode
+    configuration's epilogue). Prints microseconds per step for B = 1 .. --decode-batch (a latency figure;
     the step moves only ~5 MB per token, so it is bound by the 230 launches, not by HBM)."""
     import torch
     from halo_flash_b200 import chain as chain_mod, synth
@@ -292,7 +293,7 @@ def decode_steps(args) -> None:
     for B in sorted({1, 2, 4, args.decode_batch}):
         if B > args.decode_batch:
             continue
-        ch = chain_mod.LayerChain(synth.FULL, B, pos0=0, step_params=True)
+        ch = chain_mod.LayerChain(synth.FULL, B, pos0=0, step_params=True, q8_epilogue=True)
         ch.capture()
         pos = torch.randint(0, synth.FULL.max_pos, (64, B), dtype=torch.int32)
         tok = torch.randint(0, synth.FULL.vocab, (64, B), dtype=torch.int32)

@@ -85,7 +85,8 @@ class BlockOutputs:
 
 class LayerChain:
     def __init__(self, shapes: Shapes, tokens: int, *, pos0: int = 0, device="cuda:0", dtype=torch.bfloat16,
-                 sets: int = 2, vocab: int | None = None, seed: int = synth.SEED, step_params: bool = False):
+                 sets: int = 2, vocab: int | None = None, seed: int = synth.SEED, step_params: bool = False,
+                 q8_epilogue: bool = False):
         if not torch.cuda.is_available():
             raise RuntimeError("LayerChain needs a CUDA device: halo_flash_b200 has no CPU path")
         self.s, self.T, self.pos0, self.dtype = shapes, tokens, pos0, dtype
@@ -109,6 +110,8 @@ class LayerChain:
         ) for _ in range(sets)]
         self.res = torch.empty(T, s.hidden, device=dev, dtype=dtype)
         self.xn = torch.empty(T, s.hidden, device=dev, dtype=dtype)
+        # decode form of the add + norm: the normalized row leaves as Q8_0 blocks, the next GEMV's input
+        self.xn_q8 = torch.empty(T, s.q8_row_bytes, device=dev, dtype=torch.uint8) if q8_epilogue else None
         self.h_s = torch.empty(T, s.ff, device=dev, dtype=dtype)
         self.h_r = torch.empty(T * k, s.ff, device=dev, dtype=dtype)
         self.rope_tab = torch.empty(T, 2, s.rot // 2, device=dev, dtype=torch.float32)
@@ -147,13 +150,14 @@ class LayerChain:
     # ---- one step, eager ------------------------------------------------------------------
     def layer(self, l: int, bo: BlockOutputs) -> None:
         s = self.s
-        ops.add_rmsnorm(self.res, bo.delta_a, self.w_attn[l], s.eps, one_plus=True, xn=self.xn)
+        xn = None if self.xn_q8 is not None else self.xn
+        ops.add_rmsnorm(self.res, bo.delta_a, self.w_attn[l], s.eps, one_plus=True, xn=xn, q8_0=self.xn_q8)
         if synth.layer_is_gqa(l):
             ops.norm_rope_qk_table(bo.q, bo.k, self.w_q, self.w_k, s.eps, s.rot, self.rope_tab, one_plus=True)
         else:
             ops.l2norm(bo.qk, s.eps)
             ops.gated_norm(bo.o, self.w_gated, bo.z, s.eps, mode=0, y=bo.y)
-        ops.add_rmsnorm(self.res, bo.delta_b, self.w_post[l], s.eps, one_plus=True, xn=self.xn)
+        ops.add_rmsnorm(self.res, bo.delta_b, self.w_post[l], s.eps, one_plus=True, xn=xn, q8_0=self.xn_q8)
         ops.silu_mul_multi([(bo.gate_s, bo.up_s), (bo.gate_r, bo.up_r)], [self.h_s, self.h_r])
 
     def step(self) -> None:
