@@ -56,8 +56,11 @@ struct VecSegments {
 // The raw loads of all kUnroll octets are issued first (kUnroll * 2 * 16 bytes in flight per
 // thread); each octet is then converted, computed and stored in turn, which keeps the
 // register count low enough for 5 resident CTAs per SM.
-template <typename IT, typename OT, int OP>
+// U octets per thread: kUnroll for streaming sizes; 1 when the whole launch cannot fill the GPU (decode),
+// where its duration is one warp's chain of dependent instructions and the shortest chain wins.
+template <typename IT, typename OT, int OP, int U>
 __global__ void __launch_bounds__(kBlock, sizeof(IT) == 4 ? 3 : 5) elementwise_vec_kernel(const VecSegments v) {
+  constexpr int kUnroll = U;  // shadows the file-scope constant inside this kernel
   pdl_begin();
   // Segment lookup by compare-and-select over constant indices: indexing the parameter arrays
   // with a run-time value would make the compiler copy them to local memory.
@@ -115,7 +118,10 @@ cudaError_t LaunchOp(const EltArgs& a, cudaStream_t s) {
   if (a.vec) {
     VecSegments v = {};
     v.alpha = a.alpha;
-    const uint64_t per_cta = static_cast<uint64_t>(kBlock) * kUnroll;
+    uint64_t total_octs = 0;
+    for (int i = 0; i < a.nseg; ++i) total_octs += a.seg[i].n / 8;
+    const bool tiny = total_octs <= 148u * 256u;
+    const uint64_t per_cta = static_cast<uint64_t>(kBlock) * (tiny ? 1 : kUnroll);
     uint64_t ctas = 0;
     for (int i = 0; i < kMaxSegments; ++i) {
       v.first_cta[i] = static_cast<uint32_t>(ctas);
@@ -132,7 +138,8 @@ cudaError_t LaunchOp(const EltArgs& a, cudaStream_t s) {
     v.first_cta[kMaxSegments] = static_cast<uint32_t>(ctas);
     for (int i = a.nseg; i < kMaxSegments; ++i) v.first_cta[i] = 0xFFFFFFFFu;  // never selected
     if (ctas) {
-      LaunchKernel(elementwise_vec_kernel<IT, OT, OP>, static_cast<unsigned>(ctas), kBlock, 0, s, v);
+      if (tiny) LaunchKernel(elementwise_vec_kernel<IT, OT, OP, 1>, static_cast<unsigned>(ctas), kBlock, 0, s, v);
+      else LaunchKernel(elementwise_vec_kernel<IT, OT, OP, kUnroll>, static_cast<unsigned>(ctas), kBlock, 0, s, v);
       const cudaError_t e = cudaGetLastError();
       if (e != cudaSuccess) return e;
     }

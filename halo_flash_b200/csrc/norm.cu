@@ -276,35 +276,62 @@ __global__ void __launch_bounds__(kBlock) norm_rows_lean_kernel(const LeanArgs a
     v[k] = oct_scale(v[k], scale);
     if (MODE != 0 || a.w) v[k] = oct_mul(v[k], gm[k]);
     if (MODE != 0 || a.y) oct_store(static_cast<YT*>(a.y) + off + (j << 3), v[k]);
-    if constexpr (EPI) {
-      float arr[8];
-      oct_to_array(v[k], arr);
-      const float amax = quad_amax(arr);
-      const uint32_t c0 = j << 3;
-      if (a.q8_0) {
-        uint16_t dbits;
-        const uint2 codes = q8_0_codes(arr, amax, &dbits);
-        const size_t blk_index = static_cast<size_t>(row) * (a.d >> 5) + (c0 >> 5);
-        if (a.stage_q8) {
-          const unsigned lane = threadIdx.x & 31u;
-          uint8_t* st = stage[threadIdx.x >> 5][k];
-          uint8_t* sb = st + (lane >> 2) * 34;
-          if ((lane & 3u) == 0) *reinterpret_cast<uint16_t*>(sb) = dbits;
-          store_codes_u16(sb + 2 + ((lane & 3u) << 3), codes);
-          __syncwarp();
-          if (lane < 17) {
+  }
+  if constexpr (EPI) {
+    // The K octets go through the epilogue phase by phase, not one after the other: their block maxima,
+    // scale divisions and code roundings are independent of each other and interleave (3 % at T = 4096).
+    float arr[K][8], amax[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      oct_to_array(v[k], arr[k]);
+      float m[4];  // tree instead of a chain of eight
+#pragma unroll
+      for (int i = 0; i < 4; ++i) m[i] = fmaxf(fabsf(arr[k][2 * i]), fabsf(arr[k][2 * i + 1]));
+      amax[k] = fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
+    }
+#pragma unroll
+    for (int k = 0; k < K; ++k) amax[k] = fmaxf(amax[k], __shfl_xor_sync(kFullMask, amax[k], 1));
+#pragma unroll
+    for (int k = 0; k < K; ++k) amax[k] = fmaxf(amax[k], __shfl_xor_sync(kFullMask, amax[k], 2));
+    const unsigned lane = threadIdx.x & 31u;
+    if (a.q8_0) {
+      uint16_t dbits[K];
+      uint2 codes[K];
+#pragma unroll
+      for (int k = 0; k < K; ++k) codes[k] = q8_0_codes(arr[k], amax[k], &dbits[k]);
+      if (a.stage_q8) {
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+          uint8_t* sb = stage[threadIdx.x >> 5][k] + (lane >> 2) * 34;
+          if ((lane & 3u) == 0) *reinterpret_cast<uint16_t*>(sb) = dbits[k];
+          store_codes_u16(sb + 2 + ((lane & 3u) << 3), codes[k]);
+        }
+        __syncwarp();
+        if (lane < 17) {
+#pragma unroll
+          for (int k = 0; k < K; ++k) {
+            const uint32_t c0 = ((k << lg) + lir) << 3;
+            const size_t blk_index = static_cast<size_t>(row) * (a.d >> 5) + (c0 >> 5);
             uint8_t* out = a.q8_0 + (blk_index - (lane >> 2)) * 34;  // the warp's first block
-            reinterpret_cast<uint4*>(out)[lane] = reinterpret_cast<const uint4*>(st)[lane];
+            reinterpret_cast<uint4*>(out)[lane] = reinterpret_cast<const uint4*>(stage[threadIdx.x >> 5][k])[lane];
           }
-        } else {
-          uint8_t* blk = a.q8_0 + blk_index * 34;
-          if ((c0 & 31u) == 0) *reinterpret_cast<uint16_t*>(blk) = dbits;
-          store_codes_u16(blk + 2 + (c0 & 31u), codes);
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+          const uint32_t c0 = ((k << lg) + lir) << 3;
+          uint8_t* blk = a.q8_0 + (static_cast<size_t>(row) * (a.d >> 5) + (c0 >> 5)) * 34;
+          if ((c0 & 31u) == 0) *reinterpret_cast<uint16_t*>(blk) = dbits[k];
+          store_codes_u16(blk + 2 + (c0 & 31u), codes[k]);
         }
       }
-      if (a.xq) {
-        const float qs = amax / 127.0f;
-        *reinterpret_cast<uint2*>(a.xq + off + c0) = i8_codes(arr, qs);
+    }
+    if (a.xq) {
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const uint32_t c0 = ((k << lg) + lir) << 3;
+        const float qs = amax[k] / 127.0f;
+        *reinterpret_cast<uint2*>(a.xq + off + c0) = i8_codes(arr[k], qs);
         if ((c0 & 31u) == 0) a.xd[static_cast<size_t>(row) * (a.d >> 5) + (c0 >> 5)] = qs;
       }
     }
@@ -558,10 +585,18 @@ struct Shape {
   unsigned rows_per_cta;
   bool full;
 };
-Shape PickShape(unsigned octs, unsigned rows, int want_g, unsigned min_g, int want_k1) {
+// few_rows: the launch cannot fill the GPU (a decode step). It then lasts as long as one warp's chain of
+// dependent instructions (about 10 cycles each), so rows are spread over as many threads as they have
+// octets, one octet per thread: 1.55 -> 1.2 us for the add + norm of 8 rows of 2048. Not applied where
+// the caller pinned a layout (want_k1: the layout shared with the fused norm + RoPE kernel).
+Shape PickShape(unsigned octs, unsigned rows, int want_g, unsigned min_g, int want_k1, bool few_rows_ok = false) {
   unsigned g;
+  const bool few_rows = few_rows_ok && static_cast<uint64_t>(rows) * octs <= 148u * 256u;
   if (want_g > 0) {
     g = static_cast<unsigned>(want_g);
+  } else if (few_rows) {
+    g = 1;
+    while (g < octs && g < 256u) g <<= 1;
   } else if (octs <= 32) {
     // Short rows (one head), shuffles only. Two octets per thread measured faster than one
     // (13.8 vs 14.8 us for the 16 x 128 q/k L2 norm at 4096 tokens) and faster than several
@@ -629,7 +664,9 @@ cudaError_t LaunchNormT(const NormArgs& a, cudaStream_t s) {
     LaunchKernel(norm_rows_scalar_kernel<XT, YT, ADD>, a.rows, kBlock, 0, s, a);
     return cudaGetLastError();
   }
-  const Shape sh = PickShape(a.d / 8, a.rows, a.threads_per_row, (a.q8_0 || a.xq) ? 4u : 1u, a.short_rows_k1);
+  // rows of one head keep the layout they share with the fused norm + RoPE kernel unless they are an L2 norm
+  const Shape sh = PickShape(a.d / 8, a.rows, a.threads_per_row, (a.q8_0 || a.xq) ? 4u : 1u, a.short_rows_k1,
+                             a.d / 8 > 32 || a.l2);
   const unsigned grid = (a.rows + sh.rows_per_cta - 1) / sh.rows_per_cta;
   // (in, out) pairs the lean kernels are built for; the rest go through the general kernel
   constexpr bool kLeanTypes = (std::is_same_v<XT, float> && !std::is_same_v<YT, f16>) ||
