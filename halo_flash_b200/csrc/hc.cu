@@ -98,7 +98,10 @@ constexpr int HcMinCtas(int octets, int rt_size) {
 
 // HC: streams per thread group (hc, or 1 = one row per group). K: octets per stream per thread.
 // MOE: the block output is sum_slot mw * yp[pos] + sigmoid(sg) * sx instead of a stored row.
-template <typename RT, typename OT, typename YT, int HC, int K, bool MOE>
+// LEAN: the common call - a stored block output combined into full tiles (every group exists, every
+// thread's octets lie inside the row) with y as the only normalized output - compiled without the
+// predicates and without the code of the other outputs (the kernel is bound by instruction issue).
+template <typename RT, typename OT, typename YT, int HC, int K, bool MOE, bool LEAN = false>
 __global__ void __launch_bounds__(kBlock, HcMinCtas(HC* K, sizeof(RT)))
     hc_combine_norm_kernel(const HcArgs a, const unsigned lg, const float inv_h) {
   pdl_begin();
@@ -107,13 +110,13 @@ __global__ void __launch_bounds__(kBlock, HcMinCtas(HC* K, sizeof(RT)))
   const unsigned g = 1u << lg;
   const unsigned lir = threadIdx.x & (g - 1), lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
   const uint32_t grp = blockIdx.x * (kBlock >> lg) + (threadIdx.x >> lg);
-  const bool grp_ok = grp < (HC == 1 ? a.tokens * a.hc : a.tokens);
+  const bool grp_ok = LEAN || grp < (HC == 1 ? a.tokens * a.hc : a.tokens);
   const uint32_t t = HC == 1 ? grp / a.hc : grp;
   const uint32_t s0 = HC == 1 ? grp - t * a.hc : 0u;
   const unsigned octs = a.h >> 3;
   const size_t row0 = (static_cast<size_t>(t) * a.hc + s0) * a.h;
   RT* res = static_cast<RT*>(a.res) + row0;
-  const bool combine = MOE || a.inject != nullptr;  // false: grouped norm only, the residual is not written
+  const bool combine = LEAN || MOE || a.inject != nullptr;  // false: grouped norm only, the residual is not written
 
   // scatter weights a_s = 2 sigmoid(inject / hc): lane s of every min(g, 32)-lane segment computes
   // stream s's (first of all, so the logit's load and the exp overlap the row loads below), the others
@@ -130,7 +133,7 @@ __global__ void __launch_bounds__(kBlock, HcMinCtas(HC* K, sizeof(RT)))
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const unsigned j = (k << lg) + lir;
-      rr[s][k] = (grp_ok && j < octs) ? raw_load(res + static_cast<size_t>(s) * a.h + j * 8) : raw_zero<RT>();
+      rr[s][k] = (LEAN || (grp_ok && j < octs)) ? raw_load(res + static_cast<size_t>(s) * a.h + j * 8) : raw_zero<RT>();
     }
   Oct o[K];
   if constexpr (!MOE) {
@@ -139,7 +142,7 @@ __global__ void __launch_bounds__(kBlock, HcMinCtas(HC* K, sizeof(RT)))
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const unsigned j = (k << lg) + lir;
-      ro[k] = (combine && grp_ok && j < octs) ? raw_load(out + j * 8) : raw_zero<OT>();
+      ro[k] = (LEAN || (combine && grp_ok && j < octs)) ? raw_load(out + j * 8) : raw_zero<OT>();
     }
 #pragma unroll
     for (int k = 0; k < K; ++k) o[k] = raw_unpack(ro[k]);
@@ -191,7 +194,7 @@ __global__ void __launch_bounds__(kBlock, HcMinCtas(HC* K, sizeof(RT)))
       const unsigned j = (k << lg) + lir;
       // stored in the residual's type; the norm reads the residual as stored (core.hip:4132-4135)
       kept[s][k] = raw_pack(oct_combine<RT>(raw_unpack(rr[s][k]), o[k], as[s]), RT{});
-      if (combine && grp_ok && j < octs) raw_store(res + static_cast<size_t>(s) * a.h + j * 8, kept[s][k]);
+      if (LEAN || (combine && grp_ok && j < octs)) raw_store(res + static_cast<size_t>(s) * a.h + j * 8, kept[s][k]);
       acc = oct_sumsq(raw_unpack(kept[s][k]), acc);
     }
     ss[s] = acc.x + acc.y;
@@ -230,7 +233,7 @@ __global__ void __launch_bounds__(kBlock, HcMinCtas(HC* K, sizeof(RT)))
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const unsigned j = (k << lg) + lir;
-      const bool ok = grp_ok && j < octs;
+      const bool ok = LEAN || (grp_ok && j < octs);
       Oct gm = ok ? oct_load_cached(w + j * 8) : oct_zero();
       if (a.one_plus) {
         const float2 one = make_float2(1.0f, 1.0f);
@@ -239,8 +242,8 @@ __global__ void __launch_bounds__(kBlock, HcMinCtas(HC* K, sizeof(RT)))
       }
       v[k] = oct_mul(oct_scale(raw_unpack(kept[s][k]), scale), gm);
       const size_t dense = row0 + static_cast<size_t>(s) * a.h + j * 8;
-      if (ok && a.y) oct_store(static_cast<YT*>(a.y) + dense, v[k]);
-      if (a.y16 == nullptr && a.yq == nullptr) continue;
+      if (LEAN || (ok && a.y)) oct_store(static_cast<YT*>(a.y) + dense, v[k]);
+      if (LEAN || (a.y16 == nullptr && a.yq == nullptr)) continue;
       const uint32_t c = (s0 + s) * a.h + j * 8;  // column within the token's hc h values
       const size_t blocked = (static_cast<size_t>(c >> 6) * a.y16_tokens + t) * 64 + (c & 63u);
       if (ok && a.y16) oct_store(static_cast<f16*>(a.y16) + (a.y16_tokens ? blocked : dense), v[k]);
@@ -255,7 +258,7 @@ __global__ void __launch_bounds__(kBlock, HcMinCtas(HC* K, sizeof(RT)))
         }
       }
     }
-    if (a.iw) {
+    if (!LEAN && a.iw) {
       // partial products of this normalized stream with the next projection's fp32 rows;
       // halo_inject_reduce (kInjectReduce) sums them over the streams
       float ip[8];
@@ -293,7 +296,7 @@ __global__ void __launch_bounds__(kBlock, HcMinCtas(HC* K, sizeof(RT)))
       }
     }
   }
-  if (a.iw && g > 32u) {
+  if (!LEAN && a.iw && g > 32u) {
     __syncthreads();
     if (lir < HC * 8u && grp_ok) {
       const unsigned s = lir >> 3, r = lir & 7u;
@@ -539,6 +542,18 @@ cudaError_t LaunchHcT(const HcArgs& a, cudaStream_t s) {
   const unsigned groups = sh.hc == 1 ? a.tokens * a.hc : a.tokens;
   const unsigned grid = (groups + per_cta - 1) / per_cta;
   const float inv_h = 1.0f / static_cast<float>(a.h);
+  // the lean form: see the kernel
+  const bool lean = !MOE && a.out && a.inject && a.y && !a.y16 && !a.yq && !a.iw &&
+                    a.h / 8 == (static_cast<unsigned>(sh.k) << sh.lg) && groups % per_cta == 0;
+#define HALO_HC_LEAN(HCV, KV)                                                                                      \
+  if constexpr (!MOE) {                                                                                            \
+    if (lean && sh.hc == HCV && sh.k == KV)                                                                        \
+      return LaunchKernel(hc_combine_norm_kernel<RT, OT, YT, HCV, KV, false, true>, grid, kBlock, 0, s, a, sh.lg, inv_h); \
+  }
+  HALO_HC_LEAN(4, 1)
+  HALO_HC_LEAN(1, 2)
+  HALO_HC_LEAN(1, 5)
+#undef HALO_HC_LEAN
 #define HALO_HC_CASE(HCV, KV) \
   if (sh.hc == HCV && sh.k == KV) \
     return LaunchKernel(hc_combine_norm_kernel<RT, OT, YT, HCV, KV, MOE>, grid, kBlock, 0, s, a, sh.lg, inv_h)
