@@ -266,6 +266,7 @@ int RunNormRope(NormRopeArgs a, float theta, const char* what, halo_b200_stream 
 
 std::atomic<int> g_hc_row_level{0};
 std::atomic<int> g_hc_token_k{0};
+std::atomic<int> g_hc_fused_inject{0};
 std::atomic<int> g_conv_tile{0};
 std::atomic<int> g_conv_staged{1};
 
@@ -301,6 +302,7 @@ int RunHc(HcArgs a, const char* what, halo_b200_stream stream, char* err, size_t
     a.y_dtype = (a.out_dtype == a.res_dtype && a.res_dtype != kF32) ? a.res_dtype : kF32;
   a.row_level = g_hc_row_level.load(std::memory_order_relaxed);
   a.token_k = g_hc_token_k.load(std::memory_order_relaxed);
+  a.fused_inject = g_hc_fused_inject.load(std::memory_order_relaxed);
   const cudaError_t e = LaunchHcCombineNorm(a, S(stream));
   if (e == cudaErrorInvalidValue) return Fail(err, errlen, "%s: unsupported (res, out, y) dtype combination or shape", what);
   return Done(e, what, err, errlen);
@@ -403,6 +405,11 @@ int halo_b200_tune(const char* key, int value) {
   if (std::strcmp(key, "conv_tile") == 0) {
     if (value != 0 && value != 4 && value != 8) return -1;
     g_conv_tile.store(value, std::memory_order_relaxed);
+    return 0;
+  }
+  if (std::strcmp(key, "hc_fused_inject") == 0) {
+    if (value != 0 && value != 1) return -1;
+    g_hc_fused_inject.store(value, std::memory_order_relaxed);
     return 0;
   }
   if (std::strcmp(key, "hc_token_k") == 0) {

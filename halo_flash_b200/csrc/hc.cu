@@ -485,6 +485,137 @@ __global__ void __launch_bounds__(kBlock) inject_reduce_kernel(const HcEltArgs a
   static_cast<float*>(a.a)[idx] = acc;
 }
 
+// ---- inject partial products as a pass of their own -------------------------------------------------
+// ipart[t][s][r] = <y[t][s][:], iw[r][s h ..]>. Inside the combine kernel every token re-reads all
+// irows x hc x h weights from L2 (131 KB per token at irows 4, H 2048: 537 MB per 4096 tokens, which cost more
+// than the combine itself). Here a CTA works on ONE stream with one thread per octet of its h columns; the
+// thread keeps its 8 columns of up to 4 weight rows in registers for the whole launch and walks over tokens,
+// four at a time. The normalized values must be the fp32 ones the combine kernel had in registers (an fp16 or
+// bf16 copy would change the products), so the pass reads either an fp32 y or - as the reference's mix epilogue
+// does (src/kernels/core.hip:4097-4099) - rebuilds y = (res * rscale) * gamma from the stored residual, the row
+// scales and the gammas, with the combine kernel's own two multiplies: the same bits, 16 KB per token at H 2048
+// for a bf16 residual. The
+// 4 tokens x 4 rows = 16 partial sums of a thread are reduced over the warp by a transposing butterfly (16
+// shuffles for 16 values instead of 80), over the CTA's warps through shared memory with one barrier per batch.
+// More than 4 rows: one launch per 4 rows (the second reads y from L2).
+__device__ __forceinline__ float warp_reduce16(const float (&v)[16], unsigned lane) {
+  // after the step with stride m, a lane holds the values whose index agrees with its lane bits >= m
+  float w8[8], w4[4], w2[2];
+  const bool b3 = lane & 8u, b2 = lane & 4u, b1 = lane & 2u, b0 = lane & 1u;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) w8[i] = (b3 ? v[i + 8] : v[i]) + __shfl_xor_sync(kFullMask, b3 ? v[i] : v[i + 8], 8);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) w4[i] = (b2 ? w8[i + 4] : w8[i]) + __shfl_xor_sync(kFullMask, b2 ? w8[i] : w8[i + 4], 4);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) w2[i] = (b1 ? w4[i + 2] : w4[i]) + __shfl_xor_sync(kFullMask, b1 ? w4[i] : w4[i + 2], 2);
+  float r = (b0 ? w2[1] : w2[0]) + __shfl_xor_sync(kFullMask, b0 ? w2[0] : w2[1], 1);
+  return r + __shfl_xor_sync(kFullMask, r, 16);  // value (lane & 15), summed over all 32 lanes
+}
+
+constexpr int kInjTokens = 4, kInjRows = 4;
+
+template <typename ST, bool REBUILD, int BLOCK>
+__global__ void __launch_bounds__(BLOCK) hc_inject_kernel(const HcArgs a, const ST* __restrict__ src, const uint32_t r0) {
+  pdl_begin();
+  __shared__ float part[2][16][32];  // [buffer][value][warp]
+  const uint32_t s = blockIdx.x % a.hc, chunk = blockIdx.x / a.hc, chunks = gridDim.x / a.hc;
+  const unsigned octs = a.h >> 3, j = threadIdx.x, lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+  const unsigned warps = (blockDim.x + 31) >> 5;
+  const bool live = j < octs;
+  const uint32_t nr = a.irows - r0 < static_cast<uint32_t>(kInjRows) ? a.irows - r0 : static_cast<uint32_t>(kInjRows);
+  Oct w[kInjRows];
+#pragma unroll
+  for (int r = 0; r < kInjRows; ++r)
+    w[r] = (live && static_cast<uint32_t>(r) < nr)
+               ? oct_load_cached(a.iw + (static_cast<size_t>(r0 + r) * a.hc + s) * a.h + j * 8)
+               : oct_zero();
+  Oct gm = oct_zero();
+  if (REBUILD && live) {
+    gm = oct_load_cached(a.w + static_cast<size_t>(s) * a.h + j * 8);
+    if (a.one_plus) {
+      const float2 one = make_float2(1.0f, 1.0f);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) gm.p[i] = __fadd2_rn(one, gm.p[i]);
+    }
+  }
+  const size_t col_off = static_cast<size_t>(s) * a.h + j * 8;
+  const size_t tok_step = static_cast<size_t>(a.hc) * a.h;
+  const uint32_t batches = (a.tokens + kInjTokens - 1) / kInjTokens;
+  // the rows of the next batch are requested before this batch is computed
+  auto fetch = [&](uint32_t bt, Raw<ST> (&dst)[kInjTokens]) {
+    const uint32_t t0 = bt * kInjTokens;
+#pragma unroll
+    for (int u = 0; u < kInjTokens; ++u) {
+      if (live && bt < batches && t0 + u < a.tokens) dst[u] = raw_load(src + col_off + static_cast<size_t>(t0 + u) * tok_step);
+      else dst[u] = raw_zero<ST>();
+    }
+  };
+  Raw<ST> nxt[kInjTokens];
+  fetch(chunk, nxt);
+  uint32_t n = 0;
+  for (uint32_t bt = chunk; bt < batches; bt += chunks, ++n) {
+    const uint32_t t0 = bt * kInjTokens;
+    Raw<ST> raw[kInjTokens];
+#pragma unroll
+    for (int u = 0; u < kInjTokens; ++u) raw[u] = nxt[u];
+    fetch(bt + chunks, nxt);
+    float scale[kInjTokens];
+    if constexpr (REBUILD) {
+#pragma unroll
+      for (int u = 0; u < kInjTokens; ++u)
+        scale[u] = t0 + u < a.tokens ? a.rscale[static_cast<size_t>(t0 + u) * a.hc + s] : 0.0f;
+    }
+    float v[16];
+#pragma unroll
+    for (int u = 0; u < kInjTokens; ++u) {
+      Oct x = raw_unpack(raw[u]);
+      if constexpr (REBUILD) x = oct_mul(oct_scale(x, scale[u]), gm);  // the combine kernel's y, bit for bit
+#pragma unroll
+      for (int r = 0; r < kInjRows; ++r) {
+        float2 acc = __fmul2_rn(x.p[0], w[r].p[0]);
+        acc = __ffma2_rn(x.p[1], w[r].p[1], acc);
+        acc = __ffma2_rn(x.p[2], w[r].p[2], acc);
+        acc = __ffma2_rn(x.p[3], w[r].p[3], acc);
+        v[u * kInjRows + r] = acc.x + acc.y;
+      }
+    }
+    const float total = warp_reduce16(v, lane);
+    if (lane < 16) part[n & 1u][lane][warp] = total;
+    __syncthreads();
+    if (threadIdx.x < 16) {  // value u * 4 + r of the batch, summed over the CTA's warps
+      const unsigned u = threadIdx.x >> 2, r = threadIdx.x & 3u;
+      float sum = 0.0f;
+      for (unsigned wi = 0; wi < warps; ++wi) sum += part[n & 1u][threadIdx.x][wi];
+      if (t0 + u < a.tokens && r < nr) a.ipart[(static_cast<size_t>(t0 + u) * a.hc + s) * a.irows + r0 + r] = sum;
+    }
+    // the other buffer is written in the next iteration; this one again only after the next barrier
+  }
+}
+
+template <typename ST, bool REBUILD>
+cudaError_t LaunchHcInject(const HcArgs& a, const ST* src, cudaStream_t s) {
+  const unsigned threads = (a.h / 8 + 31) / 32 * 32;
+  const uint32_t batches = (a.tokens + kInjTokens - 1) / kInjTokens;
+  uint32_t chunks = (148u * (threads <= 256 ? 3u : (threads <= 512 ? 2u : 1u))) / a.hc;
+  if (chunks < 1) chunks = 1;
+  if (chunks > batches) chunks = batches;
+  for (uint32_t r0 = 0; r0 < a.irows; r0 += kInjRows) {
+    cudaError_t e;
+    if (threads <= 256) e = LaunchKernel(hc_inject_kernel<ST, REBUILD, 256>, chunks * a.hc, threads, 0, s, a, src, r0);
+    else if (threads <= 512) e = LaunchKernel(hc_inject_kernel<ST, REBUILD, 512>, chunks * a.hc, threads, 0, s, a, src, r0);
+    else e = LaunchKernel(hc_inject_kernel<ST, REBUILD, 1024>, chunks * a.hc, threads, 0, s, a, src, r0);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
+}
+
+// The combine + norm without the partial products, then the pass above. Possible when the fp32 normalized
+// values can be had again: from an fp32 y, or from the stored residual and the row scales.
+bool InjectAsSecondPass(const HcArgs& a) {
+  return a.iw && !a.fused_inject && a.vec && ((a.y && a.y_dtype == kF32) || a.rscale) &&
+         a.h <= 8192u;  // one thread per octet, <= 1024 threads
+}
+
 struct HcShape {
   int hc;  // streams per group: a.hc (token level) or 1 (row level)
   int k;
@@ -683,8 +814,31 @@ cudaError_t LaunchMoeCombine(const MoeCombineArgs& a, cudaStream_t s) {
 
 // (res, out, y) type triples: the reference's (fp32 | fp16 | bf16 residual, fp32 block output and
 // fp32 y) and the all-16-bit forms of a bf16 / fp16 engine.
+namespace {
+cudaError_t LaunchHcTyped(const HcArgs& a, cudaStream_t s);
+}
+
 cudaError_t LaunchHcCombineNorm(const HcArgs& a, cudaStream_t s) {
   if (a.tokens == 0 || a.hc == 0 || a.h == 0) return cudaSuccess;
+  if (!InjectAsSecondPass(a)) return LaunchHcTyped(a, s);
+  HcArgs first = a;
+  first.iw = nullptr;
+  first.ipart = nullptr;
+  first.irows = 0;
+  const cudaError_t e = LaunchHcTyped(first, s);
+  if (e != cudaSuccess) return e;
+  if (a.rscale) {  // rebuild from the residual: 2 bytes per value for a 16-bit residual
+    switch (a.res_dtype) {
+      case kF32: return LaunchHcInject<float, true>(a, static_cast<const float*>(a.res), s);
+      case kF16: return LaunchHcInject<f16, true>(a, static_cast<const f16*>(a.res), s);
+      default: return LaunchHcInject<bf16, true>(a, static_cast<const bf16*>(a.res), s);
+    }
+  }
+  return LaunchHcInject<float, false>(a, static_cast<const float*>(a.y), s);
+}
+
+namespace {
+cudaError_t LaunchHcTyped(const HcArgs& a, cudaStream_t s) {
   const int r = a.res_dtype, o = a.out_dtype, y = a.y_dtype;
   if (r == kF32 && o == kF32 && y == kF32) return LaunchHcM<float, float, float>(a, s);
   if (r == kF16 && o == kF32 && y == kF32) return LaunchHcM<f16, float, float>(a, s);
@@ -696,6 +850,7 @@ cudaError_t LaunchHcCombineNorm(const HcArgs& a, cudaStream_t s) {
   if (r == kF16 && o == kF16 && y == kF16) return LaunchHcM<f16, f16, f16>(a, s);
   return cudaErrorInvalidValue;
 }
+}  // namespace
 
 cudaError_t LaunchHcElt(const HcEltArgs& a, cudaStream_t s) {
   if (a.tokens == 0 || a.h == 0) return cudaSuccess;

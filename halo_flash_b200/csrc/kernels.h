@@ -259,6 +259,7 @@ struct HcArgs {
   int one_plus;
   int res_dtype, out_dtype, y_dtype;
   int vec;
+  int fused_inject;  // tuning: 1 = the partial products are always computed inside the combine kernel
   int token_k;    // tuning: 2 = token-level shapes take two octets per stream per thread where they fit
   int row_level;  // tuning: 1 = one thread group per (token, stream) row even where a token-level shape exists
 };

@@ -480,6 +480,8 @@ const char* halo_b200_kernel_name(size_t index);
  * "conv_staged" (1, the default = the conv kernel stages rows in shared memory by bulk asynchronous copies; 0 = rows in registers),
  * "conv_tile" (tokens per thread of the register form of the conv kernel: 4 or 8; 0 = built-in), "hc_token_k" (2 = two
  * chunks per stream per thread in the token-level hyper-connection kernel where they fit),
+ * "hc_fused_inject" (1 = the inject partial products are computed inside the combine kernel even where a second
+ * pass over the normalized rows would do; 0 = built-in choice),
  * "pdl" (1, the default = kernels are launched with programmatic stream serialization, so a kernel is scheduled
  * while its predecessor in the stream drains and waits on the device for it to complete; 0 = plain launches).
  * Returns 0, or -1 for an unknown key or value. */

@@ -521,3 +521,38 @@ def test_committed_outputs_of_the_compiled_reference():
     assert_rows_close(to_f32(cout).reshape(-1, s.lin_dim), g["conv_out"].reshape(-1, s.lin_dim), what="golden conv")
     ops.conv_state_advance(to_dev(g["conv_x"]), cst)
     assert np.array_equal(cst.cpu().numpy(), g["conv_state_out"])
+
+
+@pytest.mark.parametrize("T,hc,h,irows,rdt", [(9, 4, 2048, 4, "bf16"), (6, 4, 2560, 8, "bf16"), (7, 4, 256, 3, "f32"),
+                                              (5, 2, 512, 5, "f16"), (3, 4, 8192, 4, "bf16")])
+def test_inject_partials_in_a_pass_of_their_own(orc, T, hc, h, irows, rdt):
+    """Where the fp32 normalized values can be had again (an fp32 y, or the stored residual and the row scales),
+    the partial products run as a second pass with the weights in registers; it must agree with the products
+    computed inside the combine kernel, and with the oracle's projection of the fp32 y."""
+    res, out, inject, w = inputs(f"t.hc.inj2.{h}", T, hc, h, rdt, "f32")
+    iw = (synth.act(f"t.hc.inj2.iw.{h}", irows, hc * h) * 0.05).astype(np.float32)
+
+    def run(fused, with_y32, with_rscale):
+        lib().tune("hc_fused_inject", fused)
+        try:
+            d_res = to_dev(res, rdt)
+            y = torch.empty(T, hc, h, device=DEV) if with_y32 else None
+            y16 = torch.empty(T, hc, h, device=DEV, dtype=torch.float16)
+            rscale = torch.empty(T, hc, device=DEV) if with_rscale else None
+            ipart = torch.full((T, hc, irows), float("nan"), device=DEV)
+            ops.hc_combine_norm(d_res, to_dev(out), to_dev(inject), to_dev(w), EPS, y=y, y16=y16, rscale=rscale,
+                                iw=to_dev(iw), ipart=ipart)
+            return to_f32(ipart), (to_f32(y) if with_y32 else None), to_f32(d_res)
+        finally:
+            lib().tune("hc_fused_inject", 0)
+
+    fused, y32, res_after = run(1, True, True)
+    want = orc.hc_inject(y32.reshape(T, -1), iw)
+    bound = np.abs(y32.reshape(T, hc, 1, h) * iw.reshape(1, irows, hc, h).transpose(0, 2, 1, 3)).sum(axis=3)  # [T, hc, irows]
+    tot = bound.sum(axis=1)
+    assert np.all(np.abs(fused.sum(axis=1) - want) <= 1e-5 * tot + 1e-30), "in-kernel products"
+    for with_y32, with_rscale in ((False, True), (True, False), (True, True)):  # rebuild from res, fp32 y, rebuild preferred
+        got, _, res2 = run(0, with_y32, with_rscale)
+        assert np.array_equal(res2, res_after)
+        assert np.all(np.abs(got - fused) <= 2e-6 * bound + 1e-30), f"second pass (y32={with_y32}, rscale={with_rscale}) vs in-kernel"
+        assert np.all(np.abs(got.sum(axis=1) - want) <= 1e-5 * tot + 1e-30)
