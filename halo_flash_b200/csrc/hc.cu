@@ -517,7 +517,7 @@ constexpr int kInjTokens = 4, kInjRows = 4;
 template <typename ST, bool REBUILD, int BLOCK>
 __global__ void __launch_bounds__(BLOCK) hc_inject_kernel(const HcArgs a, const ST* __restrict__ src, const uint32_t r0) {
   pdl_begin();
-  __shared__ float part[2][16][32];  // [buffer][value][warp]
+  __shared__ float part[2][4][16][32];  // [buffer][batch of the group][value][warp]
   const uint32_t s = blockIdx.x % a.hc, chunk = blockIdx.x / a.hc, chunks = gridDim.x / a.hc;
   const unsigned octs = a.h >> 3, j = threadIdx.x, lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
   const unsigned warps = (blockDim.x + 31) >> 5;
@@ -550,6 +550,21 @@ __global__ void __launch_bounds__(BLOCK) hc_inject_kernel(const HcArgs a, const 
       else dst[u] = raw_zero<ST>();
     }
   };
+  // sums the warps' partials of the group of (up to four) batches ending with the CTA's batch number `last`
+  // and writes them: thread b * 16 + v takes value v = u * 4 + r of the group's batch b
+  auto flush = [&](uint32_t last) {
+    __syncthreads();
+    for (uint32_t idx = threadIdx.x; idx < 64; idx += blockDim.x) {
+      const uint32_t b = idx >> 4, val = idx & 15u, first = last & ~3u;
+      if (first + b <= last) {
+        const uint32_t t = (chunk + (first + b) * chunks) * kInjTokens + (val >> 2), r = val & 3u;
+        float sum = 0.0f;
+        for (unsigned wi = 0; wi < warps; ++wi) sum += part[(last >> 2) & 1u][b][val][wi];
+        if (t < a.tokens && r < nr) a.ipart[(static_cast<size_t>(t) * a.hc + s) * a.irows + r0 + r] = sum;
+      }
+    }
+    // the other buffer is written by the next group; this one again only after the next flush's barrier
+  };
   Raw<ST> nxt[kInjTokens];
   fetch(chunk, nxt);
   uint32_t n = 0;
@@ -580,16 +595,10 @@ __global__ void __launch_bounds__(BLOCK) hc_inject_kernel(const HcArgs a, const 
       }
     }
     const float total = warp_reduce16(v, lane);
-    if (lane < 16) part[n & 1u][lane][warp] = total;
-    __syncthreads();
-    if (threadIdx.x < 16) {  // value u * 4 + r of the batch, summed over the CTA's warps
-      const unsigned u = threadIdx.x >> 2, r = threadIdx.x & 3u;
-      float sum = 0.0f;
-      for (unsigned wi = 0; wi < warps; ++wi) sum += part[n & 1u][threadIdx.x][wi];
-      if (t0 + u < a.tokens && r < nr) a.ipart[(static_cast<size_t>(t0 + u) * a.hc + s) * a.irows + r0 + r] = sum;
-    }
-    // the other buffer is written in the next iteration; this one again only after the next barrier
+    if (lane < 16) part[(n >> 2) & 1u][n & 3u][lane][warp] = total;
+    if ((n & 3u) == 3u) flush(n);  // the CTA meets once per four batches
   }
+  if ((n & 3u) != 0u) flush(n - 1);  // the last, partial group (n is now the number of batches done)
 }
 
 template <typename ST, bool REBUILD>
