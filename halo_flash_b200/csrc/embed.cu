@@ -25,45 +25,72 @@ __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
 }
 
+// A warp works on one SEGMENT of one row: 1 / segs of its blocks (a multiple of 8 blocks, so a multiple of
+// 272 = 17 x 16 bytes: the segment starts 16-byte aligned in the table). segs is 1 for streaming sizes; when
+// the launch cannot fill the GPU anyway it is raised (up to 8) so that a lane converts as few octets as
+// possible: a lane's chain of dependent instructions is what such a launch lasts (8 octets per lane at
+// 2048 columns and segs = 1, one at segs = 8).
 template <typename OT>
 __global__ void __launch_bounds__(kBlock) embed_q8_0_kernel(const EmbedArgs a, const unsigned warps,
-                                                           const unsigned row_smem) {
+                                                           const unsigned seg_smem, const unsigned segs) {
   pdl_begin();
   extern __shared__ __align__(16) uint8_t stage[];
   const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   if (warp >= warps) return;
-  uint8_t* buf = stage + static_cast<size_t>(warp) * row_smem;
-  const unsigned chunks = static_cast<unsigned>(a.row_bytes / 16);
-  const unsigned octs = a.cols / 8;
+  uint8_t* buf = stage + static_cast<size_t>(warp) * seg_smem;
+  const unsigned seg_blocks = (a.cols / 32) / segs;
+  const unsigned seg_bytes = seg_blocks * 34;
+  const unsigned chunks = segs > 1 ? seg_bytes / 16 : static_cast<unsigned>(a.row_bytes / 16);
+  const unsigned octs = seg_blocks * 4;
   OT* out = static_cast<OT*>(a.out);
-  for (uint32_t t = blockIdx.x * warps + warp; t < a.tokens; t += gridDim.x * warps) {
+  const uint32_t items = a.tokens * segs;
+  for (uint32_t item = blockIdx.x * warps + warp; item < items; item += gridDim.x * warps) {
+    const uint32_t t = item / segs, sg = item - t * segs;
     const uint32_t id = a.ids ? a.ids[static_cast<size_t>(t) * a.id_stride + a.id_slot] : a.token;
     const bool in_range = a.vocab == 0 || id < a.vocab;
     if (in_range) {
-      const uint8_t* src = a.table + static_cast<size_t>(id) * a.row_bytes;
+      const uint8_t* src = a.table + static_cast<size_t>(id) * a.row_bytes + static_cast<size_t>(sg) * seg_bytes;
       for (unsigned c = lane; c < chunks; c += 32) cp_async16(buf + c * 16, src + c * 16);
       cp_async_wait_all();
     }
     __syncwarp();
+    OT* dst = out + static_cast<size_t>(t) * a.cols + static_cast<size_t>(sg) * seg_blocks * 32;
     for (unsigned j = lane; j < octs; j += 32) {
       float v[8];
       if (in_range) {
         const uint8_t* blk = buf + (j >> 2) * 34;
         const float d = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(blk)));
-        const uint16_t* q = reinterpret_cast<const uint16_t*>(blk + 2 + 8 * (j & 3u));
+        // the 8 code bytes start 2 bytes into a block, so on a 4-byte boundary in odd blocks only: three
+        // aligned words and a funnel shift by 0 or 16 bits give them as two words either way
+        const unsigned at = static_cast<unsigned>(blk - buf) + 2u + 8u * (j & 3u);
+        const uint32_t* w32 = reinterpret_cast<const uint32_t*>(buf + (at & ~3u));
+        const unsigned sh = (at & 2u) * 8u;
+        // the third word is needed only for the shifted case, which never is the buffer's last block (a
+        // segment has a multiple of 8 blocks and odd blocks are aligned; a whole row of any other block
+        // count ends at least 2 bytes before its 16-byte padded buffer does): reading it unconditionally
+        // ran 4 bytes past the last warp's buffer
+        const uint32_t w0 = w32[0], w1 = w32[1], w2 = sh ? w32[2] : 0u;
+        const uint32_t code[2] = {__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh)};
+        // int8 -> float without a conversion instruction: the byte, biased by 128, becomes the low mantissa
+        // byte of 2^23 (0x4B0000xx = 2^23 + xx); subtracting 2^23 + 128 leaves the code, exactly; then x scale
+        const float2 bias = make_float2(-8388736.0f, -8388736.0f), d2 = make_float2(d, d);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint16_t pair = q[i];
-          v[2 * i] = d * static_cast<float>(static_cast<int8_t>(pair & 0xFFu));
-          v[2 * i + 1] = d * static_cast<float>(static_cast<int8_t>(pair >> 8));
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t x = code[h] ^ 0x80808080u;
+          const float2 lo = make_float2(__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7540)),
+                                        __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7541)));
+          const float2 hi = make_float2(__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7542)),
+                                        __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7543)));
+          const float2 a0 = __fmul2_rn(__fadd2_rn(lo, bias), d2), a1 = __fmul2_rn(__fadd2_rn(hi, bias), d2);
+          v[4 * h] = a0.x, v[4 * h + 1] = a0.y, v[4 * h + 2] = a1.x, v[4 * h + 3] = a1.y;
         }
       } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = 0.0f;
       }
-      store8(out + static_cast<size_t>(t) * a.cols + j * 8, v);
+      store8(dst + j * 8, v);
     }
-    __syncwarp();  // the row buffer is reused by the next token
+    __syncwarp();  // the segment buffer is reused by the warp's next item
   }
 }
 
@@ -93,9 +120,14 @@ cudaError_t LaunchEmbedT(const EmbedArgs& a, cudaStream_t s) {
   unsigned warps = kWarps;
   while (warps > 1 && static_cast<size_t>(warps) * row_smem > 48u * 1024u) warps >>= 1;
   if (a.vec && static_cast<size_t>(warps) * row_smem <= 48u * 1024u) {
-    unsigned grid = (a.tokens + warps - 1) / warps;
+    // segments per row: as many (<= 8) as keep every warp busy once, whole groups of 8 blocks each
+    const unsigned blocks = a.cols / 32;
+    unsigned segs = 1;
+    while (segs < 8 && blocks % (16 * segs) == 0 && static_cast<uint64_t>(a.tokens) * segs * 2 <= 148u * 64u) segs <<= 1;
+    unsigned grid = (a.tokens * segs + warps - 1) / warps;
     if (grid > 148u * 8u) grid = 148u * 8u;
-    LaunchKernel(embed_q8_0_kernel<OT>, grid, kBlock, static_cast<size_t>(warps) * row_smem, s, a, warps, row_smem);
+    const unsigned seg_smem = segs > 1 ? (blocks / segs) * 34 : row_smem;
+    LaunchKernel(embed_q8_0_kernel<OT>, grid, kBlock, static_cast<size_t>(warps) * seg_smem, s, a, warps, seg_smem, segs);
     return cudaGetLastError();
   }
   const size_t total = static_cast<size_t>(a.tokens) * a.cols;
