@@ -244,10 +244,12 @@ __global__ void __launch_bounds__(kBlock) norm_rows_lean_kernel(const LeanArgs a
     Raw<XT> rd[K];
 #pragma unroll
     for (int k = 0; k < K; ++k) rd[k] = raw_load(dl + (((k << lg) + lir) << 3));
+    const uint64_t keep = l2_keep_policy();
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       v[k] = oct_add(raw_unpack(rx[k]), raw_unpack(rd[k]));
-      oct_store_round(res + (((k << lg) + lir) << 3), v[k]);  // the norm reads the residual as stored
+      // the norm reads the residual as stored; the next add + norm reads it again: ask L2 to keep it
+      oct_store_round_keep(res + (((k << lg) + lir) << 3), v[k], keep);
     }
   } else {
 #pragma unroll
