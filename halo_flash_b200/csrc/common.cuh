@@ -213,6 +213,13 @@ __device__ __forceinline__ uint64_t l2_keep_policy() {
   asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
   return p;
 }
+// The keep policy, or the ordinary one when the buffer is too large to stay (selected without a branch).
+__device__ __forceinline__ uint64_t l2_policy(bool keep) {
+  uint64_t normal;
+  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(normal));
+  const uint64_t last = l2_keep_policy();
+  return keep ? last : normal;
+}
 __device__ __forceinline__ void store16_keep(void* p, uint4 u, uint64_t policy) {
   asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(p), "r"(u.x), "r"(u.y), "r"(u.z),
                "r"(u.w), "l"(policy)
