@@ -31,6 +31,7 @@ SIGNATURES: dict[str, list] = {
     "halo_b200_quantize_q8_rows": [_p, _p, _p, _u32, _u32],
     "halo_b200_quantize_q8_kblocked": [_p, _p, _p, _u32, _u32],
     "halo_b200_q8x_cols": [_p, _u32, _u32, _p, _p, _p, _p, _u32],
+    "halo_b200_hc_norm_q8x": [_p, _p, _p, _p, _u32, _u32, _p, _p, _p, _p, _u32],
     "halo_b200_encode_q8_0_rows": [_p, _i, _p, _u32, _u32],
     "halo_b200_l2norm": [_p, _u32, _f, _u32],
     "halo_b200_l2norm_ex": [_p, _i, _p, _i, _u32, _f, _u32],
@@ -90,8 +91,10 @@ SIGNATURES: dict[str, list] = {
     "halo_b200_conv_l2norm_ex": [_p, _i, _p, _p, _p, _i, _u32, _u32, _u32, _u32, _f, _u32],
     "halo_b200_conv_state_advance": [_p, _i, _p, _u32, _u32, _u32],
     "halo_b200_conv_l2norm": [_p, _p, _p, _p, _u32, _u32, _u32, _f, _u32],
+    "halo_b200_conv_l2norm_y": [_p, _p, _u32, _u32, _p, _p, _u32, _u32, _u32, _f, _u32, _u32, _u32],
     "halo_b200_conv_step": [_p, _p, _p, _p, _u32, _u32],
     "halo_b200_copy_at": [_p, _i, _p, _p, _u32, _u32, _u32],
+    "halo_b200_copy_at_y": [_p, _u32, _u32, _i, _p, _p, _u32, _u32, _u32, _u32, _u32, _u32],
     "halo_b200_copy": [_p, _p, _u32],
     "halo_b200_f16_rows": [_p, _p, _u32],
     "halo_b200_scale_silu": [_p, _p, _i, _f, _u32],

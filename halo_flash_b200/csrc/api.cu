@@ -174,7 +174,13 @@ int RunQuant(QuantArgs a, const char* what, halo_b200_stream stream, char* err, 
   if (a.kb_tokens) REQUIRE(a.cols % 64 == 0, "%s: K-blocked layout needs cols %% 64 == 0", what);
   REQUIRE(Aligned(a.x, DTypeSize(a.x_dtype)) && Aligned(a.xd, 4) && Aligned(a.xd2, 4) && Aligned(a.q8_0, 2),
           "%s: pointer not aligned to its element type", what);
-  a.vec = Aligned(a.x, 16) && a.x_stride % 8 == 0 && Aligned(a.xq, 8) && Aligned(a.xq2, 8);
+  if (a.pre_w) {
+    REQUIRE(a.pre_scale && a.xn, "%s: null pointer", what);
+    REQUIRE(a.pre_h > 0 && a.cols % a.pre_h == 0, "%s: h = %u does not divide the row of %u", what, a.pre_h, a.cols);
+    REQUIRE(Aligned(a.pre_scale, 4) && Aligned(a.pre_w, 4) && Aligned(a.xn, 4), "%s: pointer not aligned to its element type", what);
+  }
+  a.vec = Aligned(a.x, 16) && a.x_stride % 8 == 0 && Aligned(a.xq, 8) && Aligned(a.xq2, 8) &&
+          (a.pre_w == nullptr || (a.pre_h % 8 == 0 && Aligned(a.pre_w, 16) && Aligned(a.xn, 16)));
   return Done(LaunchQuantize(a, S(stream)), what, err, errlen);
 }
 
@@ -346,6 +352,28 @@ int RunConv(ConvArgs a, bool advance_only, const char* what, halo_b200_stream st
   a.staged = g_conv_staged.load(std::memory_order_relaxed);
   const cudaError_t e = LaunchConvL2norm(a, S(stream));
   if (e == cudaErrorInvalidValue) return Fail(err, errlen, "%s: unsupported (in, out) dtype pair or chunk too long", what);
+  return Done(e, what, err, errlen);
+}
+
+
+// One decode step: conv, state shift, SiLU and L2 norm in one launch, for one session (`state`) or for
+// `entries` sessions whose states come from a table of device addresses.
+int RunConvStep(ConvArgs a, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+  if (a.entries == 0 || a.channels == 0) return Done(cudaSuccess, what, err, errlen);
+  REQUIRE(a.in && a.out && a.w, "%s: null pointer", what);
+  REQUIRE(a.kern >= 1 && a.kern <= 9, "%s: conv kernel length %u outside 1..9", what, a.kern);
+  REQUIRE(a.state_tab != nullptr || a.entries == 1, "%s: more than one entry needs the state table", what);
+  REQUIRE(a.kern < 2 || a.state_tab != nullptr || a.state != nullptr, "%s: state is null", what);
+  REQUIRE(Aligned(a.in, DTypeSize(a.in_dtype)) && Aligned(a.out, DTypeSize(a.out_dtype)) && Aligned(a.w, 4) &&
+              Aligned(a.state, 4) && Aligned(a.state_tab, 8),
+          "%s: pointer not aligned to its element type", what);
+  REQUIRE(a.l2_channels <= a.channels, "%s: l2_channels exceeds channels", what);
+  if (a.d == 0) a.d = 128;
+  REQUIRE(a.d <= 1024 && (a.l2_channels == 0 || a.l2_channels % a.d == 0),
+          "%s: the normalized channels must be whole heads of d <= 1024 channels", what);
+  REQUIRE(a.entries <= 65535u, "%s: more than 65535 entries", what);
+  const cudaError_t e = LaunchConvStep(a, S(stream));
+  if (e == cudaErrorInvalidValue) return Fail(err, errlen, "%s: unsupported (in, out) dtype pair", what);
   return Done(e, what, err, errlen);
 }
 
@@ -637,6 +665,27 @@ int halo_b200_q8x_cols(halo_b200_stream stream, const float* x, uint32_t xstride
   a.xd2 = xs2;
   REQUIRE(batch == 0 || (xq && xs), "halo_q8x_cols: null output");
   return RunQuant(a, "halo_q8x_cols", stream, err, errlen);
+}
+
+int halo_b200_hc_norm_q8x(halo_b200_stream stream, const float* res, const float* scale, const float* norm_w,
+                          float* xn, uint32_t hc, uint32_t h, int8_t* xq, float* xs, int8_t* xq2, float* xs2,
+                          uint32_t batch, char* err, size_t errlen) {
+  QuantArgs a;
+  a.x = res;
+  a.x_stride = static_cast<uint64_t>(hc) * h;
+  a.cols = hc * h;
+  a.rows = batch;
+  a.xq = xq;
+  a.xd = xs;
+  a.xq2 = xq2;
+  a.xd2 = xs2;
+  a.pre_scale = scale;
+  a.pre_w = norm_w;
+  a.pre_h = h;
+  a.xn = xn;
+  if (batch == 0 || a.cols == 0) return Done(cudaSuccess, "", err, errlen);
+  REQUIRE(scale && norm_w && xn && xq && xs, "halo_hc_norm_q8x: null pointer");
+  return RunQuant(a, "halo_hc_norm_q8x", stream, err, errlen);
 }
 
 int halo_b200_encode_q8_0_rows(halo_b200_stream stream, const void* x, int x_dtype, uint8_t* out, uint32_t cols,
@@ -1316,10 +1365,46 @@ int halo_b200_conv_l2norm_prefill8(halo_b200_stream stream, const void* in, int 
 int halo_b200_conv_l2norm(halo_b200_stream stream, const float* in, float* state, const float* w, float* out,
                           uint32_t channels, uint32_t kern, uint32_t l2_channels, float eps, uint32_t d, char* err,
                           size_t errlen) {
-  const int rc = halo_b200_conv_l2norm_ex(stream, in, kF32, state, w, out, kF32, channels, kern, l2_channels, d, eps, 1,
-                                          err, errlen);
-  if (rc != 0) return rc;
-  return halo_b200_conv_state_advance(stream, in, kF32, state, channels, kern, 1, err, errlen);
+  ConvArgs a{};
+  a.in = in;
+  a.in_dtype = kF32;
+  a.state = state;
+  a.w = w;
+  a.out = out;
+  a.out_dtype = kF32;
+  a.channels = channels;
+  a.kern = kern;
+  a.l2_channels = l2_channels;
+  a.d = d;
+  a.eps = eps;
+  a.tokens = 1;
+  a.entries = 1;
+  return RunConvStep(a, "halo_conv_l2norm", stream, err, errlen);
+}
+
+int halo_b200_conv_l2norm_y(halo_b200_stream stream, const float* in, const uint64_t* tab, uint32_t tstride,
+                            uint32_t tslot, const float* w, float* out, uint32_t channels, uint32_t kern,
+                            uint32_t l2_channels, float eps, uint32_t stride, uint32_t d, uint32_t entries, char* err,
+                            size_t errlen) {
+  ConvArgs a{};
+  a.in = in;
+  a.in_dtype = kF32;
+  a.w = w;
+  a.out = out;
+  a.out_dtype = kF32;
+  a.channels = channels;
+  a.kern = kern;
+  a.l2_channels = l2_channels;
+  a.d = d;
+  a.eps = eps;
+  a.tokens = 1;
+  a.entries = entries;
+  a.entry_stride = stride;
+  a.state_tab = tab;
+  a.tstride = tstride;
+  a.tslot = tslot;
+  REQUIRE(entries == 0 || tab != nullptr, "halo_conv_l2norm_y: the state table is null");
+  return RunConvStep(a, "halo_conv_l2norm_y", stream, err, errlen);
 }
 
 int halo_b200_conv_step(halo_b200_stream stream, const float* in, float* state, const float* w, float* out,
@@ -1346,6 +1431,30 @@ int halo_b200_copy_at(halo_b200_stream stream, void* dst, int dst_dtype, const f
   a.at_slot = slot;
   a.at_stride = stride;
   return RunHcElt(a, "halo_copy_at", stream, err, errlen);
+}
+
+int halo_b200_copy_at_y(halo_b200_stream stream, const uint64_t* tab, uint32_t tstride, uint32_t tslot, int dst_dtype,
+                        const float* src, const uint32_t* params, uint32_t slot, uint32_t stride, uint32_t n,
+                        uint32_t src_stride, uint32_t pstride, uint32_t entries, char* err, size_t errlen) {
+  if (entries == 0 || n == 0) return Done(cudaSuccess, "", err, errlen);
+  REQUIRE(tab && src && params, "halo_copy_at_y: null pointer");
+  REQUIRE(dst_dtype == kF32 || dst_dtype == kF16 || dst_dtype == kBF16, "halo_copy_at_y: unknown dtype");
+  REQUIRE(Aligned(tab, 8) && Aligned(src, 4) && Aligned(params, 4), "halo_copy_at_y: pointer not aligned to its element type");
+  REQUIRE(entries <= 65535u, "halo_copy_at_y: more than 65535 entries");
+  CopyAtArgs a{};
+  a.tab = tab;
+  a.tstride = tstride;
+  a.tslot = tslot;
+  a.dst_dtype = dst_dtype;
+  a.src = src;
+  a.params = params;
+  a.slot = slot;
+  a.stride = stride;
+  a.n = n;
+  a.src_stride = src_stride;
+  a.pstride = pstride;
+  a.entries = entries;
+  return Done(LaunchCopyAtEntries(a, S(stream)), "halo_copy_at_y", err, errlen);
 }
 
 int halo_b200_copy(halo_b200_stream stream, float* dst, const float* src, uint32_t n, char* err, size_t errlen) {

@@ -327,6 +327,54 @@ __global__ void __launch_bounds__(1024) conv_l2norm_scalar_kernel(const ConvArgs
   if (live) static_cast<OT*>(a.out)[static_cast<size_t>(t) * a.channels + ch] = from_f32<OT>(v);
 }
 
+// One decode step of `entries` sessions (src/kernels/core.hip:3005-3028, src/kernels/batch_decode.hip:1741-1748):
+// the conv over the session's state and its new input, the state shifted by one with the input appended, SiLU,
+// and the L2 norm of the q/k heads, in one launch. One CTA per (head, entry), one channel per thread: a thread
+// reads its own state column before it writes it, so nothing else orders the update.
+template <typename IT, typename OT>
+__global__ void __launch_bounds__(1024) conv_step_kernel(const ConvArgs a) {
+  pdl_begin();
+  __shared__ float scratch[32];
+  __shared__ float total;
+  const uint32_t e = blockIdx.y;
+  const uint32_t ch = blockIdx.x * a.d + threadIdx.x;
+  const bool live = threadIdx.x < a.d && ch < a.channels;
+  const IT* in = static_cast<const IT*>(a.in) + static_cast<size_t>(e) * a.entry_stride;
+  OT* out = static_cast<OT*>(a.out) + static_cast<size_t>(e) * a.entry_stride;
+  float* state = a.state_tab ? reinterpret_cast<float*>(a.state_tab[static_cast<size_t>(e) * a.tstride + a.tslot]) : a.state;
+  float v = 0.0f;
+  if (live) {
+    const float* w = a.w + static_cast<size_t>(ch) * a.kern;
+    const float x = to_f32(in[ch]);
+    float acc = __fmul_rn(w[a.kern - 1], x);
+    float older[8];  // kern <= 9
+#pragma unroll
+    for (uint32_t k = 0; k < 8; ++k)
+      if (k + 1 < a.kern) {
+        older[k] = state[static_cast<size_t>(k) * a.channels + ch];
+        acc = __fmaf_rn(w[k], older[k], acc);
+      }
+#pragma unroll
+    for (uint32_t k = 0; k < 7; ++k)
+      if (k + 2 < a.kern) state[static_cast<size_t>(k) * a.channels + ch] = older[k + 1];
+    if (a.kern > 1) state[static_cast<size_t>(a.kern - 2) * a.channels + ch] = x;
+    v = silu_f(acc);
+  }
+  if (blockIdx.x * a.d < a.l2_channels) {  // CTA-uniform
+    const float ss = warp_sum(live ? __fmul_rn(v, v) : 0.0f);
+    if ((threadIdx.x & 31u) == 0) scratch[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float s = 0.0f;
+      for (unsigned i = 0; i < (blockDim.x + 31) / 32; ++i) s += scratch[i];
+      total = s;
+    }
+    __syncthreads();
+    v *= rsqrtf(total + a.eps);
+  }
+  if (live) out[ch] = from_f32<OT>(v);
+}
+
 // The conv state after a chunk: the last kern - 1 inputs, the older ones from the previous state when
 // the chunk is shorter than that (src/kernels/core.hip:3578-3611). One thread per channel.
 template <typename IT>
@@ -417,6 +465,24 @@ cudaError_t LaunchConvL2norm(const ConvArgs& a, cudaStream_t s) {
   if (i == kF16 && o == kF16) return LaunchConvT<f16, f16>(a, s);
   if (i == kBF16 && o == kBF16) return LaunchConvT<bf16, bf16>(a, s);
   if (i == kBF16 && o == kF32) return LaunchConvT<bf16, float>(a, s);
+  return cudaErrorInvalidValue;
+}
+
+template <typename IT, typename OT>
+cudaError_t LaunchConvStepT(const ConvArgs& a, cudaStream_t s) {
+  const dim3 grid((a.channels + a.d - 1) / a.d, a.entries);
+  return LaunchKernel(conv_step_kernel<IT, OT>, grid, dim3((a.d + 31) / 32 * 32), 0, s, a);
+}
+
+cudaError_t LaunchConvStep(const ConvArgs& a, cudaStream_t s) {
+  if (a.entries == 0 || a.channels == 0) return cudaSuccess;
+  if (a.d == 0 || a.d > 1024 || a.entries > 65535u || a.kern < 1 || a.kern > 9) return cudaErrorInvalidValue;
+  const int i = a.in_dtype, o = a.out_dtype;
+  if (i == kF32 && o == kF32) return LaunchConvStepT<float, float>(a, s);
+  if (i == kF16 && o == kF32) return LaunchConvStepT<f16, float>(a, s);
+  if (i == kF16 && o == kF16) return LaunchConvStepT<f16, f16>(a, s);
+  if (i == kBF16 && o == kBF16) return LaunchConvStepT<bf16, bf16>(a, s);
+  if (i == kBF16 && o == kF32) return LaunchConvStepT<bf16, float>(a, s);
   return cudaErrorInvalidValue;
 }
 

@@ -861,6 +861,34 @@ cudaError_t LaunchHcTyped(const HcArgs& a, cudaStream_t s) {
 }
 }  // namespace
 
+namespace {
+// One thread per element: the destinations come from a table in device memory, so nothing about their
+// alignment is known at launch.
+template <typename AT>
+__global__ void __launch_bounds__(kBlock) copy_at_entries_kernel(const CopyAtArgs a) {
+  pdl_begin();
+  const uint32_t e = blockIdx.y;
+  AT* dst = reinterpret_cast<AT*>(a.tab[static_cast<size_t>(e) * a.tstride + a.tslot]) +
+            static_cast<size_t>(a.params[static_cast<size_t>(e) * a.pstride + a.slot]) * a.stride;
+  const float* src = a.src + static_cast<size_t>(e) * a.src_stride;
+  for (uint32_t i = blockIdx.x * kBlock + threadIdx.x; i < a.n; i += gridDim.x * kBlock) dst[i] = from_f32<AT>(src[i]);
+}
+}  // namespace
+
+cudaError_t LaunchCopyAtEntries(const CopyAtArgs& a, cudaStream_t s) {
+  if (a.entries == 0 || a.n == 0) return cudaSuccess;
+  if (a.entries > 65535u) return cudaErrorInvalidValue;
+  unsigned gx = (a.n + kBlock - 1) / kBlock;
+  if (gx > 148u * 8u) gx = 148u * 8u;
+  const dim3 grid(gx, a.entries);
+  switch (a.dst_dtype) {
+    case kF32: return LaunchKernel(copy_at_entries_kernel<float>, grid, kBlock, 0, s, a);
+    case kF16: return LaunchKernel(copy_at_entries_kernel<f16>, grid, kBlock, 0, s, a);
+    case kBF16: return LaunchKernel(copy_at_entries_kernel<bf16>, grid, kBlock, 0, s, a);
+  }
+  return cudaErrorInvalidValue;
+}
+
 cudaError_t LaunchHcElt(const HcEltArgs& a, cudaStream_t s) {
   if (a.tokens == 0 || a.h == 0) return cudaSuccess;
   if (a.op == kInjectReduce) {

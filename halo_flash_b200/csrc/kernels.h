@@ -227,6 +227,11 @@ struct QuantArgs {
   uint32_t kb_tokens = 0;   // > 0: K-blocked
   int8_t* xq2 = nullptr;    // optional second (residual) level, row-major only
   float* xd2 = nullptr;
+  // optional product in front of the quantizer: v = (x * pre_scale[row][c / pre_h]) * pre_w[c], also stored to xn
+  const float* pre_scale = nullptr;
+  const float* pre_w = nullptr;
+  uint32_t pre_h = 0;
+  float* xn = nullptr;
   bool vec = true;
 };
 cudaError_t LaunchQuantize(const QuantArgs& a, cudaStream_t s);
@@ -289,6 +294,19 @@ struct HcEltArgs {
 };
 cudaError_t LaunchHcElt(const HcEltArgs& a, cudaStream_t s);
 
+// Row append for `entries` sessions in one launch (src/kernels/batch_decode.hip:1700-1707): entry e copies
+// src[e * src_stride ..+ n] to row params[e * pstride + slot] (rows `stride` elements apart) of the buffer whose
+// device address is tab[e * tstride + tslot].
+struct CopyAtArgs {
+  const uint64_t* tab;
+  uint32_t tstride, tslot;
+  const float* src;
+  const uint32_t* params;
+  uint32_t slot, stride, n, src_stride, pstride, entries;
+  int dst_dtype;
+};
+cudaError_t LaunchCopyAtEntries(const CopyAtArgs& a, cudaStream_t s);
+
 // Causal depthwise conv + SiLU + per-head L2 norm of a Gated DeltaNet layer (src/kernels/core.hip:
 // 445-456, 3002-3028, 3486-3611).
 struct ConvArgs {
@@ -302,8 +320,15 @@ struct ConvArgs {
   int vec;
   int tile;    // tuning: tokens per thread of the register form, 4 or 8 (0 = built-in choice)
   int staged;  // 1 = rows staged in shared memory by bulk asynchronous copies; 0 = rows held in registers
+  // decode step over `entries` sessions in one launch (LaunchConvStep): entry e reads in + e * entry_stride, writes
+  // out + e * entry_stride, and owns the state whose device address is state_tab[e * tstride + tslot]
+  // (state_tab == NULL: one entry, `state`)
+  const uint64_t* state_tab;
+  uint32_t tstride, tslot, entries;
+  uint64_t entry_stride;
 };
 cudaError_t ReadConvStageTimeouts(unsigned int* out);
+cudaError_t LaunchConvStep(const ConvArgs& a, cudaStream_t s);
 cudaError_t LaunchConvL2norm(const ConvArgs& a, cudaStream_t s);
 cudaError_t LaunchConvStateAdvance(const ConvArgs& a, cudaStream_t s);
 

@@ -241,6 +241,13 @@ HANDLER(H_q8x_cols) {
   CHECK_ARGS("halo_q8x_cols");
   return halo_b200_q8x_cols(c.s, x, xstride, cols, xq, xs, xq2, xs2, c.grid[1], c.err, c.errlen);
 }
+HANDLER(H_hc_norm_q8x) {
+  auto* res = r.ptr<const float>(); auto* scale = r.ptr<const float>(); auto* nw = r.ptr<const float>();
+  auto* xn = r.ptr<float>(); const uint32_t hc = r.u32(), h = r.u32();
+  auto* xq = r.ptr<int8_t>(); auto* xs = r.ptr<float>(); auto* xq2 = r.ptr<int8_t>(); auto* xs2 = r.ptr<float>();
+  CHECK_ARGS("halo_hc_norm_q8x");
+  return halo_b200_hc_norm_q8x(c.s, res, scale, nw, xn, hc, h, xq, xs, xq2, xs2, c.grid[1], c.err, c.errlen);
+}
 HANDLER(H_embed) {
   auto* w = r.ptr<const uint8_t>(); auto* out = r.ptr<float>(); const uint32_t token = r.u32(), cols = r.u32();
   const uint64_t rb = r.u64();
@@ -364,6 +371,14 @@ HANDLER(H_conv_l2norm) {
   CHECK_ARGS("halo_conv_l2norm");
   return halo_b200_conv_l2norm(c.s, in, state, w, out, channels, kern, l2, eps, c.block[0], c.err, c.errlen);
 }
+HANDLER(H_conv_l2norm_y) {
+  auto* in = r.ptr<const float>(); auto* tab = r.ptr<const uint64_t>(); const uint32_t tstride = r.u32(), tslot = r.u32();
+  auto* w = r.ptr<const float>(); auto* out = r.ptr<float>();
+  const uint32_t channels = r.u32(), kern = r.u32(), l2 = r.u32(); const float eps = r.f32(); const uint32_t stride = r.u32();
+  CHECK_ARGS("halo_conv_l2norm_y");
+  return halo_b200_conv_l2norm_y(c.s, in, tab, tstride, tslot, w, out, channels, kern, l2, eps, stride, c.block[0],
+                                 c.grid[1], c.err, c.errlen);
+}
 HANDLER(H_conv_l2norm_prefill) {
   auto* in = r.ptr<const float>(); auto* state = r.ptr<const float>(); auto* w = r.ptr<const float>();
   auto* out = r.ptr<float>();
@@ -396,6 +411,14 @@ HANDLER(H_copy_at) {
   const uint32_t slot = r.u32(), stride = r.u32(), n = r.u32();
   CHECK_ARGS("halo_copy_at");
   return halo_b200_copy_at(c.s, dst, DT, src, params, slot, stride, n, c.err, c.errlen);
+}
+HANDLER(H_copy_at_y) {
+  auto* tab = r.ptr<const uint64_t>(); const uint32_t tstride = r.u32(), tslot = r.u32();
+  auto* src = r.ptr<const float>(); auto* params = r.ptr<const uint32_t>();
+  const uint32_t slot = r.u32(), stride = r.u32(), n = r.u32(), src_stride = r.u32(), pstride = r.u32();
+  CHECK_ARGS("halo_copy_at_y");
+  return halo_b200_copy_at_y(c.s, tab, tstride, tslot, HALO_B200_F32, src, params, slot, stride, n, src_stride, pstride,
+                             c.grid[1], c.err, c.errlen);
 }
 HANDLER(H_copy) {
   auto* dst = r.ptr<float>(); auto* src = r.ptr<const float>(); const uint32_t n = r.u32();
@@ -481,6 +504,7 @@ const Entry kTable[] = {
     {"halo_quantize_q8_rows", H_quantize_q8_rows},
     {"halo_quantize_q8_kblocked", H_quantize_q8_kblocked},
     {"halo_q8x_cols", H_q8x_cols},
+    {"halo_hc_norm_q8x", H_hc_norm_q8x},
     {"halo_matvec_q8_0_embed", H_embed},
     {"halo_matvec_q8_0_embed_p", H_embed_p},
     {"halo_matvec_q8_0_embed_rows", H_embed_rows},
@@ -516,12 +540,14 @@ const Entry kTable[] = {
     {"halo_hc_norm_scales_u", H_hc_norm_scales},
     {"halo_conv_step", H_conv_step},
     {"halo_conv_l2norm", H_conv_l2norm},
+    {"halo_conv_l2norm_y", H_conv_l2norm_y},
     {"halo_conv_l2norm_prefill", H_conv_l2norm_prefill},
     {"halo_conv_l2norm_prefill8", H_conv_l2norm_prefill8<HALO_B200_F32, HALO_B200_F32>},
     {"halo_conv_l2norm_prefill8_h", H_conv_l2norm_prefill8<HALO_B200_F16, HALO_B200_F32>},
     {"halo_conv_l2norm_prefill8_hh", H_conv_l2norm_prefill8<HALO_B200_F16, HALO_B200_F16>},
     {"halo_conv_state_advance", H_conv_state_advance<HALO_B200_F32>},
     {"halo_conv_state_advance_h", H_conv_state_advance<HALO_B200_F16>},
+    {"halo_copy_at_y", H_copy_at_y},
     {"halo_copy_at", H_copy_at<HALO_B200_F32>},
     {"halo_copy_at_h", H_copy_at<HALO_B200_F16>},
     {"halo_copy", H_copy},

@@ -1,6 +1,7 @@
 // Standalone Q8 activation quantizers for sm_100a. Replaces halo_quantize_q8_rows,
 // halo_quantize_q8_kblocked (src/kernels/core.hip:3086-3101, 3313-3331) and
-// halo_q8x_cols (src/kernels/batch_decode.hip:197-222), and adds the true Q8_0
+// halo_q8x_cols and halo_hc_norm_q8x (src/kernels/batch_decode.hip:197-222, 977-999: the
+// same two-level quantizer behind xn = (res x scale) x norm_w), and adds the true Q8_0
 // row encoder of src/core/lowbit.cpp:285-298 as a device op. The same block
 // routines run as the epilogue of the fused add + RMSNorm kernel (norm.cu).
 //
@@ -26,6 +27,14 @@ __global__ void __launch_bounds__(kBlock) quantize_vec_kernel(const QuantArgs a)
   } else {
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+  }
+  if (a.pre_w && ok) {  // xn = (x * scale of the row's group) * w, kept as well as quantized
+    const float sc = a.pre_scale[static_cast<size_t>(row) * (a.cols / a.pre_h) + c0 / a.pre_h];
+    float w[8];
+    load8_cached(a.pre_w + c0, w);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(v[i], sc), w[i]);
+    store8(a.xn + static_cast<size_t>(row) * a.cols + c0, v);
   }
   const float amax = quad_amax(v);
   if (a.q8_0) {
@@ -79,7 +88,11 @@ __global__ void __launch_bounds__(kBlock) quantize_scalar_kernel(const QuantArgs
        b += static_cast<uint64_t>(gridDim.x) * (kBlock / 32)) {
     const uint32_t row = static_cast<uint32_t>(b / bpr), blk = static_cast<uint32_t>(b % bpr);
     const uint32_t c = blk * 32 + lane;
-    const float v = to_f32(static_cast<const XT*>(a.x)[static_cast<size_t>(row) * a.x_stride + c]);
+    float v = to_f32(static_cast<const XT*>(a.x)[static_cast<size_t>(row) * a.x_stride + c]);
+    if (a.pre_w) {
+      v = __fmul_rn(__fmul_rn(v, a.pre_scale[static_cast<size_t>(row) * (a.cols / a.pre_h) + c / a.pre_h]), a.pre_w[c]);
+      a.xn[static_cast<size_t>(row) * a.cols + c] = v;
+    }
     const float amax = warp_max(fabsf(v));
     if (a.q8_0) {
       const f16 dh = __float2half_rn(amax / 127.0f);

@@ -113,6 +113,12 @@ int halo_b200_quantize_q8_kblocked(halo_b200_stream stream, const float* x, int8
 /* halo_q8x_cols, src/kernels/batch_decode.hip:197-222 (batch = grid.y); xq2 / xs2 may be NULL. */
 int halo_b200_q8x_cols(halo_b200_stream stream, const float* x, uint32_t xstride, uint32_t cols, int8_t* xq,
                        float* xs, int8_t* xq2, float* xs2, uint32_t batch, char* err, size_t errlen);
+/* halo_hc_norm_q8x, src/kernels/batch_decode.hip:977-999 (batch = grid.y): xn[b][i] = (res[b][i] * scale[b * hc + i / h])
+ * norm_w[i] over the hc * h values of each column, stored, and quantized to two int8 levels per 32 values as by
+ * halo_q8x_cols (xq2 / xs2 may be NULL: one level). */
+int halo_b200_hc_norm_q8x(halo_b200_stream stream, const float* res, const float* scale, const float* norm_w,
+                          float* xn, uint32_t hc, uint32_t h, int8_t* xq, float* xs, int8_t* xq2, float* xs2,
+                          uint32_t batch, char* err, size_t errlen);
 /* EncodeQ8_0, src/core/lowbit.cpp:285-298, as a device op over rows of x_dtype values. */
 int halo_b200_encode_q8_0_rows(halo_b200_stream stream, const void* x, int x_dtype, uint8_t* out, uint32_t cols,
                                uint32_t rows, char* err, size_t errlen);
@@ -393,10 +399,17 @@ int halo_b200_conv_l2norm_ex(halo_b200_stream stream, const void* in, int in_dty
 int halo_b200_conv_state_advance(halo_b200_stream stream, const void* in, int in_dtype, float* state,
                                  uint32_t channels, uint32_t kern, uint32_t tokens, char* err, size_t errlen);
 /* halo_conv_l2norm, src/kernels/core.hip:3002-3028: one decode step (conv of one token, then the state
- * shifts by it). d = block.x. Two launches: the conv, then the advance. */
+ * shifts by it), in one launch. d = block.x; in and out may be the same buffer. */
 int halo_b200_conv_l2norm(halo_b200_stream stream, const float* in, float* state, const float* w, float* out,
                           uint32_t channels, uint32_t kern, uint32_t l2_channels, float eps, uint32_t d, char* err,
                           size_t errlen);
+/* halo_conv_l2norm_y, src/kernels/batch_decode.hip:1741-1748: the same step for `entries` (= grid.y) sessions in
+ * one launch. Entry e reads in + e * stride, writes out + e * stride (floats), and owns the conv state whose
+ * device address is tab[e * tstride + tslot] (a table of 64-bit device addresses in device memory). */
+int halo_b200_conv_l2norm_y(halo_b200_stream stream, const float* in, const uint64_t* tab, uint32_t tstride,
+                            uint32_t tslot, const float* w, float* out, uint32_t channels, uint32_t kern,
+                            uint32_t l2_channels, float eps, uint32_t stride, uint32_t d, uint32_t entries, char* err,
+                            size_t errlen);
 /* halo_conv_step, src/kernels/core.hip:445-456: the same without the L2 norm. */
 int halo_b200_conv_step(halo_b200_stream stream, const float* in, float* state, const float* w, float* out,
                         uint32_t channels, uint32_t kern, char* err, size_t errlen);
@@ -437,6 +450,12 @@ int halo_b200_moe_combine_ex(halo_b200_stream stream, const void* yp, int yp_dty
  * rounded to nearest even. */
 int halo_b200_copy_at(halo_b200_stream stream, void* dst, int dst_dtype, const float* src, const uint32_t* params,
                       uint32_t slot, uint32_t stride, uint32_t n, char* err, size_t errlen);
+/* halo_copy_at_y, src/kernels/batch_decode.hip:1700-1707: the row append for `entries` (= grid.y) sessions in one
+ * launch. Entry e copies src[e * src_stride ..+ n] to row params[e * pstride + slot] (rows `stride` elements apart)
+ * of the buffer whose device address is tab[e * tstride + tslot]; the buffers hold dst_dtype elements. */
+int halo_b200_copy_at_y(halo_b200_stream stream, const uint64_t* tab, uint32_t tstride, uint32_t tslot, int dst_dtype,
+                        const float* src, const uint32_t* params, uint32_t slot, uint32_t stride, uint32_t n,
+                        uint32_t src_stride, uint32_t pstride, uint32_t entries, char* err, size_t errlen);
 /* halo_copy, src/kernels/core.hip:352-354. */
 int halo_b200_copy(halo_b200_stream stream, float* dst, const float* src, uint32_t n, char* err, size_t errlen);
 /* halo_f16_rows, src/kernels/core.hip:8157-8161: y[i] = fp16(x[i]). */

@@ -198,3 +198,76 @@ def test_conv_kernels_by_name(orc):
                [Arg.Buf(b_in), Arg.Buf(b_st), Arg.Buf(b_w), Arg.Buf(b_o), Arg.U32(C), Arg.U32(kern)])
     want2 = orc.conv_l2norm(x[0:1], st, w, 0, d, EPS)
     check(dev.download(b_o, 0, C * 4, np.float32).reshape(1, C), want2, C, "f32", "halo_conv_step")
+
+
+@pytest.mark.parametrize("B,C,l2,d,kern", [(1, 512, 256, 128, 4), (3, 1024, 512, 128, 4), (4, 320, 128, 64, 3),
+                                           (2, 200, 0, 128, 2), (2, 256, 256, 128, 1)])
+def test_conv_step_entries(orc, B, C, l2, d, kern):
+    """halo_conv_l2norm_y (src/kernels/batch_decode.hip:1741-1748): one launch steps B sessions, each with its own
+    conv state found through a table of device addresses; every entry equals the single-session step bit for bit
+    and the oracle within tolerance, and each state moves by its entry's input."""
+    st = torch.cuda.current_stream().cuda_stream
+    x, _, w = make("t.conv.y", B, C, kern)
+    stride = C + 24  # entries are slices of a wider scratch row
+    xin = np.zeros((B, stride), np.float32)
+    xin[:, :C] = x
+    states = [np.ascontiguousarray(synth.act(f"t.conv.y.s{e}", max(kern - 1, 1), C)[:kern - 1]) for e in range(B)]
+    d_states = [to_dev(s.copy()) if kern > 1 else torch.zeros(1, device=DEV) for s in states]
+    tstride, tslot = 5, 3
+    tab = np.zeros((B, tstride), np.uint64)
+    for e in range(B):
+        tab[e, tslot] = d_states[e].data_ptr()
+    d_tab = torch.from_numpy(tab.view(np.int64)).to(DEV)
+    d_in, d_w = to_dev(xin), to_dev(w)
+    d_out = torch.full((B, stride), 7.0, device=DEV)
+    lib().call("conv_l2norm_y", st, d_in.data_ptr(), d_tab.data_ptr(), tstride, tslot, d_w.data_ptr(), d_out.data_ptr(),
+               C, kern, l2, EPS, stride, d, B)
+    got = d_out.cpu().numpy()
+    assert np.all(got[:, C:] == 7.0), "wrote past an entry's channels"
+    for e in range(B):
+        hist = states[e].copy()
+        want = orc.conv_l2norm(x[e:e + 1], hist, w, l2, d, EPS)  # advances hist
+        if l2:
+            check(got[e:e + 1, :l2], want[:, :l2], d, "f32", f"entry {e} q/k")
+        if l2 < C:
+            assert_rows_close(got[e:e + 1, l2:C], want[:, l2:], what=f"entry {e} v")
+        if kern > 1:
+            assert np.array_equal(d_states[e].cpu().numpy(), hist), f"entry {e} state"
+        # the single-session step on the same inputs: same bits
+        s1 = to_dev(states[e].copy()) if kern > 1 else torch.zeros(1, device=DEV)
+        o1 = torch.empty(C, device=DEV)
+        lib().call("conv_l2norm", st, d_in[e].data_ptr(), s1.data_ptr(), d_w.data_ptr(), o1.data_ptr(), C, kern, l2, EPS, d)
+        assert np.array_equal(o1.cpu().numpy(), got[e, :C])
+    with pytest.raises(HaloError, match="state table"):
+        lib().call("conv_l2norm_y", st, d_in.data_ptr(), 0, tstride, tslot, d_w.data_ptr(), d_out.data_ptr(),
+                   C, kern, l2, EPS, stride, d, B)
+    # no entries: nothing runs
+    lib().call("conv_l2norm_y", st, d_in.data_ptr(), 0, tstride, tslot, d_w.data_ptr(), d_out.data_ptr(),
+               C, kern, l2, EPS, stride, d, 0)
+
+
+def test_conv_step_entries_by_name(orc):
+    """The batched decoder's launch (grid (channels / 128, B), block 128) through the launch-by-name boundary."""
+    dev = Device.create(0)
+    B, C, l2, d, kern = 3, 512, 256, 128, 4
+    x, _, w = make("t.conv.yn", B, C, kern)
+
+    def up(a):
+        b = dev.alloc(a.nbytes)
+        dev.upload(b, 0, a)
+        return b
+
+    states = [np.ascontiguousarray(synth.act(f"t.conv.yn.s{e}", 3, C)) for e in range(B)]
+    d_states = [to_dev(s.copy()) for s in states]
+    tab = np.array([[0, s.data_ptr()] for s in d_states], np.uint64)
+    b_in, b_tab, b_w, b_out = up(x), up(tab), up(w), dev.alloc(B * C * 4)
+    dev.launch(dev.kernel("halo_conv_l2norm_y"), (C // 128, B), (128,),
+               [Arg.Buf(b_in), Arg.Buf(b_tab), Arg.U32(2), Arg.U32(1), Arg.Buf(b_w), Arg.Buf(b_out), Arg.U32(C),
+                Arg.U32(kern), Arg.U32(l2), Arg.F32(EPS), Arg.U32(C)])
+    got = dev.download(b_out, 0, B * C * 4, np.float32).reshape(B, C)
+    for e in range(B):
+        hist = states[e].copy()
+        want = orc.conv_l2norm(x[e:e + 1], hist, w, l2, d, EPS)
+        check(got[e:e + 1, :l2], want[:, :l2], d, "f32", f"entry {e}")
+        assert_rows_close(got[e:e + 1, l2:], want[:, l2:], what=f"entry {e} v")
+        assert np.array_equal(d_states[e].cpu().numpy(), hist)

@@ -562,6 +562,84 @@ def test_quantizers(orc, rows, cols):
     assert q2.t.cpu().numpy().tobytes() == rq.tobytes() and to_f32(s2.t).tobytes() == rd.tobytes()
 
 
+@pytest.mark.parametrize("B,hc,h", [(1, 4, 2048), (3, 4, 2560), (8, 2, 96), (2, 8, 36)])
+def test_hc_norm_q8x(orc, B, hc, h):
+    """halo_hc_norm_q8x (src/kernels/batch_decode.hip:977-999): xn = (res x scale of the stream) x norm_w, stored,
+    then two int8 levels per 32 values. xn is bit-exact (two fp32 products, no contraction); codes and scales are
+    bit-exact against the quantizer recipe run on xn. h = 36 leaves blocks that straddle two streams."""
+    D = hc * h
+    res = (synth.act("t.hq.res", B, D) * 3).astype(np.float32)
+    scale = np.abs(synth.act("t.hq.sc", B, hc)).astype(np.float32) + np.float32(0.25)
+    nw = (1 + 0.1 * synth.act("t.hq.w", 1, D)[0]).astype(np.float32)
+    res[0, :32] = 0
+    st = torch.cuda.current_stream().cuda_stream
+    xn = Guarded((B, D), torch.float32)
+    q1, s1 = Guarded((B, D), torch.int8), Guarded((B, D // 32), torch.float32)
+    q2, s2 = Guarded((B, D), torch.int8), Guarded((B, D // 32), torch.float32)
+    d_res, d_sc, d_w = to_dev(res), to_dev(scale), to_dev(nw)
+    lib().call("hc_norm_q8x", st, d_res.data_ptr(), d_sc.data_ptr(), d_w.data_ptr(), xn.t.data_ptr(), hc, h,
+               q1.t.data_ptr(), s1.t.data_ptr(), q2.t.data_ptr(), s2.t.data_ptr(), B)
+    want = (res * np.repeat(scale, h, axis=1)) * nw[None, :]
+    got = to_f32(xn.t)
+    assert got.tobytes() == want.astype(np.float32).tobytes()
+    wq, wd = orc.quantize_i8_rows(got)
+    assert q1.t.cpu().numpy().tobytes() == wq.tobytes() and to_f32(s1.t).tobytes() == wd.tobytes()
+    resid = (got.reshape(B, -1, 32) - wq.reshape(B, -1, 32).astype(np.float32) * wd[..., None]).reshape(B, D)
+    rq, rd = orc.quantize_i8_rows(resid.astype(np.float32))
+    assert q2.t.cpu().numpy().tobytes() == rq.tobytes() and to_f32(s2.t).tobytes() == rd.tobytes()
+    for g in (xn, q1, s1, q2, s2):
+        g.check()
+    # the same through the scalar kernel (an unaligned xn)
+    buf = torch.zeros(B * D + 1, device=DEV)
+    lib().call("hc_norm_q8x", st, d_res.data_ptr(), d_sc.data_ptr(), d_w.data_ptr(), buf[1:].data_ptr(), hc, h,
+               q1.t.data_ptr(), s1.t.data_ptr(), q2.t.data_ptr(), s2.t.data_ptr(), B)
+    assert to_f32(buf[1:]).reshape(B, D).tobytes() == got.tobytes()
+    assert q1.t.cpu().numpy().tobytes() == wq.tobytes() and q2.t.cpu().numpy().tobytes() == rq.tobytes()
+    with pytest.raises(HaloError, match="does not divide|cols % 32"):
+        lib().call("hc_norm_q8x", st, d_res.data_ptr(), d_sc.data_ptr(), d_w.data_ptr(), xn.t.data_ptr(), 3, 10,
+                   q1.t.data_ptr(), s1.t.data_ptr(), q2.t.data_ptr(), s2.t.data_ptr(), 1)
+
+
+@pytest.mark.parametrize("ddt", ["f32", "f16"])
+def test_copy_at_entries(ddt):
+    """halo_copy_at_y (src/kernels/batch_decode.hip:1700-1707): every session appends its row to its own cache,
+    found through a table of device addresses, at the position in its own step parameters."""
+    B, n, rows, pstride, slot, tstride, tslot = 3, 520, 6, 16, 1, 4, 2
+    tdt = torch.float32 if ddt == "f32" else torch.float16
+    src_stride = n + 8
+    src = synth.act("t.cay.src", B, src_stride)
+    caches = [torch.full((rows, n), -1.0, device=DEV, dtype=tdt) for _ in range(B)]
+    pos = [4, 0, 5]
+    params = np.zeros((B, pstride), np.uint32)
+    params[:, slot] = pos
+    tab = np.zeros((B, tstride), np.uint64)
+    for e in range(B):
+        tab[e, tslot] = caches[e].data_ptr()
+    d_tab, d_par, d_src = torch.from_numpy(tab.view(np.int64)).to(DEV), to_dev(params.view(np.int32)), to_dev(src)
+    st = torch.cuda.current_stream().cuda_stream
+    lib().call("copy_at_y", st, d_tab.data_ptr(), tstride, tslot, 0 if ddt == "f32" else 1, d_src.data_ptr(),
+               d_par.data_ptr(), slot, n, n, src_stride, pstride, B)
+    for e in range(B):
+        got = caches[e].float().cpu().numpy()
+        want = np.full((rows, n), -1.0, np.float32)
+        want[pos[e]] = src[e, :n] if ddt == "f32" else src[e, :n].astype(np.float16).astype(np.float32)
+        assert got.tobytes() == want.tobytes(), f"entry {e}"
+    if ddt == "f32":  # by name, as the batched decoder launches it: grid (ceil(n / 256), B)
+        from halo_flash_b200.device import Arg, Device
+        dev = Device.create(0)
+        for c in caches:
+            c.fill_(-1.0)
+        torch.cuda.synchronize()  # the device object launches on its own stream
+        b_tab, b_src, b_par = dev.alloc(tab.nbytes), dev.alloc(src.nbytes), dev.alloc(params.nbytes)
+        dev.upload(b_tab, 0, tab), dev.upload(b_src, 0, src), dev.upload(b_par, 0, params)
+        dev.launch(dev.kernel("halo_copy_at_y"), ((n + 255) // 256, B), (256,),
+                   [Arg.Buf(b_tab), Arg.U32(tstride), Arg.U32(tslot), Arg.Buf(b_src), Arg.Buf(b_par), Arg.U32(slot),
+                    Arg.U32(n), Arg.U32(n), Arg.U32(src_stride), Arg.U32(pstride)])
+        dev.synchronize()
+        for e in range(B):
+            assert caches[e][pos[e]].cpu().numpy().tobytes() == src[e, :n].tobytes()
+
+
 # ---- empty and ragged inputs ---------------------------------------------------------------
 def test_empty_inputs_are_no_ops():
     e = torch.empty(0, 256, device=DEV)
