@@ -18,6 +18,7 @@ std::atomic<int> g_norm_threads_per_row{0};
 std::atomic<int> g_norm_short_rows_k1{0};
 std::atomic<int> g_norm_force_general{0};
 std::atomic<int> g_rope_rows_per_group{0};
+std::atomic<int> g_rope_lean_k{0};
 std::atomic<int> g_gated_rows_per_group{0};
 std::atomic<int> g_pdl{1};
 
@@ -200,6 +201,7 @@ int RunNormRope(NormRopeArgs a, float theta, const char* what, halo_b200_stream 
     REQUIRE(FillInvFreq(&f, a.rot, theta), "%s: rotary_dim too large", what);
   }
   a.rows_per_group = g_rope_rows_per_group.load(std::memory_order_relaxed);
+  a.lean_k = g_rope_lean_k.load(std::memory_order_relaxed);
   a.force_general = g_norm_force_general.load(std::memory_order_relaxed);
   const bool vec = a.d % 8 == 0 && (a.rot / 2) % 8 == 0 && a.in_row_stride % 8 == 0 && Aligned(a.in, 16) &&
                    Aligned(a.out, 16) && Aligned(a.gate, 16) && Aligned(a.cache, 16) && Aligned(a.w, 16) &&
@@ -418,6 +420,11 @@ int halo_b200_tune(const char* key, int value) {
   if (std::strcmp(key, "rope_rows_per_group") == 0) {
     if (value != 0 && value != 2 && value != 4) return -1;
     g_rope_rows_per_group.store(value, std::memory_order_relaxed);
+    return 0;
+  }
+  if (std::strcmp(key, "rope_lean_k") == 0) {
+    if (value != 0 && value != 1 && value != 2) return -1;
+    g_rope_lean_k.store(value, std::memory_order_relaxed);
     return 0;
   }
   if (std::strcmp(key, "norm_force_general") == 0) {

@@ -153,6 +153,7 @@ struct NormRopeArgs {
   // has no barrier; pos / pos_out / the inverse frequencies are then unused.
   const float* table = nullptr;
   int rows_per_group = 0;       // rows a thread group keeps in flight: 2 (default) or 4
+  int lean_k = 0;               // tuning: octets per lane of the lean kernel, 1 or 2 (0 = built-in choice)
   int force_general = 0;        // 1: never take the lean kernel (tests compare the two)
 };
 cudaError_t LaunchNormRope(const NormRopeArgs& a, const InvFreq& f, cudaStream_t s);

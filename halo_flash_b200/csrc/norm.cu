@@ -219,10 +219,10 @@ struct LeanArgs {
 
 // WIDE: more than one warp per row (g > 32), the reduction crosses shared memory and a barrier.
 // MODE: 0 = w, y, one_plus and l2 are tested at run time; 1 = RMSNorm with gamma w into y;
-// 2 = the same with gamma 1 + w. The two fixed modes exist because even warp-uniform tests
+// 2 = the same with gamma 1 + w; 3 = L2 norm without gamma into y. The fixed modes exist because even warp-uniform tests
 // cost these microsecond CTAs 3-4 % (12.6 vs 12.1 us on the add + norm of 4096 x 2048).
 template <typename XT, typename YT, int K, bool ADD, bool EPI, bool WIDE, int MODE>
-__global__ void __launch_bounds__(kBlock) norm_rows_lean_kernel(const LeanArgs a) {
+__global__ void __launch_bounds__(kBlock, (!EPI && MODE != 0 && sizeof(XT) == 2) ? 6 : 1) norm_rows_lean_kernel(const LeanArgs a) {
   pdl_begin();
   __shared__ float scratch[WIDE ? kBlock / 32 : 1];
   // Q8_0 staging: the 32 octets of a warp's slab are 8 blocks = 272 contiguous output bytes that
@@ -256,8 +256,9 @@ __global__ void __launch_bounds__(kBlock) norm_rows_lean_kernel(const LeanArgs a
 #pragma unroll
     for (int k = 0; k < K; ++k) v[k] = raw_unpack(rx[k]);
   }
+  constexpr bool kLateGamma = !EPI && (MODE == 1 || MODE == 2);  // gamma fetched per octet after the reduction: fewer live registers
   Oct gm[K];
-  if (MODE != 0 || a.w) {  // fetched before the reduction: the L2 round trip overlaps the shuffles / barrier
+  if (!kLateGamma && MODE != 3 && (MODE != 0 || a.w)) {  // fetched before the reduction: the L2 round trip overlaps the shuffles / barrier
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       gm[k] = oct_load_cached(a.w + (((k << lg) + lir) << 3));
@@ -272,12 +273,20 @@ __global__ void __launch_bounds__(kBlock) norm_rows_lean_kernel(const LeanArgs a
 #pragma unroll
   for (int k = 0; k < K; ++k) acc = oct_sumsq(v[k], acc);
   const float ss = WIDE ? group_sum(acc.x + acc.y, g, scratch) : group_sum_narrow(acc.x + acc.y, g);
-  const float scale = (MODE == 0 && a.l2) ? rsqrtf(ss + a.eps) : rsqrtf(__fmaf_rn(ss, a.inv_d, a.eps));
+  const float scale = (MODE == 3 || (MODE == 0 && a.l2)) ? rsqrtf(ss + a.eps) : rsqrtf(__fmaf_rn(ss, a.inv_d, a.eps));
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const unsigned j = (k << lg) + lir;
     v[k] = oct_scale(v[k], scale);
-    if (MODE != 0 || a.w) v[k] = oct_mul(v[k], gm[k]);
+    if constexpr (kLateGamma) {
+      gm[k] = oct_load_cached(a.w + (j << 3));
+      if (MODE == 2) {
+        const float2 one = make_float2(1.0f, 1.0f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) gm[k].p[i] = __fadd2_rn(one, gm[k].p[i]);
+      }
+    }
+    if (MODE == 1 || MODE == 2 || (MODE == 0 && a.w)) v[k] = oct_mul(v[k], gm[k]);
     if (MODE != 0 || a.y) oct_store(static_cast<YT*>(a.y) + off + (j << 3), v[k]);
   }
   if constexpr (EPI) {
@@ -650,16 +659,18 @@ cudaError_t LaunchLean(const NormArgs& a, const Shape& sh, unsigned grid, cudaSt
   // a warp's 32 octets must be consecutive in the output: rows of at least a warp, or one octet per thread
   l.stage_q8 = a.q8_0 && (reinterpret_cast<uintptr_t>(a.q8_0) & 15u) == 0 && (sh.lg >= 5 || K == 1);
   const bool epi = a.q8_0 || a.xq;
-  const int mode = (!epi && a.w && a.y && !a.l2) ? (a.one_plus ? 2 : 1) : 0;
+  const int mode = (!epi && a.w && a.y && !a.l2) ? (a.one_plus ? 2 : 1) : (!epi && !a.w && a.y && a.l2) ? 3 : 0;
   if (sh.lg > 5) {
     if (epi) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, true, 0>, grid, kBlock, 0, s, l);
     else if (mode == 2) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, true, 2>, grid, kBlock, 0, s, l);
     else if (mode == 1) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, true, 1>, grid, kBlock, 0, s, l);
+    else if (mode == 3) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, true, 3>, grid, kBlock, 0, s, l);
     else LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, true, 0>, grid, kBlock, 0, s, l);
   } else {
     if (epi) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, false, 0>, grid, kBlock, 0, s, l);
     else if (mode == 2) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, false, 2>, grid, kBlock, 0, s, l);
     else if (mode == 1) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, false, 1>, grid, kBlock, 0, s, l);
+    else if (mode == 3) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, false, 3>, grid, kBlock, 0, s, l);
     else LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, false, 0>, grid, kBlock, 0, s, l);
   }
   return cudaGetLastError();

@@ -305,7 +305,7 @@ struct RopeLeanArgs {  // scalar fields on purpose: indexing a parameter array b
 };
 
 template <typename IT, typename OT, int K, bool ONEPLUS>
-__global__ void __launch_bounds__(kBlock) norm_rope_lean_kernel(const RopeLeanArgs a) {
+__global__ void __launch_bounds__(kBlock, K == 2 ? 5 : 6) norm_rope_lean_kernel(const RopeLeanArgs a) {
   pdl_begin();
   const bool sel = blockIdx.x >= a.ctas0;
   const uint32_t cta = blockIdx.x - (sel ? a.ctas0 : 0u);
@@ -319,31 +319,10 @@ __global__ void __launch_bounds__(kBlock) norm_rope_lean_kernel(const RopeLeanAr
 #pragma unroll
   for (int k = 0; k < K; ++k) rx[k] = raw_load(src + (((k << lg) + lir) << 3));
   const float* w = sel ? a.w1 : a.w0;
-  Oct gm[K];
-#pragma unroll
-  for (int k = 0; k < K; ++k) {
-    gm[k] = oct_load_cached(w + (((k << lg) + lir) << 3));
-    if (ONEPLUS) {
-      const float2 one = make_float2(1.0f, 1.0f);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) gm[k].p[i] = __fadd2_rn(one, gm[k].p[i]);
-    }
-  }
   const unsigned hp = a.rot >> 4;  // lanes per half of the rotated span
   const bool rotates = lir < 2 * hp;
   const bool low = lir < hp;
   const unsigned src_lane = lane - lir + (rotates ? (low ? lir + hp : lir - hp) : lir);
-  float4 c0 = make_float4(1.0f, 1.0f, 1.0f, 1.0f), c1 = c0;
-  float4 s0 = make_float4(0.0f, 0.0f, 0.0f, 0.0f), s1 = s0;
-  if (rotates) {  // this token's cos / sin, requested while the row is still in flight
-    const uint32_t token = div_magic(row, sel ? a.heads1 : a.heads0, sel ? a.magic1 : a.magic0);
-    const float* tc = a.table + static_cast<size_t>(token) * a.rot + ((low ? lir : lir - hp) << 3);
-    const float* ts = tc + (a.rot >> 1);
-    const float sign = low ? -1.0f : 1.0f;  // first halves take -sin, second halves +sin (exact)
-    c0 = __ldg(reinterpret_cast<const float4*>(tc)), c1 = __ldg(reinterpret_cast<const float4*>(tc + 4));
-    s0 = scale4(__ldg(reinterpret_cast<const float4*>(ts)), sign);
-    s1 = scale4(__ldg(reinterpret_cast<const float4*>(ts + 4)), sign);
-  }
   Oct x[K];
   float2 acc = make_float2(0.0f, 0.0f);
 #pragma unroll
@@ -353,10 +332,29 @@ __global__ void __launch_bounds__(kBlock) norm_rope_lean_kernel(const RopeLeanAr
   }
   const float ss = group_sum_narrow(acc.x + acc.y, g);
   const float scale = rsqrtf(__fmaf_rn(ss, a.inv_d, a.eps));
+  // gammas and this token's cos / sin are requested only now: they come from L1 / L2 (a few KB shared by every
+  // row), and holding them in registers while the row is in flight would cost a resident CTA per SM
 #pragma unroll
-  for (int k = 0; k < K; ++k) x[k] = oct_mul(oct_scale(x[k], scale), gm[k]);
+  for (int k = 0; k < K; ++k) {
+    Oct gm = oct_load_cached(w + (((k << lg) + lir) << 3));
+    if (ONEPLUS) {
+      const float2 one = make_float2(1.0f, 1.0f);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) gm.p[i] = __fadd2_rn(one, gm.p[i]);
+    }
+    x[k] = oct_mul(oct_scale(x[k], scale), gm);
+  }
   const Oct o = shuffle_oct(x[0], src_lane);
-  if (rotates) rotate8(x[0], o, c0, c1, s0, s1);
+  if (rotates) {
+    const uint32_t token = div_magic(row, sel ? a.heads1 : a.heads0, sel ? a.magic1 : a.magic0);
+    const float* tc = a.table + static_cast<size_t>(token) * a.rot + ((low ? lir : lir - hp) << 3);
+    const float* ts = tc + (a.rot >> 1);
+    const float sign = low ? -1.0f : 1.0f;  // first halves take -sin, second halves +sin (exact)
+    const float4 c0 = __ldg(reinterpret_cast<const float4*>(tc)), c1 = __ldg(reinterpret_cast<const float4*>(tc + 4));
+    const float4 s0 = scale4(__ldg(reinterpret_cast<const float4*>(ts)), sign);
+    const float4 s1 = scale4(__ldg(reinterpret_cast<const float4*>(ts + 4)), sign);
+    rotate8(x[0], o, c0, c1, s0, s1);
+  }
   OT* dst = static_cast<OT*>(sel ? a.out1 : a.out0) + off;
 #pragma unroll
   for (int k = 0; k < K; ++k) oct_store(dst + (((k << lg) + lir) << 3), x[k]);
@@ -426,7 +424,8 @@ cudaError_t LaunchNormRopeT(const NormRopeArgs& a, const InvFreq& f, cudaStream_
   const unsigned octs = a.d / 8;
   // Two octets per lane halve the instructions per row; the rotated span must then sit in
   // the first octet of the lanes (rot <= d / 2), which holds for 64-of-256 and 16-of-64.
-  const int k = (octs >= 2 && a.rot * 2 <= a.d) ? 2 : 1;
+  int k = (octs >= 2 && a.rot * 2 <= a.d) ? 2 : 1;
+  if (a.lean_k == 1 && octs <= 32) k = 1;
   unsigned g = 1, lg = 0;
   while (g * k < octs) g <<= 1, ++lg;
   const unsigned rows_in_flight = a.rows_per_group ? static_cast<unsigned>(a.rows_per_group) : 2u;
