@@ -222,7 +222,7 @@ struct LeanArgs {
 // 2 = the same with gamma 1 + w; 3 = L2 norm without gamma into y. The fixed modes exist because even warp-uniform tests
 // cost these microsecond CTAs 3-4 % (12.6 vs 12.1 us on the add + norm of 4096 x 2048).
 template <typename XT, typename YT, int K, bool ADD, bool EPI, bool WIDE, int MODE>
-__global__ void __launch_bounds__(kBlock, (!EPI && MODE != 0 && sizeof(XT) == 2) ? 6 : 1) norm_rows_lean_kernel(const LeanArgs a) {
+__global__ void __launch_bounds__(kBlock, (!EPI && MODE != 0 && sizeof(XT) == 2) ? 6 : (EPI && sizeof(XT) == 2) ? 5 : 1) norm_rows_lean_kernel(const LeanArgs a) {
   pdl_begin();
   __shared__ float scratch[WIDE ? kBlock / 32 : 1];
   // Q8_0 staging: the 32 octets of a warp's slab are 8 blocks = 272 contiguous output bytes that
@@ -256,7 +256,7 @@ __global__ void __launch_bounds__(kBlock, (!EPI && MODE != 0 && sizeof(XT) == 2)
 #pragma unroll
     for (int k = 0; k < K; ++k) v[k] = raw_unpack(rx[k]);
   }
-  constexpr bool kLateGamma = !EPI && (MODE == 1 || MODE == 2);  // gamma fetched per octet after the reduction: fewer live registers
+  constexpr bool kLateGamma = MODE == 1 || MODE == 2 || (EPI && MODE == 0);  // gamma fetched per octet after the reduction: fewer live registers
   Oct gm[K];
   if (!kLateGamma && MODE != 3 && (MODE != 0 || a.w)) {  // fetched before the reduction: the L2 round trip overlaps the shuffles / barrier
 #pragma unroll
@@ -279,11 +279,13 @@ __global__ void __launch_bounds__(kBlock, (!EPI && MODE != 0 && sizeof(XT) == 2)
     const unsigned j = (k << lg) + lir;
     v[k] = oct_scale(v[k], scale);
     if constexpr (kLateGamma) {
-      gm[k] = oct_load_cached(a.w + (j << 3));
-      if (MODE == 2) {
-        const float2 one = make_float2(1.0f, 1.0f);
+      if (MODE != 0 || a.w) {
+        gm[k] = oct_load_cached(a.w + (j << 3));
+        if (MODE == 2 || (MODE == 0 && a.one_plus)) {
+          const float2 one = make_float2(1.0f, 1.0f);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) gm[k].p[i] = __fadd2_rn(one, gm[k].p[i]);
+          for (int i = 0; i < 4; ++i) gm[k].p[i] = __fadd2_rn(one, gm[k].p[i]);
+        }
       }
     }
     if (MODE == 1 || MODE == 2 || (MODE == 0 && a.w)) v[k] = oct_mul(v[k], gm[k]);
