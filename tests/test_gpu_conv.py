@@ -238,6 +238,11 @@ def test_conv_step_entries(orc, B, C, l2, d, kern):
         o1 = torch.empty(C, device=DEV)
         lib().call("conv_l2norm", st, d_in[e].data_ptr(), s1.data_ptr(), d_w.data_ptr(), o1.data_ptr(), C, kern, l2, EPS, d)
         assert np.array_equal(o1.cpu().numpy(), got[e, :C])
+        # and in place (a thread reads its input before it writes its output)
+        s2 = to_dev(states[e].copy()) if kern > 1 else torch.zeros(1, device=DEV)
+        io = d_in[e, :C].clone()
+        lib().call("conv_l2norm", st, io.data_ptr(), s2.data_ptr(), d_w.data_ptr(), io.data_ptr(), C, kern, l2, EPS, d)
+        assert np.array_equal(io.cpu().numpy(), got[e, :C])
     with pytest.raises(HaloError, match="state table"):
         lib().call("conv_l2norm_y", st, d_in.data_ptr(), 0, tstride, tslot, d_w.data_ptr(), d_out.data_ptr(),
                    C, kern, l2, EPS, stride, d, B)
