@@ -146,10 +146,39 @@ class ClockSampler:
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.proc = index, None
+    def __init__(self, index: int, uuid: str | None = None):
+        self.index, self.uuid, self.proc = index, uuid, None  # uuid: the CUDA device's, when visibility is restricted
+        self.thread, self.halt, self.rows = None, None, []
+
+    def _poll(self, nv, handle):
+        """NVML polled every 5 ms (reads only): the timed region of the default run lasts 60-70 ms, too short
+        for more than one sample of nvidia-smi's loop."""
+        bits = {"hw_slowdown": nv.nvmlClocksThrottleReasonHwSlowdown,
+                "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown,
+                "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap}
+        mx = nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM)
+        while not self.halt.is_set():
+            try:
+                sm = nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                self.rows.append((float(sm), float(mx), [k for k, b in bits.items() if mask & b]))
+            except nv.NVMLError:
+                pass
+            self.halt.wait(0.005)
 
     def start(self):
+        try:
+            import pynvml as nv
+            import threading
+            nv.nvmlInit()
+            handle = nv.nvmlDeviceGetHandleByUUID(self.uuid) if self.uuid else nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.halt = threading.Event()
+            self.thread = threading.Thread(target=self._poll, args=(nv, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:  # no NVML binding or no access: nvidia-smi's own loop
+            self.thread = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                                           "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE,
@@ -158,6 +187,13 @@ class ClockSampler:
             self.proc = None
 
     def stop(self) -> dict:
+        if self.thread is not None:
+            self.halt.set()
+            self.thread.join(timeout=2)
+            sm = [r[0] for r in self.rows]
+            reasons = sorted({k for r in self.rows for k in r[2]})
+            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.rows[0][1] if self.rows else None,
+                    "samples": len(sm), "reasons": reasons, "source": "nvml, 5 ms"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -427,7 +463,11 @@ def run_ours(args) -> None:
     torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
-    sampler = ClockSampler(local)
+    try:
+        uuid = "GPU-" + str(torch.cuda.get_device_properties(local).uuid)
+    except Exception:
+        uuid = None
+    sampler = ClockSampler(local, uuid)
     if rank == 0:
         sampler.start()
     torch.cuda.synchronize()
