@@ -11,11 +11,15 @@ own contiguous token shard (tokens [rank*T, (rank+1)*T), positions offset accord
 are row-local, so there is no collective on the data path (weak scaling, global batch N*T).
 
 Prints ONE JSON line: metric = prefill tokens/s of the chain (`value`: inputs resident in HBM,
-one CUDA-graph replay per step, CUDA-event time, max over ranks), `roofline` for the dominant
-kernel (fused residual-add + RMSNorm) from CUDA-event timing of back-to-back launches over a
-ring of buffer sets larger than L2, `e2e` through host buffers (every synthetic block output
-copied from pinned host memory each step, final hidden state read back), `cpu_baseline` (the
-reference's own CPU operators on this box's host cores, bounded token sample), clocks.
+one CUDA-graph replay per step, CUDA-event time, max over ranks; the block of --steps replays is
+repeated until at least a second has been timed and the median block is reported with the
+spread), `roofline` for the dominant kernel (fused residual-add + RMSNorm) from CUDA-event timing
+of back-to-back launches over a ring of buffer sets larger than L2, `e2e` through host buffers
+(every synthetic block output copied from pinned host memory each step, final hidden state read
+back), `config5` (the long-context configuration: 65 536 tokens in all, token-sharded over the N
+GPUs, i.e. strong scaling, with the unsharded single-GPU time of the same run beside it),
+`decode` (microseconds per single-token step for 1..8 sessions), `cpu_baseline` (the reference's
+own CPU operators on this box's host cores, bounded token sample), clocks.
 
 `--impl reference` times only the CPU path (the reference's compiled operators from oracle/_ref
 when present, else the restatement in oracle/), all host threads, same metric and config.
@@ -37,6 +41,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 METRIC = "prefill_tokens_per_s_layer_op_chain"
+DEFAULT_TOKENS = 4096
 UNIT = "tokens/s"
 
 
@@ -112,12 +117,17 @@ def time_cpu_chain(shapes, tokens: int, threads: int, steps: int, warmup: int) -
         chain.step()
     dt = (time.perf_counter() - t0) / max(steps, 1)
     return {"value": tokens / dt, "unit": UNIT, "cores": threads, "kind": chain.o.kind,
-            "sample": f"{tokens}-token shard through all 48 layers, fp32, {steps} step(s) of {dt * 1e3:.0f} ms",
+            "sample": f"{tokens}-token shard (not the bench's {DEFAULT_TOKENS}) through all 48 layers, fp32, gather from a "
+                      f"{chain.vocab}-row Q8_0 table (it reads one row per token whatever the table size), {steps} step(s) "
+                      f"of {dt * 1e3:.0f} ms; rows split over {threads} std::threads spawned and joined by every operator call",
             "ms_per_step": dt * 1e3}
 
 
-def config_dict(shapes, tokens: int, n_gpus: int) -> dict:
-    return {"workload": f"48-layer op chain (36 DeltaNet + 12 GQA), T={tokens} tokens per GPU, full-size dims",
+def config_dict(shapes, tokens: int, n_gpus: int, cpu_sample: int | None = None) -> dict:
+    extra = {} if cpu_sample is None else {
+        "cpu_sample": f"each step runs a {cpu_sample}-token shard of this workload on the host cores and gathers from a "
+                      "4096-row Q8_0 table; tokens/s is per token, so the figure compares with the GPU arm's"}
+    return {**extra, "workload": f"48-layer op chain (36 DeltaNet + 12 GQA), T={tokens} tokens per GPU, full-size dims",
             "tokens_per_gpu": tokens, "global_tokens": tokens * n_gpus, "hidden": shapes.hidden, "layers": 48,
             "parallelism": f"token-sharded x{n_gpus}, no collective", "l2": "inputs larger than L2 (rotating buffer sets)"}
 
@@ -133,7 +143,7 @@ def run_reference(args) -> None:
     line = {"metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
-            "config": config_dict(synth.FULL, args.tokens, args.gpus),
+            "config": config_dict(synth.FULL, args.tokens, args.gpus, cpu_sample=sample),
             "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -236,9 +246,13 @@ def time_graph(torch, fn_capture, replays: int):
     return e0.elapsed_time(e1) / replays
 
 
-# DRAM traffic per token of the add + RMSNorm kernel from its ncu capture (profiles/): equal to its
-# algorithmic bytes (2 rows read, 2 rows written, 2 bytes per element, H = 2048).
+# DRAM traffic per token of the add + RMSNorm kernel. A constant taken from the ncu captures summarized under
+# profiles/ (not measured by this run): equal to the algorithmic bytes (2 rows read, 2 rows written, 2 bytes per
+# element, H = 2048).
 TRAFFIC_PER_TOKEN = 16384
+TRAFFIC_HOW = ("constant from the ncu captures under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum of one "
+               "launch), not measured by this run, scaled by tokens. At 4096 tokens ncu sees the 33.6 MB read; the "
+               "33.6 MB written leave L2 after the kernel and are counted at their algorithmic size")
 
 
 def op_specs(torch, shapes, T: int):
@@ -294,15 +308,18 @@ def op_specs(torch, shapes, T: int):
     return specs, {k_: v * T for k_, v in nbytes.items()}
 
 
-def kernel_table(torch, shapes, T: int, peaks: dict) -> dict:
+def kernel_table(torch, shapes, T: int, peaks: dict, only=None) -> dict:
     """Average duration of each kernel of the chain, launched back to back over a ring of distinct
     buffer sets totalling >= 512 MB (so no launch finds its inputs in the 126 MB L2); one CUDA graph
-    per kernel, CUDA-event timed on the launching stream."""
+    per kernel, CUDA-event timed on the launching stream. The add + norm stores its residual with an
+    L2 keep hint (16.8 MB per launch at 4096 tokens): its ring is sized so that the hinted bytes alone
+    exceed twice the L2, and the same kernel is also timed with the hint switched off."""
+    from halo_flash_b200 import lib
     specs, nbytes_of = op_specs(torch, shapes, T)
     out = {}
-    for name, (make, run) in specs.items():
-        nbytes = nbytes_of[name]
-        n = max(3, -(-512 * 2**20 // nbytes))
+
+    def one(name, make, run, nbytes, min_total):
+        n = max(3, -(-min_total // nbytes))
         sets = [make() for _ in range(n)]
         run(sets[0])
         torch.cuda.synchronize()
@@ -310,24 +327,38 @@ def kernel_table(torch, shapes, T: int, peaks: dict) -> dict:
         ms = time_graph(torch, lambda: [run(b) for _ in range(reps) for b in sets], 5)
         us = ms * 1e3 / (reps * len(sets))
         gbs = nbytes / (us * 1e-6) / 1e9
-        out[name] = {"us": round(us, 3), "bytes": nbytes, "gbs": round(gbs, 1),
-                     "frac_measured": round(gbs / peaks["hbm_gbs"], 4), "frac_8000": round(gbs / 8000.0, 4)}
         del sets
         torch.cuda.empty_cache()
+        return {"us": round(us, 3), "bytes": nbytes, "gbs": round(gbs, 1), "ring_sets": n,
+                "frac_measured": round(gbs / peaks["hbm_gbs"], 4), "frac_8000": round(gbs / 8000.0, 4)}
+
+    for name, (make, run) in specs.items():
+        if only is not None and name not in only:
+            continue
+        nbytes = nbytes_of[name]
+        hinted = name.startswith("add_rmsnorm")
+        # hinted bytes per launch = the residual = a quarter of the plain kernel's bytes; ring of hinted bytes > 2 x L2
+        min_total = max(512 * 2**20, 4 * 2 * 126 * 2**20 + nbytes) if hinted and nbytes < 256 * 2**20 else 512 * 2**20
+        out[name] = one(name, make, run, nbytes, min_total)
+        if name == "add_rmsnorm":
+            lib().tune("l2_keep", 0)
+            try:
+                out["add_rmsnorm_no_keep_hint"] = one(name, make, run, nbytes, min_total)
+            finally:
+                lib().tune("l2_keep", 1)
     return out
 
 
-def decode_steps(args) -> None:
+def decode_table(torch, max_batch: int) -> dict:
     """Decode form of the chain (config 2): B tokens per step, the full 151 936-row Q8_0 table, token and
     position of every batch entry read from device memory, one captured graph replayed after the host rewrites
     those 64-byte parameter rows; the add + norm writes its normalized row as Q8_0 blocks (the decode
-    configuration's epilogue). Prints microseconds per step for B = 1 .. --decode-batch (a latency figure;
+    configuration's epilogue). Microseconds per step for B = 1, 2, 4 .. max_batch (a latency figure;
     the step moves only ~5 MB per token, so it is bound by the 230 launches, not by HBM)."""
-    import torch
     from halo_flash_b200 import chain as chain_mod, synth
     out = {}
-    for B in sorted({1, 2, 4, args.decode_batch}):
-        if B > args.decode_batch:
+    for B in sorted({1, 2, 4, max_batch}):
+        if B > max_batch:
             continue
         ch = chain_mod.LayerChain(synth.FULL, B, pos0=0, step_params=True, q8_epilogue=True)
         ch.capture()
@@ -352,20 +383,26 @@ def decode_steps(args) -> None:
                        "tokens_per_s": round(B / (us * 1e-6), 1)}
         del ch
         torch.cuda.empty_cache()
-    print(json.dumps({"metric": "decode_us_per_step_layer_op_chain", "unit": "us", "higher_is_better": False,
-                      "launches_per_step": 230, "vocab": synth.FULL.vocab, "batch": out,
-                      "how": "CUDA events around 200 steps; each step = a 64-byte-per-token parameter upload + one graph replay"}),
+    return {"unit": "us per step", "launches_per_step": 230, "vocab": synth.FULL.vocab, "batch": out,
+            "how": "CUDA events around 200 steps; each step = a 64-byte-per-token parameter upload + one graph replay"}
+
+
+def decode_steps(args) -> None:
+    import torch
+    d = decode_table(torch, args.decode_batch)
+    print(json.dumps({"metric": "decode_us_per_step_layer_op_chain", "unit": "us", "higher_is_better": False, **d}),
           flush=True)
 
 
 def profile_op(args) -> None:
     """A few eager launches of ONE op over distinct buffer sets and nothing else: the small case a
-    profiler capture wants (ncu -k <kernel> -s 2 -c 1 python bench.py --profile-op <op>)."""
+    profiler capture wants (ncu --clock-control none -k <kernel> -s 2 -c 1 python bench.py --profile-op <op>;
+    --profile-sets picks the number of launches, --tokens the size)."""
     import torch
     from halo_flash_b200 import synth
     specs, _ = op_specs(torch, synth.FULL, args.tokens)
     make, run = specs[args.profile_op]
-    sets = [make() for _ in range(6)]
+    sets = [make() for _ in range(args.profile_sets)]
     torch.cuda.synchronize()
     for b in sets:
         run(b)
@@ -430,6 +467,88 @@ def run_e2e(torch, ch, steps: int) -> dict:
     return {"ms_per_step": dt * 1e3, "tokens_per_s": ch.T / dt, "h2d": h2d, "d2h": d2h}
 
 
+def time_chain_blocks(torch, dist, ch, steps: int, min_total_s: float = 1.0, max_blocks: int = 64) -> list[float]:
+    """Blocks of EXACTLY `steps` graph replays, each bracketed by a barrier + synchronize on both sides and
+    timed with CUDA events on the launching stream; per block the max over ranks. Blocks are repeated until
+    `min_total_s` has been timed. Returns the per-block milliseconds."""
+    def block() -> float:
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            ch.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if dist is not None:
+            dist.barrier()
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    out = [block()]
+    n = int(min(max_blocks, max(1, -(-min_total_s * 1e3 // out[0]))))  # the same on every rank: out[0] is reduced
+    out += [block() for _ in range(n - 1)]
+    return out
+
+
+def spread(block_ms: list[float], steps: int) -> dict:
+    per = sorted(m / steps for m in block_ms)
+    return {"blocks": len(per), "steps_per_block": steps, "ms_per_step_median": round(statistics.median(per), 4),
+            "ms_per_step_min": round(per[0], 4), "ms_per_step_max": round(per[-1], 4),
+            "timed_region_s": round(sum(block_ms) / 1e3, 3)}
+
+
+def run_config5(torch, dist, args, rank: int, world: int, local: int, peaks: dict) -> dict:
+    """The long-context configuration: `--tokens5` tokens IN ALL (65 536), token-sharded over the N GPUs of the
+    run (strong scaling: rank r owns tokens [r T/N, (r+1) T/N) at positions offset by its first token). Rank 0
+    also runs the unsharded chain on its own GPU in the same process, so the line carries the efficiency against
+    one GPU without reference to another run."""
+    from halo_flash_b200 import chain as chain_mod, synth
+    total = args.tokens5
+    begin, end = chain_mod.shard_range(total, rank, world)
+    steps = max(2, args.steps5)
+    ch = chain_mod.LayerChain(synth.FULL, end - begin, pos0=begin, device=f"cuda:{local}")
+    ch.capture()
+    for _ in range(3):
+        ch.replay()
+    blocks = time_chain_blocks(torch, dist, ch, steps, min_total_s=0.5, max_blocks=8)
+    sp = spread(blocks, steps)
+    ms = sp["ms_per_step_median"]
+    step_bytes = chain_mod.chain_bytes_per_token(synth.FULL, 2) * (end - begin)
+    del ch
+    torch.cuda.empty_cache()
+    out = {"global_tokens": total, "tokens_per_gpu": end - begin, "n_gpus": world, "scaling": "strong",
+           "steps": steps, "ms_per_step": ms, "tokens_per_s": round(total / (ms * 1e-3), 1), "timing": sp,
+           "chain_effective_gbs_per_gpu": round(step_bytes / (ms * 1e-3) / 1e9, 1),
+           "chain_effective_frac_per_gpu": round(step_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)}
+    if world > 1:
+        ms1 = None
+        if rank == 0:  # the same 65 536 tokens on ONE GPU, in this run
+            ch1 = chain_mod.LayerChain(synth.FULL, total, pos0=0, device=f"cuda:{local}")
+            ch1.capture()
+            for _ in range(3):
+                ch1.replay()
+            b1 = time_chain_blocks(torch, None, ch1, steps, min_total_s=0.5, max_blocks=8)
+            ms1 = spread(b1, steps)["ms_per_step_median"]
+            del ch1
+            torch.cuda.empty_cache()
+        dist.barrier()
+        if rank == 0:
+            out["one_gpu_ms_per_step_same_run"] = ms1
+            out["speedup_vs_one_gpu"] = round(ms1 / ms, 3)
+            out["strong_efficiency_vs_one_gpu"] = round(ms1 / ms / world, 4)
+    if rank == 0 and not args.no_kernel_table:
+        table = kernel_table(torch, synth.FULL, end - begin, peaks,
+                             only=("add_rmsnorm", "l2norm", "gated_norm", "norm_rope_qk", "swiglu_moe", "embed",
+                                   "add_rmsnorm_q8"))
+        out["kernels"] = {k: {"us": v["us"], "gbs": v["gbs"], "frac_measured": v["frac_measured"]} for k, v in table.items()}
+    return out
+
+
 def run_ours(args) -> None:
     import torch
     from halo_flash_b200 import chain as chain_mod, lib, synth
@@ -461,8 +580,6 @@ def run_ours(args) -> None:
     for _ in range(max(args.warmup, 3)):
         ch.replay()
     torch.cuda.synchronize()
-    if dist is not None:
-        dist.barrier()
     try:
         uuid = "GPU-" + str(torch.cuda.get_device_properties(local).uuid)
     except Exception:
@@ -470,22 +587,23 @@ def run_ours(args) -> None:
     sampler = ClockSampler(local, uuid)
     if rank == 0:
         sampler.start()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        ch.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    ms_total = e0.elapsed_time(e1)
-    if dist is not None:
-        dist.barrier()
-        t = torch.tensor([ms_total], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
+    blocks = time_chain_blocks(torch, dist, ch, args.steps, min_total_s=args.min_seconds)
     clocks = sampler.stop() if rank == 0 else None
-    ms_step = ms_total / args.steps
+    timing = spread(blocks, args.steps)
+    ms_step = timing["ms_per_step_median"]
     value = T * n_gpus / (ms_step * 1e-3)
+
+    # the same chain with every output buffer rotating too (no dirty line is overwritten in L2 before it is
+    # written back): the difference to `value` is what single output buffers save
+    rot_ms = None
+    if not args.no_kernel_table:
+        chr_ = chain_mod.LayerChain(synth.FULL, T, pos0=begin, device=f"cuda:{local}", rotate_outputs=True)
+        chr_.capture()
+        for _ in range(3):
+            chr_.replay()
+        rot_ms = spread(time_chain_blocks(torch, dist, chr_, args.steps, min_total_s=0.3, max_blocks=8), args.steps)["ms_per_step_median"]
+        del chr_
+        torch.cuda.empty_cache()
 
     # end to end through host buffers (every rank, max over ranks)
     e2e = {"ms_per_step": float("nan"), "h2d": 0, "d2h": 0} if args.no_e2e else \
@@ -495,18 +613,24 @@ def run_ours(args) -> None:
         t = torch.tensor([e2e_ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
+    del ch
+    torch.cuda.empty_cache()
+
+    config5 = None
+    if not args.no_config5:
+        config5 = run_config5(torch, dist, args, rank, world, local, peaks)
+
     if rank != 0:
         if dist is not None:
             dist.barrier()
             dist.destroy_process_group()
         return
 
-    del ch
-    torch.cuda.empty_cache()
     top = "add_rmsnorm"
     if args.no_kernel_table:
         print(json.dumps({"metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": n_gpus,
-                          "ms_per_step": round(ms_step, 4), "note": "profiler run: legs skipped"}), flush=True)
+                          "ms_per_step": round(ms_step, 4), "timing": timing, "config5": config5,
+                          "note": "profiler run: legs skipped"}), flush=True)
         if dist is not None:
             dist.barrier()
             dist.destroy_process_group()
@@ -515,31 +639,43 @@ def run_ours(args) -> None:
     launches = {"add_rmsnorm": 96, "l2norm": 36, "gated_norm": 36, "norm_rope_qk": 12, "swiglu_moe": 48, "embed": 1}
     est = {k: table[k]["us"] * n for k, n in launches.items()}
     step_bytes = chain_mod.chain_bytes_per_token(synth.FULL, 2) * T
+    eff = step_bytes / (ms_step * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": "norm_rows_lean_kernel<bf16,bf16,K=2,ADD> (residual add + RMSNorm(1+w), H=2048)",
                 "achieved": table[top]["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": round(table[top]["gbs"] / peaks["hbm_gbs"], 4), "peak_kind": peak_kind,
                 "frac_of_8000": table[top]["frac_8000"], "traffic": TRAFFIC_PER_TOKEN * T,
-                "traffic_how": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at T=4096 "
-                               "(33.6 MB read; the write-back of the 33.6 MB written is deferred in L2 and is "
-                               "counted at its algorithmic size), scaled by tokens", "us_per_launch": table[top]["us"],
+                "traffic_how": TRAFFIC_HOW, "us_per_launch": table[top]["us"],
                 "bytes_per_launch": table[top]["bytes"],
-                "how": "CUDA events around one graph of back-to-back launches over a >=512 MB ring of buffer sets",
-                "chain": {"bytes_per_step": step_bytes, "gbs": round(step_bytes / (ms_step * 1e-3) / 1e9, 1),
-                          "frac": round(step_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                "how": "CUDA events around one graph of back-to-back launches over a ring of buffer sets whose "
+                       "keep-hinted bytes exceed twice the L2; `add_rmsnorm_no_keep_hint` is the same kernel with the hint off",
+                "chain": {"bytes_per_step": step_bytes, "effective_gbs": round(eff, 1),
+                          "effective_frac": round(eff / peaks["hbm_gbs"], 4),
+                          "what": "algorithmic bytes / step time; NOT a DRAM fraction: the residual re-read is served "
+                                  "from L2 by design and single output buffers can be overwritten in L2 before write-back",
+                          "rotating_outputs_ms_per_step": rot_ms,
+                          "rotating_outputs_effective_frac": None if not rot_ms else
+                          round(step_bytes / (rot_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
                           "ms_from_kernel_table": round(sum(est.values()) / 1e3, 4)},
                 "kernels": table}
     cpu = None
     if n_gpus == 1 and not args.no_cpu:
         cpu = time_cpu_chain(synth.FULL, args.cpu_tokens, host_threads(), 1, 1)
         cpu.pop("ms_per_step")
+    decode = None
+    if n_gpus == 1 and not args.no_decode:
+        decode = decode_table(torch, 8)
+    e2e_line = None
+    if not args.no_e2e:
+        e2e_line = {"value": round(T * n_gpus / (e2e_ms * 1e-3), 1), "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"],
+                    "d2h_bytes_per_step": e2e["d2h"], "ms_per_step": round(e2e_ms, 3),
+                    "h2d_gbs_per_rank": round(e2e["h2d"] / (e2e_ms * 1e-3) / 1e9, 2),
+                    "limiter": "host-to-device copies from pinned host memory (PCIe and host memory bandwidth shared by the ranks)"}
     line = {"metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": n_gpus, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": config_dict(synth.FULL, T, n_gpus), "clocks": clocks,
-            "e2e": None if args.no_e2e else
-            {"value": round(T * n_gpus / (e2e_ms * 1e-3), 1), "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"],
-             "d2h_bytes_per_step": e2e["d2h"], "ms_per_step": round(e2e_ms, 3)},
-            "gpu_launches": launches_per_step * args.steps, "roofline": roofline, "cpu_baseline": cpu}
+            "config": config_dict(synth.FULL, T, n_gpus), "clocks": clocks, "timing": timing,
+            "e2e": e2e_line, "gpu_launches": launches_per_step * args.steps, "roofline": roofline,
+            "config5": config5, "decode": decode, "cpu_baseline": cpu}
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
@@ -551,13 +687,19 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--tokens", type=int, default=4096, help="tokens per GPU per step")
+    ap.add_argument("--tokens", type=int, default=DEFAULT_TOKENS, help="tokens per GPU per step")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--cpu-tokens", type=int, default=1024, help="token sample of the CPU path")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
     ap.add_argument("--no-kernel-table", action="store_true", help="skip the per-kernel timing leg (profiler captures)")
+    ap.add_argument("--min-seconds", type=float, default=1.0, help="repeat the block of --steps replays until this much is timed")
+    ap.add_argument("--tokens5", type=int, default=65536, help="global tokens of the long-context configuration (sharded over the GPUs)")
+    ap.add_argument("--steps5", type=int, default=5, help="steps per timed block of the long-context configuration")
+    ap.add_argument("--no-config5", action="store_true", help="skip the long-context configuration")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode latency table")
+    ap.add_argument("--profile-sets", type=int, default=6, help="launches of --profile-op")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream-ordered launches (no programmatic dependent launch)")
     ap.add_argument("--decode-batch", type=int, default=0, help="time the decode form of the chain for batch 1 .. B and exit")
     ap.add_argument("--profile-op", default=None, help="run 6 eager launches of one op and exit (profiler captures): "

@@ -86,7 +86,7 @@ class BlockOutputs:
 class LayerChain:
     def __init__(self, shapes: Shapes, tokens: int, *, pos0: int = 0, device="cuda:0", dtype=torch.bfloat16,
                  sets: int = 2, vocab: int | None = None, seed: int = synth.SEED, step_params: bool = False,
-                 q8_epilogue: bool = False):
+                 q8_epilogue: bool = False, rotate_outputs: bool = False):
         if not torch.cuda.is_available():
             raise RuntimeError("LayerChain needs a CUDA device: halo_flash_b200 has no CPU path")
         self.s, self.T, self.pos0, self.dtype = shapes, tokens, pos0, dtype
@@ -114,6 +114,13 @@ class LayerChain:
         self.xn_q8 = torch.empty(T, s.q8_row_bytes, device=dev, dtype=torch.uint8) if q8_epilogue else None
         self.h_s = torch.empty(T, s.ff, device=dev, dtype=dtype)
         self.h_r = torch.empty(T * k, s.ff, device=dev, dtype=dtype)
+        # Measurement variant: the normalized rows and the SwiGLU outputs rotate through four buffers each, so
+        # that no output line is overwritten while it still sits dirty in L2 (the default writes each into one
+        # buffer, as an engine does with its scratch arena).
+        self.out_ring = None
+        if rotate_outputs:
+            self.out_ring = [(torch.empty_like(self.xn), torch.empty_like(self.h_s), torch.empty_like(self.h_r))
+                             for _ in range(4)]
         self.rope_tab = torch.empty(T, 2, s.rot // 2, device=dev, dtype=torch.float32)
         # weights: zero-centred norm gammas (applied as 1 + w), plain gated-norm gamma
         wg = torch.Generator(device="cpu").manual_seed(seed)
@@ -150,15 +157,19 @@ class LayerChain:
     # ---- one step, eager ------------------------------------------------------------------
     def layer(self, l: int, bo: BlockOutputs) -> None:
         s = self.s
-        xn = None if self.xn_q8 is not None else self.xn
-        ops.add_rmsnorm(self.res, bo.delta_a, self.w_attn[l], s.eps, one_plus=True, xn=xn, q8_0=self.xn_q8)
+        xn_a = xn_b = None if self.xn_q8 is not None else self.xn
+        h_s, h_r = self.h_s, self.h_r
+        if self.out_ring is not None and self.xn_q8 is None:
+            xn_a, h_s, h_r = self.out_ring[(2 * l) % 4]
+            xn_b = self.out_ring[(2 * l + 1) % 4][0]
+        ops.add_rmsnorm(self.res, bo.delta_a, self.w_attn[l], s.eps, one_plus=True, xn=xn_a, q8_0=self.xn_q8)
         if synth.layer_is_gqa(l):
             ops.norm_rope_qk_table(bo.q, bo.k, self.w_q, self.w_k, s.eps, s.rot, self.rope_tab, one_plus=True)
         else:
             ops.l2norm(bo.qk, s.eps)
             ops.gated_norm(bo.o, self.w_gated, bo.z, s.eps, mode=0, y=bo.y)
-        ops.add_rmsnorm(self.res, bo.delta_b, self.w_post[l], s.eps, one_plus=True, xn=xn, q8_0=self.xn_q8)
-        ops.silu_mul_multi([(bo.gate_s, bo.up_s), (bo.gate_r, bo.up_r)], [self.h_s, self.h_r])
+        ops.add_rmsnorm(self.res, bo.delta_b, self.w_post[l], s.eps, one_plus=True, xn=xn_b, q8_0=self.xn_q8)
+        ops.silu_mul_multi([(bo.gate_s, bo.up_s), (bo.gate_r, bo.up_r)], [h_s, h_r])
 
     def step(self) -> None:
         """Enqueue one full step on the current stream: the embedding gather and the rotation table,

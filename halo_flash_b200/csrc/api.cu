@@ -17,8 +17,11 @@ namespace {
 std::atomic<int> g_norm_threads_per_row{0};
 std::atomic<int> g_norm_short_rows_k1{0};
 std::atomic<int> g_norm_force_general{0};
+std::atomic<int> g_l2_keep{1};
 std::atomic<int> g_rope_rows_per_group{0};
 std::atomic<int> g_rope_lean_k{0};
+std::atomic<int> g_rope_variant{0};
+std::atomic<int> g_embed_variant{0};
 std::atomic<int> g_gated_rows_per_group{0};
 std::atomic<int> g_pdl{1};
 
@@ -78,6 +81,7 @@ int RunNorm(NormArgs a, const char* what, halo_b200_stream stream, char* err, si
   a.threads_per_row = g_norm_threads_per_row.load(std::memory_order_relaxed);
   if (g_norm_short_rows_k1.load(std::memory_order_relaxed)) a.short_rows_k1 = 1;
   a.force_general = g_norm_force_general.load(std::memory_order_relaxed);
+  a.keep_hint = g_l2_keep.load(std::memory_order_relaxed);
   bool vec = a.d % 8 == 0 && a.d <= 256u * 8u * 8u && Aligned(a.x, 16) && Aligned(a.y, 16) && Aligned(a.delta, 16) &&
              Aligned(a.res, 16) && Aligned(a.y16, 16) && Aligned(a.w, 16) && a.w_stride % 4 == 0 &&
              Aligned(a.xq, 8) && a.entry_stride % 8 == 0;
@@ -160,6 +164,7 @@ int RunEmbed(EmbedArgs a, const char* what, halo_b200_stream stream, char* err, 
   REQUIRE(Aligned(a.out, DTypeSize(a.out_dtype)) && Aligned(a.ids, 4), "%s: pointer not aligned to its element type",
           what);
   a.vec = a.row_bytes % 16 == 0 && Aligned(a.table, 16) && Aligned(a.out, 16);
+  a.variant = g_embed_variant.load(std::memory_order_relaxed);
   return Done(LaunchEmbedQ8_0(a, S(stream)), what, err, errlen);
 }
 
@@ -185,7 +190,10 @@ int RunQuant(QuantArgs a, const char* what, halo_b200_stream stream, char* err, 
   return Done(LaunchQuantize(a, S(stream)), what, err, errlen);
 }
 
-int RunNormRope(NormRopeArgs a, float theta, const char* what, halo_b200_stream stream, char* err, size_t errlen) {
+// check_only: validate and return 0 when the vector kernels (and with them the rotation-table form) can run these
+// arguments, 1 when only the unfused fallback can, -1 with a message when the call is invalid; nothing is launched.
+int RunNormRope(NormRopeArgs a, float theta, const char* what, halo_b200_stream stream, char* err, size_t errlen,
+                bool check_only = false) {
   if (a.rows == 0) return Done(cudaSuccess, what, err, errlen);  // an empty chunk is a no-op
   REQUIRE(a.in && a.out, "%s: null pointer", what);
   REQUIRE(ValidDType(a.in_dtype) && ValidDType(a.out_dtype), "%s: unknown dtype", what);
@@ -202,6 +210,7 @@ int RunNormRope(NormRopeArgs a, float theta, const char* what, halo_b200_stream 
   }
   a.rows_per_group = g_rope_rows_per_group.load(std::memory_order_relaxed);
   a.lean_k = g_rope_lean_k.load(std::memory_order_relaxed);
+  a.variant = g_rope_variant.load(std::memory_order_relaxed);
   a.force_general = g_norm_force_general.load(std::memory_order_relaxed);
   const bool vec = a.d % 8 == 0 && (a.rot / 2) % 8 == 0 && a.in_row_stride % 8 == 0 && Aligned(a.in, 16) &&
                    Aligned(a.out, 16) && Aligned(a.gate, 16) && Aligned(a.cache, 16) && Aligned(a.w, 16) &&
@@ -213,6 +222,15 @@ int RunNormRope(NormRopeArgs a, float theta, const char* what, halo_b200_stream 
     REQUIRE(a.rows % a.heads == 0, "%s: rows %u not a multiple of heads %u", what, a.rows, a.heads);
     REQUIRE(a.in_row_stride2 >= a.d, "%s: in_row_stride2 < d", what);
     REQUIRE(vec, "%s: two tensors in one launch need 16-byte aligned rows, d %% 8 == 0 and rot %% 16 == 0", what);
+  }
+  if (vec) {
+    const bool combo = a.in_dtype == kF32 || (a.in_dtype == kBF16 && a.out_dtype != kF16) ||
+                       (a.in_dtype == kF16 && a.out_dtype == kF16);
+    REQUIRE(combo, "%s: unsupported (in, out) dtype combination", what);
+  }
+  if (check_only) {
+    if (err && errlen) err[0] = '\0';
+    return vec ? 0 : 1;
   }
   if (vec) {
     const cudaError_t e = LaunchNormRope(a, f, S(stream));
@@ -395,10 +413,46 @@ int RunMoeCombine(MoeCombineArgs a, const char* what, halo_b200_stream stream, c
   return Done(e, what, err, errlen);
 }
 
+// Q and K of one layer as one NormRopeArgs (positions and table left to the caller).
+NormRopeArgs QkArgs(const void* q_in, uint64_t q_row_stride, void* q_out, void* q_gate, const float* w_q, uint32_t q_heads,
+                    const void* k_in, void* k_out, void* k_cache, const float* w_k, uint32_t k_heads, int in_dtype,
+                    int out_dtype, int one_plus, float eps, uint32_t d, uint32_t rotary_dim, uint32_t tokens) {
+  NormRopeArgs a;
+  a.in = q_in;
+  a.in_dtype = in_dtype;
+  a.in_row_stride = q_row_stride;
+  a.out = q_out;
+  a.out_dtype = out_dtype;
+  a.gate = q_gate;
+  a.w = w_q;
+  a.heads = q_heads;
+  a.rows = tokens * q_heads;
+  a.in2 = k_heads ? k_in : nullptr;
+  a.in_row_stride2 = d;
+  a.out2 = k_heads ? k_out : nullptr;
+  a.cache2 = k_heads ? k_cache : nullptr;
+  a.w2 = k_heads ? w_k : nullptr;
+  a.heads2 = k_heads;
+  a.one_plus = one_plus;
+  a.eps = eps;
+  a.d = d;
+  a.rot = rotary_dim;
+  return a;
+}
+
 }  // namespace
 
 namespace halo_b200 {
 bool PdlEnabled() { return g_pdl.load(std::memory_order_relaxed) != 0; }
+
+int CheckNormRopeQk(const void* q_in, uint64_t q_row_stride, void* q_out, void* q_gate, const float* w_q, uint32_t q_heads,
+                    const void* k_in, void* k_out, void* k_cache, const float* w_k, uint32_t k_heads, int in_dtype,
+                    int out_dtype, uint32_t d, uint32_t rotary_dim, uint32_t tokens, float theta, char* err,
+                    size_t errlen) {
+  const NormRopeArgs a = QkArgs(q_in, q_row_stride, q_out, q_gate, w_q, q_heads, k_in, k_out, k_cache, w_k, k_heads,
+                                in_dtype, out_dtype, 0, 0.0f, d, rotary_dim, tokens);
+  return RunNormRope(a, theta, "halo_norm_rope_qk_noalloc", nullptr, err, errlen, true);
+}
 }  // namespace halo_b200
 
 extern "C" {
@@ -425,6 +479,21 @@ int halo_b200_tune(const char* key, int value) {
   if (std::strcmp(key, "rope_lean_k") == 0) {
     if (value != 0 && value != 1 && value != 2) return -1;
     g_rope_lean_k.store(value, std::memory_order_relaxed);
+    return 0;
+  }
+  if (std::strcmp(key, "l2_keep") == 0) {
+    if (value != 0 && value != 1) return -1;
+    g_l2_keep.store(value, std::memory_order_relaxed);
+    return 0;
+  }
+  if (std::strcmp(key, "embed_variant") == 0) {
+    if (value < 0 || value > 1) return -1;
+    g_embed_variant.store(value, std::memory_order_relaxed);
+    return 0;
+  }
+  if (std::strcmp(key, "rope_variant") == 0) {
+    if (value < 0 || value > 3) return -1;
+    g_rope_variant.store(value, std::memory_order_relaxed);
     return 0;
   }
   if (std::strcmp(key, "norm_force_general") == 0) {
@@ -910,26 +979,8 @@ int halo_b200_norm_rope_qk_ex(halo_b200_stream stream, const void* q_in, uint64_
                               int one_plus, float eps, uint32_t d, uint32_t rotary_dim, uint32_t tokens, float theta,
                               const uint32_t* params, uint32_t pstride, uint32_t slot, uint32_t pos0, uint32_t scale,
                               uint32_t* pos_out, char* err, size_t errlen) {
-  NormRopeArgs a;
-  a.in = q_in;
-  a.in_dtype = in_dtype;
-  a.in_row_stride = q_row_stride;
-  a.out = q_out;
-  a.out_dtype = out_dtype;
-  a.gate = q_gate;
-  a.w = w_q;
-  a.heads = q_heads;
-  a.rows = tokens * q_heads;
-  a.in2 = k_in;
-  a.in_row_stride2 = d;
-  a.out2 = k_out;
-  a.cache2 = k_cache;
-  a.w2 = w_k;
-  a.heads2 = k_heads;
-  a.one_plus = one_plus;
-  a.eps = eps;
-  a.d = d;
-  a.rot = rotary_dim;
+  NormRopeArgs a = QkArgs(q_in, q_row_stride, q_out, q_gate, w_q, q_heads, k_in, k_out, k_cache, w_k, k_heads, in_dtype,
+                          out_dtype, one_plus, eps, d, rotary_dim, tokens);
   a.pos.params = params;
   a.pos.pstride = pstride;
   a.pos.slot = slot;
@@ -967,26 +1018,8 @@ int halo_b200_norm_rope_qk_table_ex(halo_b200_stream stream, const void* q_in, u
                                     int one_plus, float eps, uint32_t d, uint32_t rotary_dim, uint32_t tokens,
                                     const float* table, char* err, size_t errlen) {
   REQUIRE(tokens == 0 || table != nullptr, "halo_norm_rope_qk_table: table is null");
-  NormRopeArgs a;
-  a.in = q_in;
-  a.in_dtype = in_dtype;
-  a.in_row_stride = q_row_stride;
-  a.out = q_out;
-  a.out_dtype = out_dtype;
-  a.gate = q_gate;
-  a.w = w_q;
-  a.heads = q_heads;
-  a.rows = tokens * q_heads;
-  a.in2 = k_heads ? k_in : nullptr;
-  a.in_row_stride2 = d;
-  a.out2 = k_heads ? k_out : nullptr;
-  a.cache2 = k_heads ? k_cache : nullptr;
-  a.w2 = k_heads ? w_k : nullptr;
-  a.heads2 = k_heads;
-  a.one_plus = one_plus;
-  a.eps = eps;
-  a.d = d;
-  a.rot = rotary_dim;
+  NormRopeArgs a = QkArgs(q_in, q_row_stride, q_out, q_gate, w_q, q_heads, k_in, k_out, k_cache, w_k, k_heads, in_dtype,
+                          out_dtype, one_plus, eps, d, rotary_dim, tokens);
   a.table = table;
   return RunNormRope(a, 0.0f, "halo_norm_rope_qk_table", stream, err, errlen);
 }

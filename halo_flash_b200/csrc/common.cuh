@@ -7,7 +7,8 @@
 //     separately as on the CPU; the only deliberate departures are the sum of
 //     squares (fused multiply-add), the norm scale (hardware rsqrt, 2 ulp) and the
 //     gate functions (hardware exp2 / reciprocal), all far inside the 1e-5 the
-//     path allows. Q8 encoders use IEEE division: their codes must be bit-exact;
+//     path allows. The Q8 encoders produce the codes and scales of the IEEE divisions bit for
+//     bit without dividing (div127, round_div_codes below);
 //   * 16-bit outputs are rounded once, to nearest even, from the fp32 value
 //     (bf16 as src/kernels/core.hip:70-73, fp16 as a _Float16 cast).
 #ifndef HALO_B200_COMMON_CUH_
@@ -390,14 +391,42 @@ __device__ __forceinline__ float2 sigmoid2_f(float2 x) {
 __device__ __forceinline__ float2 silu2_f(float2 x) { return __fmul2_rn(x, sigmoid2_f(x)); }
 
 // ---- Q8 block epilogues (32 values = the 4 lanes of a quad, 8 values each) ----
+// Three-input maximum (one FMNMX3 on sm_100): max3f ignores NaN operands as fmaxf does, max3f_nan
+// returns NaN when any operand is NaN.
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ float max3f_nan(float a, float b, float c) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// max |v[i]| over 8 values in four instructions.
+__device__ __forceinline__ float amax8(const float (&v)[8]) {
+  const float a = max3f(fabsf(v[0]), fabsf(v[1]), fabsf(v[2]));
+  const float b = max3f(fabsf(v[3]), fabsf(v[4]), fabsf(v[5]));
+  return fmaxf(max3f(fabsf(v[6]), fabsf(v[7]), a), b);
+}
 // Maximum |v| over the quad this lane belongs to; all 32 lanes must call.
 __device__ __forceinline__ float quad_amax(const float (&v)[8]) {
-  float m = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
+  float m = amax8(v);
   m = fmaxf(m, __shfl_xor_sync(kFullMask, m, 1));
   m = fmaxf(m, __shfl_xor_sync(kFullMask, m, 2));
   return m;
+}
+
+// x / 127.0f, correctly rounded, without the division: q0 = x * z with z = RN(1 / 127), the exact
+// remainder r = x - 127 q0 from one FMA, and the correction q0 + r z from a second. Equal to the IEEE
+// quotient for EVERY non-negative finite float, subnormals included (checked exhaustively over all 2^31 - 2^23
+// bit patterns against the host's division); infinity and NaN pass through q0, as x / 127 gives them.
+__device__ __forceinline__ float div127(float x) {
+  constexpr float z = 1.0f / 127.0f;
+  const float q0 = __fmul_rn(x, z);
+  const float r = __fmaf_rn(-q0, 127.0f, x);
+  const float q = __fmaf_rn(r, z, q0);
+  return fabsf(x) < __int_as_float(0x7F800000) ? q : q0;
 }
 
 // q[i] = clamp(rint(v[i] / d), +-127) for 8 values as 8 packed two's-complement bytes, with the
@@ -408,25 +437,28 @@ __device__ __forceinline__ float quad_amax(const float (&v)[8]) {
 // code. The fast path also skips the clamp: with |v| <= amax and d a normal half within 2^-11
 // of amax / 127 the quotient stays below 127.1. A thread redoes its 8 values with the division
 // and the clamp when one of them is within 1e-4 of a boundary (about 1 in 600) or is NaN (the
-// test is written so that NaN fails it), or when d is a subnormal half, infinite or NaN.
-// Clamping before the rounding equals clamping after it (the bounds are integers), and NaN
-// clamps to -127 either way. The fast path runs on packed fp32x2 instructions.
+// distance is then NaN and the NaN-propagating maximum fails the test), or when d is a subnormal
+// half, infinite or NaN. Clamping before the rounding equals clamping after it (the bounds are
+// integers), and NaN clamps to -127 either way. The fast path runs on packed fp32x2 instructions.
 __device__ __forceinline__ uint2 round_div_codes(const float (&v)[8], float d) {
   constexpr float kMagic = 12582912.0f;
   const float r = rcp_approx(d);
   const float2 r2 = make_float2(r, r), magic2 = make_float2(kMagic, kMagic), neg2 = make_float2(-kMagic, -kMagic);
   uint32_t bits[8];
-  bool ok = d >= 6.2e-5f && d < 1e30f;
+  float2 f[4];
 #pragma unroll
-  for (int i = 0; i < 8; i += 2) {
-    const float2 t = __fmul2_rn(make_float2(v[i], v[i + 1]), r2);
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __fmul2_rn(make_float2(v[2 * i], v[2 * i + 1]), r2);
     const float2 s = __fadd2_rn(t, magic2);
     const float2 n = __fadd2_rn(s, neg2);
-    const float2 f = __fadd2_rn(t, make_float2(-n.x, -n.y));
-    ok = ok && fabsf(f.x) <= 0.4999f && fabsf(f.y) <= 0.4999f;
-    bits[i] = __float_as_uint(s.x);
-    bits[i + 1] = __float_as_uint(s.y);
+    f[i] = __fadd2_rn(t, make_float2(-n.x, -n.y));
+    bits[2 * i] = __float_as_uint(s.x);
+    bits[2 * i + 1] = __float_as_uint(s.y);
   }
+  const float far = max3f_nan(max3f_nan(fabsf(f[0].x), fabsf(f[0].y), fabsf(f[1].x)),
+                              max3f_nan(fabsf(f[1].y), fabsf(f[2].x), fabsf(f[2].y)),
+                              max3f_nan(fabsf(f[3].x), fabsf(f[3].y), 0.0f));
+  const bool ok = d >= 6.2e-5f && d < 1e30f && far <= 0.4999f;
   if (!ok) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -441,7 +473,7 @@ __device__ __forceinline__ uint2 round_div_codes(const float (&v)[8], float d) {
 // True Q8_0 (src/core/lowbit.cpp:285-298): d = half(amax / 127); q = clamp(rint(x / float(d)), +-127),
 // 0 when d == 0. Returns the 8 codes packed little-endian and the scale bits.
 __device__ __forceinline__ uint2 q8_0_codes(const float (&v)[8], float amax, uint16_t* dbits) {
-  const f16 dh = __float2half_rn(amax / 127.0f);
+  const f16 dh = __float2half_rn(div127(amax));
   const float d = __half2float(dh);
   *dbits = __half_as_ushort(dh);
   return d > 0.0f ? round_div_codes(v, d) : make_uint2(0u, 0u);

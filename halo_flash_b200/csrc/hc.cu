@@ -250,7 +250,7 @@ __global__ void __launch_bounds__(kBlock, HcMinCtas(HC* K, sizeof(RT)))
       if (a.yq) {  // int8 copy per 32 values = the 4 lanes of a quad (all lanes shuffle)
         float arr[8];
         oct_to_array(v[k], arr);
-        const float qs = quad_amax(arr) / 127.0f;
+        const float qs = div127(quad_amax(arr));
         const uint2 codes = i8_codes(arr, qs);
         if (ok) {
           *reinterpret_cast<uint2*>(a.yq + blocked) = codes;

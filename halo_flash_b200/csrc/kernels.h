@@ -84,6 +84,7 @@ struct NormArgs {
   int threads_per_row = 0;      // 0 = pick automatically
   int short_rows_k1 = 0;        // 1: rows of <= 32 octets keep one octet per thread (default two)
   int force_general = 0;        // 1: never take the lean kernel (tests compare the two)
+  int keep_hint = 1;            // 0: the add + norm stores its residual without the L2 keep policy
   bool vec = true;
 };
 cudaError_t LaunchNorm(const NormArgs& a, cudaStream_t s);
@@ -154,9 +155,17 @@ struct NormRopeArgs {
   const float* table = nullptr;
   int rows_per_group = 0;       // rows a thread group keeps in flight: 2 (default) or 4
   int lean_k = 0;               // tuning: octets per lane of the lean kernel, 1 or 2 (0 = built-in choice)
+  int variant = 0;              // tuning: bit 0 = per-lane gamma loads, bit 1 = scalar rotation (bf16 lean kernel)
   int force_general = 0;        // 1: never take the lean kernel (tests compare the two)
 };
 cudaError_t LaunchNormRope(const NormRopeArgs& a, const InvFreq& f, cudaStream_t s);
+// Validates the arguments of the Q + K fused norm + RoPE without launching anything: 0 = the vector kernels (and so
+// the rotation-table form) can run them, 1 = valid but only the unfused fallback can (unaligned rows), -1 = invalid
+// (message in err).
+int CheckNormRopeQk(const void* q_in, uint64_t q_row_stride, void* q_out, void* q_gate, const float* w_q, uint32_t q_heads,
+                    const void* k_in, void* k_out, void* k_cache, const float* w_k, uint32_t k_heads, int in_dtype,
+                    int out_dtype, uint32_t d, uint32_t rotary_dim, uint32_t tokens, float theta, char* err,
+                    size_t errlen);
 
 // cos / sin of float(pos) * inv_freq[i] for every token: table[t][0][i] = cos, table[t][1][i] = sin.
 struct RopeTableArgs {
@@ -213,6 +222,7 @@ struct EmbedArgs {
   void* out = nullptr;  // [tokens][cols]
   int out_dtype = kF32;
   bool vec = true;
+  int variant = 0;  // tuning: 1 = never take the streaming kernel
 };
 cudaError_t LaunchEmbedQ8_0(const EmbedArgs& a, cudaStream_t s);
 

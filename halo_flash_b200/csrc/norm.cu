@@ -17,6 +17,10 @@
 #include "common.cuh"
 #include "kernels.h"
 
+#ifndef HALO_EPI_CTAS
+#define HALO_EPI_CTAS 5
+#endif
+
 namespace halo_b200 {
 namespace {
 
@@ -39,7 +43,7 @@ __device__ __forceinline__ void q8_epilogues(const NormArgs& a, const float (&v)
     }
   }
   if (a.xq) {
-    const float scale = amax / 127.0f;
+    const float scale = div127(amax);
     const uint2 codes = i8_codes(v, scale);
     if (ok) {
       if (a.kb_tokens) {
@@ -222,7 +226,7 @@ struct LeanArgs {
 // 2 = the same with gamma 1 + w; 3 = L2 norm without gamma into y. The fixed modes exist because even warp-uniform tests
 // cost these microsecond CTAs 3-4 % (12.6 vs 12.1 us on the add + norm of 4096 x 2048).
 template <typename XT, typename YT, int K, bool ADD, bool EPI, bool WIDE, int MODE>
-__global__ void __launch_bounds__(kBlock, (!EPI && MODE != 0 && sizeof(XT) == 2) ? 6 : (EPI && sizeof(XT) == 2) ? 5 : 1) norm_rows_lean_kernel(const LeanArgs a) {
+__global__ void __launch_bounds__(kBlock, K > 2 ? (sizeof(XT) == 2 ? 4 : 1) : (!EPI && MODE != 0 && sizeof(XT) == 2) ? 6 : (EPI && sizeof(XT) == 2) ? HALO_EPI_CTAS : 1) norm_rows_lean_kernel(const LeanArgs a) {
   pdl_begin();
   __shared__ float scratch[WIDE ? kBlock / 32 : 1];
   // Q8_0 staging: the 32 octets of a warp's slab are 8 blocks = 272 contiguous output bytes that
@@ -298,10 +302,7 @@ __global__ void __launch_bounds__(kBlock, (!EPI && MODE != 0 && sizeof(XT) == 2)
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       oct_to_array(v[k], arr[k]);
-      float m[4];  // tree instead of a chain of eight
-#pragma unroll
-      for (int i = 0; i < 4; ++i) m[i] = fmaxf(fabsf(arr[k][2 * i]), fabsf(arr[k][2 * i + 1]));
-      amax[k] = fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
+      amax[k] = amax8(arr[k]);
     }
 #pragma unroll
     for (int k = 0; k < K; ++k) amax[k] = fmaxf(amax[k], __shfl_xor_sync(kFullMask, amax[k], 1));
@@ -344,7 +345,7 @@ __global__ void __launch_bounds__(kBlock, (!EPI && MODE != 0 && sizeof(XT) == 2)
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         const uint32_t c0 = ((k << lg) + lir) << 3;
-        const float qs = amax[k] / 127.0f;
+        const float qs = div127(amax[k]);
         *reinterpret_cast<uint2*>(a.xq + off + c0) = i8_codes(arr[k], qs);
         if ((c0 & 31u) == 0) a.xd[static_cast<size_t>(row) * (a.d >> 5) + (c0 >> 5)] = qs;
       }
@@ -618,6 +619,8 @@ Shape PickShape(unsigned octs, unsigned rows, int want_g, unsigned min_g, int wa
     // kernel, for callers that need the two to agree bit for bit.
     g = 1;
     while ((want_k1 ? g : 2 * g) < octs) g <<= 1;
+    // rows of 256 (a GQA head): eight lanes with four octets each, the layout of the fused norm + RoPE kernel
+    if (!want_k1 && octs == 32) g = 8;
   } else {
     // Two octets per thread keep registers low (many resident CTAs, many loads in flight)
     // and the gammas prefetchable; measured best at d = 2048 (g = 128) on B200.
@@ -635,6 +638,15 @@ Shape PickShape(unsigned octs, unsigned rows, int want_g, unsigned min_g, int wa
   sh.rows_per_cta = kBlock / g;
   sh.full = octs == kp * g && rows % sh.rows_per_cta == 0;
   return sh;
+}
+
+template <typename XT, typename YT, int K, bool ADD, bool WIDE>
+void LaunchLeanMode(const LeanArgs& l, bool epi, int mode, unsigned grid, cudaStream_t s) {
+  if (epi) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 0>, grid, kBlock, 0, s, l);
+  else if (mode == 2) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, WIDE, 2>, grid, kBlock, 0, s, l);
+  else if (mode == 1) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, WIDE, 1>, grid, kBlock, 0, s, l);
+  else if (mode == 3) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, WIDE, 3>, grid, kBlock, 0, s, l);
+  else LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, WIDE, 0>, grid, kBlock, 0, s, l);
 }
 
 template <typename XT, typename YT, int K, bool ADD>
@@ -657,24 +669,18 @@ cudaError_t LaunchLean(const NormArgs& a, const Shape& sh, unsigned grid, cudaSt
   // The residual is asked to stay in L2 when it is small enough to survive there until the next add + norm:
   // 4096 x 2048 bf16 is 16.8 MB of the 126 MB. (Keeping the normalized rows as well measured no gain at 4096
   // tokens and cost 3 % at 65 536, where the two buffers are 537 MB.)
-  l.keep_res = ADD && static_cast<size_t>(a.rows) * a.d * sizeof(XT) <= (40u << 20);
+  l.keep_res = ADD && a.keep_hint && static_cast<size_t>(a.rows) * a.d * sizeof(XT) <= (40u << 20);
   // a warp's 32 octets must be consecutive in the output: rows of at least a warp, or one octet per thread
   l.stage_q8 = a.q8_0 && (reinterpret_cast<uintptr_t>(a.q8_0) & 15u) == 0 && (sh.lg >= 5 || K == 1);
   const bool epi = a.q8_0 || a.xq;
   const int mode = (!epi && a.w && a.y && !a.l2) ? (a.one_plus ? 2 : 1) : (!epi && !a.w && a.y && a.l2) ? 3 : 0;
-  if (sh.lg > 5) {
-    if (epi) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, true, 0>, grid, kBlock, 0, s, l);
-    else if (mode == 2) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, true, 2>, grid, kBlock, 0, s, l);
-    else if (mode == 1) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, true, 1>, grid, kBlock, 0, s, l);
-    else if (mode == 3) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, true, 3>, grid, kBlock, 0, s, l);
-    else LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, true, 0>, grid, kBlock, 0, s, l);
-  } else {
-    if (epi) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, false, 0>, grid, kBlock, 0, s, l);
-    else if (mode == 2) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, false, 2>, grid, kBlock, 0, s, l);
-    else if (mode == 1) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, false, 1>, grid, kBlock, 0, s, l);
-    else if (mode == 3) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, false, 3>, grid, kBlock, 0, s, l);
-    else LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, false, 0>, grid, kBlock, 0, s, l);
+  if constexpr (K <= 2) {  // rows wider than a warp per row exist only with one or two octets per thread
+    if (sh.lg > 5) {
+      LaunchLeanMode<XT, YT, K, ADD, true>(l, epi, mode, grid, s);
+      return cudaGetLastError();
+    }
   }
+  LaunchLeanMode<XT, YT, K, ADD, false>(l, epi, mode, grid, s);
   return cudaGetLastError();
 }
 
@@ -692,10 +698,13 @@ cudaError_t LaunchNormT(const NormArgs& a, cudaStream_t s) {
   constexpr bool kLeanTypes = (std::is_same_v<XT, float> && !std::is_same_v<YT, f16>) ||
                               (std::is_same_v<XT, bf16> && !std::is_same_v<YT, f16>) ||
                               (std::is_same_v<XT, f16> && std::is_same_v<YT, f16>);
-  const bool lean = sh.full && sh.k <= 2 && a.rows_per_entry == 0 && a.w_period <= 1 && a.y16 == nullptr &&
+  const bool lean = sh.full && (sh.k <= 2 || (sh.k == 4 && sh.lg == 3)) && a.rows_per_entry == 0 && a.w_period <= 1 && a.y16 == nullptr &&
                     a.rscale == nullptr && a.kb_tokens == 0 && !a.force_general;
   if constexpr (kLeanTypes) {
-    if (lean) return sh.k == 1 ? LaunchLean<XT, YT, 1, ADD>(a, sh, grid, s) : LaunchLean<XT, YT, 2, ADD>(a, sh, grid, s);
+    if (lean) {
+      if (sh.k == 4) return LaunchLean<XT, YT, 4, ADD>(a, sh, grid, s);
+      return sh.k == 1 ? LaunchLean<XT, YT, 1, ADD>(a, sh, grid, s) : LaunchLean<XT, YT, 2, ADD>(a, sh, grid, s);
+    }
   }
   const float inv_d = 1.0f / static_cast<float>(a.d);
   switch (sh.k) {

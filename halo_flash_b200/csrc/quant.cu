@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(kBlock) quantize_vec_kernel(const QuantArgs a)
     }
   }
   if (a.xq) {
-    const float scale = amax / 127.0f;
+    const float scale = div127(amax);
     const uint2 codes = i8_codes(v, scale);
     if (ok) {
       if (a.kb_tokens) {
@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(kBlock) quantize_vec_kernel(const QuantArgs a)
         r[i] = v[i] - static_cast<float>(q) * scale;
       }
       const float rmax = quad_amax(r);
-      const float s2 = rmax / 127.0f;
+      const float s2 = div127(rmax);
       const uint2 c2 = i8_codes(r, s2);
       if (ok) {
         *reinterpret_cast<uint2*>(a.xq2 + static_cast<size_t>(row) * a.cols + c0) = c2;

@@ -9,6 +9,8 @@
 // pow(theta, -2 i / rot) with the CPU's libm and passes the table as a kernel
 // argument; the device does the single fp32 multiply float(pos) * freq and a
 // full-range sincosf.
+#include <type_traits>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -197,7 +199,7 @@ __device__ __forceinline__ void norm_rope_body(const RopeCta t, const NormRopeAr
   const float* lane_sin;
   uint32_t tok_step;  // floats between two tokens' table rows
   if constexpr (GT) {
-    // precomputed table in global memory (L2-resident, read through the read-only path)
+    // precomputed table in global memory (L2-resident)
     lane_cos = a.table + fbase;
     lane_sin = a.table + half + fbase;
     tok_step = a.rot;
@@ -247,13 +249,11 @@ __device__ __forceinline__ void norm_rope_body(const RopeCta t, const NormRopeAr
     const Oct o = shuffle_oct(x[0], src_lane);
     if (rotates) {
       float4 c0, c1, s0, s1;
-      if constexpr (GT) {
-        c0 = __ldg(reinterpret_cast<const float4*>(tc)), c1 = __ldg(reinterpret_cast<const float4*>(tc + 4));
-        s0 = __ldg(reinterpret_cast<const float4*>(ts)), s1 = __ldg(reinterpret_cast<const float4*>(ts + 4));
-      } else {
-        c0 = *reinterpret_cast<const float4*>(tc), c1 = *reinterpret_cast<const float4*>(tc + 4);
-        s0 = *reinterpret_cast<const float4*>(ts), s1 = *reinterpret_cast<const float4*>(ts + 4);
-      }
+      // plain loads in both cases: the global table was written by the kernel before this one, which may still
+      // have been running when this grid was scheduled (programmatic dependent launch), so it is not read-only for
+      // this kernel's lifetime and must not go through the non-coherent path
+      c0 = *reinterpret_cast<const float4*>(tc), c1 = *reinterpret_cast<const float4*>(tc + 4);
+      s0 = *reinterpret_cast<const float4*>(ts), s1 = *reinterpret_cast<const float4*>(ts + 4);
       rotate8(x[0], o, c0, c1, scale4(s0, sign), scale4(s1, sign));  // +-sin is exact
     }
     OT* dst = static_cast<OT*>(t.out) + static_cast<size_t>(row) * a.d;
@@ -288,11 +288,44 @@ __global__ void __launch_bounds__(kBlock, K * ROWS >= 8 ? 2 : 3) norm_rope_kerne
   else norm_rope_body<IT, OT, K, ROWS, false, GT>(t, a, f, lg, cta, inv_d, rope_smem);
 }
 
+// Packed fp32x2 multiply and add with explicit round-to-nearest: PTX never contracts an
+// instruction that names its rounding, so a product feeding a sum stays two roundings (the
+// rotation must equal the standalone rope kernel and the CPU operator bit for bit).
+__device__ __forceinline__ float2 mul2_rn(float2 a, float2 b) {
+  float2 r;
+  asm("{\n\t.reg .b64 ra, rb, rr;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rr, ra, rb;\n\tmov.b64 {%0, %1}, rr;\n\t}"
+      : "=f"(r.x), "=f"(r.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return r;
+}
+__device__ __forceinline__ float2 add2_rn(float2 a, float2 b) {
+  float2 r;
+  asm("{\n\t.reg .b64 ra, rb, rr;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rr, ra, rb;\n\tmov.b64 {%0, %1}, rr;\n\t}"
+      : "=f"(r.x), "=f"(r.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return r;
+}
+// x = x * cos + o * sin on four pairs: 12 packed instructions for what rotate8 does in 24.
+__device__ __forceinline__ void rotate8_packed(Oct& x, const Oct& o, const Oct& c, const Oct& s) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) x.p[i] = add2_rn(mul2_rn(x.p[i], c.p[i]), mul2_rn(o.p[i], s.p[i]));
+}
+__device__ __forceinline__ Oct oct_from(float4 a, float4 b) {
+  Oct o;
+  o.p[0] = make_float2(a.x, a.y), o.p[1] = make_float2(a.z, a.w);
+  o.p[2] = make_float2(b.x, b.y), o.p[3] = make_float2(b.z, b.w);
+  return o;
+}
+
 // The lean fused kernel for the common case: Q (and K) rows that fill the grid exactly, gammas
-// present, rotation table given, no q|gate split and no cache copy. One row per thread group, one or
-// two octets per lane, operands as plain arguments, no shared memory, no barrier, nothing
-// predicated; which tensor a CTA works on is uniform. Same arithmetic, bit for bit, as the general
-// kernel above.
+// present, rotation table given, no q|gate split and no cache copy. One row per thread group, K
+// octets per lane (4 at d = 256: eight lanes own a row and the 64 rotated dims are the first octet
+// of each, so every lane of the warp takes part in the exchange), operands as plain arguments,
+// nothing predicated; which tensor a CTA works on is uniform. The CTA's gamma (1 + w applied once)
+// is staged in shared memory in the lanes' read order while the rows are in flight. Same arithmetic,
+// bit for bit, as the general kernel above.
 struct RopeLeanArgs {  // scalar fields on purpose: indexing a parameter array by tensor copies it to local memory
   const void *in0, *in1;
   void *out0, *out1;
@@ -304,9 +337,12 @@ struct RopeLeanArgs {  // scalar fields on purpose: indexing a parameter array b
   const float* table;
 };
 
-template <typename IT, typename OT, int K, bool ONEPLUS>
-__global__ void __launch_bounds__(kBlock, K == 2 ? 5 : 6) norm_rope_lean_kernel(const RopeLeanArgs a) {
+constexpr int kLeanCtas(int K) { return K == 4 ? 4 : (K == 2 ? 5 : 6); }
+
+template <typename IT, typename OT, int K, bool ONEPLUS, bool SMEMG, bool PACKROT>
+__global__ void __launch_bounds__(kBlock, kLeanCtas(K)) norm_rope_lean_kernel(const RopeLeanArgs a) {
   pdl_begin();
+  __shared__ __align__(16) float gs[SMEMG ? 8 * K * 32 : 4];  // d <= 8 K g, g <= 32
   const bool sel = blockIdx.x >= a.ctas0;
   const uint32_t cta = blockIdx.x - (sel ? a.ctas0 : 0u);
   const unsigned lg = a.lg, g = 1u << lg;
@@ -319,6 +355,16 @@ __global__ void __launch_bounds__(kBlock, K == 2 ? 5 : 6) norm_rope_lean_kernel(
 #pragma unroll
   for (int k = 0; k < K; ++k) rx[k] = raw_load(src + (((k << lg) + lir) << 3));
   const float* w = sel ? a.w1 : a.w0;
+  if constexpr (SMEMG) {
+    // element e of octet j = k g + l goes to float4 slot (2 k + e / 4 % 2) g + l: a lane's two 16-byte reads per
+    // octet are then contiguous across the lanes of its group (no bank conflicts)
+    for (unsigned e = threadIdx.x; e < a.d; e += kBlock) {
+      const unsigned j = e >> 3, k = j >> lg, l = j & (g - 1), h = (e >> 2) & 1u;
+      const float wv = __ldg(w + e);
+      gs[((((k << 1) + h) << lg) + l) * 4 + (e & 3u)] = ONEPLUS ? 1.0f + wv : wv;
+    }
+    __syncthreads();
+  }
   const unsigned hp = a.rot >> 4;  // lanes per half of the rotated span
   const bool rotates = lir < 2 * hp;
   const bool low = lir < hp;
@@ -332,15 +378,21 @@ __global__ void __launch_bounds__(kBlock, K == 2 ? 5 : 6) norm_rope_lean_kernel(
   }
   const float ss = group_sum_narrow(acc.x + acc.y, g);
   const float scale = rsqrtf(__fmaf_rn(ss, a.inv_d, a.eps));
-  // gammas and this token's cos / sin are requested only now: they come from L1 / L2 (a few KB shared by every
-  // row), and holding them in registers while the row is in flight would cost a resident CTA per SM
+  // gammas and this token's cos / sin are requested only now: they come from shared memory / L1 (a few KB shared
+  // by every row), and holding them in registers while the row is in flight would cost a resident CTA per SM
 #pragma unroll
   for (int k = 0; k < K; ++k) {
-    Oct gm = oct_load_cached(w + (((k << lg) + lir) << 3));
-    if (ONEPLUS) {
-      const float2 one = make_float2(1.0f, 1.0f);
+    Oct gm;
+    if constexpr (SMEMG) {
+      gm = oct_from(*reinterpret_cast<const float4*>(gs + ((((2 * k) << lg) + lir) << 2)),
+                    *reinterpret_cast<const float4*>(gs + ((((2 * k + 1) << lg) + lir) << 2)));
+    } else {
+      gm = oct_load_cached(w + (((k << lg) + lir) << 3));
+      if (ONEPLUS) {
+        const float2 one = make_float2(1.0f, 1.0f);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) gm.p[i] = __fadd2_rn(one, gm.p[i]);
+        for (int i = 0; i < 4; ++i) gm.p[i] = __fadd2_rn(one, gm.p[i]);
+      }
     }
     x[k] = oct_mul(oct_scale(x[k], scale), gm);
   }
@@ -350,10 +402,15 @@ __global__ void __launch_bounds__(kBlock, K == 2 ? 5 : 6) norm_rope_lean_kernel(
     const float* tc = a.table + static_cast<size_t>(token) * a.rot + ((low ? lir : lir - hp) << 3);
     const float* ts = tc + (a.rot >> 1);
     const float sign = low ? -1.0f : 1.0f;  // first halves take -sin, second halves +sin (exact)
-    const float4 c0 = __ldg(reinterpret_cast<const float4*>(tc)), c1 = __ldg(reinterpret_cast<const float4*>(tc + 4));
-    const float4 s0 = scale4(__ldg(reinterpret_cast<const float4*>(ts)), sign);
-    const float4 s1 = scale4(__ldg(reinterpret_cast<const float4*>(ts + 4)), sign);
-    rotate8(x[0], o, c0, c1, s0, s1);
+    // plain (coherent) loads: the table was written by an earlier kernel of the stream that may still have been
+    // running when this grid was scheduled, so it is not read-only for this kernel's lifetime
+    const float4 c0 = *reinterpret_cast<const float4*>(tc), c1 = *reinterpret_cast<const float4*>(tc + 4);
+    const float4 t0 = *reinterpret_cast<const float4*>(ts), t1 = *reinterpret_cast<const float4*>(ts + 4);
+    if constexpr (PACKROT) {
+      rotate8_packed(x[0], o, oct_from(c0, c1), oct_scale(oct_from(t0, t1), sign));
+    } else {
+      rotate8(x[0], o, c0, c1, scale4(t0, sign), scale4(t1, sign));
+    }
   }
   OT* dst = static_cast<OT*>(sel ? a.out1 : a.out0) + off;
 #pragma unroll
@@ -419,16 +476,43 @@ uint32_t Magic(uint32_t divisor, uint64_t max_n) {
                                                           : 0u;
 }
 
+template <typename IT, typename OT, int K>
+void LaunchLeanRope(const RopeLeanArgs& l, unsigned grid, bool one_plus, int variant, cudaStream_t s) {
+  if constexpr (std::is_same_v<IT, bf16> && std::is_same_v<OT, bf16>) {
+    // tuning variants (bit 0: gammas fetched per lane instead of staged; bit 1: scalar rotation)
+    if (variant == 1) {
+      if (one_plus) LaunchKernel(norm_rope_lean_kernel<IT, OT, K, true, false, true>, grid, kBlock, 0, s, l);
+      else LaunchKernel(norm_rope_lean_kernel<IT, OT, K, false, false, true>, grid, kBlock, 0, s, l);
+      return;
+    }
+    if (variant == 2) {
+      if (one_plus) LaunchKernel(norm_rope_lean_kernel<IT, OT, K, true, true, false>, grid, kBlock, 0, s, l);
+      else LaunchKernel(norm_rope_lean_kernel<IT, OT, K, false, true, false>, grid, kBlock, 0, s, l);
+      return;
+    }
+    if (variant == 3) {
+      if (one_plus) LaunchKernel(norm_rope_lean_kernel<IT, OT, K, true, false, false>, grid, kBlock, 0, s, l);
+      else LaunchKernel(norm_rope_lean_kernel<IT, OT, K, false, false, false>, grid, kBlock, 0, s, l);
+      return;
+    }
+  }
+  if (one_plus) LaunchKernel(norm_rope_lean_kernel<IT, OT, K, true, true, true>, grid, kBlock, 0, s, l);
+  else LaunchKernel(norm_rope_lean_kernel<IT, OT, K, false, true, true>, grid, kBlock, 0, s, l);
+}
+
 template <typename IT, typename OT>
 cudaError_t LaunchNormRopeT(const NormRopeArgs& a, const InvFreq& f, cudaStream_t s) {
   const unsigned octs = a.d / 8;
   // Two octets per lane halve the instructions per row; the rotated span must then sit in
   // the first octet of the lanes (rot <= d / 2), which holds for 64-of-256 and 16-of-64.
   int k = (octs >= 2 && a.rot * 2 <= a.d) ? 2 : 1;
+  // Rows of 256: four octets per lane, eight lanes per row (the layout the standalone norm kernel picks for
+  // such rows, so fused equals separate bit for bit); the rotated span must be the first octet of the lanes.
+  if (octs == 32 && a.rot * 4 <= a.d && a.lean_k != 2) k = 4;
   if (a.lean_k == 1 && octs <= 32) k = 1;
   unsigned g = 1, lg = 0;
   while (g * k < octs) g <<= 1, ++lg;
-  const unsigned rows_in_flight = a.rows_per_group ? static_cast<unsigned>(a.rows_per_group) : 2u;
+  const unsigned rows_in_flight = k == 4 ? 1u : (a.rows_per_group ? static_cast<unsigned>(a.rows_per_group) : 2u);
   const unsigned rows_per_cta = kBlock / g * rows_in_flight;
   const unsigned tokens = (a.rows + a.heads - 1) / a.heads;
   const uint64_t rows2 = static_cast<uint64_t>(tokens) * a.heads2;
@@ -453,13 +537,14 @@ cudaError_t LaunchNormRopeT(const NormRopeArgs& a, const InvFreq& f, cudaStream_
     l.ctas0 = a.rows / rpc1;
     l.d = a.d, l.rot = a.rot, l.lg = lg, l.eps = a.eps, l.inv_d = inv_d, l.table = a.table;
     const unsigned lgrid = l.ctas0 + static_cast<unsigned>(rows2 / rpc1);
-    if (k == 2) {
-      if (a.one_plus) LaunchKernel(norm_rope_lean_kernel<IT, OT, 2, true>, lgrid, kBlock, 0, s, l);
-      else LaunchKernel(norm_rope_lean_kernel<IT, OT, 2, false>, lgrid, kBlock, 0, s, l);
-    } else {
-      if (a.one_plus) LaunchKernel(norm_rope_lean_kernel<IT, OT, 1, true>, lgrid, kBlock, 0, s, l);
-      else LaunchKernel(norm_rope_lean_kernel<IT, OT, 1, false>, lgrid, kBlock, 0, s, l);
-    }
+    if (k == 4) LaunchLeanRope<IT, OT, 4>(l, lgrid, a.one_plus != 0, a.variant, s);
+    else if (k == 2) LaunchLeanRope<IT, OT, 2>(l, lgrid, a.one_plus != 0, a.variant, s);
+    else LaunchLeanRope<IT, OT, 1>(l, lgrid, a.one_plus != 0, a.variant, s);
+    return cudaGetLastError();
+  }
+  if (k == 4) {
+    if (a.table) LaunchKernel(norm_rope_kernel<IT, OT, 4, 1, true>, grid, kBlock, 0, s, a, f, lg, ctas1, inv_d, m1, m2);
+    else LaunchKernel(norm_rope_kernel<IT, OT, 4, 1, false>, grid, kBlock, smem, s, a, f, lg, ctas1, inv_d, m1, m2);
     return cudaGetLastError();
   }
   if (a.table) {

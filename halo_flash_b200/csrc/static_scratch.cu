@@ -15,7 +15,11 @@
 //
 // Costs and rules, all consequences of the array being one fixed, shared object:
 //   * 4 MiB of device memory on every GPU that loads the library, held until the process exits.
-//   * tokens * rotary_dim <= kMaxTableFloats, else the call fails with a message (no fallback).
+//   * tokens * rotary_dim <= kMaxTableFloats, else the call fails with a message.
+//   * The arguments are validated before anything is enqueued: a call that returns -1 has launched nothing and
+//     has not touched the array. Shapes the table form cannot take (rows that are not 16-byte aligned, d or
+//     rotary_dim / 2 not multiples of 8, no rotation at all) are forwarded to halo_b200_norm_rope_qk_ex, which
+//     needs no table and allocates nothing either, so the accepted arguments are exactly that call's.
 //   * The array keeps the previous call's table. Nothing in it has to start at zero - each call
 //     overwrites every entry it later reads - but two calls whose kernels overlap on the GPU
 //     (different streams, or the same graph launched twice concurrently) race on it. Calls on one
@@ -28,6 +32,7 @@
 #include <mutex>
 
 #include "../../include/halo_b200.h"
+#include "kernels.h"
 
 namespace {
 
@@ -77,6 +82,14 @@ extern "C" int halo_b200_norm_rope_qk_noalloc(halo_b200_stream stream, const voi
     if (err && errlen) err[0] = '\0';
     return 0;
   }
+  // Validate first: nothing may be enqueued (and the shared array must stay untouched) when the call fails.
+  const int form = halo_b200::CheckNormRopeQk(q_in, q_row_stride, q_out, q_gate, w_q, q_heads, k_in, k_out, k_cache, w_k,
+                                              k_heads, in_dtype, out_dtype, d, rotary_dim, tokens, theta, err, errlen);
+  if (form < 0) return -1;
+  if (form == 1 || rotary_dim < 2)  // no table can serve these rows: the table-free form (it allocates nothing either)
+    return halo_b200_norm_rope_qk_ex(stream, q_in, q_row_stride, q_out, q_gate, w_q, q_heads, k_in, k_out, k_cache, w_k,
+                                     k_heads, in_dtype, out_dtype, one_plus, eps, d, rotary_dim, tokens, theta, params,
+                                     pstride, slot, pos0, scale, pos_out, err, errlen);
   if (static_cast<uint64_t>(tokens) * rotary_dim > kMaxTableFloats) {
     char detail[128];
     std::snprintf(detail, sizeof detail, " (tokens %u x rotary_dim %u; limit %zu floats)", tokens, rotary_dim,
