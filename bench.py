@@ -299,8 +299,13 @@ def op_specs(torch, shapes, T: int):
         "conv_l2norm": (lambda: (r(T, conv_c), torch.empty(T, conv_c, device=dev, dtype=bf)),
                         lambda b: ops.conv_l2norm(b[0], conv_state, conv_w, b[1], l2_channels=2 * s.k_heads * s.lin_dim,
                                                   d=s.lin_dim, eps=s.eps)),
+        # not in the chain: the experts' combine (10 fp16 rows gathered per token + the gated shared expert, fp32 out)
+        "moe_combine": (lambda: (torch.randn(T * k, s.hidden, device=dev).half(), torch.randperm(T * k, device=dev).int().view(T, k),
+                                 torch.rand(T, k, device=dev), torch.randn(T, s.hidden, device=dev), torch.randn(T, device=dev),
+                                 torch.empty(T, s.hidden, device=dev)),
+                        lambda b: ops.moe_combine(b[0], b[1], b[2], b[5], sx=b[3], sg=b[4])),
     }
-    nbytes = {"add_rmsnorm": bpt["add_rmsnorm"], "l2norm": bpt["l2norm"], "gated_norm": bpt["gated_norm"],
+    nbytes = {"add_rmsnorm": bpt["add_rmsnorm"], "moe_combine": k * 2 * s.hidden + 2 * 4 * s.hidden + 8 * k + 4, "l2norm": bpt["l2norm"], "gated_norm": bpt["gated_norm"],
               "norm_rope_qk": bpt["norm_rope"], "swiglu_moe": bpt["swiglu_shared"] + bpt["swiglu_routed"],
               "embed": bpt["embed"], "add_rmsnorm_q8": 3 * 2 * s.hidden + s.q8_row_bytes,
               "hc_combine_norm": (3 * 4 + 1) * 2 * s.hidden + 16,
@@ -703,7 +708,7 @@ def main() -> None:
     ap.add_argument("--no-pdl", action="store_true", help="plain stream-ordered launches (no programmatic dependent launch)")
     ap.add_argument("--decode-batch", type=int, default=0, help="time the decode form of the chain for batch 1 .. B and exit")
     ap.add_argument("--profile-op", default=None, help="run 6 eager launches of one op and exit (profiler captures): "
-                    "add_rmsnorm, add_rmsnorm_q8, l2norm, gated_norm, norm_rope_qk, swiglu_moe, embed, hc_combine_norm, conv_l2norm")
+                    "add_rmsnorm, add_rmsnorm_q8, l2norm, gated_norm, norm_rope_qk, swiglu_moe, embed, hc_combine_norm, conv_l2norm, moe_combine")
     args = ap.parse_args()
     if args.no_pdl:
         from halo_flash_b200 import lib

@@ -108,7 +108,7 @@ SIGNATURES: dict[str, list] = {
 
 # Entry points with other calling shapes.
 OTHER_EXPORTS = ["halo_b200_version", "halo_b200_launch", "halo_b200_kernel_count", "halo_b200_kernel_name",
-                 "halo_b200_tune", "halo_b200_conv_stage_timeouts"]
+                 "halo_b200_tune", "halo_b200_conv_stage_timeouts", "halo_b200_stage_timeouts"]
 
 
 class HaloArgValue(C.Union):

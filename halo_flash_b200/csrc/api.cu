@@ -18,10 +18,11 @@ std::atomic<int> g_norm_threads_per_row{0};
 std::atomic<int> g_norm_short_rows_k1{0};
 std::atomic<int> g_norm_force_general{0};
 std::atomic<int> g_l2_keep{1};
+std::atomic<int> g_norm_staged{1};
 std::atomic<int> g_rope_rows_per_group{0};
 std::atomic<int> g_rope_lean_k{0};
-std::atomic<int> g_rope_variant{0};
-std::atomic<int> g_embed_variant{0};
+std::atomic<int> g_rope_staged{1};
+std::atomic<int> g_carveout{-1};
 std::atomic<int> g_gated_rows_per_group{0};
 std::atomic<int> g_pdl{1};
 
@@ -82,6 +83,7 @@ int RunNorm(NormArgs a, const char* what, halo_b200_stream stream, char* err, si
   if (g_norm_short_rows_k1.load(std::memory_order_relaxed)) a.short_rows_k1 = 1;
   a.force_general = g_norm_force_general.load(std::memory_order_relaxed);
   a.keep_hint = g_l2_keep.load(std::memory_order_relaxed);
+  a.staged = g_norm_staged.load(std::memory_order_relaxed);
   bool vec = a.d % 8 == 0 && a.d <= 256u * 8u * 8u && Aligned(a.x, 16) && Aligned(a.y, 16) && Aligned(a.delta, 16) &&
              Aligned(a.res, 16) && Aligned(a.y16, 16) && Aligned(a.w, 16) && a.w_stride % 4 == 0 &&
              Aligned(a.xq, 8) && a.entry_stride % 8 == 0;
@@ -164,7 +166,6 @@ int RunEmbed(EmbedArgs a, const char* what, halo_b200_stream stream, char* err, 
   REQUIRE(Aligned(a.out, DTypeSize(a.out_dtype)) && Aligned(a.ids, 4), "%s: pointer not aligned to its element type",
           what);
   a.vec = a.row_bytes % 16 == 0 && Aligned(a.table, 16) && Aligned(a.out, 16);
-  a.variant = g_embed_variant.load(std::memory_order_relaxed);
   return Done(LaunchEmbedQ8_0(a, S(stream)), what, err, errlen);
 }
 
@@ -210,7 +211,7 @@ int RunNormRope(NormRopeArgs a, float theta, const char* what, halo_b200_stream 
   }
   a.rows_per_group = g_rope_rows_per_group.load(std::memory_order_relaxed);
   a.lean_k = g_rope_lean_k.load(std::memory_order_relaxed);
-  a.variant = g_rope_variant.load(std::memory_order_relaxed);
+  a.staged = g_rope_staged.load(std::memory_order_relaxed);
   a.force_general = g_norm_force_general.load(std::memory_order_relaxed);
   const bool vec = a.d % 8 == 0 && (a.rot / 2) % 8 == 0 && a.in_row_stride % 8 == 0 && Aligned(a.in, 16) &&
                    Aligned(a.out, 16) && Aligned(a.gate, 16) && Aligned(a.cache, 16) && Aligned(a.w, 16) &&
@@ -444,6 +445,7 @@ NormRopeArgs QkArgs(const void* q_in, uint64_t q_row_stride, void* q_out, void* 
 
 namespace halo_b200 {
 bool PdlEnabled() { return g_pdl.load(std::memory_order_relaxed) != 0; }
+int CarveoutPreference() { return g_carveout.load(std::memory_order_relaxed); }
 
 int CheckNormRopeQk(const void* q_in, uint64_t q_row_stride, void* q_out, void* q_gate, const float* w_q, uint32_t q_heads,
                     const void* k_in, void* k_out, void* k_cache, const float* w_k, uint32_t k_heads, int in_dtype,
@@ -477,7 +479,7 @@ int halo_b200_tune(const char* key, int value) {
     return 0;
   }
   if (std::strcmp(key, "rope_lean_k") == 0) {
-    if (value != 0 && value != 1 && value != 2) return -1;
+    if (value != 0 && value != 1 && value != 2) return -1;  // 0 = built-in (four chunks per lane on rows of 256)
     g_rope_lean_k.store(value, std::memory_order_relaxed);
     return 0;
   }
@@ -486,14 +488,19 @@ int halo_b200_tune(const char* key, int value) {
     g_l2_keep.store(value, std::memory_order_relaxed);
     return 0;
   }
-  if (std::strcmp(key, "embed_variant") == 0) {
-    if (value < 0 || value > 1) return -1;
-    g_embed_variant.store(value, std::memory_order_relaxed);
+  if (std::strcmp(key, "norm_staged") == 0) {
+    if (value < 0 || value > 2) return -1;
+    g_norm_staged.store(value, std::memory_order_relaxed);
     return 0;
   }
-  if (std::strcmp(key, "rope_variant") == 0) {
-    if (value < 0 || value > 3) return -1;
-    g_rope_variant.store(value, std::memory_order_relaxed);
+  if (std::strcmp(key, "carveout") == 0) {
+    if (value < -1 || value > 100) return -1;
+    g_carveout.store(value, std::memory_order_relaxed);
+    return 0;
+  }
+  if (std::strcmp(key, "rope_staged") == 0) {
+    if (value != 0 && value != 1) return -1;
+    g_rope_staged.store(value, std::memory_order_relaxed);
     return 0;
   }
   if (std::strcmp(key, "norm_force_general") == 0) {
@@ -1522,9 +1529,18 @@ int halo_b200_scale_silu(halo_b200_stream stream, const float* x, void* y, int y
 }
 
 
+int halo_b200_stage_timeouts(unsigned int* count, char* err, size_t errlen) {
+  REQUIRE(count != nullptr, "halo_b200_stage_timeouts: count is null");
+  unsigned int conv = 0, rope = 0, norm = 0;
+  cudaError_t e = ReadConvStageTimeouts(&conv);
+  if (e == cudaSuccess) e = ReadRopeStageTimeouts(&rope);
+  if (e == cudaSuccess) e = ReadNormStageTimeouts(&norm);
+  *count = conv + rope + norm;
+  return Done(e, "halo_b200_stage_timeouts", err, errlen);
+}
+
 int halo_b200_conv_stage_timeouts(unsigned int* count, char* err, size_t errlen) {
-  REQUIRE(count != nullptr, "halo_b200_conv_stage_timeouts: count is null");
-  return Done(ReadConvStageTimeouts(count), "halo_b200_conv_stage_timeouts", err, errlen);
+  return halo_b200_stage_timeouts(count, err, errlen);
 }
 
 

@@ -16,6 +16,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "stage.cuh"
 
 namespace halo_b200 {
 namespace {
@@ -131,14 +132,10 @@ __global__ void __launch_bounds__(kBlock, kTile >= 8 ? 2 : 3) conv_l2norm_kernel
 // of the CTA's channel slice per row, completion counted on an mbarrier per buffer). Bytes in flight
 // cost no registers and the loads of the next tile overlap the arithmetic of this one.
 //
-// Every wait is bounded: kStageSpinLimit polls (seconds), after which the CTA counts a timeout in
-// g_conv_stage_timeouts and all of its threads return together without writing further tiles. Nothing
-// else in the library waits on a barrier object. Rows outside the chunk are not copied; their lanes
-// read zeros (or the conv state).
-__device__ unsigned int g_conv_stage_timeouts = 0;
-constexpr unsigned kStageSpinLimit = 1u << 22;
-
-__device__ __forceinline__ unsigned smem_addr(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
+// Every wait is bounded (stage.cuh): a CTA whose wait ran out counts it in g_stage_timeouts, gives the copies
+// it has in flight one more bounded wait and all of its threads return together without writing further
+// tiles. Rows outside the chunk are not copied; their lanes read zeros (or the conv state).
+__device__ unsigned int g_stage_timeouts = 0;
 
 template <typename IT, typename OT, unsigned HL, int kTile, int MODE>  // MODE 0: per-thread q/k test, 1: all q/k, 2: none
 __device__ __forceinline__ void conv_stage_compute(const ConvArgs& a, const Oct (&w)[kTaps], const IT* tile,
@@ -217,11 +214,7 @@ __global__ void __launch_bounds__(kBlock, 2) conv_l2norm_staged_kernel(const Con
   IT* bufs = reinterpret_cast<IT*>(conv_smem);
   const unsigned row_bytes = slice_octs * 8u * static_cast<unsigned>(sizeof(IT));  // a multiple of 16
 
-  if (threadIdx.x == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&bars[0])) : "memory");
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&bars[1])) : "memory");
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
+  if (threadIdx.x == 0) stage_init(bars, 2);
   __syncthreads();
 
   // thread 0 asks the copy engine for the rows of token tile `by` into buffer `b`
@@ -229,13 +222,12 @@ __global__ void __launch_bounds__(kBlock, 2) conv_l2norm_staged_kernel(const Con
     uint32_t first_row, last_row;
     tile_rows<kTile>(by * kTile, a.tokens, &first_row, &last_row);
     const unsigned bar = smem_addr(&bars[b]);
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((last_row - first_row) * row_bytes) : "memory");
+    stage_expect(bar, (last_row - first_row) * row_bytes);
     const IT* src = static_cast<const IT*>(a.in) + static_cast<size_t>(by * kTile + first_row - 3u) * a.channels +
                     (static_cast<size_t>(oc0) << 3);
     unsigned dst = smem_addr(bufs + b * buf_elems + first_row * row_elems);
     for (uint32_t j = first_row; j < last_row; ++j, src += a.channels, dst += row_elems * sizeof(IT))
-      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                   ::"r"(dst), "l"(src), "r"(row_bytes), "r"(bar) : "memory");
+      stage_copy(dst, src, row_bytes, bar);
   };
 
   uint32_t by = lane_of_slice;
@@ -265,18 +257,17 @@ __global__ void __launch_bounds__(kBlock, 2) conv_l2norm_staged_kernel(const Con
     const unsigned b = n & 1u;
     // the other buffer was last read in iteration n - 1, which ended with a CTA barrier: refill it now
     if (threadIdx.x == 0 && by + stride < token_tiles) request(by + stride, b ^ 1u);
-    // wait for this buffer's bytes: its (n / 2)-th use, so phase parity (n / 2) & 1; bounded polls
-    const unsigned bar = smem_addr(&bars[b]), parity = (n >> 1) & 1u;
-    unsigned done = 0;
-    for (unsigned spin = 0; spin < kStageSpinLimit && !done; ++spin) {
-      asm volatile(
-          "{\n.reg .pred p;\n"
-          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-          "selp.u32 %0, 1, 0, p;\n}"
-          : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-    }
-    if (!__syncthreads_and(static_cast<int>(done))) {  // never seen; all threads leave together
-      if (threadIdx.x == 0) atomicAdd(&g_conv_stage_timeouts, 1u);
+    // wait for this buffer's bytes: its (n / 2)-th use, so phase parity (n / 2) & 1; bounded (see stage_wait)
+    const bool prefetched = by + stride < token_tiles;
+    const unsigned done = stage_wait(smem_addr(&bars[b]), (n >> 1) & 1u);
+    if (!__syncthreads_and(static_cast<int>(done))) {
+      // Never seen. All threads leave together, and nothing more is requested; but the CTA must not hand its shared
+      // memory back while a copy into it may still be in flight, so this buffer and the prefetch issued above (the
+      // other buffer's ((n + 1) / 2)-th use) each get one more bounded wait first. The output tiles this CTA still
+      // owned stay unwritten: the counter is how the host learns that the call's results are invalid.
+      stage_wait(smem_addr(&bars[b]), (n >> 1) & 1u);
+      if (prefetched) stage_wait(smem_addr(&bars[b ^ 1u]), ((n + 1) >> 1) & 1u);
+      if (threadIdx.x == 0) atomicAdd(&g_stage_timeouts, 1u);
       return;
     }
     uint32_t first_row, last_row;
@@ -487,7 +478,7 @@ cudaError_t LaunchConvStep(const ConvArgs& a, cudaStream_t s) {
 }
 
 cudaError_t ReadConvStageTimeouts(unsigned int* out) {
-  return cudaMemcpyFromSymbol(out, g_conv_stage_timeouts, sizeof(unsigned int));
+  return cudaMemcpyFromSymbol(out, g_stage_timeouts, sizeof(unsigned int));
 }
 
 cudaError_t LaunchConvStateAdvance(const ConvArgs& a, cudaStream_t s) {

@@ -94,104 +94,6 @@ __global__ void __launch_bounds__(kBlock) embed_q8_0_kernel(const EmbedArgs a, c
   }
 }
 
-// The streaming form for rows of whole groups of 64 blocks (cols % 2048 == 0 ... any cols % 256 == 0): every
-// lane converts OPL = cols / 256 octets, octet j = lane + 32 i, so its quarter (lane % 4), its block within a
-// group of eight (lane / 4), the alignment of its code bytes and therefore the funnel shift are the same for
-// every i, and consecutive i are exactly 272 bytes = one group of 8 blocks apart: the conversion loop is
-// straight-line code with immediate offsets (about 30 instructions per octet instead of 75). Each warp owns two
-// row buffers: while it converts one row the gather of its next row is already in flight (cp.async groups, no
-// barrier object, no spin). A warp walks over rows first + i * stride.
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
-
-template <typename OT, int OPL>
-__global__ void __launch_bounds__(kBlock) embed_q8_0_stream_kernel(const EmbedArgs a, const unsigned row_smem,
-                                                                  const unsigned opl_rt) {
-  pdl_begin();
-  extern __shared__ __align__(16) uint8_t stage[];
-  const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-  uint8_t* buf0 = stage + static_cast<size_t>(warp) * 2 * row_smem;
-  const unsigned opl = OPL ? OPL : opl_rt;
-  const unsigned chunks = opl * 17;  // 16-byte chunks of a row: 272 bytes per group of 8 blocks
-  const uint32_t stride = gridDim.x * kWarps;
-  const uint32_t first = blockIdx.x * kWarps + warp;
-  OT* out = static_cast<OT*>(a.out);
-  // lane constants of the conversion
-  const unsigned at0 = (lane >> 2) * 34u + 2u + 8u * (lane & 3u);  // this lane's 8 code bytes within a group
-  const unsigned sh = (at0 & 2u) * 8u;                               // 0 in odd blocks, 16 in even ones
-  const unsigned woff = at0 & ~3u, doff = (lane >> 2) * 34u;
-
-  auto row_id = [&](uint32_t t) -> uint32_t {
-    return a.ids ? a.ids[static_cast<size_t>(t) * a.id_stride + a.id_slot] : a.token;
-  };
-  auto gather = [&](uint32_t id, uint8_t* buf) {
-    if (a.vocab == 0 || id < a.vocab) {
-      const uint8_t* src = a.table + static_cast<size_t>(id) * a.row_bytes;
-      for (unsigned c = lane; c < chunks; c += 32) cp_async16(buf + c * 16, src + c * 16);
-    }
-    cp_async_commit();
-  };
-
-  uint32_t t = first;
-  if (t >= a.tokens) return;  // whole warp
-  uint32_t id_cur = row_id(t);
-  uint32_t id_next = t + stride < a.tokens ? row_id(t + stride) : 0u;
-  gather(id_cur, buf0);
-  if (t + stride < a.tokens) gather(id_next, buf0 + row_smem);
-  else cp_async_commit();
-  unsigned which = 0;
-  for (; t < a.tokens; t += stride) {
-    // the id of the row after next is requested before this row is converted
-    const uint32_t t2 = t + 2 * stride;
-    const uint32_t id_after = t2 < a.tokens ? row_id(t2) : 0u;
-    cp_async_wait<1>();
-    __syncwarp();
-    const uint8_t* buf = buf0 + which * row_smem;
-    const bool in_range = a.vocab == 0 || id_cur < a.vocab;
-    OT* dst = out + static_cast<size_t>(t) * a.cols + lane * 8u;
-    if (in_range) {
-      const float2 bias = make_float2(-8388736.0f, -8388736.0f);
-#pragma unroll
-      for (unsigned i = 0; i < (OPL ? OPL : 1); ++i) {
-        for (unsigned ii = i; ii < opl; ii += (OPL ? opl : 1)) {  // OPL == 0: a run-time loop over ii
-          const uint32_t* w32 = reinterpret_cast<const uint32_t*>(buf + woff + ii * 272u);
-          const float d = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(buf + doff + ii * 272u)));
-          const float2 d2 = make_float2(d, d);
-          // three aligned words and a funnel shift by 0 or 16 bits give the 8 code bytes as two words; the
-          // third word exists whenever the shift is 16 (even blocks never end a group of eight)
-          const uint32_t w0 = w32[0], w1 = w32[1], w2 = sh ? w32[2] : 0u;
-          const uint32_t code[2] = {__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh)};
-          float v[8];
-          // int8 -> float without a conversion instruction: the byte, biased by 128, becomes the low mantissa
-          // byte of 2^23 (0x4B0000xx = 2^23 + xx); subtracting 2^23 + 128 leaves the code, exactly; then x scale
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const uint32_t x = code[h] ^ 0x80808080u;
-            const float2 lo = make_float2(__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7540)),
-                                          __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7541)));
-            const float2 hi = make_float2(__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7542)),
-                                          __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7543)));
-            const float2 a0 = __fmul2_rn(__fadd2_rn(lo, bias), d2), a1 = __fmul2_rn(__fadd2_rn(hi, bias), d2);
-            v[4 * h] = a0.x, v[4 * h + 1] = a0.y, v[4 * h + 2] = a1.x, v[4 * h + 3] = a1.y;
-          }
-          store8(dst + ii * 256u, v);
-        }
-      }
-    } else {
-      const float z[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-      for (unsigned ii = 0; ii < opl; ++ii) store8(dst + ii * 256u, z);
-    }
-    __syncwarp();  // every lane is done with this buffer before it is refilled
-    if (t2 < a.tokens) gather(id_after, buf0 + which * row_smem);
-    else cp_async_commit();
-    id_cur = id_next;
-    id_next = id_after;
-    which ^= 1u;
-  }
-  cp_async_wait<0>();
-}
-
 // One thread per element, byte loads: any alignment, any row_bytes.
 template <typename OT>
 __global__ void __launch_bounds__(kBlock) embed_q8_0_scalar_kernel(const EmbedArgs a) {
@@ -217,28 +119,6 @@ cudaError_t LaunchEmbedT(const EmbedArgs& a, cudaStream_t s) {
   const unsigned row_smem = static_cast<unsigned>((a.row_bytes + 15) / 16 * 16);
   unsigned warps = kWarps;
   while (warps > 1 && static_cast<size_t>(warps) * row_smem > 48u * 1024u) warps >>= 1;
-  // streaming form: rows of whole groups of eight blocks per lane step and enough rows to fill the GPU
-  if (a.vec && a.cols % 256 == 0 && a.row_bytes == static_cast<uint64_t>(a.cols / 32) * 34 && a.variant != 1 &&
-      static_cast<uint64_t>(a.tokens) * (a.cols / 32) * 2 > 148u * 64u * 16u && 2u * kWarps * row_smem <= 200u * 1024u) {
-    const unsigned opl = a.cols / 256;
-    const size_t smem = static_cast<size_t>(2u * kWarps) * row_smem;
-    unsigned per_sm = static_cast<unsigned>((227u * 1024u) / (smem + 1024u));
-    if (per_sm > 8) per_sm = 8;
-    if (per_sm < 1) per_sm = 1;
-    unsigned grid = (a.tokens + kWarps - 1) / kWarps;
-    if (grid > 148u * per_sm) grid = 148u * per_sm;
-    cudaError_t e;
-    if (opl == 8) {
-      e = cudaFuncSetAttribute(embed_q8_0_stream_kernel<OT, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-      if (e != cudaSuccess) return e;
-      LaunchKernel(embed_q8_0_stream_kernel<OT, 8>, grid, kBlock, smem, s, a, row_smem, opl);
-    } else {
-      e = cudaFuncSetAttribute(embed_q8_0_stream_kernel<OT, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-      if (e != cudaSuccess) return e;
-      LaunchKernel(embed_q8_0_stream_kernel<OT, 0>, grid, kBlock, smem, s, a, row_smem, opl);
-    }
-    return cudaGetLastError();
-  }
   if (a.vec && static_cast<size_t>(warps) * row_smem <= 48u * 1024u) {
     // segments per row: as many (<= 8) as keep every warp busy once, whole groups of 8 blocks each
     const unsigned blocks = a.cols / 32;

@@ -739,7 +739,7 @@ cudaError_t LaunchHcEltT(const HcEltArgs& a, cudaStream_t s) {
 // 16 loads in flight per thread), then summed in slot order with the product and the sum rounded
 // separately, then the gated shared expert is added (src/model/reference.cpp:558-578).
 template <typename YT, typename OT>
-__global__ void __launch_bounds__(kBlock) moe_combine_kernel(const MoeCombineArgs a, const uint32_t chunks) {
+__global__ void __launch_bounds__(kBlock, sizeof(YT) == 2 ? 4 : 2) moe_combine_kernel(const MoeCombineArgs a, const uint32_t chunks) {
   pdl_begin();
   __shared__ float gate;
   const uint32_t t = blockIdx.x / chunks, chunk = blockIdx.x - t * chunks;
@@ -754,19 +754,24 @@ __global__ void __launch_bounds__(kBlock) moe_combine_kernel(const MoeCombineArg
   Oct acc = oct_zero();
   OT* out = static_cast<OT*>(a.out) + static_cast<size_t>(t) * a.n + j * 8;
   if (a.accumulate) acc = oct_load(out);
-  for (uint32_t s0 = 0; s0 < a.k; s0 += 16) {
-    Raw<YT> rows[16];
+  // Eight expert rows in flight per thread (128 bytes of 16-bit rows): with sixteen the kernel held 89 registers
+  // and two CTAs per SM, and spent its time waiting on the index -> row dependency with too little in flight.
+  constexpr int kRows = 8;
+  for (uint32_t s0 = 0; s0 < a.k; s0 += kRows) {
+    Raw<YT> rows[kRows];
+    float wv[kRows];
 #pragma unroll
-    for (int u = 0; u < 16; ++u) {
+    for (int u = 0; u < kRows; ++u) {
       const uint32_t s = s0 + u;
       if (s < a.k) {
         const size_t r = a.pos ? a.pos[static_cast<size_t>(t) * a.k + s] : static_cast<size_t>(t) * a.k + s;
         rows[u] = raw_load(yp + r * a.n);
+        wv[u] = ww[s];
       }
     }
 #pragma unroll
-    for (int u = 0; u < 16; ++u)
-      if (s0 + u < a.k) acc = oct_axpy_unfused(acc, raw_unpack(rows[u]), ww[s0 + u]);
+    for (int u = 0; u < kRows; ++u)
+      if (s0 + u < a.k) acc = oct_axpy_unfused(acc, raw_unpack(rows[u]), wv[u]);
   }
   if (a.sx) {
     const size_t off = static_cast<size_t>(t) * a.n + j * 8;

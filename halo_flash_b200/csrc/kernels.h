@@ -15,6 +15,8 @@ namespace halo_b200 {
 
 // True unless halo_b200_tune("pdl", 0) switched programmatic dependent launch off.
 bool PdlEnabled();
+// Preferred shared-memory carveout of a launch in percent (halo_b200_tune("carveout", p)); < 0: the driver's choice.
+int CarveoutPreference();
 
 // Every kernel launch of the library: a plain stream-ordered launch that additionally allows the
 // kernel to be scheduled while its predecessor in the stream drains (the kernels order
@@ -29,11 +31,21 @@ inline cudaError_t LaunchKernel(void (*kernel)(KArgs...), dim3 grid, dim3 block,
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  if (PdlEnabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  const int carveout = CarveoutPreference();
+  if (carveout >= 0) {
+    attr[n].id = cudaLaunchAttributePreferredSharedMemoryCarveout;
+    attr[n].val.sharedMemCarveout = static_cast<unsigned>(carveout);
+    ++n;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = PdlEnabled() ? 1u : 0u;
+  cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
@@ -85,6 +97,7 @@ struct NormArgs {
   int short_rows_k1 = 0;        // 1: rows of <= 32 octets keep one octet per thread (default two)
   int force_general = 0;        // 1: never take the lean kernel (tests compare the two)
   int keep_hint = 1;            // 0: the add + norm stores its residual without the L2 keep policy
+  int staged = 1;               // persistent shared-memory-staged kernel: 0 never, 1 with a Q8 epilogue, 2 every wide 16-bit norm
   bool vec = true;
 };
 cudaError_t LaunchNorm(const NormArgs& a, cudaStream_t s);
@@ -155,7 +168,7 @@ struct NormRopeArgs {
   const float* table = nullptr;
   int rows_per_group = 0;       // rows a thread group keeps in flight: 2 (default) or 4
   int lean_k = 0;               // tuning: octets per lane of the lean kernel, 1 or 2 (0 = built-in choice)
-  int variant = 0;              // tuning: bit 0 = per-lane gamma loads, bit 1 = scalar rotation (bf16 lean kernel)
+  int staged = 1;               // 0: the lean kernel never stages rows in shared memory (tuning)
   int force_general = 0;        // 1: never take the lean kernel (tests compare the two)
 };
 cudaError_t LaunchNormRope(const NormRopeArgs& a, const InvFreq& f, cudaStream_t s);
@@ -222,7 +235,6 @@ struct EmbedArgs {
   void* out = nullptr;  // [tokens][cols]
   int out_dtype = kF32;
   bool vec = true;
-  int variant = 0;  // tuning: 1 = never take the streaming kernel
 };
 cudaError_t LaunchEmbedQ8_0(const EmbedArgs& a, cudaStream_t s);
 
@@ -339,6 +351,8 @@ struct ConvArgs {
   uint64_t entry_stride;
 };
 cudaError_t ReadConvStageTimeouts(unsigned int* out);
+cudaError_t ReadRopeStageTimeouts(unsigned int* out);
+cudaError_t ReadNormStageTimeouts(unsigned int* out);
 cudaError_t LaunchConvStep(const ConvArgs& a, cudaStream_t s);
 cudaError_t LaunchConvL2norm(const ConvArgs& a, cudaStream_t s);
 cudaError_t LaunchConvStateAdvance(const ConvArgs& a, cudaStream_t s);

@@ -13,6 +13,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "stage.cuh"
 
 namespace halo_b200 {
 namespace {
@@ -288,30 +289,6 @@ __global__ void __launch_bounds__(kBlock, K * ROWS >= 8 ? 2 : 3) norm_rope_kerne
   else norm_rope_body<IT, OT, K, ROWS, false, GT>(t, a, f, lg, cta, inv_d, rope_smem);
 }
 
-// Packed fp32x2 multiply and add with explicit round-to-nearest: PTX never contracts an
-// instruction that names its rounding, so a product feeding a sum stays two roundings (the
-// rotation must equal the standalone rope kernel and the CPU operator bit for bit).
-__device__ __forceinline__ float2 mul2_rn(float2 a, float2 b) {
-  float2 r;
-  asm("{\n\t.reg .b64 ra, rb, rr;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
-      "mul.rn.f32x2 rr, ra, rb;\n\tmov.b64 {%0, %1}, rr;\n\t}"
-      : "=f"(r.x), "=f"(r.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-  return r;
-}
-__device__ __forceinline__ float2 add2_rn(float2 a, float2 b) {
-  float2 r;
-  asm("{\n\t.reg .b64 ra, rb, rr;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
-      "add.rn.f32x2 rr, ra, rb;\n\tmov.b64 {%0, %1}, rr;\n\t}"
-      : "=f"(r.x), "=f"(r.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-  return r;
-}
-// x = x * cos + o * sin on four pairs: 12 packed instructions for what rotate8 does in 24.
-__device__ __forceinline__ void rotate8_packed(Oct& x, const Oct& o, const Oct& c, const Oct& s) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) x.p[i] = add2_rn(mul2_rn(x.p[i], c.p[i]), mul2_rn(o.p[i], s.p[i]));
-}
 __device__ __forceinline__ Oct oct_from(float4 a, float4 b) {
   Oct o;
   o.p[0] = make_float2(a.x, a.y), o.p[1] = make_float2(a.z, a.w);
@@ -319,19 +296,20 @@ __device__ __forceinline__ Oct oct_from(float4 a, float4 b) {
   return o;
 }
 
-// The lean fused kernel for the common case: Q (and K) rows that fill the grid exactly, gammas
+// The lean fused kernels for the common case: Q (and K) rows that fill whole CTA passes, gammas
 // present, rotation table given, no q|gate split and no cache copy. One row per thread group, K
 // octets per lane (4 at d = 256: eight lanes own a row and the 64 rotated dims are the first octet
 // of each, so every lane of the warp takes part in the exchange), operands as plain arguments,
-// nothing predicated; which tensor a CTA works on is uniform. The CTA's gamma (1 + w applied once)
-// is staged in shared memory in the lanes' read order while the rows are in flight. Same arithmetic,
-// bit for bit, as the general kernel above.
+// nothing predicated; which tensor a pass works on is uniform. The gammas (1 + w applied once) are
+// staged in shared memory in the lanes' read order. Same arithmetic, bit for bit, as the general
+// kernel above.
 struct RopeLeanArgs {  // scalar fields on purpose: indexing a parameter array by tensor copies it to local memory
   const void *in0, *in1;
   void *out0, *out1;
   const float *w0, *w1;
   uint32_t heads0, heads1, magic0, magic1;
-  uint32_t ctas0;  // CTAs that belong to tensor 0
+  uint32_t ctas0;  // passes (CTAs of the direct kernel, tiles of the staged one) that belong to tensor 0
+  uint32_t tiles;  // staged kernel: passes in all
   uint32_t d, rot, lg;
   float eps, inv_d;
   const float* table;
@@ -339,10 +317,69 @@ struct RopeLeanArgs {  // scalar fields on purpose: indexing a parameter array b
 
 constexpr int kLeanCtas(int K) { return K == 4 ? 4 : (K == 2 ? 5 : 6); }
 
-template <typename IT, typename OT, int K, bool ONEPLUS, bool SMEMG, bool PACKROT>
+// Element e of a gamma row goes to float4 slot (2 k + e / 4 % 2) g + l of its octet j = k g + l: a lane's two
+// 16-byte reads per octet are then contiguous across the lanes of its group (no bank conflicts).
+template <bool ONEPLUS>
+__device__ __forceinline__ void stage_gamma(float* gs, const float* w, unsigned d, unsigned lg) {
+  const unsigned g = 1u << lg;
+  for (unsigned e = threadIdx.x; e < d; e += kBlock) {
+    const unsigned j = e >> 3, k = j >> lg, l = j & (g - 1), h = (e >> 2) & 1u;
+    const float wv = __ldg(w + e);
+    gs[((((k << 1) + h) << lg) + l) * 4 + (e & 3u)] = ONEPLUS ? 1.0f + wv : wv;
+  }
+}
+
+// This token's eight cosines and eight sines for a lane of the rotated span. Plain (coherent) loads: the table
+// was written by an earlier kernel of the stream that may still have been running when this grid was scheduled
+// (programmatic dependent launch), so it is not read-only for this kernel's lifetime and must not go through
+// the non-coherent path.
+struct CosSin {
+  float4 c0, c1, t0, t1;
+};
+__device__ __forceinline__ CosSin load_cos_sin(const float* table, uint32_t token, unsigned rot, unsigned lir, unsigned hp) {
+  const float* tc = table + static_cast<size_t>(token) * rot + ((lir < hp ? lir : lir - hp) << 3);
+  const float* ts = tc + (rot >> 1);
+  CosSin r;
+  r.c0 = *reinterpret_cast<const float4*>(tc), r.c1 = *reinterpret_cast<const float4*>(tc + 4);
+  r.t0 = *reinterpret_cast<const float4*>(ts), r.t1 = *reinterpret_cast<const float4*>(ts + 4);
+  return r;
+}
+
+// One row held as K octets per lane -> normalized and scaled by the staged gamma. Returns nothing: x is updated.
+template <int K>
+__device__ __forceinline__ void norm_row(Oct (&x)[K], const float* gs, const unsigned lg, const unsigned lir,
+                                         const float eps, const float inv_d) {
+  const unsigned g = 1u << lg;
+  float2 acc = make_float2(0.0f, 0.0f);
+#pragma unroll
+  for (int k = 0; k < K; ++k) acc = oct_sumsq(x[k], acc);
+  const float ss = group_sum_narrow(acc.x + acc.y, g);
+  const float scale = rsqrtf(__fmaf_rn(ss, inv_d, eps));
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const Oct gm = oct_from(*reinterpret_cast<const float4*>(gs + ((((2 * k) << lg) + lir) << 2)),
+                            *reinterpret_cast<const float4*>(gs + ((((2 * k + 1) << lg) + lir) << 2)));
+    x[k] = oct_mul(oct_scale(x[k], scale), gm);
+  }
+}
+
+// Partners of the rotated span exchange their first octet (all 32 lanes call) and rotate.
+__device__ __forceinline__ void rotate_row(Oct& x0, const unsigned lir, const unsigned lane, const unsigned hp,
+                                           const CosSin& cs) {
+  const bool rotates = lir < 2 * hp;
+  const bool low = lir < hp;
+  const unsigned src_lane = lane - lir + (rotates ? (low ? lir + hp : lir - hp) : lir);
+  const Oct o = shuffle_oct(x0, src_lane);
+  if (rotates) {
+    const float sign = low ? -1.0f : 1.0f;  // first halves take -sin, second halves +sin (exact)
+    rotate8(x0, o, cs.c0, cs.c1, scale4(cs.t0, sign), scale4(cs.t1, sign));
+  }
+}
+
+template <typename IT, typename OT, int K, bool ONEPLUS>
 __global__ void __launch_bounds__(kBlock, kLeanCtas(K)) norm_rope_lean_kernel(const RopeLeanArgs a) {
   pdl_begin();
-  __shared__ __align__(16) float gs[SMEMG ? 8 * K * 32 : 4];  // d <= 8 K g, g <= 32
+  __shared__ __align__(16) float gs[8 * K * 32];  // d <= 8 K g, g <= 32
   const bool sel = blockIdx.x >= a.ctas0;
   const uint32_t cta = blockIdx.x - (sel ? a.ctas0 : 0u);
   const unsigned lg = a.lg, g = 1u << lg;
@@ -354,67 +391,103 @@ __global__ void __launch_bounds__(kBlock, kLeanCtas(K)) norm_rope_lean_kernel(co
   Raw<IT> rx[K];
 #pragma unroll
   for (int k = 0; k < K; ++k) rx[k] = raw_load(src + (((k << lg) + lir) << 3));
-  const float* w = sel ? a.w1 : a.w0;
-  if constexpr (SMEMG) {
-    // element e of octet j = k g + l goes to float4 slot (2 k + e / 4 % 2) g + l: a lane's two 16-byte reads per
-    // octet are then contiguous across the lanes of its group (no bank conflicts)
-    for (unsigned e = threadIdx.x; e < a.d; e += kBlock) {
-      const unsigned j = e >> 3, k = j >> lg, l = j & (g - 1), h = (e >> 2) & 1u;
-      const float wv = __ldg(w + e);
-      gs[((((k << 1) + h) << lg) + l) * 4 + (e & 3u)] = ONEPLUS ? 1.0f + wv : wv;
-    }
-    __syncthreads();
-  }
+  stage_gamma<ONEPLUS>(gs, sel ? a.w1 : a.w0, a.d, lg);  // while the rows are in flight
+  __syncthreads();
   const unsigned hp = a.rot >> 4;  // lanes per half of the rotated span
-  const bool rotates = lir < 2 * hp;
-  const bool low = lir < hp;
-  const unsigned src_lane = lane - lir + (rotates ? (low ? lir + hp : lir - hp) : lir);
   Oct x[K];
-  float2 acc = make_float2(0.0f, 0.0f);
 #pragma unroll
-  for (int k = 0; k < K; ++k) {
-    x[k] = raw_unpack(rx[k]);
-    acc = oct_sumsq(x[k], acc);
-  }
-  const float ss = group_sum_narrow(acc.x + acc.y, g);
-  const float scale = rsqrtf(__fmaf_rn(ss, a.inv_d, a.eps));
-  // gammas and this token's cos / sin are requested only now: they come from shared memory / L1 (a few KB shared
-  // by every row), and holding them in registers while the row is in flight would cost a resident CTA per SM
-#pragma unroll
-  for (int k = 0; k < K; ++k) {
-    Oct gm;
-    if constexpr (SMEMG) {
-      gm = oct_from(*reinterpret_cast<const float4*>(gs + ((((2 * k) << lg) + lir) << 2)),
-                    *reinterpret_cast<const float4*>(gs + ((((2 * k + 1) << lg) + lir) << 2)));
-    } else {
-      gm = oct_load_cached(w + (((k << lg) + lir) << 3));
-      if (ONEPLUS) {
-        const float2 one = make_float2(1.0f, 1.0f);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) gm.p[i] = __fadd2_rn(one, gm.p[i]);
-      }
-    }
-    x[k] = oct_mul(oct_scale(x[k], scale), gm);
-  }
-  const Oct o = shuffle_oct(x[0], src_lane);
-  if (rotates) {
-    const uint32_t token = div_magic(row, sel ? a.heads1 : a.heads0, sel ? a.magic1 : a.magic0);
-    const float* tc = a.table + static_cast<size_t>(token) * a.rot + ((low ? lir : lir - hp) << 3);
-    const float* ts = tc + (a.rot >> 1);
-    const float sign = low ? -1.0f : 1.0f;  // first halves take -sin, second halves +sin (exact)
-    // plain (coherent) loads: the table was written by an earlier kernel of the stream that may still have been
-    // running when this grid was scheduled, so it is not read-only for this kernel's lifetime
-    const float4 c0 = *reinterpret_cast<const float4*>(tc), c1 = *reinterpret_cast<const float4*>(tc + 4);
-    const float4 t0 = *reinterpret_cast<const float4*>(ts), t1 = *reinterpret_cast<const float4*>(ts + 4);
-    if constexpr (PACKROT) {
-      rotate8_packed(x[0], o, oct_from(c0, c1), oct_scale(oct_from(t0, t1), sign));
-    } else {
-      rotate8(x[0], o, c0, c1, scale4(t0, sign), scale4(t1, sign));
-    }
-  }
+  for (int k = 0; k < K; ++k) x[k] = raw_unpack(rx[k]);
+  norm_row<K>(x, gs, lg, lir, a.eps, a.inv_d);
+  // this token's cos / sin are requested only now: they come from L1 / L2 (a few KB shared by the rows of a token),
+  // and holding them in registers while the row is in flight would cost a resident CTA per SM
+  CosSin cs = {};
+  if (lir < 2 * hp)
+    cs = load_cos_sin(a.table, div_magic(row, sel ? a.heads1 : a.heads0, sel ? a.magic1 : a.magic0), a.rot, lir, hp);
+  rotate_row(x[0], lir, lane, hp, cs);
   OT* dst = static_cast<OT*>(sel ? a.out1 : a.out0) + off;
 #pragma unroll
   for (int k = 0; k < K; ++k) oct_store(dst + (((k << lg) + lir) << 3), x[k]);
+}
+
+// The same rows through persistent CTAs that STAGE them: a pass of kBlock / g rows is one contiguous span of
+// the tensor (16 KiB at d = 256, bf16), fetched by ONE bulk asynchronous copy into one of two shared-memory
+// buffers and counted on an mbarrier. While the CTA normalizes and rotates pass n out of one buffer the copy
+// engine fills the other with pass n + 1: bytes in flight cost no registers and the load latency of a pass
+// hides behind the arithmetic of the one before, which the direct kernel above (every CTA loads, waits,
+// computes, stores, exits) cannot do. Passes are dealt round-robin: CTA c takes c, c + grid, c + 2 grid, ...
+// over the passes of tensor 0 followed by those of tensor 1. Results leave with ordinary 16-byte stores, in
+// place or not. Every wait is bounded; a wait that runs out is counted and ends the CTA (see stage_wait).
+__device__ unsigned int g_stage_timeouts = 0;
+
+template <typename T, int K, bool ONEPLUS>
+__global__ void __launch_bounds__(kBlock, 4) norm_rope_staged_kernel(const RopeLeanArgs a) {
+  pdl_begin();
+  extern __shared__ __align__(128) uint8_t rope_stage[];
+  __shared__ __align__(8) unsigned long long bars[2];
+  const unsigned lg = a.lg, g = 1u << lg;
+  const unsigned rows_per_pass = kBlock >> lg;
+  const unsigned pass_elems = rows_per_pass * a.d;
+  const unsigned pass_bytes = pass_elems * static_cast<unsigned>(sizeof(T));  // a multiple of 16: d % 8 == 0
+  T* bufs = reinterpret_cast<T*>(rope_stage);
+  float* gs = reinterpret_cast<float*>(rope_stage + 2 * static_cast<size_t>(pass_bytes));  // [2 tensors][d]
+  const unsigned lane = threadIdx.x & 31u, lir = threadIdx.x & (g - 1), slot = threadIdx.x >> lg;
+  const unsigned hp = a.rot >> 4;
+
+  if (threadIdx.x == 0) stage_init(bars, 2);
+  __syncthreads();
+  // thread 0 asks the copy engine for pass `p` into buffer `b`
+  auto request = [&](uint32_t p, unsigned b) {
+    const bool second = p >= a.ctas0;
+    const T* src = static_cast<const T*>(second ? a.in1 : a.in0) + static_cast<size_t>(second ? p - a.ctas0 : p) * pass_elems;
+    const unsigned bar = smem_addr(&bars[b]);
+    stage_expect(bar, pass_bytes);
+    stage_copy(smem_addr(bufs + b * pass_elems), src, pass_bytes, bar);
+  };
+  uint32_t p = blockIdx.x;
+  if (p >= a.tiles) return;  // uniform: the whole CTA has no pass
+  const uint32_t stride = gridDim.x;
+  if (threadIdx.x == 0) {
+    request(p, 0);
+    if (p + stride < a.tiles) request(p + stride, 1);
+  }
+  stage_gamma<ONEPLUS>(gs, a.w0, a.d, lg);
+  if (a.w1) stage_gamma<ONEPLUS>(gs + a.d, a.w1, a.d, lg);
+  __syncthreads();
+
+  for (uint32_t n = 0; p < a.tiles; ++n, p += stride) {
+    const unsigned b = n & 1u;
+    const bool sel = p >= a.ctas0;
+    const uint32_t row = (sel ? p - a.ctas0 : p) * rows_per_pass + slot;
+    // this token's cos / sin are requested before the wait: they arrive while the pass is read and reduced
+    CosSin cs = {};
+    if (lir < 2 * hp)
+      cs = load_cos_sin(a.table, div_magic(row, sel ? a.heads1 : a.heads0, sel ? a.magic1 : a.magic0), a.rot, lir, hp);
+    // buffer b's (n / 2)-th use: phase parity (n / 2) & 1
+    const unsigned done = stage_wait(smem_addr(&bars[b]), (n >> 1) & 1u);
+    if (!__syncthreads_and(static_cast<int>(done))) {
+      // Never seen. Nothing more is requested, and the copies that may still be in flight into this CTA's shared
+      // memory (this buffer, and the other one's next use) get one more bounded wait before the CTA leaves.
+      stage_wait(smem_addr(&bars[b]), (n >> 1) & 1u);
+      if (p + stride < a.tiles) stage_wait(smem_addr(&bars[b ^ 1u]), ((n + 1) >> 1) & 1u);
+      if (threadIdx.x == 0) atomicAdd(&g_stage_timeouts, 1u);
+      return;
+    }
+    const T* mine = bufs + b * pass_elems + slot * a.d;
+    Oct x[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const uint4 u = *reinterpret_cast<const uint4*>(mine + (((k << lg) + lir) << 3));
+      if constexpr (std::is_same_v<T, bf16>) x[k] = oct_unpack_bf16(u);
+      else x[k] = oct_unpack_f16(u);
+    }
+    norm_row<K>(x, gs + (sel ? a.d : 0u), lg, lir, a.eps, a.inv_d);
+    rotate_row(x[0], lir, lane, hp, cs);
+    T* dst = static_cast<T*>(sel ? a.out1 : a.out0) + static_cast<size_t>(row) * a.d;
+#pragma unroll
+    for (int k = 0; k < K; ++k) oct_store(dst + (((k << lg) + lir) << 3), x[k]);
+    __syncthreads();  // every thread has read buffer b: refill it with the pass after next
+    if (threadIdx.x == 0 && p + 2 * stride < a.tiles) request(p + 2 * stride, b);
+  }
 }
 
 // One thread per (token, frequency): the rotation table of a step, shared by every layer.
@@ -477,27 +550,20 @@ uint32_t Magic(uint32_t divisor, uint64_t max_n) {
 }
 
 template <typename IT, typename OT, int K>
-void LaunchLeanRope(const RopeLeanArgs& l, unsigned grid, bool one_plus, int variant, cudaStream_t s) {
-  if constexpr (std::is_same_v<IT, bf16> && std::is_same_v<OT, bf16>) {
-    // tuning variants (bit 0: gammas fetched per lane instead of staged; bit 1: scalar rotation)
-    if (variant == 1) {
-      if (one_plus) LaunchKernel(norm_rope_lean_kernel<IT, OT, K, true, false, true>, grid, kBlock, 0, s, l);
-      else LaunchKernel(norm_rope_lean_kernel<IT, OT, K, false, false, true>, grid, kBlock, 0, s, l);
-      return;
-    }
-    if (variant == 2) {
-      if (one_plus) LaunchKernel(norm_rope_lean_kernel<IT, OT, K, true, true, false>, grid, kBlock, 0, s, l);
-      else LaunchKernel(norm_rope_lean_kernel<IT, OT, K, false, true, false>, grid, kBlock, 0, s, l);
-      return;
-    }
-    if (variant == 3) {
-      if (one_plus) LaunchKernel(norm_rope_lean_kernel<IT, OT, K, true, false, false>, grid, kBlock, 0, s, l);
-      else LaunchKernel(norm_rope_lean_kernel<IT, OT, K, false, false, false>, grid, kBlock, 0, s, l);
+void LaunchLeanRope(const RopeLeanArgs& l, unsigned grid, bool one_plus, bool staged, cudaStream_t s) {
+  if constexpr (std::is_same_v<IT, OT> && sizeof(IT) == 2 && K >= 2) {
+    if (staged) {
+      // two pass buffers + the two gamma rows; persistent CTAs, four per SM
+      const unsigned pass_bytes = (kBlock >> l.lg) * l.d * static_cast<unsigned>(sizeof(IT));
+      const size_t smem = 2 * static_cast<size_t>(pass_bytes) + 2 * static_cast<size_t>(l.d) * sizeof(float);
+      const unsigned pgrid = l.tiles < 148u * 4u ? l.tiles : 148u * 4u;
+      if (one_plus) LaunchKernel(norm_rope_staged_kernel<IT, K, true>, pgrid, kBlock, smem, s, l);
+      else LaunchKernel(norm_rope_staged_kernel<IT, K, false>, pgrid, kBlock, smem, s, l);
       return;
     }
   }
-  if (one_plus) LaunchKernel(norm_rope_lean_kernel<IT, OT, K, true, true, true>, grid, kBlock, 0, s, l);
-  else LaunchKernel(norm_rope_lean_kernel<IT, OT, K, false, true, true>, grid, kBlock, 0, s, l);
+  if (one_plus) LaunchKernel(norm_rope_lean_kernel<IT, OT, K, true>, grid, kBlock, 0, s, l);
+  else LaunchKernel(norm_rope_lean_kernel<IT, OT, K, false>, grid, kBlock, 0, s, l);
 }
 
 template <typename IT, typename OT>
@@ -537,9 +603,15 @@ cudaError_t LaunchNormRopeT(const NormRopeArgs& a, const InvFreq& f, cudaStream_
     l.ctas0 = a.rows / rpc1;
     l.d = a.d, l.rot = a.rot, l.lg = lg, l.eps = a.eps, l.inv_d = inv_d, l.table = a.table;
     const unsigned lgrid = l.ctas0 + static_cast<unsigned>(rows2 / rpc1);
-    if (k == 4) LaunchLeanRope<IT, OT, 4>(l, lgrid, a.one_plus != 0, a.variant, s);
-    else if (k == 2) LaunchLeanRope<IT, OT, 2>(l, lgrid, a.one_plus != 0, a.variant, s);
-    else LaunchLeanRope<IT, OT, 1>(l, lgrid, a.one_plus != 0, a.variant, s);
+    l.tiles = lgrid;
+    // staged (bulk copies into shared memory, persistent CTAs) where the launch has several passes per CTA slot
+    // and a pass with its gammas fits the default 48 KiB of dynamic shared memory
+    const size_t pass_bytes = static_cast<size_t>(rpc1) * a.d * sizeof(IT);
+    const bool staged = a.staged != 0 && std::is_same_v<IT, OT> && sizeof(IT) == 2 && k >= 2 && lgrid > 148u * 4u &&
+                        2 * pass_bytes + 2 * a.d * sizeof(float) <= 48u * 1024u;
+    if (k == 4) LaunchLeanRope<IT, OT, 4>(l, lgrid, a.one_plus != 0, staged, s);
+    else if (k == 2) LaunchLeanRope<IT, OT, 2>(l, lgrid, a.one_plus != 0, staged, s);
+    else LaunchLeanRope<IT, OT, 1>(l, lgrid, a.one_plus != 0, false, s);
     return cudaGetLastError();
   }
   if (k == 4) {
@@ -583,6 +655,10 @@ cudaError_t LaunchNormRope(const NormRopeArgs& a, const InvFreq& f, cudaStream_t
     case kF16 * 3 + kF16: return LaunchNormRopeT<f16, f16>(a, f, s);
   }
   return cudaErrorInvalidValue;
+}
+
+cudaError_t ReadRopeStageTimeouts(unsigned int* out) {
+  return cudaMemcpyFromSymbol(out, g_stage_timeouts, sizeof(unsigned int));
 }
 
 cudaError_t LaunchRopeTable(const RopeTableArgs& a, const InvFreq& f, cudaStream_t s) {

@@ -150,7 +150,8 @@ class Device:
     def launch(self, kernel: int, grid, block, args: list[Arg]) -> None:
         g = tuple(grid) + (1,) * (3 - len(grid))
         b = tuple(block) + (1,) * (3 - len(block))
-        lib().launch(self.stream.cuda_stream, self._names[kernel], [a.to_c() for a in args], g, b)
+        with torch.cuda.device(self.index):  # the launch goes to the CURRENT device: make it this object's
+            lib().launch(self.stream.cuda_stream, self._names[kernel], [a.to_c() for a in args], g, b)
 
     def synchronize(self) -> None:
         if self._capturing is not None:

@@ -24,10 +24,30 @@ bool Check(cudaError_t e, const char* what, std::string* error) {
   return false;
 }
 
+// Makes a device current for the calling thread for the length of a scope. Every method below acts through the
+// CUDA runtime, whose allocations, launches and memory queries go to the CURRENT device: a second Device object,
+// or a worker thread that starts on device 0, must not send this object's work to another GPU.
+class Current {
+ public:
+  explicit Current(int ordinal) : ordinal_(ordinal) {
+    if (cudaGetDevice(&previous_) != cudaSuccess) previous_ = ordinal;
+    if (previous_ != ordinal_) cudaSetDevice(ordinal_);
+  }
+  ~Current() {
+    if (previous_ != ordinal_) cudaSetDevice(previous_);
+  }
+  Current(const Current&) = delete;
+  Current& operator=(const Current&) = delete;
+
+ private:
+  int ordinal_, previous_ = 0;
+};
+
 class CudaDevice final : public Device {
  public:
   CudaDevice(int ordinal, cudaStream_t stream) : ordinal_(ordinal), stream_(stream) {}
   ~CudaDevice() override {
+    const Current here(ordinal_);
     cudaStreamSynchronize(stream_);
     cudaStreamDestroy(stream_);
   }
@@ -35,6 +55,7 @@ class CudaDevice final : public Device {
   Backend backend() const noexcept override { return kBackendCuda; }
 
   Buffer Alloc(std::size_t bytes, std::string* error) override {
+    const Current here(ordinal_);
     Buffer b;
     void* p = nullptr;
     if (!Check(cudaMalloc(&p, bytes ? bytes : 1), "cudaMalloc", error)) return b;
@@ -43,11 +64,13 @@ class CudaDevice final : public Device {
     return b;
   }
   void Free(Buffer& buffer) noexcept override {
+    const Current here(ordinal_);
     if (buffer.device) cudaFree(buffer.device);
     buffer = {};
   }
 
   bool Upload(const Buffer& dst, std::size_t offset, const void* src, std::size_t bytes, std::string* error) override {
+    const Current here(ordinal_);
     if (!InRange(dst, offset, bytes, "Upload", error) || !NotCapturing("Upload", error)) return false;
     if (!Check(cudaMemcpyAsync(static_cast<char*>(dst.device) + offset, src, bytes, cudaMemcpyHostToDevice, stream_),
                "Upload", error))
@@ -56,11 +79,13 @@ class CudaDevice final : public Device {
   }
   bool UploadAsync(const Buffer& dst, std::size_t offset, const void* src, std::size_t bytes,
                    std::string* error) override {
+    const Current here(ordinal_);
     if (!InRange(dst, offset, bytes, "UploadAsync", error) || !NotCapturing("UploadAsync", error)) return false;
     return Check(cudaMemcpyAsync(static_cast<char*>(dst.device) + offset, src, bytes, cudaMemcpyHostToDevice, stream_),
                  "UploadAsync", error);
   }
   bool Download(const Buffer& src, std::size_t offset, void* dst, std::size_t bytes, std::string* error) override {
+    const Current here(ordinal_);
     if (!InRange(src, offset, bytes, "Download", error) || !NotCapturing("Download", error)) return false;
     if (!Check(cudaMemcpyAsync(dst, static_cast<const char*>(src.device) + offset, bytes, cudaMemcpyDeviceToHost, stream_),
                "Download", error))
@@ -68,18 +93,22 @@ class CudaDevice final : public Device {
     return Check(cudaStreamSynchronize(stream_), "Download", error);  // device faults surface here
   }
   bool Fill(const Buffer& dst, std::uint8_t value, std::string* error) override {
+    const Current here(ordinal_);
     return Check(cudaMemsetAsync(dst.device, value, dst.bytes, stream_), "Fill", error);  // capturable
   }
 
   void* AllocHost(std::size_t bytes, std::string* error) override {
+    const Current here(ordinal_);
     void* p = nullptr;
     if (!Check(cudaHostAlloc(&p, bytes ? bytes : 1, cudaHostAllocDefault), "cudaHostAlloc", error)) return nullptr;
     return p;
   }
   void FreeHost(void* p) noexcept override {
+    const Current here(ordinal_);
     if (p) cudaFreeHost(p);
   }
   std::size_t AvailableBytes() const override {
+    const Current here(ordinal_);
     std::size_t free_b = 0, total = 0;
     return cudaMemGetInfo(&free_b, &total) == cudaSuccess ? free_b : SIZE_MAX;
   }
@@ -100,6 +129,7 @@ class CudaDevice final : public Device {
   }
 
   bool Launch(KernelId kernel, Dim3 grid, Dim3 block, std::span<const Arg> args, std::string* error) override {
+    const Current here(ordinal_);
     if (kernel < 0 || static_cast<std::size_t>(kernel) >= names_.size()) {
       if (error) *error = "Launch: invalid kernel id";
       return false;
@@ -123,11 +153,13 @@ class CudaDevice final : public Device {
   }
 
   bool Synchronize(std::string* error) override {
+    const Current here(ordinal_);
     if (!NotCapturing("Synchronize", error)) return false;
     return Check(cudaStreamSynchronize(stream_), "Synchronize", error);
   }
 
   bool BeginCapture(std::string* error) override {
+    const Current here(ordinal_);
     if (capturing_) {
       if (error) *error = "BeginCapture: already capturing";
       return false;
@@ -137,6 +169,7 @@ class CudaDevice final : public Device {
     return true;
   }
   bool EndCapture(Graph* out, std::string* error) override {
+    const Current here(ordinal_);
     if (!capturing_) {
       if (error) *error = "EndCapture: not capturing";
       return false;
@@ -152,6 +185,7 @@ class CudaDevice final : public Device {
     return true;
   }
   bool LaunchGraph(const Graph& graph, std::string* error) override {
+    const Current here(ordinal_);
     if (!graph.exec) {
       if (error) *error = "LaunchGraph: empty graph";
       return false;
@@ -159,6 +193,7 @@ class CudaDevice final : public Device {
     return Check(cudaGraphLaunch(static_cast<cudaGraphExec_t>(graph.exec), stream_), "LaunchGraph", error);
   }
   void FreeGraph(Graph& graph) noexcept override {
+    const Current here(ordinal_);
     if (graph.exec) cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(graph.exec));
     graph = {};
   }

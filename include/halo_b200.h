@@ -18,19 +18,43 @@
  * Contract
  *   - Returns 0 on success, -1 on failure with a NUL-terminated message in err
  *     (truncated to errlen; err may be NULL).
- *   - All pointers are device pointers owned by the caller. Nothing is allocated,
- *     no state is kept, nothing synchronizes: every call only enqueues kernels on
- *     `stream` and may be recorded by CUDA stream capture.
+ *   - All pointers are device pointers owned by the caller. No call allocates or
+ *     synchronizes (halo_b200_stage_timeouts, a diagnostic read, is the exception):
+ *     every other call only enqueues kernels on `stream` and may be recorded by CUDA
+ *     stream capture.
+ *   - State the library keeps, all of it listed here: (1) the fixed 4 MiB device array of
+ *     halo_b200_norm_rope_qk_noalloc (per GPU, shared by its calls); (2) a device counter
+ *     of staging waits that ran out (halo_b200_stage_timeouts; zero in normal
+ *     operation); (3) the process-wide tuning switches of halo_b200_tune (host atomics,
+ *     for experiments; production code never needs to touch them). Everything else is
+ *     stateless and re-entrant.
  *   - In-place use is allowed wherever the reference kernel works in place.
  *   - Buffers that are 16-byte aligned with row lengths that are multiples of 8
  *     elements take the vector kernels; anything else takes a slower scalar
- *     kernel with identical results. Q8 outputs need cols % 32 == 0.
+ *     kernel with results inside the same tolerances. Q8 outputs need cols % 32 == 0.
  *   - No CPU fallback exists: without a CUDA device every call fails.
- *   - Thread-compatible: concurrent calls on different streams are fine.
+ *   - Thread-compatible: concurrent calls on different streams are fine (the noalloc
+ *     entry point excepted, see there).
  *
  * Numerics: fp32 arithmetic in the evaluation order of the CPU operators
- * (src/model/cpu_ops.cpp), IEEE division/sqrt, no fused multiply-add; 16-bit
- * outputs are rounded once from the fp32 result, to nearest even.
+ * (src/model/cpu_ops.cpp), multiplies and adds rounded separately (-fmad=false), with
+ * these deliberate departures, each far inside the 1e-5 relative the path allows:
+ *   - sums of squares are accumulated in fp32 with fused multiply-adds (the CPU sums in
+ *     double), and the norm scale is the hardware rsqrt (2 ulp) of fma(ss, 1/d, eps) or
+ *     of ss + eps (L2 norm) instead of 1 / sqrtf;
+ *   - SiLU and sigmoid gates use the hardware exp2 and reciprocal (ex2.approx.ftz,
+ *     rcp.approx.ftz; relative error about 1e-6; a gate whose exact value is subnormal
+ *     comes out as zero); the scatter weights of the hyper-connection ops, which scale
+ *     whole rows, use expf and a true division;
+ *   - RoPE angles are float(pos) * inv_freq with inv_freq computed on the host by the CPU
+ *     operator's own pow(), and cos / sin by the device's full-range sincosf.
+ * Bit-exact by construction: residual sums (one add, one rounding), Q8_0 dequantisation
+ * (fp16 scale x int8, exact in fp32), position selection, copies and conversions, and the
+ * Q8 encoders: their scales amax / 127 and codes rint(x / d) are the IEEE results,
+ * obtained without dividing (two fused multiply-adds correct x * (1/127) to the exactly
+ * rounded quotient for every finite x; codes come from x * rcp(d) and are redone with a
+ * true division for the values, about 1 in 5000, that land within 1e-4 of a rounding
+ * boundary). 16-bit outputs are rounded once from the fp32 result, to nearest even.
  */
 #ifndef HALO_B200_H_
 #define HALO_B200_H_
@@ -414,9 +438,13 @@ int halo_b200_conv_l2norm_y(halo_b200_stream stream, const float* in, const uint
 int halo_b200_conv_step(halo_b200_stream stream, const float* in, float* state, const float* w, float* out,
                         uint32_t channels, uint32_t kern, char* err, size_t errlen);
 
-/* No counterpart in the reference. The conv kernel stages its input rows in shared memory with asynchronous
- * bulk copies and waits for them on a barrier object with a bounded number of polls; a CTA whose wait ran out
- * (never observed) returns without writing and is counted. Reads the count (this call synchronizes). */
+/* No counterpart in the reference. The persistent kernels of the library (the conv + SiLU + L2 norm and the fused
+ * norm + RoPE at streaming sizes) stage their input rows in shared memory with bulk asynchronous copies and wait
+ * for them on a barrier object for a bounded time (about half a second); a CTA whose wait ran out (never
+ * observed) returns without writing its remaining output tiles and is counted. halo_b200_stage_timeouts reads the
+ * count (this call synchronizes the device). A non-zero count means the outputs of the calls made before it are
+ * invalid. halo_b200_conv_stage_timeouts is the same call under its earlier name. */
+int halo_b200_stage_timeouts(unsigned int* count, char* err, size_t errlen);
 int halo_b200_conv_stage_timeouts(unsigned int* count, char* err, size_t errlen);
 
 /* ---- MoE combine (the step after the routed experts' down projections) --------------------------- */
@@ -489,12 +517,16 @@ int halo_b200_launch(halo_b200_stream stream, const char* name, const halo_b200_
 size_t halo_b200_kernel_count(void);
 const char* halo_b200_kernel_name(size_t index);
 
-/* Tuning hook for experiments (process-wide, not for production dispatch). Keys:
+/* Tuning hook for experiments (process-wide host atomics read at call time; not for production dispatch). Keys:
  * "norm_threads_per_row" (power of two <= 256; 0 = built-in choice),
  * "norm_short_rows_k1" (1 = rows of <= 256 elements use one 8-element chunk per thread; 0 = built-in choice),
  * "norm_force_general" (1 = the row norms always run their general kernel, never the lean one),
+ * "l2_keep" (1, the default = the add + norm stores a residual of at most 40 MB with an L2 evict_last hint; 0 = plain stores),
  * "gated_rows_per_group" (1 or 2 rows in flight per thread group of the gated norm on short rows; 0 = built-in),
- * "rope_rows_per_group" (2 or 4 rows in flight per thread group of the fused norm + RoPE kernel; 0 = built-in),
+ * "rope_rows_per_group" (2 or 4 rows in flight per thread group of the general fused norm + RoPE kernel; 0 = built-in),
+ * "rope_lean_k" (chunks per lane of the fused norm + RoPE kernels on rows of 256: 1 or 2; 0 = built-in, four),
+ * "rope_staged" (1, the default = the lean fused norm + RoPE kernel at streaming sizes runs persistent CTAs that stage
+ * rows in shared memory by bulk asynchronous copies; 0 = every CTA loads its rows directly),
  * "hc_row_level" (1 = the hyper-connection combine + norm always runs one (token, stream) row per thread group),
  * "conv_staged" (1, the default = the conv kernel stages rows in shared memory by bulk asynchronous copies; 0 = rows in registers),
  * "conv_tile" (tokens per thread of the register form of the conv kernel: 4 or 8; 0 = built-in), "hc_token_k" (2 = two

@@ -26,7 +26,8 @@ import numpy as np
 HERE = Path(__file__).resolve().parent
 PORT_LIB = HERE / "libhalo_oracle.so"
 REF_LIB = HERE / "_ref" / "libhalo_ref.so"
-REFERENCE_ROOT = Path(os.environ.get("HALO_REFERENCE_ROOT", "/root/reference"))
+# The halo-flash checkout: $HALO_REFERENCE_ROOT, else a directory named `reference` beside this repository.
+REFERENCE_ROOT = Path(os.environ.get("HALO_REFERENCE_ROOT") or HERE.parent.parent / "reference")
 
 _sz, _u32, _f32, _int, _p = C.c_size_t, C.c_uint32, C.c_float, C.c_int, C.c_void_p
 

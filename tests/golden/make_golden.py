@@ -1,5 +1,5 @@
 """Generates the committed golden fixtures. Run in a container that has the
-reference checkout (default /root/reference):
+reference checkout ($HALO_REFERENCE_ROOT, else a directory named `reference` beside this repository):
 
     python tests/golden/make_golden.py
 

@@ -386,11 +386,13 @@ def test_rope_scalar_path_odd_rotary_dim(orc):
 
 
 @pytest.mark.parametrize("shape", [synth.C1, synth.FULL])
-def test_fused_norm_rope_equals_separate_kernels_and_oracle(orc, shape):
+@pytest.mark.parametrize("T", [9, 64])
+def test_fused_norm_rope_equals_separate_kernels_and_oracle(orc, shape, T):
     """Fused per-head RMSNorm + RoPE vs the separate kernels bit for bit (the reference's
     NormRopeEqualsSeparateKernels / SplitQgateNormRopeEqualsSeparateKernels,
-    tests/gpu/quant_gpu_test.cpp:2635-2749, pos0 up to 300000) and vs the oracle."""
-    s, T, pos0 = shape, 9, 299990
+    tests/gpu/quant_gpu_test.cpp:2635-2749, pos0 up to 300000) and vs the oracle. T = 9 leaves ragged CTAs
+    (the general kernels), T = 64 fills them (the lean ones)."""
+    s, pos0 = shape, 299990
     heads, hd = s.q_heads, s.head_dim
     qg = synth.act("t.f.qg", T * heads, 2 * hd)
     w = synth.norm_w("t.f.w", hd)
@@ -949,3 +951,15 @@ def test_decode_batch_with_device_step_params(orc):
         for bo, saved in zip(ch.sets, sets0):
             for t, v in zip(bo.inputs(), saved):
                 t.copy_(v)
+
+
+def test_no_staging_wait_ran_out():
+    """Every wait of the persistent, shared-memory-staging kernels (conv + SiLU + L2 norm, fused norm + RoPE) is
+    bounded; one that runs out is counted. After the tests collected before this one: zero."""
+    import ctypes as C
+    n = C.c_uint(123)
+    err = C.create_string_buffer(256)
+    f = lib().cdll.halo_b200_stage_timeouts
+    f.restype, f.argtypes = C.c_int, [C.POINTER(C.c_uint), C.c_char_p, C.c_size_t]
+    assert f(C.byref(n), err, len(err)) == 0, err.value
+    assert n.value == 0
