@@ -119,7 +119,7 @@ def time_cpu_chain(shapes, tokens: int, threads: int, steps: int, warmup: int) -
     return {"value": tokens / dt, "unit": UNIT, "cores": threads, "kind": chain.o.kind,
             "sample": f"{tokens}-token shard (not the bench's {DEFAULT_TOKENS}) through all 48 layers, fp32, gather from a "
                       f"{chain.vocab}-row Q8_0 table (it reads one row per token whatever the table size), {steps} step(s) "
-                      f"of {dt * 1e3:.0f} ms; rows split over {threads} std::threads spawned and joined by every operator call",
+                      f"of {dt * 1e3:.0f} ms; rows split over {threads} persistent worker threads (the reference threads only its MatVec)",
             "ms_per_step": dt * 1e3}
 
 
@@ -313,12 +313,13 @@ def op_specs(torch, shapes, T: int):
     return specs, {k_: v * T for k_, v in nbytes.items()}
 
 
-def kernel_table(torch, shapes, T: int, peaks: dict, only=None) -> dict:
+def kernel_table(torch, shapes, T: int, peaks: dict, only=None, copies: bool = True) -> dict:
     """Average duration of each kernel of the chain, launched back to back over a ring of distinct
     buffer sets totalling >= 512 MB (so no launch finds its inputs in the 126 MB L2); one CUDA graph
     per kernel, CUDA-event timed on the launching stream. The add + norm stores its residual with an
     L2 keep hint (16.8 MB per launch at 4096 tokens): its ring is sized so that the hinted bytes alone
-    exceed twice the L2, and the same kernel is also timed with the hint switched off."""
+    exceed twice the L2, and the same kernel is also timed with the hint switched off. `copy_same_bytes_us` is the
+    library's plain copy kernel moving as many bytes under the same protocol (the ceiling for a launch that short)."""
     from halo_flash_b200 import lib
     specs, nbytes_of = op_specs(torch, shapes, T)
     out = {}
@@ -337,6 +338,15 @@ def kernel_table(torch, shapes, T: int, peaks: dict, only=None) -> dict:
         return {"us": round(us, 3), "bytes": nbytes, "gbs": round(gbs, 1), "ring_sets": n,
                 "frac_measured": round(gbs / peaks["hbm_gbs"], 4), "frac_8000": round(gbs / 8000.0, 4)}
 
+    def copy_same_bytes(nbytes, min_total):
+        """The library's plain copy (halo_copy, fp32 elements) moving the same number of bytes, read + write: the
+        size-matched ceiling of a kernel this short (launch ramp and tail included), under the same protocol."""
+        n = nbytes // 8
+        st = lambda: torch.cuda.current_stream().cuda_stream
+        r = one("copy", lambda: (torch.empty(n, device="cuda"), torch.empty(n, device="cuda")),
+                lambda b: lib().call("copy", st(), b[0].data_ptr(), b[1].data_ptr(), n), 8 * n, min_total)
+        return r["us"]
+
     for name, (make, run) in specs.items():
         if only is not None and name not in only:
             continue
@@ -345,6 +355,10 @@ def kernel_table(torch, shapes, T: int, peaks: dict, only=None) -> dict:
         # hinted bytes per launch = the residual = a quarter of the plain kernel's bytes; ring of hinted bytes > 2 x L2
         min_total = max(512 * 2**20, 4 * 2 * 126 * 2**20 + nbytes) if hinted and nbytes < 256 * 2**20 else 512 * 2**20
         out[name] = one(name, make, run, nbytes, min_total)
+        if copies:
+            cu = copy_same_bytes(nbytes, 512 * 2**20)
+            out[name]["copy_same_bytes_us"] = cu
+            out[name]["frac_of_copy"] = round(cu / out[name]["us"], 4)
         if name == "add_rmsnorm":
             lib().tune("l2_keep", 0)
             try:
@@ -549,7 +563,7 @@ def run_config5(torch, dist, args, rank: int, world: int, local: int, peaks: dic
     if rank == 0 and not args.no_kernel_table:
         table = kernel_table(torch, synth.FULL, end - begin, peaks,
                              only=("add_rmsnorm", "l2norm", "gated_norm", "norm_rope_qk", "swiglu_moe", "embed",
-                                   "add_rmsnorm_q8"))
+                                   "add_rmsnorm_q8"), copies=False)
         out["kernels"] = {k: {"us": v["us"], "gbs": v["gbs"], "frac_measured": v["frac_measured"]} for k, v in table.items()}
     return out
 

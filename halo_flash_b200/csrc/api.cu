@@ -18,11 +18,9 @@ std::atomic<int> g_norm_threads_per_row{0};
 std::atomic<int> g_norm_short_rows_k1{0};
 std::atomic<int> g_norm_force_general{0};
 std::atomic<int> g_l2_keep{1};
-std::atomic<int> g_norm_staged{1};
 std::atomic<int> g_rope_rows_per_group{0};
 std::atomic<int> g_rope_lean_k{0};
 std::atomic<int> g_rope_staged{1};
-std::atomic<int> g_carveout{-1};
 std::atomic<int> g_gated_rows_per_group{0};
 std::atomic<int> g_pdl{1};
 
@@ -83,7 +81,6 @@ int RunNorm(NormArgs a, const char* what, halo_b200_stream stream, char* err, si
   if (g_norm_short_rows_k1.load(std::memory_order_relaxed)) a.short_rows_k1 = 1;
   a.force_general = g_norm_force_general.load(std::memory_order_relaxed);
   a.keep_hint = g_l2_keep.load(std::memory_order_relaxed);
-  a.staged = g_norm_staged.load(std::memory_order_relaxed);
   bool vec = a.d % 8 == 0 && a.d <= 256u * 8u * 8u && Aligned(a.x, 16) && Aligned(a.y, 16) && Aligned(a.delta, 16) &&
              Aligned(a.res, 16) && Aligned(a.y16, 16) && Aligned(a.w, 16) && a.w_stride % 4 == 0 &&
              Aligned(a.xq, 8) && a.entry_stride % 8 == 0;
@@ -445,7 +442,6 @@ NormRopeArgs QkArgs(const void* q_in, uint64_t q_row_stride, void* q_out, void* 
 
 namespace halo_b200 {
 bool PdlEnabled() { return g_pdl.load(std::memory_order_relaxed) != 0; }
-int CarveoutPreference() { return g_carveout.load(std::memory_order_relaxed); }
 
 int CheckNormRopeQk(const void* q_in, uint64_t q_row_stride, void* q_out, void* q_gate, const float* w_q, uint32_t q_heads,
                     const void* k_in, void* k_out, void* k_cache, const float* w_k, uint32_t k_heads, int in_dtype,
@@ -462,85 +458,35 @@ extern "C" {
 const char* halo_b200_version(void) { return "halo_b200 0.1 sm_100a"; }
 
 int halo_b200_tune(const char* key, int value) {
+  // key, the switch it sets, and the values it accepts (a zero-terminated list; 0 is always one of them)
+  struct Key {
+    const char* name;
+    std::atomic<int>* slot;
+    int allowed[10];
+  };
+  static const Key kKeys[] = {
+      {"norm_threads_per_row", &g_norm_threads_per_row, {1, 2, 4, 8, 16, 32, 64, 128, 256, 0}},
+      {"norm_short_rows_k1", &g_norm_short_rows_k1, {1, 0}},
+      {"norm_force_general", &g_norm_force_general, {1, 0}},
+      {"l2_keep", &g_l2_keep, {1, 0}},
+      {"gated_rows_per_group", &g_gated_rows_per_group, {1, 2, 0}},
+      {"rope_rows_per_group", &g_rope_rows_per_group, {2, 4, 0}},
+      {"rope_lean_k", &g_rope_lean_k, {1, 2, 0}},
+      {"rope_staged", &g_rope_staged, {1, 0}},
+      {"conv_staged", &g_conv_staged, {1, 0}},
+      {"conv_tile", &g_conv_tile, {4, 8, 0}},
+      {"hc_fused_inject", &g_hc_fused_inject, {1, 0}},
+      {"hc_token_k", &g_hc_token_k, {1, 2, 0}},
+      {"hc_row_level", &g_hc_row_level, {1, 0}},
+      {"pdl", &g_pdl, {1, 0}},
+  };
   if (!key) return -1;
-  if (std::strcmp(key, "norm_threads_per_row") == 0) {
-    if (value < 0 || value > 256 || (value & (value - 1)) != 0) return -1;
-    g_norm_threads_per_row.store(value, std::memory_order_relaxed);
-    return 0;
-  }
-  if (std::strcmp(key, "gated_rows_per_group") == 0) {
-    if (value != 0 && value != 1 && value != 2) return -1;
-    g_gated_rows_per_group.store(value, std::memory_order_relaxed);
-    return 0;
-  }
-  if (std::strcmp(key, "rope_rows_per_group") == 0) {
-    if (value != 0 && value != 2 && value != 4) return -1;
-    g_rope_rows_per_group.store(value, std::memory_order_relaxed);
-    return 0;
-  }
-  if (std::strcmp(key, "rope_lean_k") == 0) {
-    if (value != 0 && value != 1 && value != 2) return -1;  // 0 = built-in (four chunks per lane on rows of 256)
-    g_rope_lean_k.store(value, std::memory_order_relaxed);
-    return 0;
-  }
-  if (std::strcmp(key, "l2_keep") == 0) {
-    if (value != 0 && value != 1) return -1;
-    g_l2_keep.store(value, std::memory_order_relaxed);
-    return 0;
-  }
-  if (std::strcmp(key, "norm_staged") == 0) {
-    if (value < 0 || value > 2) return -1;
-    g_norm_staged.store(value, std::memory_order_relaxed);
-    return 0;
-  }
-  if (std::strcmp(key, "carveout") == 0) {
-    if (value < -1 || value > 100) return -1;
-    g_carveout.store(value, std::memory_order_relaxed);
-    return 0;
-  }
-  if (std::strcmp(key, "rope_staged") == 0) {
-    if (value != 0 && value != 1) return -1;
-    g_rope_staged.store(value, std::memory_order_relaxed);
-    return 0;
-  }
-  if (std::strcmp(key, "norm_force_general") == 0) {
-    if (value != 0 && value != 1) return -1;
-    g_norm_force_general.store(value, std::memory_order_relaxed);
-    return 0;
-  }
-  if (std::strcmp(key, "conv_staged") == 0) {
-    if (value != 0 && value != 1) return -1;
-    g_conv_staged.store(value, std::memory_order_relaxed);
-    return 0;
-  }
-  if (std::strcmp(key, "conv_tile") == 0) {
-    if (value != 0 && value != 4 && value != 8) return -1;
-    g_conv_tile.store(value, std::memory_order_relaxed);
-    return 0;
-  }
-  if (std::strcmp(key, "hc_fused_inject") == 0) {
-    if (value != 0 && value != 1) return -1;
-    g_hc_fused_inject.store(value, std::memory_order_relaxed);
-    return 0;
-  }
-  if (std::strcmp(key, "hc_token_k") == 0) {
-    if (value != 0 && value != 1 && value != 2) return -1;
-    g_hc_token_k.store(value, std::memory_order_relaxed);
-    return 0;
-  }
-  if (std::strcmp(key, "hc_row_level") == 0) {
-    if (value != 0 && value != 1) return -1;
-    g_hc_row_level.store(value, std::memory_order_relaxed);
-    return 0;
-  }
-  if (std::strcmp(key, "pdl") == 0) {
-    if (value != 0 && value != 1) return -1;
-    g_pdl.store(value, std::memory_order_relaxed);
-    return 0;
-  }
-  if (std::strcmp(key, "norm_short_rows_k1") == 0) {
-    if (value != 0 && value != 1) return -1;
-    g_norm_short_rows_k1.store(value, std::memory_order_relaxed);
+  for (const Key& k : kKeys) {
+    if (std::strcmp(key, k.name) != 0) continue;
+    bool ok = value == 0;
+    for (int i = 0; !ok && k.allowed[i] != 0; ++i) ok = value == k.allowed[i];
+    if (!ok) return -1;
+    k.slot->store(value, std::memory_order_relaxed);
     return 0;
   }
   return -1;
@@ -1531,11 +1477,10 @@ int halo_b200_scale_silu(halo_b200_stream stream, const float* x, void* y, int y
 
 int halo_b200_stage_timeouts(unsigned int* count, char* err, size_t errlen) {
   REQUIRE(count != nullptr, "halo_b200_stage_timeouts: count is null");
-  unsigned int conv = 0, rope = 0, norm = 0;
+  unsigned int conv = 0, rope = 0;
   cudaError_t e = ReadConvStageTimeouts(&conv);
   if (e == cudaSuccess) e = ReadRopeStageTimeouts(&rope);
-  if (e == cudaSuccess) e = ReadNormStageTimeouts(&norm);
-  *count = conv + rope + norm;
+  *count = conv + rope;
   return Done(e, "halo_b200_stage_timeouts", err, errlen);
 }
 

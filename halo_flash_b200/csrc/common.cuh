@@ -3,11 +3,18 @@
 //
 // Arithmetic rules for every kernel in this library (they make the results
 // comparable with halo-flash's scalar CPU operators, src/model/cpu_ops.cpp):
-//   * fp32 arithmetic compiled with -fmad=false, so multiplies and adds round
-//     separately as on the CPU; the only deliberate departures are the sum of
-//     squares (fused multiply-add), the norm scale (hardware rsqrt, 2 ulp) and the
-//     gate functions (hardware exp2 / reciprocal), all far inside the 1e-5 the
-//     path allows. The Q8 encoders produce the codes and scales of the IEEE divisions bit for
+//   * fp32 arithmetic compiled with -fmad=false, so scalar multiplies and adds round
+//     separately as on the CPU. The deliberate departures, all far inside the 1e-5 the
+//     path allows: the sum of squares (fused multiply-adds in fp32; the CPU sums in
+//     double), the norm scale (hardware rsqrt, 2 ulp), the gate functions (hardware
+//     exp2 / reciprocal, .ftz forms) and the conv taps (an FMA chain in tap order);
+//   * packed fp32x2 instructions (FMUL2 / FADD2 / FFMA2) are used only where no product
+//     feeds a sum whose two roundings matter: ptxas contracts a packed multiply into the
+//     packed add that consumes it - measured on sm_100a, also for inline PTX that names
+//     .rn on both - so every "a * b + c * d as the CPU rounds it" (the rotation, the
+//     experts' sum, the combine into an fp32 residual) is written with scalar
+//     multiplies and adds;
+//   * the Q8 encoders produce the scales and codes of the CPU's IEEE divisions bit for
 //     bit without dividing (div127, round_div_codes below);
 //   * 16-bit outputs are rounded once, to nearest even, from the fp32 value
 //     (bf16 as src/kernels/core.hip:70-73, fp16 as a _Float16 cast).
@@ -312,6 +319,32 @@ __device__ __forceinline__ Oct raw_unpack(const Raw<float>& r) {
 }
 __device__ __forceinline__ Oct raw_unpack(const Raw<bf16>& r) { return oct_unpack_bf16(r.u); }
 __device__ __forceinline__ Oct raw_unpack(const Raw<f16>& r) { return oct_unpack_f16(r.u); }
+
+// Sum of two 16-bit octets IN their storage type: four packed add.rn instructions instead of two unpacks, four
+// packed fp32 adds and a pack (24 instructions). The result is the residual the fp32 path stores, bit for bit:
+// for two bf16 (fp16) operands the fp32 sum is exact whenever their exponents are at most 16 (13) apart, and
+// beyond that the smaller operand is below half a unit in the last place of the larger one either way, so
+// "add in fp32, round once to 16 bits" and the correctly rounded 16-bit add agree for all finite inputs.
+__device__ __forceinline__ uint32_t add2_bf16(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t add2_f16(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ Raw<bf16> raw_add(const Raw<bf16>& a, const Raw<bf16>& b) {
+  Raw<bf16> r;
+  r.u = make_uint4(add2_bf16(a.u.x, b.u.x), add2_bf16(a.u.y, b.u.y), add2_bf16(a.u.z, b.u.z), add2_bf16(a.u.w, b.u.w));
+  return r;
+}
+__device__ __forceinline__ Raw<f16> raw_add(const Raw<f16>& a, const Raw<f16>& b) {
+  Raw<f16> r;
+  r.u = make_uint4(add2_f16(a.u.x, b.u.x), add2_f16(a.u.y, b.u.y), add2_f16(a.u.z, b.u.z), add2_f16(a.u.w, b.u.w));
+  return r;
+}
 
 // ---- reductions ---------------------------------------------------------------
 // Sum over the `g` threads of a row group (g a power of two, g <= kBlock, groups

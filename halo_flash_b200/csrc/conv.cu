@@ -137,14 +137,19 @@ __global__ void __launch_bounds__(kBlock, kTile >= 8 ? 2 : 3) conv_l2norm_kernel
 // tiles. Rows outside the chunk are not copied; their lanes read zeros (or the conv state).
 __device__ unsigned int g_stage_timeouts = 0;
 
-template <typename IT, typename OT, unsigned HL, int kTile, int MODE>  // MODE 0: per-thread q/k test, 1: all q/k, 2: none
+// MODE 0: per-thread q/k test, 1: all q/k, 2: none. FULL: the tile and its three rows of history lie inside the
+// chunk and every thread owns a real octet, so no load or store is predicated and the eight tokens form ONE
+// straight-line block: their convolutions, gates and head reductions are independent and the compiler
+// interleaves them (with the bounds tests in the loop each token was a block of its own, and a warp issued
+// once in fifteen cycles, stalled on its own dependent chain).
+template <typename IT, typename OT, unsigned HL, int kTile, int MODE, bool FULL>
 __device__ __forceinline__ void conv_stage_compute(const ConvArgs& a, const Oct (&w)[kTaps], const IT* tile,
                                                    const unsigned row_elems, const unsigned c0, const uint32_t t0,
                                                    const bool live, const uint32_t first_row, const uint32_t last_row) {
   const IT* mine = tile + threadIdx.x * 8;
   // window row j holds input t0 - 3 + j; rows [first_row, last_row) were copied, the rest read as zero
   auto row = [&](int j) -> Oct {
-    if (static_cast<uint32_t>(j) >= first_row && static_cast<uint32_t>(j) < last_row) {
+    if (FULL || (static_cast<uint32_t>(j) >= first_row && static_cast<uint32_t>(j) < last_row)) {
       if constexpr (std::is_same_v<IT, float>) {
         const float4 lo = *reinterpret_cast<const float4*>(mine + static_cast<size_t>(j) * row_elems);
         const float4 hi = *reinterpret_cast<const float4*>(mine + static_cast<size_t>(j) * row_elems + 4);
@@ -161,7 +166,7 @@ __device__ __forceinline__ void conv_stage_compute(const ConvArgs& a, const Oct 
     return oct_zero();
   };
   Oct x0 = row(0), x1 = row(1), x2 = row(2);
-  if (t0 == 0 && live && a.state) {
+  if (!FULL && t0 == 0 && live && a.state) {
     x0 = oct_load(a.state + c0);
     x1 = oct_load(a.state + static_cast<size_t>(a.channels) + c0);
     x2 = oct_load(a.state + 2 * static_cast<size_t>(a.channels) + c0);
@@ -183,7 +188,7 @@ __device__ __forceinline__ void conv_stage_compute(const ConvArgs& a, const Oct 
         if (of < HL) ss += __shfl_xor_sync(kFullMask, ss, of);
       if (l2) v = oct_scale(v, rsqrtf(ss + a.eps));
     }
-    if (live && t0 + t < a.tokens) oct_store(out, v);
+    if (FULL || (live && t0 + t < a.tokens)) oct_store(out, v);
   }
 }
 
@@ -273,9 +278,17 @@ __global__ void __launch_bounds__(kBlock, 2) conv_l2norm_staged_kernel(const Con
     uint32_t first_row, last_row;
     tile_rows<kTile>(by * kTile, a.tokens, &first_row, &last_row);
     const IT* tile = bufs + b * buf_elems;
-    if (mode == 2) conv_stage_compute<IT, OT, HL, kTile, 2>(a, w, tile, row_elems, c0, by * kTile, live, first_row, last_row);
-    else if (mode == 1) conv_stage_compute<IT, OT, HL, kTile, 1>(a, w, tile, row_elems, c0, by * kTile, live, first_row, last_row);
-    else conv_stage_compute<IT, OT, HL, kTile, 0>(a, w, tile, row_elems, c0, by * kTile, live, first_row, last_row);
+    const bool full = first_row == 0 && last_row == static_cast<uint32_t>(kTile + 3) && slice_octs == kBlock &&
+                      by * kTile + kTile <= a.tokens;  // uniform over the CTA
+    if (full) {
+      if (mode == 2) conv_stage_compute<IT, OT, HL, kTile, 2, true>(a, w, tile, row_elems, c0, by * kTile, live, first_row, last_row);
+      else if (mode == 1) conv_stage_compute<IT, OT, HL, kTile, 1, true>(a, w, tile, row_elems, c0, by * kTile, live, first_row, last_row);
+      else conv_stage_compute<IT, OT, HL, kTile, 0, true>(a, w, tile, row_elems, c0, by * kTile, live, first_row, last_row);
+    } else {
+      if (mode == 2) conv_stage_compute<IT, OT, HL, kTile, 2, false>(a, w, tile, row_elems, c0, by * kTile, live, first_row, last_row);
+      else if (mode == 1) conv_stage_compute<IT, OT, HL, kTile, 1, false>(a, w, tile, row_elems, c0, by * kTile, live, first_row, last_row);
+      else conv_stage_compute<IT, OT, HL, kTile, 0, false>(a, w, tile, row_elems, c0, by * kTile, live, first_row, last_row);
+    }
     __syncthreads();  // every thread is done reading this buffer before it is refilled
   }
 }

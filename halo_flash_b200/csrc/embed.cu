@@ -55,25 +55,34 @@ __global__ void __launch_bounds__(kBlock) embed_q8_0_kernel(const EmbedArgs a, c
     }
     __syncwarp();
     OT* dst = out + static_cast<size_t>(t) * a.cols + static_cast<size_t>(sg) * seg_blocks * 32;
-    for (unsigned j = lane; j < octs; j += 32) {
-      float v[8];
-      if (in_range) {
-        const uint8_t* blk = buf + (j >> 2) * 34;
-        const float d = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(blk)));
+    if (!in_range) {
+      const float z[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+      for (unsigned j = lane; j < octs; j += 32) store8(dst + j * 8, z);
+    } else {
+      // A lane's octets j = lane, lane + 32, ... are eight blocks = 272 bytes apart, so its quarter of a block, the
+      // alignment of its eight code bytes and therefore the funnel shift are the same for every one of them: they
+      // are computed once and the loop only steps two pointers (the per-octet index arithmetic used to cost
+      // more instructions than the conversion).
+      const unsigned at0 = (lane >> 2) * 34u + 2u + 8u * (lane & 3u);
+      const unsigned sh = (at0 & 2u) * 8u;
+      const uint8_t* wp = buf + (at0 & ~3u);
+      const uint8_t* dp = buf + (lane >> 2) * 34u;
+      const float2 bias = make_float2(-8388736.0f, -8388736.0f);
+      OT* o = dst + lane * 8;
+      for (unsigned j = lane; j < octs; j += 32, wp += 272, dp += 272, o += 256) {
+        const float d = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(dp)));
+        const float2 d2 = make_float2(d, d);
         // the 8 code bytes start 2 bytes into a block, so on a 4-byte boundary in odd blocks only: three
-        // aligned words and a funnel shift by 0 or 16 bits give them as two words either way
-        const unsigned at = static_cast<unsigned>(blk - buf) + 2u + 8u * (j & 3u);
-        const uint32_t* w32 = reinterpret_cast<const uint32_t*>(buf + (at & ~3u));
-        const unsigned sh = (at & 2u) * 8u;
-        // the third word is needed only for the shifted case, which never is the buffer's last block (a
-        // segment has a multiple of 8 blocks and odd blocks are aligned; a whole row of any other block
-        // count ends at least 2 bytes before its 16-byte padded buffer does): reading it unconditionally
-        // ran 4 bytes past the last warp's buffer
+        // aligned words and a funnel shift by 0 or 16 bits give them as two words either way. The third word is
+        // needed only for the shifted case, which never is the buffer's last block (a segment has a multiple of 8
+        // blocks and odd blocks are aligned; a whole row of any other block count ends at least 2 bytes before
+        // its 16-byte padded buffer does): reading it unconditionally ran 4 bytes past the last warp's buffer
+        const uint32_t* w32 = reinterpret_cast<const uint32_t*>(wp);
         const uint32_t w0 = w32[0], w1 = w32[1], w2 = sh ? w32[2] : 0u;
         const uint32_t code[2] = {__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh)};
         // int8 -> float without a conversion instruction: the byte, biased by 128, becomes the low mantissa
         // byte of 2^23 (0x4B0000xx = 2^23 + xx); subtracting 2^23 + 128 leaves the code, exactly; then x scale
-        const float2 bias = make_float2(-8388736.0f, -8388736.0f), d2 = make_float2(d, d);
+        float v[8];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const uint32_t x = code[h] ^ 0x80808080u;
@@ -84,11 +93,8 @@ __global__ void __launch_bounds__(kBlock) embed_q8_0_kernel(const EmbedArgs a, c
           const float2 a0 = __fmul2_rn(__fadd2_rn(lo, bias), d2), a1 = __fmul2_rn(__fadd2_rn(hi, bias), d2);
           v[4 * h] = a0.x, v[4 * h + 1] = a0.y, v[4 * h + 2] = a1.x, v[4 * h + 3] = a1.y;
         }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+        store8(o, v);
       }
-      store8(dst + j * 8, v);
     }
     __syncwarp();  // the segment buffer is reused by the warp's next item
   }

@@ -15,8 +15,6 @@ namespace halo_b200 {
 
 // True unless halo_b200_tune("pdl", 0) switched programmatic dependent launch off.
 bool PdlEnabled();
-// Preferred shared-memory carveout of a launch in percent (halo_b200_tune("carveout", p)); < 0: the driver's choice.
-int CarveoutPreference();
 
 // Every kernel launch of the library: a plain stream-ordered launch that additionally allows the
 // kernel to be scheduled while its predecessor in the stream drains (the kernels order
@@ -31,21 +29,11 @@ inline cudaError_t LaunchKernel(void (*kernel)(KArgs...), dim3 grid, dim3 block,
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
-  cudaLaunchAttribute attr[2];
-  unsigned n = 0;
-  if (PdlEnabled()) {
-    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[n].val.programmaticStreamSerializationAllowed = 1;
-    ++n;
-  }
-  const int carveout = CarveoutPreference();
-  if (carveout >= 0) {
-    attr[n].id = cudaLaunchAttributePreferredSharedMemoryCarveout;
-    attr[n].val.sharedMemCarveout = static_cast<unsigned>(carveout);
-    ++n;
-  }
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = n;
+  cfg.numAttrs = PdlEnabled() ? 1u : 0u;
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
@@ -97,7 +85,6 @@ struct NormArgs {
   int short_rows_k1 = 0;        // 1: rows of <= 32 octets keep one octet per thread (default two)
   int force_general = 0;        // 1: never take the lean kernel (tests compare the two)
   int keep_hint = 1;            // 0: the add + norm stores its residual without the L2 keep policy
-  int staged = 1;               // persistent shared-memory-staged kernel: 0 never, 1 with a Q8 epilogue, 2 every wide 16-bit norm
   bool vec = true;
 };
 cudaError_t LaunchNorm(const NormArgs& a, cudaStream_t s);
@@ -352,7 +339,6 @@ struct ConvArgs {
 };
 cudaError_t ReadConvStageTimeouts(unsigned int* out);
 cudaError_t ReadRopeStageTimeouts(unsigned int* out);
-cudaError_t ReadNormStageTimeouts(unsigned int* out);
 cudaError_t LaunchConvStep(const ConvArgs& a, cudaStream_t s);
 cudaError_t LaunchConvL2norm(const ConvArgs& a, cudaStream_t s);
 cudaError_t LaunchConvStateAdvance(const ConvArgs& a, cudaStream_t s);

@@ -16,7 +16,6 @@
 
 #include "common.cuh"
 #include "kernels.h"
-#include "stage.cuh"
 
 #ifndef HALO_EPI_CTAS
 #define HALO_EPI_CTAS 5
@@ -240,9 +239,15 @@ __device__ __forceinline__ void norm_lean_row(const LeanArgs& a, const Raw<XT> (
     const uint64_t keep = l2_policy(a.keep_res != 0);
 #pragma unroll
     for (int k = 0; k < K; ++k) {
-      v[k] = oct_add(raw_unpack(rx[k]), raw_unpack(rd[k]));
       // the norm reads the residual as stored; the next add + norm reads it again: ask L2 to keep it
-      oct_store_round_keep(res + (((k << lg) + lir) << 3), v[k], keep);
+      if constexpr (sizeof(XT) == 2) {  // summed in the storage type (raw_add: the same bits, a third of the instructions)
+        const Raw<XT> sum = raw_add(rx[k], rd[k]);
+        store16_keep(res + (((k << lg) + lir) << 3), sum.u, keep);
+        v[k] = raw_unpack(sum);
+      } else {
+        v[k] = oct_add(raw_unpack(rx[k]), raw_unpack(rd[k]));
+        oct_store_round_keep(res + (((k << lg) + lir) << 3), v[k], keep);
+      }
     }
   } else {
 #pragma unroll
@@ -365,73 +370,6 @@ __global__ void __launch_bounds__(kBlock, K > 2 ? (sizeof(XT) == 2 ? 4 : 1) : (!
     for (int k = 0; k < K; ++k) rd[k] = raw_load(dl + (((k << lg) + lir) << 3));
   }
   norm_lean_row<XT, YT, K, ADD, EPI, WIDE, MODE>(a, rx, rd, row, scratch, stage);
-}
-
-// The same rows through persistent CTAs that stage them (stage.cuh): a pass of kBlock / g rows of x (and of
-// delta) is one contiguous span per tensor, fetched by one bulk asynchronous copy each into one of two
-// shared-memory buffers. While the CTA works on pass n the copy engine fills the other buffer with pass n + 1,
-// so the load latency of a pass hides behind the reduction and the epilogue of the pass before it: what the
-// Q8_0 epilogue's long dependent chain needs, since the direct kernel above holds nothing in flight while it
-// runs. 16-bit rows only (a pass of fp32 rows would double the buffers).
-__device__ unsigned int g_stage_timeouts = 0;
-
-template <typename XT, typename YT, int K, bool ADD, bool EPI, int MODE>
-__global__ void __launch_bounds__(kBlock, (!EPI && MODE != 0) ? 6 : (EPI ? HALO_EPI_CTAS : 4)) norm_rows_staged_kernel(const LeanArgs a, const uint32_t passes) {
-  static_assert(sizeof(XT) == 2, "staged rows are 16-bit");
-  pdl_begin();
-  extern __shared__ __align__(128) uint8_t norm_stage[];
-  __shared__ float scratch[kBlock / 32];
-  __shared__ __align__(16) uint8_t stage[EPI ? kBlock / 32 : 1][EPI ? K : 1][EPI ? 272 : 16];
-  __shared__ __align__(8) unsigned long long bars[2];
-  const unsigned lg = a.lg, g = 1u << lg;
-  const unsigned lir = threadIdx.x & (g - 1), slot = threadIdx.x >> lg;
-  const unsigned rows_per_pass = kBlock >> lg;
-  const unsigned pass_elems = rows_per_pass * a.d;
-  const unsigned pass_bytes = pass_elems * 2u;
-  constexpr unsigned kTensors = ADD ? 2u : 1u;
-  XT* bufs = reinterpret_cast<XT*>(norm_stage);  // [2 buffers][kTensors][pass_elems]
-  if (threadIdx.x == 0) stage_init(bars, 2);
-  __syncthreads();
-  auto request = [&](uint32_t p, unsigned b) {
-    const unsigned bar = smem_addr(&bars[b]);
-    stage_expect(bar, kTensors * pass_bytes);
-    stage_copy(smem_addr(bufs + (b * kTensors) * pass_elems), static_cast<const XT*>(a.x) + static_cast<size_t>(p) * pass_elems,
-               pass_bytes, bar);
-    if constexpr (ADD)
-      stage_copy(smem_addr(bufs + (b * kTensors + 1) * pass_elems),
-                 static_cast<const XT*>(a.delta) + static_cast<size_t>(p) * pass_elems, pass_bytes, bar);
-  };
-  uint32_t p = blockIdx.x;
-  if (p >= passes) return;  // uniform
-  const uint32_t stride = gridDim.x;
-  if (threadIdx.x == 0) {
-    request(p, 0);
-    if (p + stride < passes) request(p + stride, 1);
-  }
-  for (uint32_t n = 0; p < passes; ++n, p += stride) {
-    const unsigned b = n & 1u;
-    const unsigned done = stage_wait(smem_addr(&bars[b]), (n >> 1) & 1u);
-    if (!__syncthreads_and(static_cast<int>(done))) {
-      // Never seen: count it, give the copies still in flight into this CTA's shared memory one more bounded wait
-      // (this buffer, and the other one's next use), and leave without writing the remaining passes.
-      stage_wait(smem_addr(&bars[b]), (n >> 1) & 1u);
-      if (p + stride < passes) stage_wait(smem_addr(&bars[b ^ 1u]), ((n + 1) >> 1) & 1u);
-      if (threadIdx.x == 0) atomicAdd(&g_stage_timeouts, 1u);
-      return;
-    }
-    const XT* mine = bufs + (b * kTensors) * pass_elems + slot * a.d;
-    Raw<XT> rx[K];
-    Raw<XT> rd[ADD ? K : 1];
-#pragma unroll
-    for (int k = 0; k < K; ++k) rx[k].u = *reinterpret_cast<const uint4*>(mine + (((k << lg) + lir) << 3));
-    if constexpr (ADD) {
-#pragma unroll
-      for (int k = 0; k < K; ++k) rd[k].u = *reinterpret_cast<const uint4*>(mine + pass_elems + (((k << lg) + lir) << 3));
-    }
-    norm_lean_row<XT, YT, K, ADD, EPI, true, MODE>(a, rx, rd, p * rows_per_pass + slot, scratch, stage);
-    __syncthreads();  // every thread has read buffer b (and the reduction scratch): refill it with the pass after next
-    if (threadIdx.x == 0 && p + 2 * stride < passes) request(p + 2 * stride, b);
-  }
 }
 
 // Any d, any alignment: one CTA per row, scalar accesses, the row is re-read
@@ -757,22 +695,6 @@ cudaError_t LaunchLean(const NormArgs& a, const Shape& sh, unsigned grid, cudaSt
   const int mode = (!epi && a.w && a.y && !a.l2) ? (a.one_plus ? 2 : 1) : (!epi && !a.w && a.y && a.l2) ? 3 : 0;
   if constexpr (K <= 2) {  // rows wider than a warp per row exist only with one or two octets per thread
     if (sh.lg > 5) {
-      if constexpr (sizeof(XT) == 2) {
-        // persistent, shared-memory-staged form: the Q8 epilogue at streaming sizes (norm_staged 1, the default),
-        // or every wide 16-bit row norm (norm_staged 2)
-        const size_t pass_bytes = static_cast<size_t>(kBlock >> sh.lg) * a.d * 2u;
-        const size_t smem = 2 * (ADD ? 2 : 1) * pass_bytes;
-        const unsigned slots = 148u * (epi ? HALO_EPI_CTAS : (mode != 0 ? 6 : 4));
-        if (((a.staged == 1 && epi) || a.staged == 2) && grid > 2 * slots && smem <= 40u * 1024u) {
-          const unsigned pgrid = slots;
-          if (epi) LaunchKernel(norm_rows_staged_kernel<XT, YT, K, ADD, true, 0>, pgrid, kBlock, smem, s, l, grid);
-          else if (mode == 2) LaunchKernel(norm_rows_staged_kernel<XT, YT, K, ADD, false, 2>, pgrid, kBlock, smem, s, l, grid);
-          else if (mode == 1) LaunchKernel(norm_rows_staged_kernel<XT, YT, K, ADD, false, 1>, pgrid, kBlock, smem, s, l, grid);
-          else if (mode == 3) LaunchKernel(norm_rows_staged_kernel<XT, YT, K, ADD, false, 3>, pgrid, kBlock, smem, s, l, grid);
-          else LaunchKernel(norm_rows_staged_kernel<XT, YT, K, ADD, false, 0>, pgrid, kBlock, smem, s, l, grid);
-          return cudaGetLastError();
-        }
-      }
       LaunchLeanMode<XT, YT, K, ADD, true>(l, epi, mode, grid, s);
       return cudaGetLastError();
     }
@@ -878,10 +800,6 @@ cudaError_t LaunchGatedT(const GatedArgs& a, cudaStream_t s) {
 }
 
 }  // namespace
-
-cudaError_t ReadNormStageTimeouts(unsigned int* out) {
-  return cudaMemcpyFromSymbol(out, g_stage_timeouts, sizeof(unsigned int));
-}
 
 // Largest d the vector path accepts: 256 threads x 8 octets x 8 elements.
 cudaError_t LaunchNorm(const NormArgs& a, cudaStream_t s) {

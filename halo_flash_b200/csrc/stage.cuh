@@ -4,7 +4,7 @@
 // no registers and a tile's load latency hides behind the arithmetic of the tile before it.
 //
 // Completion is counted on an mbarrier per buffer. EVERY wait is bounded: stage_wait() polls at most
-// kStageSpinLimit times with a 128 ns sleep between polls once the first few have failed (about half a second
+// kStageSpinLimit times, with a 256 ns sleep between polls once the first 4096 have failed (about a second
 // in all). A kernel whose wait ran out counts it (its translation unit's g_stage_timeouts), gives the copies
 // it still has in flight one more bounded wait so that no copy lands in shared memory the SM has handed to
 // another CTA, and returns without writing its remaining tiles. That has never been observed; a non-zero
@@ -47,7 +47,7 @@ __device__ __forceinline__ unsigned stage_wait(unsigned bar, unsigned parity) {
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
         "selp.u32 %0, 1, 0, p;\n}"
         : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-    if (!done && spin >= 16) __nanosleep(128);
+    if (!done && spin >= 4096) __nanosleep(256);  // the fast path never sleeps; the limit is about a second
   }
   return done;
 }

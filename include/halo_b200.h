@@ -440,7 +440,7 @@ int halo_b200_conv_step(halo_b200_stream stream, const float* in, float* state, 
 
 /* No counterpart in the reference. The persistent kernels of the library (the conv + SiLU + L2 norm and the fused
  * norm + RoPE at streaming sizes) stage their input rows in shared memory with bulk asynchronous copies and wait
- * for them on a barrier object for a bounded time (about half a second); a CTA whose wait ran out (never
+ * for them on a barrier object for a bounded time (about a second); a CTA whose wait ran out (never
  * observed) returns without writing its remaining output tiles and is counted. halo_b200_stage_timeouts reads the
  * count (this call synchronizes the device). A non-zero count means the outputs of the calls made before it are
  * invalid. halo_b200_conv_stage_timeouts is the same call under its earlier name. */

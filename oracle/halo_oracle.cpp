@@ -15,6 +15,7 @@
 // Build: g++ -std=c++20 -O2 (no -march, no -ffast-math: x86-64 baseline has no
 // FMA, so every multiply and add rounds separately, as in the reference build).
 
+#include "row_pool.hpp"
 #include <algorithm>
 #include <cmath>
 #include <cstddef>
@@ -114,18 +115,7 @@ void RopeToken(float* x, std::uint32_t heads, std::uint32_t hd, std::uint32_t ro
 // Rows [begin, end) of `fn` on `threads` host threads, contiguous chunks. The
 // reference threads only its MatVec (src/model/cpu_ops.cpp:120-131); its
 // trainer splits norm rows the same way (src/train/last_k.cpp:41-52).
-template <typename Fn>
-void ForRows(std::size_t rows, int threads, Fn fn) {
-  if (threads <= 1 || rows < 2) {
-    fn(0, rows);
-    return;
-  }
-  const std::size_t nt = std::min<std::size_t>(static_cast<std::size_t>(threads), rows);
-  const std::size_t chunk = (rows + nt - 1) / nt;
-  std::vector<std::thread> pool;
-  for (std::size_t b = 0; b < rows; b += chunk) pool.emplace_back(fn, b, std::min(rows, b + chunk));
-  for (auto& t : pool) t.join();
-}
+using halo_oracle::ForRows;  // persistent row-parallel workers (row_pool.hpp)
 
 }  // namespace
 

@@ -7,6 +7,7 @@
 // oracle/halo_oracle.cpp so the two can be compared bit for bit and either can
 // serve as the checker or as the timed CPU baseline.
 
+#include "row_pool.hpp"
 #include <algorithm>
 #include <cstddef>
 #include <cstdint>
@@ -24,18 +25,7 @@ namespace {
 
 namespace cpu = halo::model::cpu;
 
-template <typename Fn>
-void ForRows(std::size_t rows, int threads, Fn fn) {
-  if (threads <= 1 || rows < 2) {
-    fn(0, rows);
-    return;
-  }
-  const std::size_t nt = std::min<std::size_t>(static_cast<std::size_t>(threads), rows);
-  const std::size_t chunk = (rows + nt - 1) / nt;
-  std::vector<std::thread> pool;
-  for (std::size_t b = 0; b < rows; b += chunk) pool.emplace_back(fn, b, std::min(rows, b + chunk));
-  for (auto& t : pool) t.join();
-}
+using halo_oracle::ForRows;  // persistent row-parallel workers (row_pool.hpp)
 
 // What a bf16 residual buffer holds after a store of v: round to nearest even on the upper 16 bits
 // (the GPU side's HaloBf16 store, src/kernels/core.hip:62-73), decoded by the reference's Bf16ToFloat.

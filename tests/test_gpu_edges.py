@@ -8,7 +8,7 @@ import pytest
 import torch
 
 import oracle
-from conftest import assert_bf16_within_1ulp, assert_rows_close
+from conftest import assert_bf16_rope, assert_bf16_within_1ulp, assert_rows_close
 from halo_flash_b200 import chain as chain_mod, lib, ops, synth
 
 pytestmark = pytest.mark.gpu
@@ -79,6 +79,28 @@ def test_full_size_seeded_deltanet_and_rope_rows(orc):
     h = torch.empty(T * s.top_k, s.ff, device=DEV, dtype=torch.bfloat16)
     ops.silu_mul(to_dev(g, "bf16"), to_dev(u, "bf16"), y=h)
     assert_bf16_within_1ulp(bits16(h), orc.silu_mul(g.copy(), u, threads=THREADS), "routed SwiGLU")
+    # fused Q / K per-head norm + RoPE with the step's rotation table: the persistent, shared-memory-staged kernel
+    # (the default at this size) against the oracle, and against the direct kernel bit for bit
+    q = oracle.round_bf16(synth.act("c5.q", T, s.q_heads, s.head_dim))
+    k = oracle.round_bf16(synth.act("c5.k", T, s.kv_heads, s.head_dim))
+    wq, wk = synth.norm_w("c5.wq", s.head_dim), synth.norm_w("c5.wk", s.head_dim)
+    pos0 = 262144 - T
+    tab = ops.rope_table(torch.empty(T, 2, s.rot // 2, device=DEV), s.rot, s.theta, pos0=pos0)
+    outs = []
+    for staged in (1, 0):
+        lib().tune("rope_staged", staged)
+        try:
+            dq, dk = to_dev(q, "bf16"), to_dev(k, "bf16")
+            ops.norm_rope_qk_table(dq, dk, to_dev(wq), to_dev(wk), s.eps, s.rot, tab)
+            outs.append((dq, dk))
+        finally:
+            lib().tune("rope_staged", 1)
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1]), "staged and direct kernels differ"
+    pos = np.arange(pos0, pos0 + T, dtype=np.uint32)
+    for got, x, w, heads in ((outs[0][0], q, wq, s.q_heads), (outs[0][1], k, wk, s.kv_heads)):
+        want = orc.rope_rows(orc.rmsnorm_rows(x.reshape(-1, s.head_dim).copy(), ONE + w, s.eps, threads=THREADS)
+                             .reshape(T, heads, s.head_dim), pos, s.rot, s.theta, threads=THREADS)
+        assert_bf16_rope(bits16(got), want, "full-size norm + RoPE")
 
 
 # ---- the gates over their whole argument range ------------------------------------------------------
