@@ -250,9 +250,11 @@ def time_graph(torch, fn_capture, replays: int):
 # profiles/ (not measured by this run): equal to the algorithmic bytes (2 rows read, 2 rows written, 2 bytes per
 # element, H = 2048).
 TRAFFIC_PER_TOKEN = 16384
-TRAFFIC_HOW = ("constant from the ncu captures under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum of one "
-               "launch), not measured by this run, scaled by tokens. At 4096 tokens ncu sees the 33.6 MB read; the "
-               "33.6 MB written leave L2 after the kernel and are counted at their algorithmic size")
+TRAFFIC_HOW = ("constant from the ncu captures under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum), not measured "
+               "by this run, scaled by tokens. At 65 536 tokens (output four times the L2) one launch reads 536.9 MB = "
+               "8192 B per token, exactly the algorithmic read bytes, and writes 481 MB inside the launch with the last "
+               "56 MB still dirty in L2 at its end: 16 384 B per token once drained. At 4096 tokens ncu sees the 33.6 MB "
+               "read; the 33.6 MB written leave L2 after the kernel")
 
 
 def op_specs(torch, shapes, T: int):
@@ -581,8 +583,19 @@ def run_ours(args) -> None:
     dist = None
     if world > 1:
         import torch.distributed as dist
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # stdout carries the one JSON line only
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # stdout carries the one JSON line only: NCCL announces itself on file descriptor 1 while the communicator
+        # is built (at the first collective), so that descriptor points at stderr until then
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            os.dup2(saved, 1)
+            os.close(saved)
     n_gpus = world
     T = args.tokens
     peaks_path = ROOT / "MEASURED_PEAKS.json"
