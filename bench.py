@@ -736,10 +736,16 @@ def main() -> None:
     ap.add_argument("--decode-batch", type=int, default=0, help="time the decode form of the chain for batch 1 .. B and exit")
     ap.add_argument("--profile-op", default=None, help="run 6 eager launches of one op and exit (profiler captures): "
                     "add_rmsnorm, add_rmsnorm_q8, l2norm, gated_norm, norm_rope_qk, swiglu_moe, embed, hc_combine_norm, conv_l2norm, moe_combine")
+    ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
+                    help="set one of the library's experiment switches (halo_b200_tune) before anything runs; repeatable")
     args = ap.parse_args()
     if args.no_pdl:
+        args.tune.append("pdl=0")
+    if args.tune and args.impl != "reference":
         from halo_flash_b200 import lib
-        lib().tune("pdl", 0)
+        for kv in args.tune:
+            key, _, val = kv.partition("=")
+            lib().tune(key, int(val))
     if args.decode_batch:
         decode_steps(args)
     elif args.profile_op:

@@ -55,7 +55,9 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         src, obj = CSRC / name, OBJ / (Path(name).stem + ".o")
         if not force and not _stale(obj, [src, *headers]):
             return name, None
-        cmd = [nvcc, *NVCC_FLAGS, "-I", str(INCLUDE), "-c", str(src), "-o", str(obj)]
+        # HALO_B200_NVCC_FLAGS: extra flags for experiments (e.g. -DHALO_PF_HC=0); use --force when it changes
+        extra = os.environ.get("HALO_B200_NVCC_FLAGS", "").split()
+        cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", str(INCLUDE), "-c", str(src), "-o", str(obj)]
         p = subprocess.run(cmd, capture_output=True, text=True)
         if p.returncode != 0:
             raise RuntimeError(f"nvcc failed on {name}:\n{p.stdout}\n{p.stderr}")

@@ -39,9 +39,41 @@ constexpr int kBlock = 256;  // threads per CTA of every row kernel
 // written before the wait. The launch gap between two 12-microsecond kernels (CTA scheduling,
 // parameter fetch, index arithmetic) thereby overlaps the tail of the earlier kernel. Both
 // instructions are no-ops in a kernel launched without the attribute LaunchKernel() sets.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_begin() {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  pdl_launch_dependents();
+  pdl_wait();
+}
+
+// Between the two halves of pdl_begin() a CTA may ask L2 for the span of global memory it is about to read
+// (`bytes` a multiple of 16, p 16-byte aligned; one thread, one instruction). A prefetch is only a hint and L2 is
+// the point of coherence, so this is safe even when the kernel ahead still has to WRITE those bytes (its stores
+// update the line in L2). What it buys: the CTAs that sit in griddepcontrol.wait while the kernel ahead drains
+// do not all leave it into an empty memory pipeline - their first loads find L2. Measured on 4096-token launches:
+// SwiGLU 22.4 -> 21.5 us, gated norm 16.5 -> 15.7, add + norm 11.7 -> 11.4, hyper-connection combine 37.8 -> 34.4.
+// Which kernels do it is decided per kernel at compile time: the Q8-epilogue norm kernel lost 7 - 12 % from
+// the mere presence of the preamble (its schedule is tight at 48 registers x 5 CTAs), so it has none.
+#ifndef HALO_PF_NORM
+#define HALO_PF_NORM 1
+#endif
+#ifndef HALO_PF_NORM_EPI
+#define HALO_PF_NORM_EPI 0
+#endif
+#ifndef HALO_PF_GATED
+#define HALO_PF_GATED 1
+#endif
+#ifndef HALO_PF_ELT
+#define HALO_PF_ELT 1
+#endif
+#ifndef HALO_PF_ROPE_STAGED
+#define HALO_PF_ROPE_STAGED 1
+#endif
+#ifndef HALO_PF_HC
+#define HALO_PF_HC 1
+#endif
+__device__ __forceinline__ void prefetch_l2_span(const void* p, unsigned bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 
 using bf16 = __nv_bfloat16;

@@ -104,7 +104,18 @@ constexpr int HcMinCtas(int octets, int rt_size) {
 template <typename RT, typename OT, typename YT, int HC, int K, bool MOE, bool LEAN = false>
 __global__ void __launch_bounds__(kBlock, HcMinCtas(HC* K, sizeof(RT)))
     hc_combine_norm_kernel(const HcArgs a, const unsigned lg, const float inv_h) {
-  pdl_begin();
+  pdl_launch_dependents();
+  if constexpr (LEAN) {  // full tiles: the CTA's groups are one contiguous span of the residual and one of the block output
+    if (HALO_PF_HC != 0 && threadIdx.x == 0) {
+      const size_t rspan = static_cast<size_t>(kBlock >> lg) * (HC == 1 ? 1u : a.hc) * a.h;
+      prefetch_l2_span(static_cast<const RT*>(a.res) + blockIdx.x * rspan, static_cast<unsigned>(rspan * sizeof(RT)));
+      if constexpr (HC != 1) {
+        const size_t ospan = static_cast<size_t>(kBlock >> lg) * a.h;
+        prefetch_l2_span(static_cast<const OT*>(a.out) + blockIdx.x * ospan, static_cast<unsigned>(ospan * sizeof(OT)));
+      }
+    }
+  }
+  pdl_wait();
   __shared__ float red[kBlock / 32][HC];
   __shared__ float part[kBlock / 32][HC][8];
   const unsigned g = 1u << lg;

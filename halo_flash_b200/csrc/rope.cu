@@ -421,7 +421,7 @@ __device__ unsigned int g_stage_timeouts = 0;
 
 template <typename T, int K, bool ONEPLUS>
 __global__ void __launch_bounds__(kBlock, 4) norm_rope_staged_kernel(const RopeLeanArgs a) {
-  pdl_begin();
+  pdl_launch_dependents();
   extern __shared__ __align__(128) uint8_t rope_stage[];
   __shared__ __align__(8) unsigned long long bars[2];
   const unsigned lg = a.lg, g = 1u << lg;
@@ -433,19 +433,26 @@ __global__ void __launch_bounds__(kBlock, 4) norm_rope_staged_kernel(const RopeL
   const unsigned lane = threadIdx.x & 31u, lir = threadIdx.x & (g - 1), slot = threadIdx.x >> lg;
   const unsigned hp = a.rot >> 4;
 
-  if (threadIdx.x == 0) stage_init(bars, 2);
-  __syncthreads();
+  auto pass_src = [&](uint32_t p) {
+    const bool second = p >= a.ctas0;
+    return static_cast<const T*>(second ? a.in1 : a.in0) + static_cast<size_t>(second ? p - a.ctas0 : p) * pass_elems;
+  };
   // thread 0 asks the copy engine for pass `p` into buffer `b`
   auto request = [&](uint32_t p, unsigned b) {
-    const bool second = p >= a.ctas0;
-    const T* src = static_cast<const T*>(second ? a.in1 : a.in0) + static_cast<size_t>(second ? p - a.ctas0 : p) * pass_elems;
     const unsigned bar = smem_addr(&bars[b]);
     stage_expect(bar, pass_bytes);
-    stage_copy(smem_addr(bufs + b * pass_elems), src, pass_bytes, bar);
+    stage_copy(smem_addr(bufs + b * pass_elems), pass_src(p), pass_bytes, bar);
   };
   uint32_t p = blockIdx.x;
-  if (p >= a.tiles) return;  // uniform: the whole CTA has no pass
   const uint32_t stride = gridDim.x;
+  // before the wait for the kernel ahead: the barriers, and a hint to L2 for the CTA's first pass
+  if (threadIdx.x == 0) {
+    stage_init(bars, 2);
+    if (HALO_PF_ROPE_STAGED != 0 && p < a.tiles) prefetch_l2_span(pass_src(p), pass_bytes);
+  }
+  pdl_wait();
+  if (p >= a.tiles) return;  // uniform: the whole CTA has no pass
+  __syncthreads();
   if (threadIdx.x == 0) {
     request(p, 0);
     if (p + stride < a.tiles) request(p + stride, 1);
