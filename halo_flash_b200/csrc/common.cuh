@@ -72,6 +72,24 @@ __device__ __forceinline__ void pdl_begin() {
 #ifndef HALO_PF_HC
 #define HALO_PF_HC 1
 #endif
+#ifndef HALO_PF_CONV
+#define HALO_PF_CONV 1
+#endif
+// One-shot CTAs run in waves that load, then compute, in step with each other, so HBM idles while a wave computes.
+// With "prefetch ahead" a CTA, once its own loads are issued, hints to L2 the inputs of the CTA one wave of resident
+// CTAs later (148 SMs x resident CTAs per SM), which keeps HBM busy through the compute phase. Measured at 4096 /
+// 65 536 tokens: add + norm 11.4 -> 10.4 us / 158 -> 158; L2 norm 10.6 -> 9.9 / 156 -> 169 (worse: after a few
+// dozen waves the CTAs are out of step anyway and the hint only adds L2 traffic); gated norm 15.8 -> 14.8 /
+// 240 -> 235; SwiGLU 21.5 -> 21.8 / 314 -> 371; the Q8-epilogue norm 13.0 -> 13.4 / 165 -> 155. Hence: the plain
+// norm kernel does it for launches of up to kAheadMaxWaves waves, the gated norm always, the others never.
+#ifndef HALO_PF_AHEAD_NORM
+#define HALO_PF_AHEAD_NORM 1
+#endif
+#ifndef HALO_PF_AHEAD_GATED
+#define HALO_PF_AHEAD_GATED 1
+#endif
+constexpr unsigned kSms = 148;
+constexpr unsigned kAheadMaxWaves = 16;
 __device__ __forceinline__ void prefetch_l2_span(const void* p, unsigned bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
@@ -498,7 +516,8 @@ __device__ __forceinline__ float div127(float x) {
 // results of the IEEE division but (almost always) without dividing. t = v * rcp(d) is within
 // 2.3e-5 of the real quotient for |t| <= 127.5 and the correctly rounded quotient within 8e-6,
 // so whenever t is farther than 1e-4 from a rounding boundary (n + 0.5) both round to the same
-// integer. Rounding to nearest-even is the add of 1.5 * 2^23, whose low mantissa byte is the
+// integer. Rounding to nearest-even is the add of 1.5 * 2^23 (fused with the product: away from a boundary
+// the singly and the doubly rounded sums are the same integer), whose low mantissa byte is the
 // code. The fast path also skips the clamp: with |v| <= amax and d a normal half within 2^-11
 // of amax / 127 the quotient stays below 127.1. A thread redoes its 8 values with the division
 // and the clamp when one of them is within 1e-4 of a boundary (about 1 in 600) or is NaN (the
@@ -508,15 +527,17 @@ __device__ __forceinline__ float div127(float x) {
 __device__ __forceinline__ uint2 round_div_codes(const float (&v)[8], float d) {
   constexpr float kMagic = 12582912.0f;
   const float r = rcp_approx(d);
-  const float2 r2 = make_float2(r, r), magic2 = make_float2(kMagic, kMagic), neg2 = make_float2(-kMagic, -kMagic);
+  const float2 r2 = make_float2(r, r), magic2 = make_float2(kMagic, kMagic), minus2 = make_float2(-1.0f, -1.0f);
   uint32_t bits[8];
   float2 f[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float2 t = __fmul2_rn(make_float2(v[2 * i], v[2 * i + 1]), r2);
-    const float2 s = __fadd2_rn(t, magic2);
-    const float2 n = __fadd2_rn(s, neg2);
-    f[i] = __fadd2_rn(t, make_float2(-n.x, -n.y));
+    // three packed FMAs per pair: s = v r + magic (the rounding), -n = magic - s (exact), f = v r - n (the distance
+    // of the unrounded quotient from the integer it was rounded to, with a single rounding)
+    const float2 vv = make_float2(v[2 * i], v[2 * i + 1]);
+    const float2 s = __ffma2_rn(vv, r2, magic2);
+    const float2 nn = __ffma2_rn(s, minus2, magic2);
+    f[i] = __ffma2_rn(vv, r2, nn);
     bits[2 * i] = __float_as_uint(s.x);
     bits[2 * i + 1] = __float_as_uint(s.y);
   }

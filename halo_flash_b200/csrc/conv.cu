@@ -205,7 +205,7 @@ __device__ __forceinline__ void tile_rows(uint32_t t0, uint32_t tokens, uint32_t
 template <typename IT, typename OT, unsigned HL, int kTile>
 __global__ void __launch_bounds__(kBlock, 2) conv_l2norm_staged_kernel(const ConvArgs a, const uint32_t slices,
                                                                     const uint32_t token_tiles) {
-  pdl_begin();
+  pdl_launch_dependents();
   extern __shared__ __align__(128) uint8_t conv_smem[];
   __shared__ __align__(8) unsigned long long bars[2];
   const unsigned octs = a.channels >> 3;
@@ -219,7 +219,17 @@ __global__ void __launch_bounds__(kBlock, 2) conv_l2norm_staged_kernel(const Con
   IT* bufs = reinterpret_cast<IT*>(conv_smem);
   const unsigned row_bytes = slice_octs * 8u * static_cast<unsigned>(sizeof(IT));  // a multiple of 16
 
+  uint32_t by = lane_of_slice;
+  // before the wait for the kernel ahead: the barriers, and a hint to L2 for the rows of the CTA's first tile
   if (threadIdx.x == 0) stage_init(bars, 2);
+  if (HALO_PF_CONV != 0 && by < token_tiles) {
+    uint32_t first_row, last_row;
+    tile_rows<kTile>(by * kTile, a.tokens, &first_row, &last_row);
+    if (threadIdx.x < last_row - first_row)
+      prefetch_l2_span(static_cast<const IT*>(a.in) + static_cast<size_t>(by * kTile + first_row + threadIdx.x - 3u) * a.channels +
+                           (static_cast<size_t>(oc0) << 3), row_bytes);
+  }
+  pdl_wait();
   __syncthreads();
 
   // thread 0 asks the copy engine for the rows of token tile `by` into buffer `b`
@@ -235,7 +245,6 @@ __global__ void __launch_bounds__(kBlock, 2) conv_l2norm_staged_kernel(const Con
       stage_copy(dst, src, row_bytes, bar);
   };
 
-  uint32_t by = lane_of_slice;
   if (by >= token_tiles) return;  // uniform: the whole CTA has no tile
   if (threadIdx.x == 0) request(by, 0);
 

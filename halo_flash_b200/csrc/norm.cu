@@ -219,11 +219,13 @@ struct LeanArgs {
   int one_plus, l2;
   int stage_q8;  // Q8_0 blocks leave through shared memory as 16-byte stores (see the kernel)
   int keep_res;  // store the residual with the L2 keep policy (it is small enough to stay there)
+  uint32_t ahead;  // kernels without an epilogue: hint to L2 the rows of the CTA this many CTAs later (0 = none)
 };
 
 // WIDE: more than one warp per row (g > 32), the reduction crosses shared memory and a barrier.
 // MODE: 0 = w, y, one_plus and l2 are tested at run time; 1 = RMSNorm with gamma w into y;
-// 2 = the same with gamma 1 + w; 3 = L2 norm without gamma into y. The fixed modes exist because even warp-uniform tests
+// 2 = the same with gamma 1 + w; 3 = L2 norm without gamma into y; with EPI, 4 = RMSNorm with gamma 1 + w into y and
+// into staged Q8_0 blocks, 5 = the same without y. The fixed modes exist because even warp-uniform tests
 // cost these microsecond CTAs 3-4 % (12.6 vs 12.1 us on the add + norm of 4096 x 2048).
 // Everything after the loads of one row per thread group: (add, store the sum,) sum of squares, scale, gamma,
 // stores and Q8 epilogues. rx / rd hold the thread's K octets of x (and delta) as loaded; `row` is the group's row.
@@ -253,7 +255,8 @@ __device__ __forceinline__ void norm_lean_row(const LeanArgs& a, const Raw<XT> (
 #pragma unroll
     for (int k = 0; k < K; ++k) v[k] = raw_unpack(rx[k]);
   }
-  constexpr bool kLateGamma = MODE == 1 || MODE == 2 || (EPI && MODE == 0);  // gamma fetched per octet after the reduction: fewer live registers
+  constexpr bool kEpiFixed = EPI && (MODE == 4 || MODE == 5);  // gamma 1 + w, staged Q8_0 blocks, no int8 copy; y in mode 4 only
+  constexpr bool kLateGamma = MODE == 1 || MODE == 2 || EPI;  // gamma fetched per octet after the reduction: fewer live registers
   Oct gm[K];
   if (!kLateGamma && MODE != 3 && (MODE != 0 || a.w)) {  // fetched before the reduction: the L2 round trip overlaps the shuffles / barrier
 #pragma unroll
@@ -278,15 +281,15 @@ __device__ __forceinline__ void norm_lean_row(const LeanArgs& a, const Raw<XT> (
     if constexpr (kLateGamma) {
       if (MODE != 0 || a.w) {
         gm[k] = oct_load_cached(a.w + (j << 3));
-        if (MODE == 2 || (MODE == 0 && a.one_plus)) {
+        if (MODE == 2 || kEpiFixed || (MODE == 0 && a.one_plus)) {
           const float2 one = make_float2(1.0f, 1.0f);
 #pragma unroll
           for (int i = 0; i < 4; ++i) gm[k].p[i] = __fadd2_rn(one, gm[k].p[i]);
         }
       }
     }
-    if (MODE == 1 || MODE == 2 || (MODE == 0 && a.w)) v[k] = oct_mul(v[k], gm[k]);
-    if (MODE != 0 || a.y) oct_store(static_cast<YT*>(a.y) + off + (j << 3), v[k]);
+    if (MODE == 1 || MODE == 2 || kEpiFixed || (MODE == 0 && a.w)) v[k] = oct_mul(v[k], gm[k]);
+    if (MODE == 5 ? false : (MODE != 0 || a.y)) oct_store(static_cast<YT*>(a.y) + off + (j << 3), v[k]);
   }
   if constexpr (EPI) {
     // The K octets go through the epilogue phase by phase, not one after the other: their block maxima,
@@ -302,12 +305,12 @@ __device__ __forceinline__ void norm_lean_row(const LeanArgs& a, const Raw<XT> (
 #pragma unroll
     for (int k = 0; k < K; ++k) amax[k] = fmaxf(amax[k], __shfl_xor_sync(kFullMask, amax[k], 2));
     const unsigned lane = threadIdx.x & 31u;
-    if (a.q8_0) {
+    if (kEpiFixed || a.q8_0) {
       uint16_t dbits[K];
       uint2 codes[K];
 #pragma unroll
       for (int k = 0; k < K; ++k) codes[k] = q8_0_codes(arr[k], amax[k], &dbits[k]);
-      if (a.stage_q8) {
+      if (kEpiFixed || a.stage_q8) {
 #pragma unroll
         for (int k = 0; k < K; ++k) {
           uint8_t* sb = stage[threadIdx.x >> 5][k] + (lane >> 2) * 34;
@@ -334,7 +337,7 @@ __device__ __forceinline__ void norm_lean_row(const LeanArgs& a, const Raw<XT> (
         }
       }
     }
-    if (a.xq) {
+    if (!kEpiFixed && a.xq) {
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         const uint32_t c0 = ((k << lg) + lir) << 3;
@@ -377,6 +380,14 @@ __global__ void __launch_bounds__(kBlock, K > 2 ? (sizeof(XT) == 2 ? 4 : 1) : (!
     const XT* dl = static_cast<const XT*>(a.delta) + off;
 #pragma unroll
     for (int k = 0; k < K; ++k) rd[k] = raw_load(dl + (((k << lg) + lir) << 3));
+  }
+  if constexpr (!EPI && HALO_PF_AHEAD_NORM != 0) {
+    if (threadIdx.x == 0 && a.ahead != 0 && blockIdx.x + a.ahead < gridDim.x) {
+      const size_t span = static_cast<size_t>(kBlock >> lg) * a.d;
+      prefetch_l2_span(static_cast<const XT*>(a.x) + (blockIdx.x + a.ahead) * span, static_cast<unsigned>(span * sizeof(XT)));
+      if constexpr (ADD)
+        prefetch_l2_span(static_cast<const XT*>(a.delta) + (blockIdx.x + a.ahead) * span, static_cast<unsigned>(span * sizeof(XT)));
+    }
   }
   norm_lean_row<XT, YT, K, ADD, EPI, WIDE, MODE>(a, rx, rd, row, scratch, stage);
 }
@@ -581,6 +592,14 @@ __global__ void __launch_bounds__(kBlock) gated_norm_lean_kernel(const GatedLean
   const size_t off = static_cast<size_t>(row) * a.d + (lir << 3);
   const Raw<OT> ro = raw_load(static_cast<const OT*>(a.o) + off);
   const Raw<ZT> rz = raw_load(static_cast<const ZT*>(a.z) + off);
+  constexpr unsigned kAhead = HALO_PF_AHEAD_GATED * kSms * 8u;
+  if constexpr (kAhead != 0) {
+    if (threadIdx.x == 0 && blockIdx.x + kAhead < gridDim.x) {
+      const size_t span = static_cast<size_t>(kBlock >> lg) * a.d;
+      prefetch_l2_span(static_cast<const OT*>(a.o) + (blockIdx.x + kAhead) * span, static_cast<unsigned>(span * sizeof(OT)));
+      prefetch_l2_span(static_cast<const ZT*>(a.z) + (blockIdx.x + kAhead) * span, static_cast<unsigned>(span * sizeof(ZT)));
+    }
+  }
   const Oct gm = oct_load_cached(a.w + (lir << 3));
   const Oct v = raw_unpack(ro);
   Oct zz = raw_unpack(rz);
@@ -676,7 +695,9 @@ Shape PickShape(unsigned octs, unsigned rows, int want_g, unsigned min_g, int wa
 
 template <typename XT, typename YT, int K, bool ADD, bool WIDE>
 void LaunchLeanMode(const LeanArgs& l, bool epi, int mode, unsigned grid, cudaStream_t s) {
-  if (epi) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 0>, grid, kBlock, 0, s, l);
+  if (epi && mode == 4) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 4>, grid, kBlock, 0, s, l);
+  else if (epi && mode == 5) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 5>, grid, kBlock, 0, s, l);
+  else if (epi) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 0>, grid, kBlock, 0, s, l);
   else if (mode == 2) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, WIDE, 2>, grid, kBlock, 0, s, l);
   else if (mode == 1) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, WIDE, 1>, grid, kBlock, 0, s, l);
   else if (mode == 3) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, WIDE, 3>, grid, kBlock, 0, s, l);
@@ -707,7 +728,13 @@ cudaError_t LaunchLean(const NormArgs& a, const Shape& sh, unsigned grid, cudaSt
   // a warp's 32 octets must be consecutive in the output: rows of at least a warp, or one octet per thread
   l.stage_q8 = a.q8_0 && (reinterpret_cast<uintptr_t>(a.q8_0) & 15u) == 0 && (sh.lg >= 5 || K == 1);
   const bool epi = a.q8_0 || a.xq;
-  const int mode = (!epi && a.w && a.y && !a.l2) ? (a.one_plus ? 2 : 1) : (!epi && !a.w && a.y && a.l2) ? 3 : 0;
+  // one wave of resident CTAs (the kernel's launch bounds), for launches short enough to run in step (see common.cuh)
+  const unsigned wave = kSms * ((K > 2 || sizeof(XT) == 4) ? 4u : 6u);
+  l.ahead = (!epi && grid <= kAheadMaxWaves * wave) ? wave : 0u;
+  const int mode = (!epi && a.w && a.y && !a.l2)    ? (a.one_plus ? 2 : 1)
+                   : (!epi && !a.w && a.y && a.l2) ? 3
+                   : (epi && a.w && a.one_plus && !a.l2 && l.stage_q8 && !a.xq) ? (a.y ? 4 : 5)
+                                                                                  : 0;
   if constexpr (K <= 2) {  // rows wider than a warp per row exist only with one or two octets per thread
     if (sh.lg > 5) {
       LaunchLeanMode<XT, YT, K, ADD, true>(l, epi, mode, grid, s);
