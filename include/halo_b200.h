@@ -28,6 +28,12 @@
  *     operation); (3) the process-wide tuning switches of halo_b200_tune (host atomics,
  *     for experiments; production code never needs to touch them). Everything else is
  *     stateless and re-entrant.
+ *   - Ordering: kernels are launched with programmatic stream serialization. A kernel reads
+ *     and writes memory only after the kernel ahead of it in the stream has completed; while
+ *     it waits for that it may already ask L2 to prefetch the input rows it was given (a hint
+ *     by address, no data is consumed). Every input pointer must therefore be a mapped device
+ *     address when the call is made, as any kernel argument must; its contents may still be
+ *     produced by earlier work in the stream.
  *   - In-place use is allowed wherever the reference kernel works in place.
  *   - Buffers that are 16-byte aligned with row lengths that are multiples of 8
  *     elements take the vector kernels; anything else takes a slower scalar

@@ -733,10 +733,13 @@ def test_full_size_prefill_properties(orc):
     assert np.array_equal(bits16(emb[pick]), oracle.bf16_bits(wante))
 
 
-def test_lean_and_general_norm_kernels_agree_bit_for_bit():
-    """The lean kernel (dense, full grid) and the general kernel compute the same bits."""
+@pytest.mark.parametrize("rows", [64, 1778, 28416, 28418])
+def test_lean_and_general_norm_kernels_agree_bit_for_bit(rows):
+    """The lean kernel (dense, full grid) and the general kernel compute the same bits. The row counts sit on the
+    lean kernels' launch-shape boundaries: 64 rows fit one wave of resident CTAs, 1778 rows of 2048 are one CTA more
+    than a wave (the first CTA then hints its successor's rows to L2), 28 416 rows are exactly sixteen waves (the
+    longest launch that still does so) and 28 418 one CTA more."""
     s = synth.FULL
-    rows = 64
     res, delta = to_dev(synth.act("t.lg.res", rows, s.hidden), "bf16"), to_dev(synth.act("t.lg.delta", rows, s.hidden), "bf16")
     w = to_dev(synth.norm_w("t.lg.w", s.hidden))
     outs = []
@@ -747,12 +750,15 @@ def test_lean_and_general_norm_kernels_agree_bit_for_bit():
             xn = torch.empty_like(r)
             q8 = torch.empty(rows, s.q8_row_bytes, dtype=torch.uint8, device=DEV)
             ops.add_rmsnorm(r, delta, w, s.eps, xn=xn, q8_0=q8)
-            qk = to_dev(synth.act("t.lg.qk", rows * 32, s.lin_dim), "bf16")
+            heads = 32 if rows <= 2048 else 2  # the one-head rows: 2048 of them and more already span several waves
+            qk = to_dev(synth.act("t.lg.qk", rows * heads, s.lin_dim), "bf16")
             ops.l2norm(qk, s.eps)
-            o = to_dev(synth.act("t.lg.o", rows * 32, s.lin_dim), "bf16")
-            z = to_dev(synth.act("t.lg.z", rows * 32, s.lin_dim), "bf16")
+            o = to_dev(synth.act("t.lg.o", rows * heads, s.lin_dim), "bf16")
+            z = to_dev(synth.act("t.lg.z", rows * heads, s.lin_dim), "bf16")
             ops.gated_norm(o, to_dev(synth.gated_w("t.lg.gw", s.lin_dim)), z, s.eps)
-            outs.append((r, xn, q8, qk, o))
+            r2, xn2 = res.clone(), torch.empty_like(res)
+            ops.add_rmsnorm(r2, delta, w, s.eps, xn=xn2)  # the kernel without an epilogue
+            outs.append((r, xn, q8, qk, o, r2, xn2))
         finally:
             lib().tune("norm_force_general", 0)
     for a, b in zip(*outs):
