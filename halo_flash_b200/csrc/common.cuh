@@ -75,6 +75,9 @@ __device__ __forceinline__ void pdl_begin() {
 #ifndef HALO_PF_CONV
 #define HALO_PF_CONV 1
 #endif
+#ifndef HALO_PF_MOE
+#define HALO_PF_MOE 1
+#endif
 // One-shot CTAs run in waves that load, then compute, in step with each other, so HBM idles while a wave computes.
 // With "prefetch ahead" a CTA, once its own loads are issued, hints to L2 the inputs of the CTA one wave of resident
 // CTAs later (148 SMs x resident CTAs per SM), which keeps HBM busy through the compute phase. Measured at 4096 /

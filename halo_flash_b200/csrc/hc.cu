@@ -164,7 +164,7 @@ __global__ void __launch_bounds__(kBlock, HcMinCtas(HC* K, sizeof(RT)))
       // slots in order, then the shared expert: out += weight * down (reference.cpp:558-578)
       const uint32_t* pp = a.pos + static_cast<size_t>(t) * a.k;
       const float* ww = a.mw + static_cast<size_t>(t) * a.k;
-#pragma unroll 2
+#pragma unroll(K == 1 ? 2 : 5)
       for (uint32_t slot = 0; slot < a.k; ++slot) {
         const OT* yr = static_cast<const OT*>(a.yp) + static_cast<size_t>(pp[slot]) * a.h;
         const float ws = ww[slot];
@@ -749,8 +749,11 @@ cudaError_t LaunchHcEltT(const HcEltArgs& a, cudaStream_t s) {
 // One thread per octet of a token's n columns; the k expert rows of the token are requested together (up to
 // 16 loads in flight per thread), then summed in slot order with the product and the sum rounded
 // separately, then the gated shared expert is added (src/model/reference.cpp:558-578).
-template <typename YT, typename OT>
-__global__ void __launch_bounds__(kBlock, sizeof(YT) == 2 ? 4 : 2) moe_combine_kernel(const MoeCombineArgs a, const uint32_t chunks) {
+// KR: expert rows in flight per thread; EXACT: k is a multiple of KR, so no slot of the unrolled batches is
+// predicated (with k = 10 in batches of 8 the second batch issued eight slots' instructions for two rows: 22.7 M
+// warp instructions per 4096 tokens, half of them predicated off).
+template <typename YT, typename OT, int KR, bool EXACT>
+__global__ void __launch_bounds__(kBlock, sizeof(YT) == 2 ? 4 : 2) moe_combine_kernel(const MoeCombineArgs a, const uint32_t chunks, const uint32_t ahead) {
   pdl_begin();
   __shared__ float gate;
   const uint32_t t = blockIdx.x / chunks, chunk = blockIdx.x - t * chunks;
@@ -759,30 +762,50 @@ __global__ void __launch_bounds__(kBlock, sizeof(YT) == 2 ? 4 : 2) moe_combine_k
     if (threadIdx.x == 0) gate = sigmoid_ieee(a.sg[t]);
     __syncthreads();
   }
+  // One wave of resident CTAs ahead: thread s < k looks up expert row s of the token `ahead` tokens later now, and
+  // hints this CTA's chunk of it to L2 once the CTA's own loads are on their way (below). A gather is two dependent
+  // round trips (index, then row) per one-shot CTA, and CTAs that start together wait together; the hint turns the
+  // second trip of the later CTA into an L2 hit and keeps HBM busy meanwhile.
+  const uint32_t t_ahead = t + ahead;
+  const bool hint = HALO_PF_MOE != 0 && ahead != 0 && threadIdx.x <= a.k && t_ahead < a.tokens;
+  size_t row_ahead = 0;
+  if (hint && threadIdx.x < a.k)
+    row_ahead = a.pos ? a.pos[static_cast<size_t>(t_ahead) * a.k + threadIdx.x] : static_cast<size_t>(t_ahead) * a.k + threadIdx.x;
   if (j >= (a.n >> 3)) return;
   const YT* yp = static_cast<const YT*>(a.yp) + j * 8;
   const float* ww = a.mw + static_cast<size_t>(t) * a.k;
   Oct acc = oct_zero();
   OT* out = static_cast<OT*>(a.out) + static_cast<size_t>(t) * a.n + j * 8;
   if (a.accumulate) acc = oct_load(out);
-  // Eight expert rows in flight per thread (128 bytes of 16-bit rows): with sixteen the kernel held 89 registers
-  // and two CTAs per SM, and spent its time waiting on the index -> row dependency with too little in flight.
-  constexpr int kRows = 8;
+  // At most eight expert rows in flight per thread (128 bytes of 16-bit rows): with sixteen the kernel held 89
+  // registers and two CTAs per SM, and spent its time waiting on the index -> row dependency with too little in flight.
+  constexpr int kRows = KR;
   for (uint32_t s0 = 0; s0 < a.k; s0 += kRows) {
     Raw<YT> rows[kRows];
     float wv[kRows];
 #pragma unroll
     for (int u = 0; u < kRows; ++u) {
       const uint32_t s = s0 + u;
-      if (s < a.k) {
+      if (EXACT || s < a.k) {
         const size_t r = a.pos ? a.pos[static_cast<size_t>(t) * a.k + s] : static_cast<size_t>(t) * a.k + s;
         rows[u] = raw_load(yp + r * a.n);
         wv[u] = ww[s];
       }
     }
+    if (s0 == 0 && hint) {  // the chunk's span of the row: 16-byte aligned, a multiple of 16 bytes (n % 8 == 0)
+      const unsigned c0 = chunk * kBlock * 8u;
+      const unsigned elems = a.n - c0 < kBlock * 8u ? a.n - c0 : kBlock * 8u;
+      if (threadIdx.x < a.k) {
+        prefetch_l2_span(static_cast<const YT*>(a.yp) + row_ahead * a.n + c0, elems * static_cast<unsigned>(sizeof(YT)));
+      } else if (a.sx) {
+        const size_t off = static_cast<size_t>(t_ahead) * a.n + c0;
+        if (a.sx_is_f32) prefetch_l2_span(static_cast<const float*>(a.sx) + off, elems * 4u);
+        else prefetch_l2_span(static_cast<const YT*>(a.sx) + off, elems * static_cast<unsigned>(sizeof(YT)));
+      }
+    }
 #pragma unroll
     for (int u = 0; u < kRows; ++u)
-      if (s0 + u < a.k) acc = oct_axpy_unfused(acc, raw_unpack(rows[u]), wv[u]);
+      if (EXACT || s0 + u < a.k) acc = oct_axpy_unfused(acc, raw_unpack(rows[u]), wv[u]);
   }
   if (a.sx) {
     const size_t off = static_cast<size_t>(t) * a.n + j * 8;
@@ -817,7 +840,14 @@ template <typename YT, typename OT>
 cudaError_t LaunchMoeCombineT(const MoeCombineArgs& a, cudaStream_t s) {
   if (a.vec) {
     const uint32_t chunks = (a.n / 8 + kBlock - 1) / kBlock;
-    return LaunchKernel(moe_combine_kernel<YT, OT>, a.tokens * chunks, kBlock, 0, s, a, chunks);
+    // tokens in one wave of resident CTAs (the kernel's launch bounds: 4 CTAs per SM for 16-bit rows, 2 for fp32)
+    const uint32_t ahead = (kSms * (sizeof(YT) == 2 ? 4u : 2u) + chunks - 1) / chunks;
+    const unsigned grid = a.tokens * chunks;
+    if (a.k % 8 == 0) return LaunchKernel(moe_combine_kernel<YT, OT, 8, true>, grid, kBlock, 0, s, a, chunks, ahead);
+    if (a.k % 5 == 0) return LaunchKernel(moe_combine_kernel<YT, OT, 5, true>, grid, kBlock, 0, s, a, chunks, ahead);
+    if (a.k % 6 == 0) return LaunchKernel(moe_combine_kernel<YT, OT, 6, true>, grid, kBlock, 0, s, a, chunks, ahead);
+    if (a.k % 4 == 0) return LaunchKernel(moe_combine_kernel<YT, OT, 4, true>, grid, kBlock, 0, s, a, chunks, ahead);
+    return LaunchKernel(moe_combine_kernel<YT, OT, 8, false>, grid, kBlock, 0, s, a, chunks, ahead);
   }
   size_t grid = (static_cast<size_t>(a.tokens) * a.n + kBlock - 1) / kBlock;
   if (grid > 148u * 32u) grid = 148u * 32u;
