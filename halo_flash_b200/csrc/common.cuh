@@ -52,13 +52,15 @@ __device__ __forceinline__ void pdl_begin() {
 // update the line in L2). What it buys: the CTAs that sit in griddepcontrol.wait while the kernel ahead drains
 // do not all leave it into an empty memory pipeline - their first loads find L2. Measured on 4096-token launches:
 // SwiGLU 22.4 -> 21.5 us, gated norm 16.5 -> 15.7, add + norm 11.7 -> 11.4, hyper-connection combine 37.8 -> 34.4.
-// Which kernels do it is decided per kernel at compile time: the Q8-epilogue norm kernel lost 7 - 12 % from
-// the mere presence of the preamble (its schedule is tight at 48 registers x 5 CTAs), so it has none.
+// Which kernels do it is decided per kernel at compile time, because the preamble is not free: the general form of the
+// Q8-epilogue norm kernel (all outputs tested at run time, 44 - 48 registers x 5 CTAs) lost 7 - 12 % from its mere
+// presence, and launches of a few rows (decode) gain nothing from a hint. The epilogue kernel's fixed modes (40 - 45
+// registers) do gain - 12.3 -> 11.0 us at 4096 tokens with both hints - and are compiled with and without them.
 #ifndef HALO_PF_NORM
 #define HALO_PF_NORM 1
 #endif
 #ifndef HALO_PF_NORM_EPI
-#define HALO_PF_NORM_EPI 0
+#define HALO_PF_NORM_EPI 1
 #endif
 #ifndef HALO_PF_GATED
 #define HALO_PF_GATED 1
@@ -83,8 +85,9 @@ __device__ __forceinline__ void pdl_begin() {
 // CTAs later (148 SMs x resident CTAs per SM), which keeps HBM busy through the compute phase. Measured at 4096 /
 // 65 536 tokens: add + norm 11.4 -> 10.4 us / 158 -> 158; L2 norm 10.6 -> 9.9 / 156 -> 169 (worse: after a few
 // dozen waves the CTAs are out of step anyway and the hint only adds L2 traffic); gated norm 15.8 -> 14.8 /
-// 240 -> 235; SwiGLU 21.5 -> 21.8 / 314 -> 371; the Q8-epilogue norm 13.0 -> 13.4 / 165 -> 155. Hence: the plain
-// norm kernel does it for launches of up to kAheadMaxWaves waves, the gated norm always, the others never.
+// 240 -> 235; SwiGLU 21.5 -> 21.8 / 314 -> 371; the Q8-epilogue norm in its fixed modes 12.4 -> 11.0 (with the hint
+// before the wait; 13.6 without it) / no change. Hence: the norm kernels do it for launches of up to kAheadMaxWaves
+// waves, the gated norm always, the others never.
 #ifndef HALO_PF_AHEAD_NORM
 #define HALO_PF_AHEAD_NORM 1
 #endif

@@ -349,10 +349,13 @@ __device__ __forceinline__ void norm_lean_row(const LeanArgs& a, const Raw<XT> (
   }
 }
 
-template <typename XT, typename YT, int K, bool ADD, bool EPI, bool WIDE, int MODE>
+// HINTS (epilogue kernels only; the others follow HALO_PF_NORM / HALO_PF_AHEAD_NORM): compile the L2 hints in. The
+// epilogue kernels exist with and without them, because a launch of a few rows (decode) gains nothing from a hint and
+// pays for the preamble (319.8 -> 333.0 us per 230-launch decode step when every Q8_0 add + norm carried it).
+template <typename XT, typename YT, int K, bool ADD, bool EPI, bool WIDE, int MODE, bool HINTS = false>
 __global__ void __launch_bounds__(kBlock, K > 2 ? (sizeof(XT) == 2 ? 4 : 1) : (!EPI && MODE != 0 && sizeof(XT) == 2) ? 6 : (EPI && sizeof(XT) == 2) ? HALO_EPI_CTAS : 1) norm_rows_lean_kernel(const LeanArgs a) {
   pdl_launch_dependents();
-  if constexpr (EPI ? HALO_PF_NORM_EPI != 0 : HALO_PF_NORM != 0) {
+  if constexpr (EPI ? HINTS : HALO_PF_NORM != 0) {
     if (threadIdx.x == 0) {  // the CTA's rows are one contiguous span per tensor
       const size_t span = static_cast<size_t>(kBlock >> a.lg) * a.d;
       prefetch_l2_span(static_cast<const XT*>(a.x) + blockIdx.x * span, static_cast<unsigned>(span * sizeof(XT)));
@@ -381,7 +384,7 @@ __global__ void __launch_bounds__(kBlock, K > 2 ? (sizeof(XT) == 2 ? 4 : 1) : (!
 #pragma unroll
     for (int k = 0; k < K; ++k) rd[k] = raw_load(dl + (((k << lg) + lir) << 3));
   }
-  if constexpr (!EPI && HALO_PF_AHEAD_NORM != 0) {
+  if constexpr (EPI ? HINTS : HALO_PF_AHEAD_NORM != 0) {
     if (threadIdx.x == 0 && a.ahead != 0 && blockIdx.x + a.ahead < gridDim.x) {
       const size_t span = static_cast<size_t>(kBlock >> lg) * a.d;
       prefetch_l2_span(static_cast<const XT*>(a.x) + (blockIdx.x + a.ahead) * span, static_cast<unsigned>(span * sizeof(XT)));
@@ -695,7 +698,12 @@ Shape PickShape(unsigned octs, unsigned rows, int want_g, unsigned min_g, int wa
 
 template <typename XT, typename YT, int K, bool ADD, bool WIDE>
 void LaunchLeanMode(const LeanArgs& l, bool epi, int mode, unsigned grid, cudaStream_t s) {
-  if (epi && mode == 4) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 4>, grid, kBlock, 0, s, l);
+  // the fixed epilogue modes on 16-bit rows carry the L2 hints in launches that give every SM a CTA and are short
+  // enough for the look-ahead (beyond that the unhinted kernel measured 2 % faster: 154 against 157 us at 65 536 tokens)
+  const bool hints = HALO_PF_NORM_EPI != 0 && sizeof(XT) == 2 && grid >= kSms && l.ahead != 0;
+  if (epi && mode == 4 && hints) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 4, true>, grid, kBlock, 0, s, l);
+  else if (epi && mode == 5 && hints) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 5, true>, grid, kBlock, 0, s, l);
+  else if (epi && mode == 4) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 4>, grid, kBlock, 0, s, l);
   else if (epi && mode == 5) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 5>, grid, kBlock, 0, s, l);
   else if (epi) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 0>, grid, kBlock, 0, s, l);
   else if (mode == 2) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, WIDE, 2>, grid, kBlock, 0, s, l);
@@ -730,7 +738,7 @@ cudaError_t LaunchLean(const NormArgs& a, const Shape& sh, unsigned grid, cudaSt
   const bool epi = a.q8_0 || a.xq;
   // one wave of resident CTAs (the kernel's launch bounds), for launches short enough to run in step (see common.cuh)
   const unsigned wave = kSms * ((K > 2 || sizeof(XT) == 4) ? 4u : 6u);
-  l.ahead = (!epi && grid <= kAheadMaxWaves * wave) ? wave : 0u;
+  l.ahead = grid <= kAheadMaxWaves * wave ? wave : 0u;  // read by the kernels that carry the hints
   const int mode = (!epi && a.w && a.y && !a.l2)    ? (a.one_plus ? 2 : 1)
                    : (!epi && !a.w && a.y && a.l2) ? 3
                    : (epi && a.w && a.one_plus && !a.l2 && l.stage_q8 && !a.xq) ? (a.y ? 4 : 5)
