@@ -293,6 +293,10 @@ def op_specs(torch, shapes, T: int):
         "add_rmsnorm_q8": (lambda: (r(T, s.hidden), r(T, s.hidden),
                                     torch.empty(T, s.q8_row_bytes, device=dev, dtype=torch.uint8)),
                            lambda b: ops.add_rmsnorm(b[0], b[1], w_h, s.eps, q8_0=b[2])),
+        # not in the chain: the same with the reference's int8 activation form (codes + one fp32 scale per 32 values)
+        "add_rmsnorm_i8": (lambda: (r(T, s.hidden), r(T, s.hidden), torch.empty(T, s.hidden, device=dev, dtype=torch.int8),
+                                    torch.empty(T, s.hidden // 32, device=dev)),
+                           lambda b: ops.add_rmsnorm(b[0], b[1], w_h, s.eps, xq=b[2], xd=b[3])),
         # not in the chain: Flash-Next's form of the residual op, 4 residual streams per token
         "hc_combine_norm": (lambda: (r(T, 4, s.hidden), r(T, s.hidden), torch.randn(T, 4, device=dev),
                                      torch.empty(T, 4, s.hidden, device=dev, dtype=bf)),
@@ -310,6 +314,7 @@ def op_specs(torch, shapes, T: int):
     nbytes = {"add_rmsnorm": bpt["add_rmsnorm"], "moe_combine": k * 2 * s.hidden + 2 * 4 * s.hidden + 8 * k + 4, "l2norm": bpt["l2norm"], "gated_norm": bpt["gated_norm"],
               "norm_rope_qk": bpt["norm_rope"], "swiglu_moe": bpt["swiglu_shared"] + bpt["swiglu_routed"],
               "embed": bpt["embed"], "add_rmsnorm_q8": 3 * 2 * s.hidden + s.q8_row_bytes,
+              "add_rmsnorm_i8": 3 * 2 * s.hidden + s.hidden + 4 * (s.hidden // 32),
               "hc_combine_norm": (3 * 4 + 1) * 2 * s.hidden + 16,
               "conv_l2norm": 2 * 2 * (2 * s.k_heads + s.v_heads) * s.lin_dim}  # read x, write out  # read + write res, write y (4 streams), read out, logits
     return specs, {k_: v * T for k_, v in nbytes.items()}
@@ -735,7 +740,7 @@ def main() -> None:
     ap.add_argument("--no-pdl", action="store_true", help="plain stream-ordered launches (no programmatic dependent launch)")
     ap.add_argument("--decode-batch", type=int, default=0, help="time the decode form of the chain for batch 1 .. B and exit")
     ap.add_argument("--profile-op", default=None, help="run 6 eager launches of one op and exit (profiler captures): "
-                    "add_rmsnorm, add_rmsnorm_q8, l2norm, gated_norm, norm_rope_qk, swiglu_moe, embed, hc_combine_norm, conv_l2norm, moe_combine")
+                    "add_rmsnorm, add_rmsnorm_q8, add_rmsnorm_i8, l2norm, gated_norm, norm_rope_qk, swiglu_moe, embed, hc_combine_norm, conv_l2norm, moe_combine")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
                     help="set one of the library's experiment switches (halo_b200_tune) before anything runs; repeatable")
     args = ap.parse_args()

@@ -225,7 +225,8 @@ struct LeanArgs {
 // WIDE: more than one warp per row (g > 32), the reduction crosses shared memory and a barrier.
 // MODE: 0 = w, y, one_plus and l2 are tested at run time; 1 = RMSNorm with gamma w into y;
 // 2 = the same with gamma 1 + w; 3 = L2 norm without gamma into y; with EPI, 4 = RMSNorm with gamma 1 + w into y and
-// into staged Q8_0 blocks, 5 = the same without y. The fixed modes exist because even warp-uniform tests
+// into staged Q8_0 blocks, 5 = the same without y, 6 / 7 = the same two with int8 codes + fp32 block scales instead of the
+// Q8_0 blocks. The fixed modes exist because even warp-uniform tests
 // cost these microsecond CTAs 3-4 % (12.6 vs 12.1 us on the add + norm of 4096 x 2048).
 // Everything after the loads of one row per thread group: (add, store the sum,) sum of squares, scale, gamma,
 // stores and Q8 epilogues. rx / rd hold the thread's K octets of x (and delta) as loaded; `row` is the group's row.
@@ -255,7 +256,9 @@ __device__ __forceinline__ void norm_lean_row(const LeanArgs& a, const Raw<XT> (
 #pragma unroll
     for (int k = 0; k < K; ++k) v[k] = raw_unpack(rx[k]);
   }
-  constexpr bool kEpiFixed = EPI && (MODE == 4 || MODE == 5);  // gamma 1 + w, staged Q8_0 blocks, no int8 copy; y in mode 4 only
+  constexpr bool kEpiQ8 = EPI && (MODE == 4 || MODE == 5);  // gamma 1 + w, staged Q8_0 blocks, no int8 copy; y in mode 4 only
+  constexpr bool kEpiI8 = EPI && (MODE == 6 || MODE == 7);  // gamma 1 + w, int8 codes + fp32 scales, no Q8_0 blocks; y in mode 6 only
+  constexpr bool kEpiFixed = kEpiQ8 || kEpiI8;
   constexpr bool kLateGamma = MODE == 1 || MODE == 2 || EPI;  // gamma fetched per octet after the reduction: fewer live registers
   Oct gm[K];
   if (!kLateGamma && MODE != 3 && (MODE != 0 || a.w)) {  // fetched before the reduction: the L2 round trip overlaps the shuffles / barrier
@@ -289,7 +292,7 @@ __device__ __forceinline__ void norm_lean_row(const LeanArgs& a, const Raw<XT> (
       }
     }
     if (MODE == 1 || MODE == 2 || kEpiFixed || (MODE == 0 && a.w)) v[k] = oct_mul(v[k], gm[k]);
-    if (MODE == 5 ? false : (MODE != 0 || a.y)) oct_store(static_cast<YT*>(a.y) + off + (j << 3), v[k]);
+    if ((MODE == 5 || MODE == 7) ? false : (MODE != 0 || a.y)) oct_store(static_cast<YT*>(a.y) + off + (j << 3), v[k]);
   }
   if constexpr (EPI) {
     // The K octets go through the epilogue phase by phase, not one after the other: their block maxima,
@@ -305,12 +308,12 @@ __device__ __forceinline__ void norm_lean_row(const LeanArgs& a, const Raw<XT> (
 #pragma unroll
     for (int k = 0; k < K; ++k) amax[k] = fmaxf(amax[k], __shfl_xor_sync(kFullMask, amax[k], 2));
     const unsigned lane = threadIdx.x & 31u;
-    if (kEpiFixed || a.q8_0) {
+    if (kEpiQ8 || (!kEpiI8 && a.q8_0)) {
       uint16_t dbits[K];
       uint2 codes[K];
 #pragma unroll
       for (int k = 0; k < K; ++k) codes[k] = q8_0_codes(arr[k], amax[k], &dbits[k]);
-      if (kEpiFixed || a.stage_q8) {
+      if (kEpiQ8 || a.stage_q8) {
 #pragma unroll
         for (int k = 0; k < K; ++k) {
           uint8_t* sb = stage[threadIdx.x >> 5][k] + (lane >> 2) * 34;
@@ -337,7 +340,7 @@ __device__ __forceinline__ void norm_lean_row(const LeanArgs& a, const Raw<XT> (
         }
       }
     }
-    if (!kEpiFixed && a.xq) {
+    if (kEpiI8 || (!kEpiQ8 && a.xq)) {
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         const uint32_t c0 = ((k << lg) + lir) << 3;
@@ -703,8 +706,12 @@ void LaunchLeanMode(const LeanArgs& l, bool epi, int mode, unsigned grid, cudaSt
   const bool hints = HALO_PF_NORM_EPI != 0 && sizeof(XT) == 2 && grid >= kSms && l.ahead != 0;
   if (epi && mode == 4 && hints) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 4, true>, grid, kBlock, 0, s, l);
   else if (epi && mode == 5 && hints) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 5, true>, grid, kBlock, 0, s, l);
+  else if (epi && mode == 6 && hints) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 6, true>, grid, kBlock, 0, s, l);
+  else if (epi && mode == 7 && hints) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 7, true>, grid, kBlock, 0, s, l);
   else if (epi && mode == 4) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 4>, grid, kBlock, 0, s, l);
   else if (epi && mode == 5) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 5>, grid, kBlock, 0, s, l);
+  else if (epi && mode == 6) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 6>, grid, kBlock, 0, s, l);
+  else if (epi && mode == 7) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 7>, grid, kBlock, 0, s, l);
   else if (epi) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, true, WIDE, 0>, grid, kBlock, 0, s, l);
   else if (mode == 2) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, WIDE, 2>, grid, kBlock, 0, s, l);
   else if (mode == 1) LaunchKernel(norm_rows_lean_kernel<XT, YT, K, ADD, false, WIDE, 1>, grid, kBlock, 0, s, l);
@@ -742,6 +749,7 @@ cudaError_t LaunchLean(const NormArgs& a, const Shape& sh, unsigned grid, cudaSt
   const int mode = (!epi && a.w && a.y && !a.l2)    ? (a.one_plus ? 2 : 1)
                    : (!epi && !a.w && a.y && a.l2) ? 3
                    : (epi && a.w && a.one_plus && !a.l2 && l.stage_q8 && !a.xq) ? (a.y ? 4 : 5)
+                   : (epi && a.w && a.one_plus && !a.l2 && !a.q8_0 && a.xq)     ? (a.y ? 6 : 7)
                                                                                   : 0;
   if constexpr (K <= 2) {  // rows wider than a warp per row exist only with one or two octets per thread
     if (sh.lg > 5) {
