@@ -388,9 +388,27 @@ __global__ void __launch_bounds__(kBlock) hc_combine_norm_scalar_kernel(const Hc
 // per CTA and each [h] row is loaded once however many streams use it.
 template <typename AT, typename BT, int OP>
 __global__ void __launch_bounds__(kBlock) hc_elt_vec_kernel(const HcEltArgs a, const uint32_t chunks) {
-  pdl_begin();
+  pdl_launch_dependents();
   __shared__ float sc[8];
   const uint32_t t = blockIdx.x / chunks, chunk = blockIdx.x - t * chunks;
+  if constexpr (HALO_PF_HC_ELT != 0) {
+    // ahead of the wait for the kernel before this one: hints to L2 for the rows this CTA reads, one thread per row
+    const unsigned c0 = chunk * kBlock * 8u;
+    if (c0 < a.h && threadIdx.x <= 2 * a.hc) {
+      const unsigned elems = a.h - c0 < kBlock * 8u ? a.h - c0 : kBlock * 8u;
+      const size_t row = static_cast<size_t>(t) * a.h + c0, rows = static_cast<size_t>(t) * a.hc * a.h + c0;
+      const unsigned s = threadIdx.x;
+      if constexpr (OP == kHcMix) {
+        if (s < a.hc) prefetch_l2_span(static_cast<const BT*>(a.b) + rows + static_cast<size_t>(s) * a.h, elems * static_cast<unsigned>(sizeof(BT)));
+        else if (s < 2 * a.hc) prefetch_l2_span(static_cast<const BT*>(a.c) + rows + static_cast<size_t>(s - a.hc) * a.h, elems * static_cast<unsigned>(sizeof(BT)));
+      } else {
+        if (s == 0) prefetch_l2_span(static_cast<const BT*>(a.b) + row, elems * static_cast<unsigned>(sizeof(BT)));
+        else if (OP == kHcCombine && s <= a.hc) prefetch_l2_span(static_cast<const AT*>(a.a) + rows + static_cast<size_t>(s - 1) * a.h, elems * static_cast<unsigned>(sizeof(AT)));
+        else if (OP == kAxpySigmoidRows && s == 1) prefetch_l2_span(static_cast<const AT*>(a.a) + row, elems * static_cast<unsigned>(sizeof(AT)));
+      }
+    }
+  }
+  pdl_wait();
   const unsigned j = chunk * kBlock + threadIdx.x;
   const unsigned octs = a.h >> 3;
   const bool ok = j < octs;
