@@ -666,7 +666,7 @@ def run_ours(args) -> None:
     top = "add_rmsnorm"
     if args.no_kernel_table:
         print(json.dumps({"metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": n_gpus,
-                          "ms_per_step": round(ms_step, 4), "timing": timing, "config5": config5,
+                          "ms_per_step": round(ms_step, 4), "timing": timing, "clocks": clocks, "config5": config5,
                           "note": "profiler run: legs skipped"}), flush=True)
         if dist is not None:
             dist.barrier()

@@ -18,6 +18,7 @@ std::atomic<int> g_norm_threads_per_row{0};
 std::atomic<int> g_norm_short_rows_k1{0};
 std::atomic<int> g_norm_force_general{0};
 std::atomic<int> g_l2_keep{1};
+std::atomic<int> g_embed_direct{1};
 std::atomic<int> g_rope_rows_per_group{0};
 std::atomic<int> g_rope_lean_k{0};
 std::atomic<int> g_rope_staged{1};
@@ -163,6 +164,7 @@ int RunEmbed(EmbedArgs a, const char* what, halo_b200_stream stream, char* err, 
   REQUIRE(Aligned(a.out, DTypeSize(a.out_dtype)) && Aligned(a.ids, 4), "%s: pointer not aligned to its element type",
           what);
   a.vec = a.row_bytes % 16 == 0 && Aligned(a.table, 16) && Aligned(a.out, 16);
+  a.direct = g_embed_direct.load(std::memory_order_relaxed) != 0;
   return Done(LaunchEmbedQ8_0(a, S(stream)), what, err, errlen);
 }
 
@@ -469,6 +471,7 @@ int halo_b200_tune(const char* key, int value) {
       {"norm_short_rows_k1", &g_norm_short_rows_k1, {1, 0}},
       {"norm_force_general", &g_norm_force_general, {1, 0}},
       {"l2_keep", &g_l2_keep, {1, 0}},
+      {"embed_direct", &g_embed_direct, {1, 0}},
       {"gated_rows_per_group", &g_gated_rows_per_group, {1, 2, 0}},
       {"rope_rows_per_group", &g_rope_rows_per_group, {2, 4, 0}},
       {"rope_lean_k", &g_rope_lean_k, {1, 2, 0}},

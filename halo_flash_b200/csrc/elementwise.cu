@@ -14,7 +14,10 @@ namespace {
 
 // Two octets per thread: with the L2 hint ahead of the dependent-launch wait (below) the SwiGLU of 4096 tokens takes
 // 20.4 us, against 21.5 us with four (more, shorter CTAs leave a shorter tail; four was faster before the hint).
-constexpr int kUnroll = 2;
+#ifndef HALO_ELT_UNROLL
+#define HALO_ELT_UNROLL 2
+#endif
+constexpr int kUnroll = HALO_ELT_UNROLL;
 
 __device__ __forceinline__ float apply(int op, float a, float b, float alpha) {
   switch (op) {

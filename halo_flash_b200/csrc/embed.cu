@@ -100,6 +100,66 @@ __global__ void __launch_bounds__(kBlock) embed_q8_0_kernel(const EmbedArgs a, c
   }
 }
 
+// Rows whose byte length is a multiple of 8 (a multiple of four blocks) and whose octets divide evenly over a warp:
+// straight from global memory into registers, no staging. A lane's octet j = lane + 32 i lies 34 (j / 4) + 2 +
+// 8 (j % 4) bytes into the row; since 32 octets are eight blocks = 272 bytes, that offset is the lane's own constant
+// plus 272 i, and so is its misalignment s in {0, 2, 4, 6} against 8 bytes. The lane reads the two aligned 8-byte words
+// around its codes (the second only when s != 0; it then still lies inside the row, because a row's last block is
+// 8-byte aligned when its length is), picks three of their four halves and funnel-shifts by 0 or 16 bits. Every load of
+// the row - NPL x (two words + the 2-byte scale) per lane - is issued before the first conversion.
+template <typename OT, int NPL>
+__global__ void __launch_bounds__(kBlock) embed_q8_0_direct_kernel(const EmbedArgs a) {
+  pdl_begin();
+  const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const unsigned at0 = (lane >> 2) * 34u + 2u + 8u * (lane & 3u);  // the lane's first octet in the row
+  const unsigned s = at0 & 7u;
+  const unsigned sh = (s & 2u) * 8u;
+  const bool high = s >= 4u;  // the codes start in the second half of the first word
+  OT* out = static_cast<OT*>(a.out);
+  const float2 bias = make_float2(-8388736.0f, -8388736.0f);
+  for (uint32_t t = blockIdx.x * kWarps + warp; t < a.tokens; t += gridDim.x * kWarps) {
+    const uint32_t id = a.ids ? a.ids[static_cast<size_t>(t) * a.id_stride + a.id_slot] : a.token;
+    OT* o = out + static_cast<size_t>(t) * a.cols + lane * 8;
+    if (a.vocab != 0 && id >= a.vocab) {
+      const float z[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int i = 0; i < NPL; ++i) store8(o + i * 256, z);
+      continue;
+    }
+    const uint8_t* row = a.table + static_cast<size_t>(id) * a.row_bytes;
+    const uint2* wp = reinterpret_cast<const uint2*>(row + (at0 & ~7u));
+    const uint16_t* dp = reinterpret_cast<const uint16_t*>(row + (lane >> 2) * 34u);
+    uint2 wa[NPL], wb[NPL];
+    uint16_t db[NPL];
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      wa[i] = wp[i * 34];  // 272 bytes on
+      wb[i] = s ? wp[i * 34 + 1] : make_uint2(0u, 0u);
+      db[i] = dp[i * 136];
+    }
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const float d = __half2float(__ushort_as_half(db[i]));
+      const float2 d2 = make_float2(d, d);
+      const uint32_t w0 = high ? wa[i].y : wa[i].x, w1 = high ? wb[i].x : wa[i].y, w2 = high ? wb[i].y : wb[i].x;
+      const uint32_t code[2] = {__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh)};
+      // int8 -> float by the 2^23 mantissa trick (see the staged kernel), then x scale
+      float v[8];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t x = code[h] ^ 0x80808080u;
+        const float2 lo = make_float2(__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7540)),
+                                      __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7541)));
+        const float2 hi = make_float2(__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7542)),
+                                      __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7543)));
+        const float2 a0 = __fmul2_rn(__fadd2_rn(lo, bias), d2), a1 = __fmul2_rn(__fadd2_rn(hi, bias), d2);
+        v[4 * h] = a0.x, v[4 * h + 1] = a0.y, v[4 * h + 2] = a1.x, v[4 * h + 3] = a1.y;
+      }
+      store8(o + i * 256, v);
+    }
+  }
+}
+
 // One thread per element, byte loads: any alignment, any row_bytes.
 template <typename OT>
 __global__ void __launch_bounds__(kBlock) embed_q8_0_scalar_kernel(const EmbedArgs a) {
@@ -130,6 +190,18 @@ cudaError_t LaunchEmbedT(const EmbedArgs& a, cudaStream_t s) {
     const unsigned blocks = a.cols / 32;
     unsigned segs = 1;
     while (segs < 8 && blocks % (16 * segs) == 0 && static_cast<uint64_t>(a.tokens) * segs * 2 <= 148u * 64u) segs <<= 1;
+    // whole rows of 8 NPL blocks, 8-byte aligned (the table is 16-byte aligned on this path), a row per warp and more
+    // rows than resident warps: the direct kernel
+    if (a.direct && segs == 1 && a.row_bytes == static_cast<uint64_t>(blocks) * 34 && blocks % 8 == 0) {
+      unsigned dgrid = (a.tokens + kWarps - 1) / kWarps;
+      if (dgrid > 148u * 8u) dgrid = 148u * 8u;
+      switch (blocks / 8) {
+        case 4: LaunchKernel(embed_q8_0_direct_kernel<OT, 4>, dgrid, kBlock, 0, s, a); return cudaGetLastError();
+        case 8: LaunchKernel(embed_q8_0_direct_kernel<OT, 8>, dgrid, kBlock, 0, s, a); return cudaGetLastError();
+        case 10: LaunchKernel(embed_q8_0_direct_kernel<OT, 10>, dgrid, kBlock, 0, s, a); return cudaGetLastError();
+        default: break;
+      }
+    }
     unsigned grid = (a.tokens * segs + warps - 1) / warps;
     if (grid > 148u * 8u) grid = 148u * 8u;
     const unsigned seg_smem = segs > 1 ? (blocks / segs) * 34 : row_smem;

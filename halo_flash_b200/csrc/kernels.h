@@ -222,6 +222,7 @@ struct EmbedArgs {
   void* out = nullptr;  // [tokens][cols]
   int out_dtype = kF32;
   bool vec = true;
+  bool direct = true;  // tuning: rows read straight into registers where their shape allows (embed.cu)
 };
 cudaError_t LaunchEmbedQ8_0(const EmbedArgs& a, cudaStream_t s);
 

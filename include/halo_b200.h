@@ -528,6 +528,8 @@ const char* halo_b200_kernel_name(size_t index);
  * "norm_short_rows_k1" (1 = rows of <= 256 elements use one 8-element chunk per thread; 0 = built-in choice),
  * "norm_force_general" (1 = the row norms always run their general kernel, never the lean one),
  * "l2_keep" (1, the default = the add + norm stores a residual of at most 40 MB with an L2 evict_last hint; 0 = plain stores),
+ * "embed_direct" (1, the default = embedding launches with more rows than resident warps read rows straight into
+ * registers; 0 = every launch stages rows in shared memory),
  * "gated_rows_per_group" (1 or 2 rows in flight per thread group of the gated norm on short rows; 0 = built-in),
  * "rope_rows_per_group" (2 or 4 rows in flight per thread group of the general fused norm + RoPE kernel; 0 = built-in),
  * "rope_lean_k" (chunks per lane of the fused norm + RoPE kernels on rows of 256: 1 or 2; 0 = built-in, four),
