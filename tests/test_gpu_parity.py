@@ -493,6 +493,40 @@ def test_embedding_gather_bit_exact(orc, vocab, cols, T, odt):
     out.check()
 
 
+@pytest.mark.parametrize("cols", [1024, 2048, 2560])
+@pytest.mark.parametrize("odt", ["f32", "bf16", "f16"])
+def test_embedding_long_launches_read_rows_directly(orc, cols, odt):
+    """Launches with more rows than resident warps read rows straight into registers (rows of 32, 64 and 80 blocks have
+    direct kernels): the result equals the shared-memory-staged kernel's bit for bit, the oracle's on a sample of rows,
+    and out-of-range ids give zero rows. The table's last row is among the ids: its last block ends the allocation."""
+    vocab, T = 3000, 5000
+    table = synth.q8_0_table("t.ed.table", vocab, cols)
+    ids = synth.token_ids("t.ed.ids", T, vocab)
+    ids[0], ids[1], ids[-1], ids[7] = 0, vocab - 1, vocab - 1, vocab + 5
+    dtab, dids = to_dev(table), to_dev(ids.view(np.int32))
+    outs = []
+    for direct in (1, 0):
+        lib().tune("embed_direct", direct)
+        try:
+            out = Guarded((T, cols), TDT[odt])
+            ops.embed_q8_0(dtab, dids, cols, out.t, vocab=vocab)
+            out.check()
+            outs.append(out.t)
+        finally:
+            lib().tune("embed_direct", 1)
+    assert torch.equal(outs[0], outs[1])
+    assert not outs[0][7].any()
+    pick = np.array([0, 1, 2, 100, 2500, T - 1])
+    want = orc.embed_q8_0_rows(table, ids[pick], cols)
+    got = outs[0][torch.as_tensor(pick, device=DEV)]
+    if odt == "f32":
+        assert to_f32(got).tobytes() == want.tobytes()
+    elif odt == "bf16":
+        assert np.array_equal(bits16(got), oracle.bf16_bits(want))
+    else:
+        assert np.array_equal(got.cpu().numpy().view(np.uint16), want.astype(np.float16).view(np.uint16))
+
+
 def test_embedding_reference_entry_points(orc):
     """_embed (scalar token), _embed_p (params[kHaloToken]) and _embed_rows (params[t * 16]):
     src/kernels/core.hip:219-232."""
