@@ -77,6 +77,9 @@ __device__ __forceinline__ void pdl_begin() {
 #ifndef HALO_PF_CONV
 #define HALO_PF_CONV 1
 #endif
+#ifndef HALO_PF_ROPE_GENERAL
+#define HALO_PF_ROPE_GENERAL 1
+#endif
 #ifndef HALO_PF_HC_ELT
 #define HALO_PF_HC_ELT 1
 #endif

@@ -275,7 +275,7 @@ __global__ void __launch_bounds__(kBlock, K * ROWS >= 8 ? 2 : 3) norm_rope_kerne
                                                              const unsigned lg, const uint32_t ctas1,
                                                              const float inv_d, const uint32_t magic1,
                                                              const uint32_t magic2) {
-  pdl_begin();
+  pdl_launch_dependents();
   extern __shared__ float rope_smem[];
   const unsigned slots = kBlock >> lg;
   const bool second = blockIdx.x >= ctas1;
@@ -285,6 +285,15 @@ __global__ void __launch_bounds__(kBlock, K * ROWS >= 8 ? 2 : 3) norm_rope_kerne
                    ((a.rows + a.heads - 1) / a.heads) * a.heads2, magic2};
   const uint32_t cta = second ? blockIdx.x - ctas1 : blockIdx.x;
   const bool full = (a.d >> 3) == (static_cast<unsigned>(K) << lg) && (cta + 1) * (slots * ROWS) <= t.rows;
+  // ahead of the wait for the kernel before this one: a hint to L2 for the CTA's rows where they are one dense span
+  // (plain rows, or q|gate rows whose gate halves the CTA copies through anyway)
+  if (HALO_PF_ROPE_GENERAL != 0 && threadIdx.x == 0 && full &&
+      (t.in_row_stride == a.d || (t.gate && t.in_row_stride == 2 * static_cast<uint64_t>(a.d))) &&
+      (t.in_row_stride * sizeof(IT)) % 16 == 0) {
+    const size_t span = static_cast<size_t>(slots * ROWS) * t.in_row_stride;
+    prefetch_l2_span(static_cast<const IT*>(t.in) + cta * span, static_cast<unsigned>(span * sizeof(IT)));
+  }
+  pdl_wait();
   if (full) norm_rope_body<IT, OT, K, ROWS, true, GT>(t, a, f, lg, cta, inv_d, rope_smem);
   else norm_rope_body<IT, OT, K, ROWS, false, GT>(t, a, f, lg, cta, inv_d, rope_smem);
 }
