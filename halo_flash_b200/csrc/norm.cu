@@ -356,7 +356,7 @@ __device__ __forceinline__ void norm_lean_row(const LeanArgs& a, const Raw<XT> (
 // epilogue kernels exist with and without them, because a launch of a few rows (decode) gains nothing from a hint and
 // pays for the preamble (319.8 -> 333.0 us per 230-launch decode step when every Q8_0 add + norm carried it).
 template <typename XT, typename YT, int K, bool ADD, bool EPI, bool WIDE, int MODE, bool HINTS = false>
-__global__ void __launch_bounds__(kBlock, K > 2 ? (sizeof(XT) == 2 ? 4 : 1) : (!EPI && MODE != 0 && sizeof(XT) == 2) ? 6 : (EPI && sizeof(XT) == 2) ? HALO_EPI_CTAS : 1) norm_rows_lean_kernel(const LeanArgs a) {
+__global__ void __launch_bounds__(kBlock, K > 2 ? (sizeof(XT) == 2 ? (K == 5 ? 3 : 4) : 1) : (!EPI && MODE != 0 && sizeof(XT) == 2) ? 6 : (EPI && sizeof(XT) == 2) ? HALO_EPI_CTAS : 1) norm_rows_lean_kernel(const LeanArgs a) {
   pdl_launch_dependents();
   if constexpr (EPI ? HINTS : HALO_PF_NORM != 0) {
     if (threadIdx.x == 0) {  // the CTA's rows are one contiguous span per tensor
@@ -751,6 +751,10 @@ cudaError_t LaunchLean(const NormArgs& a, const Shape& sh, unsigned grid, cudaSt
                    : (epi && a.w && a.one_plus && !a.l2 && l.stage_q8 && !a.xq) ? (a.y ? 4 : 5)
                    : (epi && a.w && a.one_plus && !a.l2 && !a.q8_0 && a.xq)     ? (a.y ? 6 : 7)
                                                                                   : 0;
+  if constexpr (K == 3 || K == 5) {  // rows of 3 g or 5 g octets, g >= 64 (PickOddShape): always wider than a warp
+    LaunchLeanMode<XT, YT, K, ADD, true>(l, epi, mode, grid, s);
+    return cudaGetLastError();
+  }
   if constexpr (K <= 2) {  // rows wider than a warp per row exist only with one or two octets per thread
     if (sh.lg > 5) {
       LaunchLeanMode<XT, YT, K, ADD, true>(l, epi, mode, grid, s);
@@ -759,6 +763,23 @@ cudaError_t LaunchLean(const NormArgs& a, const Shape& sh, unsigned grid, cudaSt
   }
   LaunchLeanMode<XT, YT, K, ADD, false>(l, epi, mode, grid, s);
   return cudaGetLastError();
+}
+
+// Rows of 3 g or 5 g octets with g = 64, 128 or 256 threads (H = 1536, 2560, 3072, 5120, ...): three or five octets
+// per thread in the lean kernel, where the general kernel pads the row to a power of two (at H = 2560 it runs 256
+// threads x 2 octets with 37 % of the lanes idle: 17.2 us = 0.75 of measured for the add + norm of 4096 rows).
+bool PickOddShape(unsigned octs, unsigned rows, size_t elem_size, Shape* sh) {
+  for (int k : {3, 5}) {
+    if (octs % k != 0) continue;
+    if (k == 5 && elem_size == 4) continue;  // fp32 rows at five octets per thread measured slower than the general kernel (19.8 against 17.1 us)
+    const unsigned g = octs / k;
+    if (g < 64 || g > 256 || (g & (g - 1)) != 0 || rows % (kBlock / g) != 0) continue;
+    sh->lg = 0;
+    while ((1u << sh->lg) < g) ++sh->lg;
+    sh->k = k, sh->r = 1, sh->rows_per_cta = kBlock / g, sh->full = true;
+    return true;
+  }
+  return false;
 }
 
 template <typename XT, typename YT, bool ADD>
@@ -781,6 +802,13 @@ cudaError_t LaunchNormT(const NormArgs& a, cudaStream_t s) {
     if (lean) {
       if (sh.k == 4) return LaunchLean<XT, YT, 4, ADD>(a, sh, grid, s);
       return sh.k == 1 ? LaunchLean<XT, YT, 1, ADD>(a, sh, grid, s) : LaunchLean<XT, YT, 2, ADD>(a, sh, grid, s);
+    }
+    Shape odd;
+    if (!sh.full && a.threads_per_row == 0 && a.rows_per_entry == 0 && a.w_period <= 1 && a.y16 == nullptr && a.rscale == nullptr &&
+        a.kb_tokens == 0 && !a.force_general && PickOddShape(a.d / 8, a.rows, sizeof(XT), &odd)) {
+      const unsigned ogrid = a.rows / odd.rows_per_cta;
+      if (odd.k == 3) return LaunchLean<XT, YT, 3, ADD>(a, odd, ogrid, s);
+      if constexpr (sizeof(XT) == 2) return LaunchLean<XT, YT, 5, ADD>(a, odd, ogrid, s);
     }
   }
   const float inv_d = 1.0f / static_cast<float>(a.d);
