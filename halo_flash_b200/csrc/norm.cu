@@ -804,7 +804,8 @@ cudaError_t LaunchNormT(const NormArgs& a, cudaStream_t s) {
       return sh.k == 1 ? LaunchLean<XT, YT, 1, ADD>(a, sh, grid, s) : LaunchLean<XT, YT, 2, ADD>(a, sh, grid, s);
     }
     Shape odd;
-    if (!sh.full && a.threads_per_row == 0 && a.rows_per_entry == 0 && a.w_period <= 1 && a.y16 == nullptr && a.rscale == nullptr &&
+    // (launches that cannot fill the GPU keep the general kernel's wide, short-chain layout: see PickShape)
+    if (!sh.full && static_cast<uint64_t>(a.rows) * (a.d / 8) > 148u * 256u && a.threads_per_row == 0 && a.rows_per_entry == 0 && a.w_period <= 1 && a.y16 == nullptr && a.rscale == nullptr &&
         a.kb_tokens == 0 && !a.force_general && PickOddShape(a.d / 8, a.rows, sizeof(XT), &odd)) {
       const unsigned ogrid = a.rows / odd.rows_per_cta;
       if (odd.k == 3) return LaunchLean<XT, YT, 3, ADD>(a, odd, ogrid, s);

@@ -148,10 +148,10 @@ def test_add_rmsnorm_fp32(orc, rows, d, one_plus):
     xn.check()
 
 
-# 2560 = 5 x 64 octets, 3072 = 3 x 128, 1536 = 3 x 64, 5120 = 5 x 128: whole CTAs of such rows take the lean kernel with
-# three or five octets per thread, other row counts the general kernel
-@pytest.mark.parametrize("rows,d", [(1, 2048), (8, 2048), (33, 2048), (5, 256), (3, 2560), (6, 104), (8, 2560), (4, 3072),
-                                    (8, 1536), (2, 5120)])
+# 2560 = 5 x 64 octets, 3072 = 3 x 128, 1536 = 3 x 64, 5120 = 5 x 128: launches of whole CTAs of such rows that can fill
+# the GPU take the lean kernel with three or five octets per thread, shorter or ragged ones the general kernel
+@pytest.mark.parametrize("rows,d", [(1, 2048), (8, 2048), (33, 2048), (5, 256), (3, 2560), (6, 104), (128, 2560), (8, 2560),
+                                    (128, 3072), (256, 1536), (64, 5120)])
 @pytest.mark.parametrize("xn_dtype", ["bf16", "f32"])
 def test_add_rmsnorm_bf16_residual(orc, rows, d, xn_dtype):
     res = rounded(synth.act("t.res", rows, d) * 3, "bf16")
@@ -168,7 +168,7 @@ def test_add_rmsnorm_bf16_residual(orc, rows, d, xn_dtype):
 
 
 @pytest.mark.parametrize("rows,d,res_dtype", [(4, 256, "f32"), (8, 2048, "bf16"), (3, 2560, "f32"), (5, 96, "f32"),
-                                              (2, 4096, "bf16"), (8, 2560, "bf16"), (4, 3072, "bf16"), (4, 1536, "f32")])
+                                              (2, 4096, "bf16"), (128, 2560, "bf16"), (128, 3072, "bf16"), (256, 1536, "f32")])
 def test_q8_epilogues_two_stage(orc, rows, d, res_dtype):
     """Stage 1: the fp32 xn matches the oracle within 1e-5. Stage 2: the Q8_0 blocks and the
     int8 + fp32-scale form equal the oracle's encoders applied to the GPU's own xn, bit for
