@@ -205,7 +205,7 @@ __device__ __forceinline__ void tile_rows(uint32_t t0, uint32_t tokens, uint32_t
 template <typename IT, typename OT, unsigned HL, int kTile>
 __global__ void __launch_bounds__(kBlock, 2) conv_l2norm_staged_kernel(const ConvArgs a, const uint32_t slices,
                                                                     const uint32_t token_tiles) {
-  pdl_launch_dependents();
+  pdl_launch_dependents();  // persistent and GPU-filling whatever its grid: the successor may be scheduled at once
   extern __shared__ __align__(128) uint8_t conv_smem[];
   __shared__ __align__(8) unsigned long long bars[2];
   const unsigned octs = a.channels >> 3;
@@ -229,7 +229,7 @@ __global__ void __launch_bounds__(kBlock, 2) conv_l2norm_staged_kernel(const Con
       prefetch_l2_span(static_cast<const IT*>(a.in) + static_cast<size_t>(by * kTile + first_row + threadIdx.x - 3u) * a.channels +
                            (static_cast<size_t>(oc0) << 3), row_bytes);
   }
-  pdl_wait();
+  pdl_wait_and_trigger();
   __syncthreads();
 
   // thread 0 asks the copy engine for the rows of token tile `by` into buffer `b`

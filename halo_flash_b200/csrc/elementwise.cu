@@ -66,7 +66,7 @@ struct VecSegments {
 template <typename IT, typename OT, int OP, int U>
 __global__ void __launch_bounds__(kBlock, sizeof(IT) == 4 ? 3 : 5) elementwise_vec_kernel(const VecSegments v) {
   constexpr int kUnroll = U;  // shadows the file-scope constant inside this kernel
-  pdl_launch_dependents();
+  pdl_trigger_early();
   // Segment lookup by compare-and-select over constant indices: indexing the parameter arrays
   // with a run-time value would make the compiler copy them to local memory.
   const void* sa = v.a[0];
@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(kBlock, sizeof(IT) == 4 ? 3 : 5) elementwise_v
     prefetch_l2_span(pa + o0 * 8, static_cast<unsigned>(n * 8 * sizeof(IT)));
     prefetch_l2_span(pb + o0 * 8, static_cast<unsigned>(n * 8 * sizeof(IT)));
   }
-  pdl_wait();
+  pdl_wait_and_trigger();
   const uint64_t base = static_cast<uint64_t>(blockIdx.x - first) * (kBlock * kUnroll) + threadIdx.x;
   if (base + static_cast<uint64_t>(kUnroll - 1) * kBlock < octs) {  // the whole tile is inside: no predicates
     Raw<IT> ra[kUnroll], rb[kUnroll];

@@ -104,7 +104,7 @@ constexpr int HcMinCtas(int octets, int rt_size) {
 template <typename RT, typename OT, typename YT, int HC, int K, bool MOE, bool LEAN = false>
 __global__ void __launch_bounds__(kBlock, HcMinCtas(HC* K, sizeof(RT)))
     hc_combine_norm_kernel(const HcArgs a, const unsigned lg, const float inv_h) {
-  pdl_launch_dependents();
+  pdl_trigger_early();
   if constexpr (LEAN) {  // full tiles: the CTA's groups are one contiguous span of the residual and one of the block output
     if (HALO_PF_HC != 0 && threadIdx.x == 0) {
       const size_t rspan = static_cast<size_t>(kBlock >> lg) * (HC == 1 ? 1u : a.hc) * a.h;
@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(kBlock, HcMinCtas(HC* K, sizeof(RT)))
       }
     }
   }
-  pdl_wait();
+  pdl_wait_and_trigger();
   __shared__ float red[kBlock / 32][HC];
   __shared__ float part[kBlock / 32][HC][8];
   const unsigned g = 1u << lg;
@@ -388,7 +388,7 @@ __global__ void __launch_bounds__(kBlock) hc_combine_norm_scalar_kernel(const Hc
 // per CTA and each [h] row is loaded once however many streams use it.
 template <typename AT, typename BT, int OP>
 __global__ void __launch_bounds__(kBlock) hc_elt_vec_kernel(const HcEltArgs a, const uint32_t chunks) {
-  pdl_launch_dependents();
+  pdl_trigger_early();
   __shared__ float sc[8];
   const uint32_t t = blockIdx.x / chunks, chunk = blockIdx.x - t * chunks;
   if constexpr (HALO_PF_HC_ELT != 0) {
@@ -408,7 +408,7 @@ __global__ void __launch_bounds__(kBlock) hc_elt_vec_kernel(const HcEltArgs a, c
       }
     }
   }
-  pdl_wait();
+  pdl_wait_and_trigger();
   const unsigned j = chunk * kBlock + threadIdx.x;
   const unsigned octs = a.h >> 3;
   const bool ok = j < octs;

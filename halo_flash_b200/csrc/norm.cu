@@ -357,7 +357,7 @@ __device__ __forceinline__ void norm_lean_row(const LeanArgs& a, const Raw<XT> (
 // pays for the preamble (319.8 -> 333.0 us per 230-launch decode step when every Q8_0 add + norm carried it).
 template <typename XT, typename YT, int K, bool ADD, bool EPI, bool WIDE, int MODE, bool HINTS = false>
 __global__ void __launch_bounds__(kBlock, K > 2 ? (sizeof(XT) == 2 ? (K == 5 ? 3 : 4) : 1) : (!EPI && MODE != 0 && sizeof(XT) == 2) ? 6 : (EPI && sizeof(XT) == 2) ? HALO_EPI_CTAS : 1) norm_rows_lean_kernel(const LeanArgs a) {
-  pdl_launch_dependents();
+  pdl_trigger_early();
   if constexpr (EPI ? HINTS : HALO_PF_NORM != 0) {
     if (threadIdx.x == 0) {  // the CTA's rows are one contiguous span per tensor
       const size_t span = static_cast<size_t>(kBlock >> a.lg) * a.d;
@@ -366,7 +366,7 @@ __global__ void __launch_bounds__(kBlock, K > 2 ? (sizeof(XT) == 2 ? (K == 5 ? 3
         prefetch_l2_span(static_cast<const XT*>(a.delta) + blockIdx.x * span, static_cast<unsigned>(span * sizeof(XT)));
     }
   }
-  pdl_wait();
+  pdl_wait_and_trigger();
   __shared__ float scratch[WIDE ? kBlock / 32 : 1];
   // Q8_0 staging: the 32 octets of a warp's slab are 8 blocks = 272 contiguous output bytes that
   // start on a 16-byte boundary (272 = 17 * 16), so the warp assembles them in shared memory
@@ -585,13 +585,13 @@ struct GatedLeanArgs {
 
 template <typename OT, typename ZT, typename YT>
 __global__ void __launch_bounds__(kBlock) gated_norm_lean_kernel(const GatedLeanArgs a) {
-  pdl_launch_dependents();
+  pdl_trigger_early();
   if (HALO_PF_GATED != 0 && threadIdx.x == 0) {
     const size_t span = static_cast<size_t>(kBlock >> a.lg) * a.d;
     prefetch_l2_span(static_cast<const OT*>(a.o) + blockIdx.x * span, static_cast<unsigned>(span * sizeof(OT)));
     prefetch_l2_span(static_cast<const ZT*>(a.z) + blockIdx.x * span, static_cast<unsigned>(span * sizeof(ZT)));
   }
-  pdl_wait();
+  pdl_wait_and_trigger();
   const unsigned lg = a.lg, g = 1u << lg;
   const unsigned lir = threadIdx.x & (g - 1);
   const uint32_t row = blockIdx.x * (kBlock >> lg) + (threadIdx.x >> lg);

@@ -15,14 +15,14 @@ namespace {
 
 template <typename XT>
 __global__ void __launch_bounds__(kBlock) quantize_vec_kernel(const QuantArgs a) {
-  pdl_launch_dependents();
+  pdl_trigger_early();
   const uint32_t opr = a.cols / 8;
   if (HALO_PF_QUANT != 0 && threadIdx.x == 0 && a.x_stride == a.cols) {  // dense rows: the CTA's octets are one span of x
     const uint64_t o0 = static_cast<uint64_t>(blockIdx.x) * kBlock, total = static_cast<uint64_t>(a.rows) * opr;
     const uint64_t n = total - o0 < kBlock ? total - o0 : kBlock;
     prefetch_l2_span(static_cast<const XT*>(a.x) + o0 * 8, static_cast<unsigned>(n * 8 * sizeof(XT)));
   }
-  pdl_wait();
+  pdl_wait_and_trigger();
   const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x;
   const uint32_t row = static_cast<uint32_t>(idx / opr), j = static_cast<uint32_t>(idx % opr);
   const bool ok = row < a.rows;

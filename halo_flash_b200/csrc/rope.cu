@@ -275,7 +275,7 @@ __global__ void __launch_bounds__(kBlock, K * ROWS >= 8 ? 2 : 3) norm_rope_kerne
                                                              const unsigned lg, const uint32_t ctas1,
                                                              const float inv_d, const uint32_t magic1,
                                                              const uint32_t magic2) {
-  pdl_launch_dependents();
+  pdl_trigger_early();
   extern __shared__ float rope_smem[];
   const unsigned slots = kBlock >> lg;
   const bool second = blockIdx.x >= ctas1;
@@ -293,7 +293,7 @@ __global__ void __launch_bounds__(kBlock, K * ROWS >= 8 ? 2 : 3) norm_rope_kerne
     const size_t span = static_cast<size_t>(slots * ROWS) * t.in_row_stride;
     prefetch_l2_span(static_cast<const IT*>(t.in) + cta * span, static_cast<unsigned>(span * sizeof(IT)));
   }
-  pdl_wait();
+  pdl_wait_and_trigger();
   if (full) norm_rope_body<IT, OT, K, ROWS, true, GT>(t, a, f, lg, cta, inv_d, rope_smem);
   else norm_rope_body<IT, OT, K, ROWS, false, GT>(t, a, f, lg, cta, inv_d, rope_smem);
 }
@@ -430,6 +430,9 @@ __device__ unsigned int g_stage_timeouts = 0;
 
 template <typename T, int K, bool ONEPLUS>
 __global__ void __launch_bounds__(kBlock, 4) norm_rope_staged_kernel(const RopeLeanArgs a) {
+  // This persistent kernel lets its successor be scheduled at once whatever its grid (at most four CTAs per SM, below
+  // kEarlyTriggerCtas): its launches always fill the GPU, so nothing can pile up behind it (7.4 against 8.4 us at 2048
+  // tokens, 12.4 against 13.5 at 4096, with the trigger after the wait).
   pdl_launch_dependents();
   extern __shared__ __align__(128) uint8_t rope_stage[];
   __shared__ __align__(8) unsigned long long bars[2];
@@ -459,7 +462,7 @@ __global__ void __launch_bounds__(kBlock, 4) norm_rope_staged_kernel(const RopeL
     stage_init(bars, 2);
     if (HALO_PF_ROPE_STAGED != 0 && p < a.tiles) prefetch_l2_span(pass_src(p), pass_bytes);
   }
-  pdl_wait();
+  pdl_wait_and_trigger();
   if (p >= a.tiles) return;  // uniform: the whole CTA has no pass
   __syncthreads();
   if (threadIdx.x == 0) {
