@@ -586,7 +586,8 @@ struct GatedLeanArgs {
 template <typename OT, typename ZT, typename YT>
 __global__ void __launch_bounds__(kBlock) gated_norm_lean_kernel(const GatedLeanArgs a) {
   pdl_trigger_early();
-  if (HALO_PF_GATED != 0 && threadIdx.x == 0) {
+  // (only the first wave: the rows of every later CTA were hinted by the look-ahead of an earlier one, below)
+  if (HALO_PF_GATED != 0 && threadIdx.x == 0 && (HALO_PF_AHEAD_GATED == 0 || blockIdx.x < HALO_PF_AHEAD_GATED * kSms * 8u)) {
     const size_t span = static_cast<size_t>(kBlock >> a.lg) * a.d;
     prefetch_l2_span(static_cast<const OT*>(a.o) + blockIdx.x * span, static_cast<unsigned>(span * sizeof(OT)));
     prefetch_l2_span(static_cast<const ZT*>(a.z) + blockIdx.x * span, static_cast<unsigned>(span * sizeof(ZT)));
