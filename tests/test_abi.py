@@ -85,6 +85,25 @@ def test_launch_by_name_rejects_unknown_and_malformed_calls():
         lib.launch(None, "halo_l2norm", [a], (4, 1, 1), (128, 1, 1))  # missing d, eps
 
 
+def test_tune_keys_match_the_header():
+    """Every key the header documents for halo_b200_tune is accepted (with 0, which every key allows, and which is then
+    put back to its documented default), and an unknown key or value is refused. Host-only: no device is touched."""
+    lib = _lib.lib()
+    doc = HEADER[HEADER.index("Tuning hook for experiments"):HEADER.index("int halo_b200_tune")]
+    keys = re.findall(r'"([a-z0-9_]+)"', doc)
+    assert len(keys) >= 15 and len(set(keys)) == len(keys)
+    defaults_on = set(re.findall(r'"([a-z0-9_]+)" \(1, the default', doc))
+    assert {"pdl", "l2_keep", "rope_staged", "conv_staged", "embed_direct"} <= defaults_on
+    for key in keys:
+        lib.tune(key, 0)
+        if key in defaults_on:
+            lib.tune(key, 1)
+    with pytest.raises(_lib.HaloError):
+        lib.tune("no_such_key", 1)
+    with pytest.raises(_lib.HaloError):
+        lib.tune("pdl", 7)
+
+
 def test_zero_sized_calls_succeed_without_a_device():
     """rows == 0 / n == 0 is a no-op (an empty prefill chunk), not an error."""
     lib = _lib.lib()
