@@ -21,7 +21,7 @@ OBJ = CSRC / "build"
 LIB = PKG / "libhalo_b200.so"
 INCLUDE = PKG.parent / "include"
 
-SOURCES = ["norm.cu", "rope.cu", "elementwise.cu", "embed.cu", "quant.cu", "hc.cu", "conv.cu", "api.cu", "launch.cu", "static_scratch.cu"]
+SOURCES = ["norm.cu", "norm_odd.cu", "rope.cu", "elementwise.cu", "embed.cu", "quant.cu", "hc.cu", "conv.cu", "api.cu", "launch.cu", "static_scratch.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

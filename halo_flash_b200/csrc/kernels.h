@@ -88,6 +88,9 @@ struct NormArgs {
   bool vec = true;
 };
 cudaError_t LaunchNorm(const NormArgs& a, cudaStream_t s);
+// The lean kernel with three or five octets per thread (rows of 3 g / 5 g octets, g = 1 << lg threads per row; five
+// only for 16-bit rows), for the (x, y) type pairs the lean kernels exist for; called by LaunchNorm.
+cudaError_t LaunchNormLeanOdd(const NormArgs& a, unsigned lg, int k, unsigned rows_per_cta, unsigned grid, cudaStream_t s);
 
 // ---- group 2: gated RMSNorm --------------------------------------------------------
 struct GatedArgs {
