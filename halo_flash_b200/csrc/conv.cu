@@ -21,6 +21,16 @@
 namespace halo_b200 {
 namespace {
 
+// Tokens per tile of the staged kernel and its resident CTAs per SM. 16-bit inputs: four tokens (two buffers of 7 rows =
+// 56 KB) and three CTAs of 80 registers measured best - 31.2 us for 4096 tokens x 8192 channels against 32.4 with eight
+// tokens and two CTAs of 128 registers (five tokens 31.6, six 34.8, four tokens with four CTAs of 64 registers 50.1:
+// spills). fp32 inputs: eight tokens (176 KB) and one CTA; four tokens and two CTAs measured slower (53.8 against 49.1 us).
+#ifndef HALO_CONV_TILE16
+#define HALO_CONV_TILE16 4
+#endif
+#ifndef HALO_CONV_T4_CTAS
+#define HALO_CONV_T4_CTAS 3
+#endif
 constexpr int kTaps = 4;
 
 // acc = w[3] x[t]; acc += w[0] x[t-3]; += w[1] x[t-2]; += w[2] x[t-1] (the order of qwen35.cpp:183-186),
@@ -203,7 +213,7 @@ __device__ __forceinline__ void tile_rows(uint32_t t0, uint32_t tokens, uint32_t
 // grid.x = a multiple of `slices` (CTA c always works on channel slice c % slices, so its taps are loaded
 // once); CTA c takes the token tiles c / slices, c / slices + grid.x / slices, ...
 template <typename IT, typename OT, unsigned HL, int kTile>
-__global__ void __launch_bounds__(kBlock, 2) conv_l2norm_staged_kernel(const ConvArgs a, const uint32_t slices,
+__global__ void __launch_bounds__(kBlock, (kTile < 8 && sizeof(IT) == 2) ? HALO_CONV_T4_CTAS : 2) conv_l2norm_staged_kernel(const ConvArgs a, const uint32_t slices,
                                                                     const uint32_t token_tiles) {
   pdl_launch_dependents();  // persistent and GPU-filling whatever its grid: the successor may be scheduled at once
   extern __shared__ __align__(128) uint8_t conv_smem[];
@@ -423,20 +433,21 @@ cudaError_t LaunchConvTile(const ConvArgs& a, unsigned head_octs, cudaStream_t s
 template <typename IT, typename OT, unsigned HL>
 cudaError_t LaunchConvStagedHL(const ConvArgs& a, unsigned grid, uint32_t slices, uint32_t token_tiles, size_t smem,
                                cudaStream_t s) {
-  auto kernel = conv_l2norm_staged_kernel<IT, OT, HL, 8>;
+  auto kernel = conv_l2norm_staged_kernel<IT, OT, HL, (sizeof(IT) == 2 ? HALO_CONV_TILE16 : 8)>;
   // more than 48 KB of dynamic shared memory has to be asked for
   const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return e;
   return LaunchKernel(kernel, grid, kBlock, smem, s, a, slices, token_tiles);
 }
 
-// Two persistent CTAs per SM (the two tile buffers of a CTA take 88 KB for 16-bit inputs, 176 KB for
-// fp32, where one CTA per SM fits), rounded to a multiple of the number of channel slices.
+// Persistent CTAs, three per SM for 16-bit inputs (the two four-token tile buffers of a CTA take 56 KB) and one for
+// fp32 (eight-token buffers, 176 KB), rounded to a multiple of the number of channel slices.
 template <typename IT, typename OT>
 cudaError_t LaunchConvStaged(const ConvArgs& a, unsigned head_octs, cudaStream_t s) {
-  const uint32_t slices = (a.channels / 8 + kBlock - 1) / kBlock, token_tiles = (a.tokens + 7) / 8;
-  const size_t smem = 2 * static_cast<size_t>(8 + 3) * kBlock * 8 * sizeof(IT);
-  const unsigned resident = 148u * (sizeof(IT) == 2 ? 2u : 1u);
+  constexpr unsigned kT = sizeof(IT) == 2 ? HALO_CONV_TILE16 : 8;
+  const uint32_t slices = (a.channels / 8 + kBlock - 1) / kBlock, token_tiles = (a.tokens + kT - 1) / kT;
+  const size_t smem = 2 * static_cast<size_t>(kT + 3) * kBlock * 8 * sizeof(IT);
+  const unsigned resident = 148u * (sizeof(IT) == 2 ? (kT < 8 ? HALO_CONV_T4_CTAS : 2u) : 1u);
   if (slices > resident) return cudaErrorNotSupported;  // wider than the persistent grid: the register form runs
   unsigned per_slice = resident / slices;
   if (per_slice > token_tiles) per_slice = token_tiles;
